@@ -1,0 +1,112 @@
+// comm.cu — tensor-parallel collectives: NCCL over NVLink/NVSwitch, one rank per process.
+// The reference is single-GPU (no counterpart).  NCCL is bound at run time with dlopen so that
+// the library shares whichever libnccl the host process already uses and single-GPU callers
+// need no NCCL at all.
+#include <dlfcn.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "comm.h"
+
+namespace {
+
+typedef struct { char internal[128]; } nccl_uid;
+typedef void* nccl_comm_t;
+enum { kNcclFloat32 = 7, kNcclSum = 0, kNcclSuccess = 0 };
+
+struct NcclApi {
+    void* lib = nullptr;
+    int (*GetUniqueId)(nccl_uid*) = nullptr;
+    int (*CommInitRank)(nccl_comm_t*, int, nccl_uid, int) = nullptr;
+    int (*CommDestroy)(nccl_comm_t) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    int (*CommGetAsyncError)(nccl_comm_t, int*) = nullptr;
+};
+NcclApi g_nccl;
+
+int load_nccl() {
+    if (g_nccl.lib) return ATLASX_OK;
+    void* h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);          // already in the process?
+    if (!h) { const char* p = getenv("ATLAS_NCCL_LIB"); if (p && *p) h = dlopen(p, RTLD_NOW | RTLD_GLOBAL); }
+    if (!h) h = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) h = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (!h) return atlasx_fail(ATLASX_ERR_COMM, "cannot load libnccl.so.2: %s", dlerror());
+    g_nccl.GetUniqueId = (int (*)(nccl_uid*))dlsym(h, "ncclGetUniqueId");
+    g_nccl.CommInitRank = (int (*)(nccl_comm_t*, int, nccl_uid, int))dlsym(h, "ncclCommInitRank");
+    g_nccl.CommDestroy = (int (*)(nccl_comm_t))dlsym(h, "ncclCommDestroy");
+    g_nccl.AllReduce = (int (*)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t))dlsym(h, "ncclAllReduce");
+    g_nccl.AllGather = (int (*)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t))dlsym(h, "ncclAllGather");
+    g_nccl.GetErrorString = (const char* (*)(int))dlsym(h, "ncclGetErrorString");
+    g_nccl.CommGetAsyncError = (int (*)(nccl_comm_t, int*))dlsym(h, "ncclCommGetAsyncError");
+    if (!g_nccl.GetUniqueId || !g_nccl.CommInitRank || !g_nccl.AllReduce || !g_nccl.AllGather || !g_nccl.CommDestroy)
+        return atlasx_fail(ATLASX_ERR_COMM, "libnccl is missing a required symbol");
+    g_nccl.lib = h;
+    return ATLASX_OK;
+}
+const char* nccl_err(int e) { return g_nccl.GetErrorString ? g_nccl.GetErrorString(e) : "nccl error"; }
+
+}  // namespace
+
+struct atlasx_comm {
+    nccl_comm_t comm = nullptr;
+    int rank = 0, world = 1;
+};
+
+void atlasx_comm_destroy(atlasx_ctx* ctx) {
+    if (ctx && ctx->comm) {
+        if (ctx->comm->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
+        delete ctx->comm;
+        ctx->comm = nullptr;
+    }
+}
+
+int ax_comm_world(const atlasx_ctx* ctx) { return ctx && ctx->comm ? ctx->comm->world : 1; }
+int ax_comm_rank(const atlasx_ctx* ctx) { return ctx && ctx->comm ? ctx->comm->rank : 0; }
+
+int ax_comm_allreduce_sum(atlasx_ctx* ctx, float* buf, size_t n) {
+    if (!ctx->comm || ctx->comm->world == 1) return ATLASX_OK;
+    const int e = g_nccl.AllReduce(buf, buf, n, kNcclFloat32, kNcclSum, ctx->comm->comm, ctx->stream);
+    if (e != kNcclSuccess) return atlasx_fail(ATLASX_ERR_COMM, "ncclAllReduce: %s", nccl_err(e));
+    return ATLASX_OK;
+}
+int ax_comm_allgather(atlasx_ctx* ctx, const float* send, float* recv, size_t n_each) {
+    if (!ctx->comm || ctx->comm->world == 1) {
+        if (send != recv) AX_CUDA(cudaMemcpyAsync(recv, send, n_each * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+        return ATLASX_OK;
+    }
+    const int e = g_nccl.AllGather(send, recv, n_each, kNcclFloat32, ctx->comm->comm, ctx->stream);
+    if (e != kNcclSuccess) return atlasx_fail(ATLASX_ERR_COMM, "ncclAllGather: %s", nccl_err(e));
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_comm_unique_id(void* id128_out) {
+    AX_ARG(id128_out, "id buffer is null");
+    int rc = load_nccl(); if (rc) return rc;
+    nccl_uid id;
+    const int e = g_nccl.GetUniqueId(&id);
+    if (e != kNcclSuccess) return atlasx_fail(ATLASX_ERR_COMM, "ncclGetUniqueId: %s", nccl_err(e));
+    memcpy(id128_out, &id, sizeof(id));
+    return ATLASX_OK;
+}
+extern "C" int atlasx_comm_init(atlasx_ctx* ctx, const void* id128, int rank, int world) {
+    AX_ARG(ctx && id128, "null argument");
+    AX_ARG(world >= 1 && rank >= 0 && rank < world, "rank/world out of range");
+    AX_ARG(!ctx->comm, "communicator already initialised");
+    int rc = load_nccl(); if (rc) return rc;
+    AX_CUDA(cudaSetDevice(ctx->device));
+    nccl_uid id; memcpy(&id, id128, sizeof(id));
+    atlasx_comm* cm = new atlasx_comm();
+    cm->rank = rank; cm->world = world;
+    const int e = g_nccl.CommInitRank(&cm->comm, world, id, rank);
+    if (e != kNcclSuccess) { delete cm; return atlasx_fail(ATLASX_ERR_COMM, "ncclCommInitRank: %s", nccl_err(e)); }
+    ctx->comm = cm;
+    return ATLASX_OK;
+}
+extern "C" int atlasx_comm_world(const atlasx_ctx* ctx) { return ax_comm_world(ctx); }
+extern "C" int atlasx_comm_allreduce(atlasx_ctx* ctx, float* buf, int n) {
+    AX_ARG(ctx && buf && n >= 0, "bad argument");
+    return ax_comm_allreduce_sum(ctx, buf, (size_t)n);
+}

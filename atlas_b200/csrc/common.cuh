@@ -1,0 +1,128 @@
+// common.cuh — shared device helpers and host-side error plumbing (sm_100a only).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+#include <stddef.h>
+#include <stdio.h>
+#include <string>
+
+#include "../../include/atlas_kernels.h"
+
+// ── host error plumbing ─────────────────────────────────────────────────────────
+void atlasx_set_error(const char* fmt, ...);
+int  atlasx_fail(int code, const char* fmt, ...);
+
+#define AX_CUDA(expr)                                                                     \
+    do {                                                                                  \
+        cudaError_t _e = (expr);                                                          \
+        if (_e != cudaSuccess)                                                            \
+            return atlasx_fail(ATLASX_ERR_CUDA, "%s failed: %s (%s:%d)", #expr,           \
+                               cudaGetErrorString(_e), __FILE__, __LINE__);               \
+    } while (0)
+
+#define AX_CHECK_LAUNCH(what)                                                             \
+    do {                                                                                  \
+        cudaError_t _e = cudaGetLastError();                                              \
+        if (_e != cudaSuccess)                                                            \
+            return atlasx_fail(ATLASX_ERR_CUDA, "launch of %s failed: %s", what,          \
+                               cudaGetErrorString(_e));                                   \
+    } while (0)
+
+#define AX_ARG(cond, msg)                                                                 \
+    do { if (!(cond)) return atlasx_fail(ATLASX_ERR_ARG, "%s: %s", __func__, msg); } while (0)
+
+// ── context ─────────────────────────────────────────────────────────────────────
+struct atlasx_comm;   // comm.cpp
+
+struct atlasx_ctx {
+    int device = 0;
+    int sm_count = 148;
+    size_t smem_optin = 0;
+    cudaStream_t stream = nullptr;
+    int gemv_impl = 0;                 // 0 auto, 1 plain loads, 2 bulk-copy pipeline
+    // attention scratch (split-K partials + tickets), grown on demand
+    float* attn_partials = nullptr;  size_t attn_partials_cap = 0;   // floats
+    unsigned* attn_tickets = nullptr; size_t attn_tickets_cap = 0;   // uints, always zero between launches
+    int* pos_dev = nullptr; size_t pos_cap = 0;
+    // argmax scratch
+    float* amax_vals = nullptr; int* amax_idx = nullptr; unsigned* amax_ticket = nullptr; int* amax_out = nullptr;
+    // device error word written by bounded waits
+    int* dev_error = nullptr;          // device
+    int* host_pin = nullptr;           // pinned scratch (ints)
+    atlasx_comm* comm = nullptr;
+};
+
+int atlasx_ctx_ensure_attn_scratch(atlasx_ctx* ctx, size_t partial_floats, size_t tickets);
+
+// ── device helpers ──────────────────────────────────────────────────────────────
+#define AX_FULL 0xFFFFFFFFu
+
+__device__ __forceinline__ float ax_warp_sum(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(AX_FULL, v, d);
+    return v;
+}
+__device__ __forceinline__ float ax_warp_max(float v) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) v = fmaxf(v, __shfl_xor_sync(AX_FULL, v, d));
+    return v;
+}
+__device__ __forceinline__ float ax_bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float ax_bf16_hi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ float ax_bf16_to_f32(uint16_t h) { return __uint_as_float(((uint32_t)h) << 16); }
+__device__ __host__ __forceinline__ uint16_t ax_f32_to_bf16_rne_bits(uint32_t u) {
+    if ((u & 0x7FFFFFFFu) > 0x7F800000u) return (uint16_t)((u >> 16) | 0x40);
+    u += 0x7FFFu + ((u >> 16) & 1u);
+    return (uint16_t)(u >> 16);
+}
+__device__ __forceinline__ uint16_t ax_f32_to_bf16_rne(float f) { return ax_f32_to_bf16_rne_bits(__float_as_uint(f)); }
+
+// 128-bit streaming load that does not pollute L1 (weights are read exactly once)
+__device__ __forceinline__ uint4 ax_ldg_stream(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+// argmax candidates: index −1 means "none yet"; NaN never beats a candidate; `last` selects the
+// CPU rule of generate() (last index among equal maxima) instead of the first.
+__device__ __forceinline__ bool ax_better(float va, int ia, float vb, int ib, int last) {
+    if (ia < 0) return false;
+    if (ib < 0) return true;
+    if (va > vb) return true;
+    if (va == vb) return last ? ia > ib : ia < ib;
+    return false;
+}
+__device__ __forceinline__ void ax_warp_best(float& v, int& i, int last) {
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const float ov = __shfl_xor_sync(AX_FULL, v, d);
+        const int oi = __shfl_xor_sync(AX_FULL, i, d);
+        if (ax_better(ov, oi, v, i, last)) { v = ov; i = oi; }
+    }
+}
+
+// ── seeded synthetic data: integer-exact hash → approximately N(0,1) ────────────
+// base = mix64(seed ^ mix64(stream)); h1 = mix64(base+2i); h2 = mix64(base+2i+1);
+// z = ((bytesum(h1)+bytesum(h2 & 0xffffffff) − 1530)·65536 + ((h2>>32)&0xffff) − 32768) / 2^24
+__host__ __device__ __forceinline__ uint64_t ax_mix64(uint64_t z) {
+    z += 0x9E3779B97F4A7C15ull;
+    z = (z ^ (z >> 30)) * 0xBF58476D1CE4E5B9ull;
+    z = (z ^ (z >> 27)) * 0x94D049BB133111EBull;
+    return z ^ (z >> 31);
+}
+__host__ __device__ __forceinline__ uint32_t ax_bytesum64(uint64_t v) {
+    v = (v & 0x00FF00FF00FF00FFull) + ((v >> 8) & 0x00FF00FF00FF00FFull);
+    v = (v & 0x0000FFFF0000FFFFull) + ((v >> 16) & 0x0000FFFF0000FFFFull);
+    return (uint32_t)(v & 0xFFFFFFFFull) + (uint32_t)(v >> 32);
+}
+__host__ __device__ __forceinline__ float ax_synth_normal(uint64_t base, uint64_t i) {
+    uint64_t h1 = ax_mix64(base + 2 * i);
+    uint64_t h2 = ax_mix64(base + 2 * i + 1);
+    int32_t s = (int32_t)(ax_bytesum64(h1) + ax_bytesum64(h2 & 0xFFFFFFFFull));
+    int32_t u = (int32_t)((h2 >> 32) & 0xFFFF);
+    int32_t zi = (s - 1530) * 65536 + (u - 32768);
+    return (float)zi * (1.0f / 16777216.0f);
+}

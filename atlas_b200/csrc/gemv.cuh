@@ -1,0 +1,44 @@
+// gemv.cuh — launch interface of the weight-streaming GEMV family.
+#pragma once
+#include "common.cuh"
+
+// One weight matrix in HBM, row-major [rows × cols].
+//   F32  : float
+//   BF16 : bf16 bit patterns
+//   INT8 : int8 + f32 scale per row                      (Int8Tensor, atlas-quant/src/lib.rs:32-39)
+//   INT4 : two nibbles per byte, even index in the high nibble, one scale per `block`
+//          elements of the flat index, f32 or f16          (Int4Tensor, :101-109)
+struct AxWeight {
+    const void* data = nullptr;
+    const void* scales = nullptr;
+    int rows = 0, cols = 0;
+    int dtype = ATLASX_F32;
+    int block = 0;
+    int scales_f16 = 0;
+};
+
+// Optional input transform run by every CTA while the first weight tiles are in flight:
+//   t   = Σ_{p<nparts} y[p·part_stride + i]                     (row-parallel partial sums)
+//   t   = wy ? rmsnorm(t, wy, eps) : t
+//   v   = base + t            (base = residual stream, or an embedding row)  [if y]
+//   resid_out = v             (CTA 0 only)
+//   x   = wx ? rmsnorm(v, wx, eps) : v
+// With y == nullptr and wx == nullptr the GEMV input is just `base`.
+struct AxPrologue {
+    const float* base = nullptr;        // f32 vector [K] …
+    const void*  embed = nullptr;       // … or an embedding table (row = seq[*pos], clamped to vocab−1)
+    int embed_bf16 = 0; int vocab = 0;
+    const int* seq = nullptr; const int* pos = nullptr;
+    const float* y = nullptr; int nparts = 0; size_t part_stride = 0;
+    const float* wy = nullptr; const float* wx = nullptr;
+    float eps = 0.f;
+    float* resid_out = nullptr;
+};
+
+enum { AX_EPI_PLAIN = 0, AX_EPI_SILU_PAIR = 1 };   // pair: out[r/2] = silu(acc[r])·acc[r+1], r even
+
+// y[rows×n] = W·x.  n == 1: pro/epi honoured.  n in 2..16: plain only, x is [cols×n] row-major.
+int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y,
+                   bool pdl = false);
+int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes
+size_t ax_weight_bytes(const AxWeight& w);

@@ -1,0 +1,759 @@
+// model.cu — the decode step of OlmoModel on one GPU (or one tensor-parallel rank).
+//
+// Restates, for the device, crates/atlas-model/src/lib.rs of the reference:
+//   OlmoModel::forward_one_gpu :1463-1505, TransformerBlock::forward_token_gpu_v2 :1015-1091,
+//   Attention::forward_token_gpu_full :837-870, FeedForward::forward_gpu :902-908,
+//   generate_with_sampling (greedy branch) :1599-1646,1713-1730, init_gpu_resources :1360-1386.
+// The reference issues 18 launches and 18 allocations per layer; here a layer is five launches
+//   QKV GEMV (prologue: residual + RMSNorm of the previous sub-layer, or embedding gather)
+//   QK-norm + RoPE + KV write
+//   split-K attention
+//   o_proj GEMV
+//   gate/up GEMV (prologue: post-attention norm + residual; epilogue: SwiGLU)
+//   down GEMV
+// and the whole token (plus lm_head, argmax and position advance) is one CUDA graph whose
+// token id and position live in device memory, so replaying it needs no host data.
+#include <limits.h>
+#include <math.h>
+#include <string.h>
+#include <vector>
+
+#include "attention.cuh"
+#include "comm.h"
+#include "common.cuh"
+#include "elementwise.cuh"
+#include "gemv.cuh"
+#include "objects.h"
+
+namespace {
+
+enum { CLS_QKV = 0, CLS_QKPREP, CLS_ATTN, CLS_OPROJ, CLS_GATEUP, CLS_DOWN, CLS_LMHEAD, CLS_SELECT, CLS_COMM, CLS_COUNT };
+const char* kClassNames[CLS_COUNT] = { "gemv_qkv", "qk_norm_rope_kvwrite", "attention_splitk", "gemv_o_proj",
+                                       "gemv_gate_up_swiglu", "gemv_down", "gemv_lm_head", "argmax_advance", "collective" };
+
+struct StepState {           // device-resident generation state
+    int pos;                 // next position to be processed
+    int n_forced;            // positions below this hold caller-given tokens
+    int last_token;          // argmax of the most recent logits
+};
+
+struct Layer {
+    AxWeight qkv, wo, gateup, down;
+    float *attn_norm = nullptr, *ffn_norm = nullptr, *q_norm = nullptr, *k_norm = nullptr;
+    atlasx_kvcache* kv = nullptr;
+    int window = 0;
+    bool have[11] = {};      // which - ATLASX_T_WQ
+};
+
+struct Profile {
+    std::vector<cudaEvent_t> ev;
+    std::vector<int> cls;
+    std::vector<double> bytes;
+    int n = 0;
+};
+
+}  // namespace
+
+struct atlasx_model {
+    atlasx_ctx* ctx = nullptr;
+    atlasx_model_config cfg;
+    int hd = 0, nh_loc = 0, nkv_loc = 0, ffn_loc = 0, vocab_loc = 0, world = 1, rank = 0;
+    int q_rows = 0, kv_rows = 0;                 // nh_loc·hd, nkv_loc·hd
+    float scale = 1.f;
+    std::vector<Layer> layers;
+    void* embed = nullptr; int embed_bf16 = 0; bool have_embed = false;
+    float* final_norm = nullptr;
+    AxWeight lm_head; bool have_lm_head = false;
+    float *cos_t = nullptr, *sin_t = nullptr;
+    // activations
+    float *resid[2] = { nullptr, nullptr }, *qkv = nullptr, *attn = nullptr, *o = nullptr, *h = nullptr, *dn = nullptr;
+    float *logits_loc = nullptr, *logits = nullptr;
+    int* seq = nullptr; StepState* st = nullptr;
+    int final_resid = 0;                         // which resid buffer holds the stream after a step
+    int host_pos = 0;
+    bool finalized = false;
+    int use_graph = 1, use_pdl = 1;
+    cudaGraphExec_t graph = nullptr;
+    int attn_splits = 1;
+    std::vector<void*> owned;                    // device allocations to free
+    int* pin = nullptr;                          // pinned host ints
+    int launches_per_step = 0;
+};
+
+namespace {
+
+int dmalloc(atlasx_model* m, void** p, size_t bytes) {
+    AX_CUDA(cudaMalloc(p, bytes ? bytes : 16));
+    m->owned.push_back(*p);
+    return ATLASX_OK;
+}
+int format_ebits(int fmt) { return fmt == ATLASX_F32 ? 32 : fmt == ATLASX_BF16 ? 16 : fmt == ATLASX_INT8 ? 8 : 4; }
+
+// Allocate the device arrays of a weight [rows × cols] in the model's storage format.
+int alloc_weight(atlasx_model* m, AxWeight& w, int rows, int cols) {
+    const int fmt = m->cfg.weight_format;
+    w.rows = rows; w.cols = cols; w.dtype = fmt;
+    w.block = fmt == ATLASX_INT4 ? m->cfg.int4_block : 0;
+    w.scales_f16 = 0;
+    void* d = nullptr;
+    int rc = dmalloc(m, &d, (size_t)rows * cols * format_ebits(fmt) / 8);
+    if (rc) return rc;
+    AX_CUDA(cudaMemsetAsync(d, 0, (size_t)rows * cols * format_ebits(fmt) / 8, m->ctx->stream));
+    w.data = d;
+    if (fmt == ATLASX_INT8) { rc = dmalloc(m, &d, (size_t)rows * 4); if (rc) return rc; w.scales = d; AX_CUDA(cudaMemsetAsync(d, 0, (size_t)rows * 4, m->ctx->stream)); }
+    if (fmt == ATLASX_INT4) {
+        const size_t nb = (size_t)rows * (cols / w.block);
+        rc = dmalloc(m, &d, nb * 4); if (rc) return rc; w.scales = d;
+        AX_CUDA(cudaMemsetAsync(d, 0, nb * 4, m->ctx->stream));
+    }
+    return ATLASX_OK;
+}
+
+// Convert the FULL tensor (device, f32 or bf16) to the storage format, then copy the slice
+// rows [r0,r0+nr) × cols [c0,c0+nc) into dest rows dest_r0 + i·step (+ phase is folded into dest_r0).
+int place_slice(atlasx_model* m, const void* src, int src_dtype, int rows, int cols,
+                int r0, int nr, int c0, int nc, AxWeight& dest, int dest_r0, int step) {
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    const int fmt = dest.dtype;
+    const size_t n = (size_t)rows * cols;
+    void *t_f32 = nullptr, *t_data = nullptr, *t_scales = nullptr;
+    const void* data = src;            // full tensor in storage format
+    const void* scales = nullptr;
+    int rc = ATLASX_OK;
+    auto cleanup = [&]() { cudaStreamSynchronize(s); cudaFree(t_f32); cudaFree(t_data); cudaFree(t_scales); };
+    if (fmt == ATLASX_F32) {
+        if (src_dtype == ATLASX_BF16) {
+            AX_CUDA(cudaMalloc(&t_data, n * 4));
+            ax_bf16_to_f32(s, (const uint16_t*)src, (float*)t_data, n); data = t_data;
+        }
+    } else if (fmt == ATLASX_BF16) {
+        if (src_dtype == ATLASX_F32) {       // f32 → bf16 by truncation, as make_linear_bf16_aware (:2271-2279)
+            AX_CUDA(cudaMalloc(&t_data, n * 2));
+            ax_f32_to_bf16(s, (const float*)src, (uint16_t*)t_data, n, 1); data = t_data;
+        }
+    } else {
+        const float* f = (const float*)src;
+        if (src_dtype == ATLASX_BF16) {
+            AX_CUDA(cudaMalloc(&t_f32, n * 4));
+            ax_bf16_to_f32(s, (const uint16_t*)src, (float*)t_f32, n); f = (const float*)t_f32;
+        }
+        if (fmt == ATLASX_INT8) {
+            if (cudaMalloc(&t_data, n) != cudaSuccess || cudaMalloc(&t_scales, (size_t)rows * 4) != cudaSuccess) {
+                cleanup(); return atlasx_fail(ATLASX_ERR_CUDA, "out of device memory while quantising");
+            }
+            ax_quant_int8(s, f, rows, cols, (int8_t*)t_data, (float*)t_scales);
+        } else {
+            const size_t nb = (n + dest.block - 1) / dest.block;
+            if (cudaMalloc(&t_data, (n + 1) / 2) != cudaSuccess || cudaMalloc(&t_scales, nb * 4) != cudaSuccess) {
+                cleanup(); return atlasx_fail(ATLASX_ERR_CUDA, "out of device memory while quantising");
+            }
+            ax_quant_int4(s, f, n, dest.block, (uint8_t*)t_data, (float*)t_scales);
+        }
+        data = t_data; scales = t_scales;
+    }
+    // data slice
+    const int eb = format_ebits(fmt);
+    if (fmt == ATLASX_INT4) {          // copy in bytes (two elements each)
+        ax_copy2d(s, (uint8_t*)dest.data + (size_t)dest_r0 * (dest.cols / 2), (size_t)step * (dest.cols / 2),
+                  (const uint8_t*)data + ((size_t)r0 * cols + c0) / 2, (size_t)cols / 2, nr, nc / 2, 1);
+        const int bs = dest.block;
+        ax_copy2d(s, (float*)dest.scales + (size_t)dest_r0 * (dest.cols / bs), (size_t)step * (dest.cols / bs),
+                  (const float*)scales + (size_t)r0 * (cols / bs) + c0 / bs, (size_t)cols / bs, nr, nc / bs, 4);
+    } else {
+        const int es = eb / 8;
+        ax_copy2d(s, (uint8_t*)dest.data + (size_t)dest_r0 * dest.cols * es, (size_t)step * dest.cols,
+                  (const uint8_t*)data + ((size_t)r0 * cols + c0) * es, (size_t)cols, nr, nc, es);
+        if (fmt == ATLASX_INT8)
+            ax_copy2d(s, (float*)dest.scales + dest_r0, (size_t)step, (const float*)scales + r0, 1, nr, 1, 4);
+    }
+    cudaError_t e = cudaGetLastError();
+    cleanup();
+    if (e != cudaSuccess) rc = atlasx_fail(ATLASX_ERR_CUDA, "weight placement failed: %s", cudaGetErrorString(e));
+    return rc;
+}
+
+// ── argmax of the logits + advance of the device-resident state ─────────────────
+// Last CTA: last_token = argmax; if the next position is not a caller-given one, the token is
+// stored as the next input; pos += 1.
+__global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, AxArgmaxScratch sc, StepState* st, int* seq, int seq_cap, int advance) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    __shared__ int s_last;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    float v = 0.f; int idx = -1;
+    const int base = blockIdx.x * 1024;
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+        const int i = base + u * 256 + threadIdx.x;
+        if (i < n) { const float xv = x[i]; if (ax_better(xv, i, v, idx, 1)) { v = xv; idx = i; } }
+    }
+    ax_warp_best(v, idx, 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (lane == 0) { sv[warp] = v; si[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        v = lane < 8 ? sv[lane] : 0.f; idx = lane < 8 ? si[lane] : -1;
+        ax_warp_best(v, idx, 1);
+        if (lane == 0) {
+            sc.vals[blockIdx.x] = v; sc.idx[blockIdx.x] = idx;
+            __threadfence();
+            s_last = atomicAdd(sc.ticket, 1u) == gridDim.x - 1;
+        }
+    }
+    __syncthreads();
+    if (!s_last || warp != 0) return;
+    __threadfence();
+    v = 0.f; idx = -1;
+    for (int j = lane; j < (int)gridDim.x; j += 32) {
+        const float bv = sc.vals[j]; const int bi = sc.idx[j];
+        if (ax_better(bv, bi, v, idx, 1)) { v = bv; idx = bi; }
+    }
+    ax_warp_best(v, idx, 1);
+    if (lane == 0) {
+        if (idx < 0) idx = n - 1;
+        *sc.ticket = 0u;
+        st->last_token = idx;
+        if (advance) {
+            const int p = st->pos + 1;
+            if (p >= st->n_forced && p < seq_cap) seq[p] = idx;
+            st->pos = p;
+        } else {
+            const int p = st->pos;                 // re-selection for the position about to be processed
+            if (p < seq_cap) seq[p] = idx;
+        }
+    }
+}
+
+// Greedy-path logit edits of generate_with_sampling (:1631-1644), applied in order by one thread:
+// first-token suppression, then the repetition penalty once per occurrence in the window.
+__global__ void logit_fixups_k(float* logits, int n, const int* suppress, int n_suppress,
+                               const int* history, int n_hist, float theta) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    for (int i = 0; i < n_suppress; i++) { const int t = suppress[i]; if (t >= 0 && t < n) logits[t] = -INFINITY; }
+    if (theta != 1.0f)
+        for (int i = 0; i < n_hist; i++) {
+            const int t = history[i];
+            if (t >= 0 && t < n) { if (logits[t] > 0.0f) logits[t] /= theta; else logits[t] *= theta; }
+        }
+}
+
+// seq_fix != null: the token at `pos` is the most recent greedy choice (it may not have been
+// stored yet when the previous steps ran with caller-given tokens)
+__global__ void set_state_k(StepState* st, int pos, int n_forced, int* seq_fix = nullptr) {
+    st->pos = pos; st->n_forced = n_forced;
+    if (seq_fix) seq_fix[pos] = st->last_token;
+}
+
+double gemv_bytes(const AxWeight& w) { return (double)ax_weight_bytes(w) + 4.0 * w.cols + 4.0 * w.rows; }
+
+#define STEP_LAUNCH(CLS, BYTES, CALL)                                                        \
+    do {                                                                                     \
+        if (prof) cudaEventRecord(prof->ev[2 * prof->n], s);                                 \
+        rc = (CALL);                                                                         \
+        if (rc) return rc;                                                                   \
+        if (prof) { cudaEventRecord(prof->ev[2 * prof->n + 1], s); prof->cls[prof->n] = (CLS); prof->bytes[prof->n] = (BYTES); prof->n++; } \
+        n_launch++;                                                                          \
+    } while (0)
+
+// One token: every launch of the step, in order, on the context stream.
+int run_step(atlasx_model* m, Profile* prof, bool advance) {
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    const atlasx_model_config& cf = m->cfg;
+    const bool pdl = m->use_pdl && !prof;
+    const int d = cf.d_model, L = cf.n_layers;
+    const bool post = cf.post_norm != 0;
+    int rc = ATLASX_OK, n_launch = 0, cur = 0;
+    const int nparts = 1;                                  // partial sums are reduced by the collective
+
+    for (int l = 0; l < L; l++) {
+        Layer& ly = m->layers[l];
+        // ── QKV projection ──────────────────────────────────────────────────────
+        AxPrologue p;
+        p.eps = cf.rms_norm_eps;
+        if (l == 0) {
+            p.embed = m->embed; p.embed_bf16 = m->embed_bf16; p.vocab = cf.vocab_size;
+            p.seq = m->seq; p.pos = &m->st->pos;
+            p.resid_out = m->resid[0]; cur = 0;
+            if (!post) p.wx = ly.attn_norm;
+        } else {
+            p.base = m->resid[cur]; p.y = m->dn; p.nparts = nparts; p.part_stride = d;
+            if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
+            p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+        }
+        STEP_LAUNCH(CLS_QKV, gemv_bytes(ly.qkv), ax_gemv_launch(c, ly.qkv, p, AX_EPI_PLAIN, 1, m->qkv, pdl));
+
+        // ── QK-norm, RoPE, cache write ──────────────────────────────────────────
+        AxQkPrepArgs qa;
+        qa.q = m->qkv; qa.k = m->qkv + m->q_rows; qa.v = m->qkv + m->q_rows + m->kv_rows;
+        qa.q_norm = ly.q_norm; qa.k_norm = ly.k_norm; qa.cos_t = m->cos_t; qa.sin_t = m->sin_t;
+        qa.kc = ly.kv->k; qa.vc = ly.kv->v; qa.pos = &m->st->pos; qa.pos_shared = 1;
+        qa.batch = 1; qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype;
+        qa.eps = 1e-6f;                                    // the reference hard-codes 1e-6 here (:850,853)
+        STEP_LAUNCH(CLS_QKPREP, 4.0 * (2 * m->q_rows + 2 * m->kv_rows) + (double)2 * m->kv_rows * (cf.kv_dtype == ATLASX_BF16 ? 2 : 4),
+                    ax_qk_prep_launch(c, qa, pdl));
+
+        // ── attention over the cache ────────────────────────────────────────────
+        AxAttnArgs aa;
+        aa.q = m->qkv; aa.kc = ly.kv->k; aa.vc = ly.kv->v; aa.out = m->attn;
+        aa.pos = &m->st->pos; aa.pos_shared = 1; aa.batch = 1;
+        aa.n_heads = m->nh_loc; aa.n_kv = m->nkv_loc; aa.hd = m->hd; aa.window = ly.window;
+        aa.kv_dtype = cf.kv_dtype; aa.scale = m->scale; aa.n_splits = m->attn_splits;
+        double abytes = 0;
+        if (prof) {
+            int rows = m->host_pos + 1;
+            if (ly.window > 0 && rows > ly.window) rows = ly.window;
+            abytes = (double)rows * 2 * m->kv_rows * (cf.kv_dtype == ATLASX_BF16 ? 2 : 4) + 8.0 * m->q_rows;
+        }
+        STEP_LAUNCH(CLS_ATTN, abytes, ax_attn_launch(c, aa, pdl));
+
+        // ── output projection (row-parallel under TP) ───────────────────────────
+        AxPrologue po; po.base = m->attn;
+        STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, pdl));
+        if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->o, (size_t)d));
+
+        // ── gate/up with SwiGLU epilogue ────────────────────────────────────────
+        AxPrologue pg;
+        pg.eps = cf.rms_norm_eps;
+        pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = nparts; pg.part_stride = d;
+        if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
+        pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+        STEP_LAUNCH(CLS_GATEUP, gemv_bytes(ly.gateup), ax_gemv_launch(c, ly.gateup, pg, AX_EPI_SILU_PAIR, 1, m->h, pdl));
+
+        // ── down projection (row-parallel under TP) ─────────────────────────────
+        AxPrologue pd; pd.base = m->h;
+        STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, pdl));
+        if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->dn, (size_t)d));
+    }
+    // ── final norm + lm_head ────────────────────────────────────────────────────
+    AxPrologue pl;
+    pl.eps = cf.rms_norm_eps;
+    pl.base = m->resid[cur]; pl.y = m->dn; pl.nparts = nparts; pl.part_stride = d;
+    if (post) pl.wy = m->layers[L - 1].ffn_norm;
+    pl.wx = m->final_norm;
+    pl.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+    m->final_resid = cur;
+    STEP_LAUNCH(CLS_LMHEAD, gemv_bytes(m->lm_head), ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, pdl));
+    if (m->world > 1)
+        STEP_LAUNCH(CLS_COMM, 4.0 * m->vocab_loc * m->world, ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc));
+
+    // ── greedy selection + state advance ────────────────────────────────────────
+    {
+        AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
+        const int n = cf.vocab_size;
+        if (prof) cudaEventRecord(prof->ev[2 * prof->n], s);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((n + 1023) / 1024)); cfg.blockDim = dim3(256); cfg.stream = s;
+        cudaLaunchAttribute attr[1];
+        if (pdl) { attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1; cfg.attrs = attr; cfg.numAttrs = 1; }
+        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, (const float*)m->logits, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0));
+        if (prof) { cudaEventRecord(prof->ev[2 * prof->n + 1], s); prof->cls[prof->n] = CLS_SELECT; prof->bytes[prof->n] = 4.0 * n; prof->n++; }
+        n_launch++;
+    }
+    m->launches_per_step = n_launch;
+    return ATLASX_OK;
+}
+
+int capture_graph(atlasx_model* m) {
+    atlasx_ctx* c = m->ctx;
+    if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    cudaGraph_t g = nullptr;
+    AX_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = run_step(m, nullptr, true);
+    cudaError_t e = cudaStreamEndCapture(c->stream, &g);
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "stream capture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&m->graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) { m->graph = nullptr; return atlasx_fail(ATLASX_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e)); }
+    return ATLASX_OK;
+}
+
+int step(atlasx_model* m) {
+    if (m->host_pos >= m->cfg.max_seq_len)
+        return atlasx_fail(ATLASX_ERR_STATE, "position %d is past max_seq_len %d", m->host_pos, m->cfg.max_seq_len);
+    int rc;
+    if (m->use_graph && m->graph) { AX_CUDA(cudaGraphLaunch(m->graph, m->ctx->stream)); rc = ATLASX_OK; }
+    else rc = run_step(m, nullptr, true);
+    if (!rc) m->host_pos++;
+    return rc;
+}
+
+}  // namespace
+
+extern "C" const char* atlasx_model_class_name(int cls) { return (cls >= 0 && cls < CLS_COUNT) ? kClassNames[cls] : ""; }
+
+extern "C" int atlasx_model_create(atlasx_ctx* ctx, const atlasx_model_config* cfg, const int* layer_sliding, atlasx_model** out) {
+    AX_ARG(ctx && cfg && out, "null argument");
+    AX_ARG(cfg->n_layers > 0 && cfg->d_model > 0 && cfg->n_heads > 0 && cfg->n_kv_heads > 0 && cfg->ffn_hidden > 0 &&
+           cfg->vocab_size > 0 && cfg->max_seq_len > 0, "dimensions must be positive");
+    AX_ARG(cfg->d_model % cfg->n_heads == 0 && cfg->n_heads % cfg->n_kv_heads == 0, "head counts do not divide");
+    AX_ARG(cfg->kv_dtype == ATLASX_BF16 || cfg->kv_dtype == ATLASX_F32, "kv_dtype must be bf16 or f32");
+    AX_ARG(cfg->weight_format >= ATLASX_F32 && cfg->weight_format <= ATLASX_INT4, "unknown weight_format");
+    const int world = cfg->tp_world > 0 ? cfg->tp_world : 1;
+    AX_ARG(cfg->tp_rank >= 0 && cfg->tp_rank < world, "tp_rank out of range");
+    AX_ARG(cfg->n_heads % world == 0 && cfg->n_kv_heads % world == 0 && cfg->ffn_hidden % world == 0,
+           "heads, kv heads and ffn_hidden must divide by the tensor-parallel degree");
+    AX_ARG(world == ax_comm_world(ctx), "tp_world does not match the context's communicator");
+    const int hd = cfg->d_model / cfg->n_heads;
+    const int epc = cfg->weight_format == ATLASX_F32 ? 4 : cfg->weight_format == ATLASX_BF16 ? 8 : cfg->weight_format == ATLASX_INT8 ? 16 : 32;
+    AX_ARG(cfg->d_model % 32 == 0 && (cfg->ffn_hidden / world) % epc == 0 && ((cfg->n_heads / world) * hd) % epc == 0,
+           "d_model must be a multiple of 32 and the sharded inner dimensions multiples of the 16-byte weight granule");
+    if (cfg->weight_format == ATLASX_INT4) {
+        AX_ARG(cfg->int4_block >= 32 && cfg->int4_block % 32 == 0, "int4_block must be a multiple of 32");
+        AX_ARG(cfg->d_model % cfg->int4_block == 0 && (cfg->ffn_hidden / world) % cfg->int4_block == 0 &&
+               ((cfg->n_heads / world) * hd) % cfg->int4_block == 0, "int4 blocks must not straddle rows or shards");
+    }
+    atlasx_model* m = new atlasx_model();
+    m->ctx = ctx; m->cfg = *cfg; m->cfg.tp_world = world;
+    m->world = world; m->rank = cfg->tp_rank;
+    m->hd = hd; m->nh_loc = cfg->n_heads / world; m->nkv_loc = cfg->n_kv_heads / world; m->ffn_loc = cfg->ffn_hidden / world;
+    m->vocab_loc = (cfg->vocab_size + world - 1) / world;
+    m->q_rows = m->nh_loc * hd; m->kv_rows = m->nkv_loc * hd;
+    // OlmoModel::new (:1331-1335): scale × attn_factor when it differs from 1 by more than 1e-6
+    m->scale = 1.0f / sqrtf((float)hd);
+    const float af = cfg->rope_scaling == 1 ? cfg->yarn_attn_factor : 1.0f;
+    if (fabsf(af - 1.0f) > 1e-6f) m->scale *= af;
+    m->layers.resize(cfg->n_layers);
+    int rc = ATLASX_OK;
+    const int d = cfg->d_model;
+    for (int l = 0; l < cfg->n_layers && !rc; l++) {
+        Layer& ly = m->layers[l];
+        ly.window = (layer_sliding && layer_sliding[l]) ? cfg->sliding_window : 0;
+        rc = alloc_weight(m, ly.qkv, m->q_rows + 2 * m->kv_rows, d);
+        if (!rc) rc = alloc_weight(m, ly.wo, d, m->q_rows);
+        if (!rc) rc = alloc_weight(m, ly.gateup, 2 * m->ffn_loc, d);
+        if (!rc) rc = alloc_weight(m, ly.down, d, m->ffn_loc);
+    }
+    if (!rc) rc = alloc_weight(m, m->lm_head, m->vocab_loc, d);
+    if (rc) { atlasx_model_free(m); return rc; }
+    *out = m;
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_model_free(atlasx_model* m) {
+    if (!m) return ATLASX_OK;
+    cudaStreamSynchronize(m->ctx->stream);
+    if (m->graph) cudaGraphExecDestroy(m->graph);
+    for (Layer& ly : m->layers) if (ly.kv) atlasx_kvcache_free(ly.kv);
+    for (void* p : m->owned) cudaFree(p);
+    if (m->pin) cudaFreeHost(m->pin);
+    delete m;
+    return ATLASX_OK;
+}
+
+static int set_vector(atlasx_model* m, float** dst, const void* src_dev, int dtype, int first, int n) {
+    if (!*dst) { int rc = dmalloc(m, (void**)dst, (size_t)n * 4); if (rc) return rc; }
+    if (dtype == ATLASX_BF16) ax_bf16_to_f32(m->ctx->stream, (const uint16_t*)src_dev + first, *dst, (size_t)n);
+    else AX_CUDA(cudaMemcpyAsync(*dst, (const float*)src_dev + first, (size_t)n * 4, cudaMemcpyDeviceToDevice, m->ctx->stream));
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_model_set_tensor(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device) {
+    AX_ARG(m && data, "null argument");
+    AX_ARG(dtype == ATLASX_F32 || dtype == ATLASX_BF16, "tensors are given as f32 or bf16");
+    AX_ARG(!m->finalized, "model already finalised");
+    const atlasx_model_config& cf = m->cfg;
+    const int d = cf.d_model, hd = m->hd;
+    int rows = 0, cols = 0;
+    switch (which) {
+        case ATLASX_T_EMBED: case ATLASX_T_LM_HEAD: rows = cf.vocab_size; cols = d; break;
+        case ATLASX_T_FINAL_NORM: case ATLASX_T_ATTN_NORM: case ATLASX_T_FFN_NORM: rows = 1; cols = d; break;
+        case ATLASX_T_WQ: rows = cf.n_heads * hd; cols = d; break;
+        case ATLASX_T_WK: case ATLASX_T_WV: rows = cf.n_kv_heads * hd; cols = d; break;
+        case ATLASX_T_WO: rows = d; cols = cf.n_heads * hd; break;
+        case ATLASX_T_GATE: case ATLASX_T_UP: rows = cf.ffn_hidden; cols = d; break;
+        case ATLASX_T_DOWN: rows = d; cols = cf.ffn_hidden; break;
+        case ATLASX_T_Q_NORM: rows = 1; cols = cf.n_heads * hd; break;
+        case ATLASX_T_K_NORM: rows = 1; cols = cf.n_kv_heads * hd; break;
+        default: return atlasx_fail(ATLASX_ERR_ARG, "unknown tensor id %d", which);
+    }
+    if (which >= ATLASX_T_WQ) AX_ARG(layer >= 0 && layer < cf.n_layers, "layer out of range");
+    const size_t n = (size_t)rows * cols, esz = dtype == ATLASX_BF16 ? 2 : 4;
+    cudaStream_t s = m->ctx->stream;
+    void* staged = nullptr;
+    const void* src = data;
+    if (!on_device) {
+        AX_CUDA(cudaMalloc(&staged, n * esz));
+        cudaError_t e = cudaMemcpyAsync(staged, data, n * esz, cudaMemcpyHostToDevice, s);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) { cudaFree(staged); return atlasx_fail(ATLASX_ERR_CUDA, "upload failed: %s", cudaGetErrorString(e)); }
+        src = staged;
+    }
+    int rc = ATLASX_OK;
+    const int r = m->rank;
+    Layer* ly = which >= ATLASX_T_WQ ? &m->layers[layer] : nullptr;
+    switch (which) {
+        case ATLASX_T_EMBED: {
+            // replicated; kept in the precision it was given in (bf16 rows are exact in f32)
+            if (!m->embed || m->embed_bf16 != (dtype == ATLASX_BF16)) { rc = dmalloc(m, &m->embed, n * esz); }
+            if (!rc) { m->embed_bf16 = dtype == ATLASX_BF16; cudaMemcpyAsync(m->embed, src, n * esz, cudaMemcpyDeviceToDevice, s); m->have_embed = true; }
+            break;
+        }
+        case ATLASX_T_LM_HEAD: {
+            const int r0 = r * m->vocab_loc;
+            int nr = cf.vocab_size - r0; if (nr > m->vocab_loc) nr = m->vocab_loc; if (nr < 0) nr = 0;
+            if (nr > 0) rc = place_slice(m, src, dtype, rows, cols, r0, nr, 0, d, m->lm_head, 0, 1);
+            m->have_lm_head = true;
+            break;
+        }
+        case ATLASX_T_FINAL_NORM: rc = set_vector(m, &m->final_norm, src, dtype, 0, d); break;
+        case ATLASX_T_ATTN_NORM: rc = set_vector(m, &ly->attn_norm, src, dtype, 0, d); break;
+        case ATLASX_T_FFN_NORM: rc = set_vector(m, &ly->ffn_norm, src, dtype, 0, d); break;
+        case ATLASX_T_Q_NORM: rc = set_vector(m, &ly->q_norm, src, dtype, r * m->q_rows, m->q_rows); break;
+        case ATLASX_T_K_NORM: rc = set_vector(m, &ly->k_norm, src, dtype, r * m->kv_rows, m->kv_rows); break;
+        case ATLASX_T_WQ: rc = place_slice(m, src, dtype, rows, cols, r * m->q_rows, m->q_rows, 0, d, ly->qkv, 0, 1); break;
+        case ATLASX_T_WK: rc = place_slice(m, src, dtype, rows, cols, r * m->kv_rows, m->kv_rows, 0, d, ly->qkv, m->q_rows, 1); break;
+        case ATLASX_T_WV: rc = place_slice(m, src, dtype, rows, cols, r * m->kv_rows, m->kv_rows, 0, d, ly->qkv, m->q_rows + m->kv_rows, 1); break;
+        case ATLASX_T_WO: rc = place_slice(m, src, dtype, rows, cols, 0, d, r * m->q_rows, m->q_rows, ly->wo, 0, 1); break;
+        case ATLASX_T_GATE: rc = place_slice(m, src, dtype, rows, cols, r * m->ffn_loc, m->ffn_loc, 0, d, ly->gateup, 0, 2); break;
+        case ATLASX_T_UP: rc = place_slice(m, src, dtype, rows, cols, r * m->ffn_loc, m->ffn_loc, 0, d, ly->gateup, 1, 2); break;
+        case ATLASX_T_DOWN: rc = place_slice(m, src, dtype, rows, cols, 0, d, r * m->ffn_loc, m->ffn_loc, ly->down, 0, 1); break;
+    }
+    if (ly && !rc) ly->have[which - ATLASX_T_WQ] = true;
+    cudaStreamSynchronize(s);
+    cudaFree(staged);
+    return rc;
+}
+
+extern "C" int atlasx_model_finalize(atlasx_model* m) {
+    AX_ARG(m, "model is null");
+    AX_ARG(!m->finalized, "model already finalised");
+    const atlasx_model_config& cf = m->cfg;
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    const int d = cf.d_model;
+    AX_ARG(m->have_embed, "embedding table was not set");
+    for (int l = 0; l < cf.n_layers; l++)
+        for (int t = ATLASX_T_WQ; t <= ATLASX_T_DOWN; t++)
+            if (!m->layers[l].have[t - ATLASX_T_WQ]) return atlasx_fail(ATLASX_ERR_STATE, "layer %d: tensor %d was not set", l, t);
+    int rc = ATLASX_OK;
+    // unit norm weights where none were loaded (TransformerBlock::new, :950-951; OlmoModel::new :1344)
+    std::vector<float> ones((size_t)d, 1.0f);
+    float* ones_dev = nullptr;
+    if ((rc = dmalloc(m, (void**)&ones_dev, (size_t)d * 4))) return rc;
+    AX_CUDA(cudaMemcpyAsync(ones_dev, ones.data(), (size_t)d * 4, cudaMemcpyHostToDevice, s));
+    AX_CUDA(cudaStreamSynchronize(s));
+    if (!m->final_norm) m->final_norm = ones_dev;
+    for (Layer& ly : m->layers) { if (!ly.attn_norm) ly.attn_norm = ones_dev; if (!ly.ffn_norm) ly.ffn_norm = ones_dev; }
+    // weight tying: lm_head is a copy of the embedding when none was given (:1345-1350)
+    if (!m->have_lm_head) {
+        const int r0 = m->rank * m->vocab_loc;
+        int nr = cf.vocab_size - r0; if (nr > m->vocab_loc) nr = m->vocab_loc;
+        if (nr > 0) rc = place_slice(m, m->embed, m->embed_bf16 ? ATLASX_BF16 : ATLASX_F32, cf.vocab_size, d, r0, nr, 0, d, m->lm_head, 0, 1);
+        if (rc) return rc;
+        m->have_lm_head = true;
+    }
+    // RoPE tables (init_gpu_resources, :1363-1376)
+    const int half = m->hd / 2;
+    std::vector<float> ch((size_t)cf.max_seq_len * (half > 0 ? half : 1)), sh(ch.size());
+    rc = atlasx_rope_tables_host(m->hd, cf.max_seq_len, cf.rope_theta, cf.rope_scaling, cf.yarn_factor, cf.yarn_orig_max_pos,
+                                 cf.yarn_beta_fast, cf.yarn_beta_slow, ch.data(), sh.data());
+    if (rc) return rc;
+    if ((rc = dmalloc(m, (void**)&m->cos_t, ch.size() * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->sin_t, ch.size() * 4))) return rc;
+    AX_CUDA(cudaMemcpyAsync(m->cos_t, ch.data(), ch.size() * 4, cudaMemcpyHostToDevice, s));
+    AX_CUDA(cudaMemcpyAsync(m->sin_t, sh.data(), sh.size() * 4, cudaMemcpyHostToDevice, s));
+    AX_CUDA(cudaStreamSynchronize(s));
+    // KV caches (:1381-1385)
+    for (Layer& ly : m->layers)
+        if ((rc = atlasx_kvcache_create(c, cf.max_seq_len, m->nkv_loc, m->hd, cf.kv_dtype, 1, &ly.kv))) return rc;
+    // activations
+    const size_t vocab_pad = (size_t)m->vocab_loc * m->world;
+    if ((rc = dmalloc(m, (void**)&m->resid[0], (size_t)d * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->resid[1], (size_t)d * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->qkv, (size_t)(m->q_rows + 2 * m->kv_rows) * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->attn, (size_t)m->q_rows * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->o, (size_t)d * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->h, (size_t)m->ffn_loc * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->dn, (size_t)d * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->logits, vocab_pad * 4))) return rc;
+    if (m->world > 1) { if ((rc = dmalloc(m, (void**)&m->logits_loc, (size_t)m->vocab_loc * 4))) return rc; }
+    else m->logits_loc = m->logits;
+    if ((rc = dmalloc(m, (void**)&m->seq, (size_t)(cf.max_seq_len + 1) * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->st, sizeof(StepState)))) return rc;
+    AX_CUDA(cudaMemsetAsync(m->seq, 0, (size_t)(cf.max_seq_len + 1) * 4, s));
+    AX_CUDA(cudaMemsetAsync(m->st, 0, sizeof(StepState), s));
+    AX_CUDA(cudaMemsetAsync(m->logits, 0, vocab_pad * 4, s));
+    AX_CUDA(cudaMallocHost((void**)&m->pin, 64 * sizeof(int)));
+    // attention split count fixed for the graph; scratch sized once
+    int max_rows = cf.max_seq_len;
+    m->attn_splits = ax_attn_pick_splits(c, m->nkv_loc, 1, max_rows);
+    rc = atlasx_ctx_ensure_attn_scratch(c, (size_t)m->nh_loc * m->attn_splits * (m->hd + 2), (size_t)m->nh_loc);
+    if (rc) return rc;
+    AX_ARG(cf.vocab_size <= 4096 * 1024, "vocabulary too large for the selection scratch");
+    m->finalized = true;
+    m->host_pos = 0;
+    set_state_k<<<1, 1, 0, s>>>(m->st, 0, INT_MAX);
+    AX_CUDA(cudaStreamSynchronize(s));
+    // one eager step loads every kernel before capture; it only touches cache row 0, which the
+    // first real token rewrites
+    rc = run_step(m, nullptr, true); if (rc) return rc;
+    set_state_k<<<1, 1, 0, s>>>(m->st, 0, INT_MAX);
+    {
+        cudaError_t e = cudaStreamSynchronize(s);
+        if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "first decode step failed: %s", cudaGetErrorString(e));
+        int code = 0;
+        rc = atlasx_ctx_poll_device_error(c, &code); if (rc) return rc;
+    }
+    if (m->use_graph) { rc = capture_graph(m); if (rc) return rc; }
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl) {
+    AX_ARG(m, "model is null");
+    const bool changed = m->use_pdl != (use_pdl ? 1 : 0) || m->use_graph != (use_graph ? 1 : 0);
+    m->use_graph = use_graph ? 1 : 0; m->use_pdl = use_pdl ? 1 : 0;
+    if (m->finalized && changed) {
+        AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+        if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+        if (m->use_graph) return capture_graph(m);
+    }
+    return ATLASX_OK;
+}
+
+// reset (:1389-1392): position back to zero, caches are not cleared
+extern "C" int atlasx_model_reset(atlasx_model* m) {
+    AX_ARG(m && m->finalized, "model is not finalised");
+    m->host_pos = 0;
+    set_state_k<<<1, 1, 0, m->ctx->stream>>>(m->st, 0, INT_MAX);
+    AX_CHECK_LAUNCH("set_state");
+    return ATLASX_OK;
+}
+extern "C" int atlasx_model_pos(const atlasx_model* m) { return m ? m->host_pos : -1; }
+
+extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* logits_host) {
+    AX_ARG(m && m->finalized, "model is not finalised");
+    cudaStream_t s = m->ctx->stream;
+    AX_ARG(m->host_pos < m->cfg.max_seq_len, "position is past max_seq_len");
+    m->pin[0] = (int)token;
+    AX_CUDA(cudaMemcpyAsync(m->seq + m->host_pos, m->pin, 4, cudaMemcpyHostToDevice, s));
+    set_state_k<<<1, 1, 0, s>>>(m->st, m->host_pos, INT_MAX);
+    int rc = step(m); if (rc) return rc;
+    if (logits_host) AX_CUDA(cudaMemcpyAsync(logits_host, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, s));
+    AX_CUDA(cudaStreamSynchronize(s));
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_model_hidden(atlasx_model* m, float* hidden_host) {
+    AX_ARG(m && m->finalized && hidden_host, "bad argument");
+    AX_CUDA(cudaMemcpyAsync(hidden_host, m->resid[m->final_resid], (size_t)m->cfg.d_model * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* prompt, int n_prompt, int max_new,
+                                            const uint32_t* suppress, int n_suppress, float rep_penalty, int rep_window,
+                                            const uint32_t* stops, int n_stops, uint32_t* out_tokens, int* n_out) {
+    AX_ARG(m && m->finalized && n_out, "bad argument");
+    AX_ARG(n_prompt >= 0 && max_new >= 0 && (n_prompt == 0 || prompt) && (max_new == 0 || out_tokens), "bad argument");
+    AX_ARG(n_prompt + max_new <= m->cfg.max_seq_len, "prompt + max_new exceeds max_seq_len");
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    const int V = m->cfg.vocab_size;
+    *n_out = 0;
+    int rc = atlasx_model_reset(m); if (rc) return rc;
+    if (n_prompt > 0) AX_CUDA(cudaMemcpyAsync(m->seq, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s));
+    set_state_k<<<1, 1, 0, s>>>(m->st, 0, n_prompt);
+    int *sup_dev = nullptr;
+    const bool fix = n_suppress > 0 || rep_penalty != 1.0f;
+    if (n_suppress > 0) {
+        AX_CUDA(cudaMalloc((void**)&sup_dev, (size_t)n_suppress * 4));
+        AX_CUDA(cudaMemcpyAsync(sup_dev, suppress, (size_t)n_suppress * 4, cudaMemcpyHostToDevice, s));
+    }
+    auto done = [&](int r) { cudaStreamSynchronize(s); cudaFree(sup_dev); return r; };
+    if (n_prompt == 0) {
+        // last_logits starts as zeros (:1609): the first choice is made among equal logits
+        AX_CUDA(cudaMemsetAsync(m->logits, 0, (size_t)V * 4, s));
+    }
+    for (int i = 0; i < n_prompt; i++) { rc = step(m); if (rc) return done(rc); }
+    AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
+    for (int stepi = 0; stepi < max_new; stepi++) {
+        const bool need_fix = fix && ((stepi == 0 && n_suppress > 0) || (rep_penalty != 1.0f && stepi > 0));
+        if (need_fix || (n_prompt == 0 && stepi == 0)) {
+            // re-select on edited logits: history = generated tokens seq[n_prompt .. n_prompt+stepi)
+            int start = stepi > rep_window ? stepi - rep_window : 0;
+            if (need_fix)
+                logit_fixups_k<<<1, 32, 0, s>>>(m->logits, V, sup_dev, stepi == 0 ? n_suppress : 0,
+                                                m->seq + n_prompt + start, rep_penalty != 1.0f ? stepi - start : 0, rep_penalty);
+            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0);
+            cudaError_t e = cudaGetLastError();
+            if (e != cudaSuccess) return done(atlasx_fail(ATLASX_ERR_CUDA, "selection launch failed: %s", cudaGetErrorString(e)));
+        }
+        AX_CUDA(cudaMemcpyAsync(m->pin, &m->st->last_token, 4, cudaMemcpyDeviceToHost, s));
+        AX_CUDA(cudaStreamSynchronize(s));
+        const uint32_t tok = (uint32_t)m->pin[0];
+        if (m->cfg.eos_token_id >= 0 && tok == (uint32_t)m->cfg.eos_token_id) break;
+        bool stop = false;
+        for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
+        if (stop) break;
+        out_tokens[(*n_out)++] = tok;
+        rc = step(m); if (rc) return done(rc);
+    }
+    return done(ATLASX_OK);
+}
+
+extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, float* elapsed_ms, uint32_t* tokens_host) {
+    AX_ARG(m && m->finalized && steps > 0, "bad argument");
+    AX_ARG(m->host_pos + steps <= m->cfg.max_seq_len, "steps run past max_seq_len");
+    cudaStream_t s = m->ctx->stream;
+    const int p0 = m->host_pos;
+    set_state_k<<<1, 1, 0, s>>>(m->st, p0, p0, m->seq);      // every token from here on is generated
+    cudaEvent_t e0, e1;
+    AX_CUDA(cudaEventCreate(&e0)); AX_CUDA(cudaEventCreate(&e1));
+    AX_CUDA(cudaStreamSynchronize(s));
+    AX_CUDA(cudaEventRecord(e0, s));
+    int rc = ATLASX_OK;
+    for (int i = 0; i < steps && !rc; i++) rc = step(m);
+    cudaEventRecord(e1, s);
+    cudaError_t e = cudaStreamSynchronize(s);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (rc) return rc;
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "decode failed: %s", cudaGetErrorString(e));
+    if (elapsed_ms) *elapsed_ms = ms;
+    if (tokens_host) AX_CUDA(cudaMemcpy(tokens_host, m->seq + p0 + 1, (size_t)steps * 4, cudaMemcpyDeviceToHost));
+    return ATLASX_OK;
+}
+
+extern "C" int atlasx_model_profile_step(atlasx_model* m, int n_max, int* launches, float* ms, double* bytes, int* n_classes) {
+    AX_ARG(m && m->finalized && launches && ms && bytes && n_classes && n_max >= CLS_COUNT, "bad argument");
+    AX_ARG(m->host_pos < m->cfg.max_seq_len, "position is past max_seq_len");
+    cudaStream_t s = m->ctx->stream;
+    const int cap = m->cfg.n_layers * 8 + 8;
+    Profile pr;
+    pr.ev.resize((size_t)cap * 2); pr.cls.resize(cap); pr.bytes.resize(cap);
+    for (auto& e : pr.ev) AX_CUDA(cudaEventCreate(&e));
+    set_state_k<<<1, 1, 0, s>>>(m->st, m->host_pos, m->host_pos, m->seq);
+    int rc = run_step(m, &pr, true);
+    cudaError_t e = cudaStreamSynchronize(s);
+    if (!rc && e != cudaSuccess) rc = atlasx_fail(ATLASX_ERR_CUDA, "profiled step failed: %s", cudaGetErrorString(e));
+    if (!rc) {
+        m->host_pos++;
+        for (int i = 0; i < CLS_COUNT; i++) { launches[i] = 0; ms[i] = 0.f; bytes[i] = 0.0; }
+        for (int i = 0; i < pr.n; i++) {
+            float t = 0.f; cudaEventElapsedTime(&t, pr.ev[2 * i], pr.ev[2 * i + 1]);
+            launches[pr.cls[i]]++; ms[pr.cls[i]] += t; bytes[pr.cls[i]] += pr.bytes[i];
+        }
+        *n_classes = CLS_COUNT;
+    }
+    for (auto& ev : pr.ev) cudaEventDestroy(ev);
+    return rc;
+}
+
+extern "C" double atlasx_model_step_bytes(const atlasx_model* m, int pos) {
+    if (!m) return 0;
+    double b = 0;
+    const double esz = m->cfg.kv_dtype == ATLASX_BF16 ? 2 : 4;
+    for (const Layer& ly : m->layers) {
+        b += (double)ax_weight_bytes(ly.qkv) + (double)ax_weight_bytes(ly.wo) + (double)ax_weight_bytes(ly.gateup) + (double)ax_weight_bytes(ly.down);
+        int rows = pos + 1;
+        if (ly.window > 0 && rows > ly.window) rows = ly.window;
+        b += (double)rows * 2 * m->kv_rows * esz + 2.0 * m->kv_rows * esz;
+    }
+    b += (double)ax_weight_bytes(m->lm_head);
+    return b;
+}
+extern "C" int atlasx_model_kernel_launches_per_step(const atlasx_model* m) { return m ? m->launches_per_step : 0; }

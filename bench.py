@@ -1,0 +1,346 @@
+#!/usr/bin/env python
+"""Decode benchmark: OLMo-3-7B-architecture BF16 batch-1 greedy decode (BASELINE config 4).
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one generated token at context ≥ prompt length (default 2048): the whole hot path
+(161 weight-streaming GEMVs, 32 attention calls, selection) over 13.77 GB of bf16 weights, so
+every step reads far more than the 126 MB L2 and no flush is needed between steps.
+Prints ONE JSON line (rank 0).  `value` is device-timed tokens/s with everything resident in
+HBM; `e2e` is the same metric through the reference-facing call forward_one_gpu(token) →
+host logits → host argmax, with the token upload and the logits download inside the timed
+region.  With N > 1 the model is sharded tensor-parallel over N GPUs (one process per GPU,
+NCCL all-reduce after o_proj and down): total work is fixed, so scaling is "strong".
+
+--impl reference times the CPU restatement of the reference's forward_one path (oracle/,
+OpenMP over output rows, all host threads) on the same model and metric.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
+
+import numpy as np  # noqa: E402
+
+METRIC = "olmo3_7b_arch_bf16_bs1_greedy_decode_tokens_per_s"
+UNIT = "tok/s"
+WORKLOAD = ("configs[3]: OLMo-3-7B arch (32 layers, d 4096, 32 heads x 128, ffn 11008, vocab 100278, "
+            "post-norm + QK-norm, SWA 4096 on 24/32 layers, YaRN), bf16 weights N(0,0.02) seed 0, batch 1")
+PER_LAYER = [("wq", 10), ("wk", 11), ("wv", 12), ("wo", 13), ("gate", 14), ("up", 15), ("down", 16)]
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            j = json.load(open(p))
+            return float(j["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.idx), "--query-gpu=" + self.Q,
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_config(ab, max_seq):
+    return ab.ModelConfig.olmo3_actual_7b(max_seq_len=max_seq)
+
+
+def build_cuda_model(ab, ctx, max_seq, rank, world):
+    """Random-init weights generated on the device from the seeded hash (full tensors, then each
+    rank keeps its tensor-parallel slice)."""
+    from atlas_b200 import _ffi
+    L = _ffi.lib()
+    mc = model_config(ab, max_seq)
+    m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.BF16, weight_format=ab.BF16, tp_rank=rank, tp_world=world)
+    d, f, V = mc.d_model, mc.ffn_hidden, mc.vocab_size
+    shapes = {"wq": (d, d), "wk": (d, d), "wv": (d, d), "wo": (d, d), "gate": (f, d), "up": (f, d), "down": (d, f)}
+    big = ctx.malloc(V * d * 2)
+
+    def give(layer, which, rows, cols, stream):
+        _ffi.check(L.atlasx_fill_normal_bf16(ctx.handle, big, rows * cols, 0, stream, 0, 0.02))
+        m.set_tensor(layer, which, big, on_device=True, dtype=ab.BF16)
+    give(0, 0, V, d, 1)          # embedding
+    give(0, 2, V, d, 2)          # lm_head
+    ones = np.ones(d, np.float32)
+    m.set_tensor(0, 1, ones)
+    for l in range(mc.n_layers):
+        for name, tid in PER_LAYER:
+            give(l, tid, shapes[name][0], shapes[name][1], 1000 + l * 32 + tid)
+        for tid in (17, 18, 19, 20):
+            m.set_tensor(l, tid, ones)
+    ctx.free(big)
+    m.init_gpu_resources()
+    return m, mc
+
+
+def cpu_reference_model(n_layers, max_seq):
+    """The oracle's model with the same seeded weights (bf16 bits in host memory)."""
+    from oracle import orc
+    cfg = dict(vocab_size=100278, d_model=4096, n_layers=n_layers, n_heads=32, n_kv_heads=32, ffn_hidden=11008,
+               max_seq_len=max_seq, rope_theta=500000.0, rms_norm_eps=1e-6, sliding_window=4096, rope_scaling=1,
+               yarn_factor=8.0, yarn_orig_max_pos=8192, yarn_attn_factor=1.2079441541679836,
+               yarn_beta_fast=32.0, yarn_beta_slow=1.0, post_norm=1)
+    d, f, V = 4096, 11008, 100278
+    m = orc.OracleModel(cfg, [0 if i % 4 == 3 else 1 for i in range(n_layers)])
+    shapes = {"wq": (d, d), "wk": (d, d), "wv": (d, d), "wo": (d, d), "gate": (f, d), "up": (f, d), "down": (d, f)}
+    lm = orc.normal_bf16(V * d, 0, 2, 0.02).reshape(V, d)
+    m.set_tensor(0, orc.T_LM_HEAD, lm)
+    if n_layers == 32:
+        m.set_tensor(0, orc.T_EMBED, orc.normal_bf16(V * d, 0, 1, 0.02).reshape(V, d))
+    else:
+        m.set_tensor(0, orc.T_EMBED, lm)       # bounded sample: any embedding row will do
+    ones = np.ones(d, np.float32)
+    for l in range(n_layers):
+        for name, tid in PER_LAYER:
+            r, c = shapes[name]
+            m.set_tensor(l, tid, orc.normal_bf16(r * c, 0, 1000 + l * 32 + tid, 0.02).reshape(r, c))
+        m.set_tensor(l, orc.T_Q_NORM, ones); m.set_tensor(l, orc.T_K_NORM, ones)
+    return m
+
+
+def cpu_baseline_sample():
+    """Bounded sample for the default run: one layer of the model plus lm_head through the
+    oracle's forward_one, all host threads; tokens/s extrapolated to 32 layers."""
+    from oracle import orc
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    m = cpu_reference_model(1, 16)
+    m.forward_one(1)                                        # warm-up
+    t0 = time.perf_counter(); n = 3
+    for i in range(n):
+        m.forward_one(2 + i)
+    t_tok = (time.perf_counter() - t0) / n                  # 1 layer + head
+    lm = m._keep[0]
+    x = orc.normal_f32(4096, 1, 1, 1.0)
+    orc.linear(lm, x)
+    t0 = time.perf_counter()
+    for i in range(n):
+        orc.linear(lm, x)
+    t_head = (time.perf_counter() - t0) / n
+    t_layer = max(t_tok - t_head, 1e-9)
+    full = 32 * t_layer + t_head
+    return {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
+            "sample": "oracle forward_one on 1 of 32 layers + lm_head at pos<4, %d tokens; per-token time = 32*layer + head = %.3f s"
+                      % (n, full)}
+
+
+def run_reference(args, rank):
+    """CPU arm: the restatement of the reference's forward_one (oracle/) on the full model."""
+    if rank != 0:
+        return
+    from oracle import orc
+    cores = os.cpu_count() or 1
+    orc.set_threads(cores)
+    try:
+        avail_gb = os.sysconf("SC_AVPHYS_PAGES") * os.sysconf("SC_PAGE_SIZE") / 1e9
+    except Exception:
+        avail_gb = 0
+    steps, warm = args.steps, max(args.warmup, 1)
+    if avail_gb > 40:
+        m = cpu_reference_model(32, steps + warm + 8)
+        for i in range(warm):
+            m.forward_one(7 + i)
+        t0 = time.perf_counter()
+        tok = 11
+        for i in range(steps):
+            tok = orc.argmax(m.forward_one(int(tok)))
+        dt = time.perf_counter() - t0
+        value = steps / dt
+        sample = "full model, %d greedy tokens from pos %d on %d host threads (OpenMP over output rows)" % (steps, warm, cores)
+        ms = dt / steps * 1e3
+    else:
+        b = cpu_baseline_sample()
+        value, sample, ms = b["value"], b["sample"] + " (host RAM too small for the full model)", 1e3 / b["value"]
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic", "impl": "reference",
+            "config": {"workload": WORKLOAD, "context": "pos %d.." % warm, "l2": "weights (13.77 GB) exceed any cache"},
+            "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--prompt", type=int, default=2048, help="context length reached before the timed steps")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            sys.exit("launch with torchrun --nproc-per-node %d for --gpus %d" % (args.gpus, args.gpus))
+        args.gpus = world
+
+    import atlas_b200 as ab
+    from atlas_b200 import _ffi
+    dist = None
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = ab.Context(local_rank)
+    if world > 1:
+        import ctypes as C
+        import torch
+        ident = (C.c_ubyte * 128)()
+        if rank == 0:
+            _ffi.check(_ffi.lib().atlasx_comm_unique_id(ident))
+        t = torch.tensor(list(bytes(ident)), dtype=torch.uint8, device="cuda")
+        dist.broadcast(t, 0)
+        ident = (C.c_ubyte * 128)(*t.cpu().tolist())
+        _ffi.check(_ffi.lib().atlasx_comm_init(ctx.handle, ident, rank, world))
+
+    steps, warm = args.steps, max(args.warmup, 3)
+    max_seq = args.prompt + warm + 2 * steps + 16
+    m, mc = build_cuda_model(ab, ctx, max_seq, rank, world)
+    prompt = np.random.default_rng(0).integers(0, mc.vocab_size, size=args.prompt, dtype=np.uint32)
+
+    # context: the prompt goes through the decode path token by token, as the reference does
+    m.generate(prompt, 1, 0.0)
+    m.decode_timed(warm)                                   # warm-up steps (untimed)
+
+    def barrier():
+        ctx.sync()
+        if dist is not None:
+            dist.barrier()
+
+    sampler = ClockSampler(local_rank)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    pos0 = m.pos
+    ms, toks = m.decode_timed(steps)                        # CUDA events on the launching stream
+    barrier()
+    clocks = sampler.stop() if rank == 0 else None
+    if dist is not None:
+        import torch
+        tt = torch.tensor([ms], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        ms = float(tt.item())
+    value = steps / (ms / 1e3)
+
+    # end to end through the reference-facing call: token in, logits out, host argmax
+    tok = int(toks[-1])
+    e2e_steps = min(steps, 64)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        logits = m.forward_one_gpu(tok)
+        tok = int(np.argmax(logits))
+    barrier()
+    e2e_dt = time.perf_counter() - t0
+    if dist is not None:
+        import torch
+        tt = torch.tensor([e2e_dt], device="cuda")
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        e2e_dt = float(tt.item())
+    e2e = {"value": e2e_steps / e2e_dt, "unit": UNIT, "h2d_bytes_per_step": 4,
+           "d2h_bytes_per_step": mc.vocab_size * 4, "steps": e2e_steps,
+           "call": "OlmoModel.forward_one_gpu(token) -> host logits, numpy argmax"}
+
+    # per-kernel-class device times (event pair around every launch, outside the graph)
+    prof_pos = m.pos
+    prof = m.profile_step()
+    for _ in range(2):
+        p2 = m.profile_step()
+        for k in prof:
+            prof[k]["ms"] = min(prof[k]["ms"], p2[k]["ms"])
+    peak, peak_kind = peaks()
+    gemv = [k for k in prof if k.startswith("gemv")]
+    g_bytes = sum(prof[k]["bytes"] for k in gemv)
+    g_ms = sum(prof[k]["ms"] for k in gemv)
+    g_launch = sum(prof[k]["launches"] for k in gemv)
+    achieved = g_bytes / (g_ms / 1e3) / 1e9
+    step_bytes = m.step_bytes(pos0 + steps // 2)
+    roofline = {"bound": "hbm", "kernel": "ax_gemv_stream_kernel<bf16> (all %d GEMV launches of a step)" % g_launch,
+                "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+                "traffic": None,
+                "step": {"algorithmic_bytes": step_bytes, "achieved": step_bytes * value / 1e9,
+                         "frac": step_bytes * value / 1e9 / peak, "frac_of_8000": step_bytes * value / 1e9 / 8000.0},
+                "per_class": {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
+                                  "gbs": (v["bytes"] / (v["ms"] / 1e3) / 1e9) if v["ms"] > 0 else None}
+                              for k, v in prof.items() if v["launches"]},
+                "profiled_at_pos": prof_pos}
+
+    if rank != 0:
+        return
+    cpu = None
+    if not args.no_cpu_baseline and world == 1:
+        try:
+            cpu = cpu_baseline_sample()
+        except Exception as e:       # the baseline is reported, never required
+            cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": "failed: %s" % e}
+    line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
+            "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "context": "pos %d..%d after a %d-token random prompt" % (pos0, pos0 + steps, args.prompt),
+                       "kv_cache": "bf16", "parallelism": "tp%d" % world,
+                       "l2": "inputs larger than L2: 13.77 GB of weights stream per step"},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": m.launches_per_step * steps,
+            "roofline": roofline, "cpu_baseline": cpu}
+    print(json.dumps(line), flush=True)
+
+
+if __name__ == "__main__":
+    main()
