@@ -125,6 +125,8 @@ SIGNATURES = {
     "atlasx_model_kernel_launches_per_step": (ci, [vp]),
     "atlasx_model_set_options": (ci, [vp, ci, ci]),
     "atlasx_model_hidden": (ci, [vp, vp]),
+    "atlasx_time_gemv": (ci, [vp, vp, ci, vp, ci, vp, ci, C.POINTER(cf)]),
+    "atlasx_time_attention": (ci, [vp, vp, vp, vp, ci, vp, cf, ci, ci, C.POINTER(cf)]),
     "atlasx_comm_unique_id": (ci, [vp]),
     "atlasx_comm_init": (ci, [vp, vp, ci, ci]),
     "atlasx_comm_world": (ci, [vp]),

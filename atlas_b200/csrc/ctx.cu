@@ -483,3 +483,44 @@ extern "C" size_t atlasx_decode_attention_bytes(const atlasx_kvcache* kv, int n_
     }
     return total;
 }
+
+// ── measurement helpers ──────────────────────────────────────────────────────────
+extern "C" int atlasx_time_gemv(atlasx_ctx* c, const atlasx_matrix* const* mats, int n_mats, const float* x, int n,
+                                float* y, int iters, float* ms_out) {
+    AX_ARG(c && mats && n_mats > 0 && x && y && iters > 0 && ms_out, "bad argument");
+    cudaEvent_t e0, e1;
+    AX_CUDA(cudaEventCreate(&e0)); AX_CUDA(cudaEventCreate(&e1));
+    int rc = ATLASX_OK;
+    for (int i = 0; i < n_mats && !rc; i++) rc = atlasx_gemv(c, mats[i], x, n, y);       // warm-up pass
+    cudaStreamSynchronize(c->stream);
+    cudaEventRecord(e0, c->stream);
+    for (int i = 0; i < iters && !rc; i++) rc = atlasx_gemv(c, mats[i % n_mats], x, n, y);
+    cudaEventRecord(e1, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (rc) return rc;
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "timed GEMV failed: %s", cudaGetErrorString(e));
+    *ms_out = ms;
+    return ATLASX_OK;
+}
+extern "C" int atlasx_time_attention(atlasx_ctx* c, const atlasx_kvcache* kv, const float* q, float* out, int n_heads,
+                                     const int* pos_host, float scale, int window, int iters, float* ms_out) {
+    AX_ARG(c && kv && q && out && pos_host && iters > 0 && ms_out, "bad argument");
+    cudaEvent_t e0, e1;
+    AX_CUDA(cudaEventCreate(&e0)); AX_CUDA(cudaEventCreate(&e1));
+    int rc = atlasx_decode_attention(c, kv, q, out, n_heads, pos_host, scale, window);   // warm-up, sizes the scratch
+    cudaStreamSynchronize(c->stream);
+    cudaEventRecord(e0, c->stream);
+    for (int i = 0; i < iters && !rc; i++) rc = atlasx_decode_attention(c, kv, q, out, n_heads, pos_host, scale, window);
+    cudaEventRecord(e1, c->stream);
+    cudaError_t e = cudaStreamSynchronize(c->stream);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (rc) return rc;
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "timed attention failed: %s", cudaGetErrorString(e));
+    *ms_out = ms;
+    return ATLASX_OK;
+}

@@ -233,6 +233,14 @@ int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
 /* residual stream after the last forward (d_model floats), for layer-level parity checks */
 int atlasx_model_hidden(atlasx_model* m, float* hidden_host);
 
+/* ── measurement helpers: `iters` launches back to back between two CUDA events on the context
+ *    stream; elapsed device time in milliseconds.  GEMV launches rotate over n_mats matrices so
+ *    that the weights come from HBM, not from L2. ─────────────────────────────────────────── */
+int atlasx_time_gemv(atlasx_ctx* ctx, const atlasx_matrix* const* mats, int n_mats, const float* x_dev, int n,
+                     float* y_dev, int iters, float* ms_out);
+int atlasx_time_attention(atlasx_ctx* ctx, const atlasx_kvcache* kv, const float* q_dev, float* out_dev, int n_heads,
+                          const int* pos_host, float scale, int window, int iters, float* ms_out);
+
 /* ── tensor parallel plumbing (no counterpart in the reference, which is single-GPU) ── */
 /* 128-byte NCCL unique id: rank 0 creates it, every rank passes it to atlasx_comm_init */
 int atlasx_comm_unique_id(void* id128_out);
