@@ -110,6 +110,7 @@ SIGNATURES = {
     "atlasx_kvcache_write": (ci, [vp, vp, vp, vp, vp]),
     "atlasx_decode_attention": (ci, [vp, vp, vp, vp, ci, vp, cf, ci]),
     "atlasx_decode_attention_bytes": (sz, [vp, ci, vp, ci]),
+    "atlasx_decode_attention_static": (ci, [vp, ci, vp, vp, ci, ci, ci, ci, vp, vp, ci, vp, cf, ci]),
     "atlasx_model_create": (ci, [vp, C.POINTER(ModelConfigC), vp, pvp]),
     "atlasx_model_free": (ci, [vp]),
     "atlasx_model_set_tensor": (ci, [vp, ci, ci, vp, ci, ci]),

@@ -427,3 +427,101 @@ int ax_qk_prep_launch(atlasx_ctx* ctx, const AxQkPrepArgs& a, bool pdl) {
     AX_CUDA(cudaLaunchKernelEx(&cfg, ax_qk_prep_kernel, a));
     return ATLASX_OK;
 }
+
+// ── decode attention for callers that must not allocate ──────────────────────────
+// Some hosts of this library may not call cudaMalloc once they are serving: a process whose
+// memory pool was handed out in full at start-up, a latency-critical loop where an allocation
+// would synchronise the device, a plugin running inside someone else's allocator.  For them
+// the split-K scratch (partial results, tickets, positions) lives in this fixed array instead
+// of context memory.  Every GPU that loads the library holds these 4.5 MiB until exit.
+namespace {
+constexpr size_t kStaticPartialFloats = 1u << 20;          // 4 MiB of split partials
+constexpr int kStaticTickets = 4096;                       // ≥ batch × n_heads
+constexpr int kStaticPos = 4096;                           // ≥ batch
+constexpr size_t kStaticTicketOff = kStaticPartialFloats * sizeof(float);
+constexpr size_t kStaticPosOff = kStaticTicketOff + kStaticTickets * sizeof(unsigned);
+constexpr size_t kStaticBytes = kStaticPosOff + kStaticPos * sizeof(int);
+}
+static __device__ __align__(256) unsigned char g_attn_static_scratch[kStaticBytes];
+
+namespace {
+struct StaticSetup { unsigned char* base = nullptr; int sm_count = 0; };
+StaticSetup g_static_setup[64];
+
+// In host code the array's name is only a handle: the device address has to be asked for,
+// once per device, with that device current.
+int static_scratch_for_current_device(StaticSetup** out) {
+    int dev = -1;
+    AX_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return atlasx_fail(ATLASX_ERR_ARG, "device index %d not supported", dev);
+    StaticSetup& s = g_static_setup[dev];
+    if (!s.base) {
+        void* p = nullptr;
+        AX_CUDA(cudaGetSymbolAddress(&p, g_attn_static_scratch));
+        int sms = 0;
+        AX_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+        s.sm_count = sms;
+        s.base = (unsigned char*)p;
+    }
+    *out = &s;
+    return ATLASX_OK;
+}
+}  // namespace
+
+extern "C" int atlasx_decode_attention_static(void* stream, int kv_dtype, const void* k_dev, const void* v_dev,
+                                              int max_seq, int n_kv_heads, int head_dim, int batch,
+                                              const float* q_dev, float* out_dev, int n_heads,
+                                              const int* pos_host, float scale, int window) {
+    AX_ARG(k_dev && v_dev && q_dev && out_dev && pos_host, "null pointer");
+    AX_ARG(kv_dtype == ATLASX_BF16 || kv_dtype == ATLASX_F32, "kv dtype must be bf16 or f32");
+    AX_ARG(max_seq > 0 && n_kv_heads > 0 && batch > 0 && n_heads > 0 && n_heads % n_kv_heads == 0, "bad head or batch counts");
+    AX_ARG(head_dim > 0 && head_dim <= 256, "head_dim must be in 1..256");
+    AX_ARG(window >= 0, "window must be non-negative");
+    if (batch > kStaticPos)
+        return atlasx_fail(ATLASX_ERR_ARG, "batch %d exceeds the fixed scratch (max %d sequences)", batch, kStaticPos);
+    if ((long long)batch * n_heads > kStaticTickets)
+        return atlasx_fail(ATLASX_ERR_ARG, "batch × n_heads = %lld exceeds the fixed scratch (max %d)",
+                           (long long)batch * n_heads, kStaticTickets);
+    int max_rows = 1;
+    for (int b = 0; b < batch; b++) {
+        if (pos_host[b] < 0 || pos_host[b] >= max_seq)
+            return atlasx_fail(ATLASX_ERR_ARG, "pos[%d] = %d is outside the cache (max_seq %d)", b, pos_host[b], max_seq);
+        int r = pos_host[b] + 1;
+        if (window > 0 && r > window) r = window;
+        if (r > max_rows) max_rows = r;
+    }
+    StaticSetup* ss = nullptr;
+    int rc = static_scratch_for_current_device(&ss);
+    if (rc) return rc;
+    cudaStream_t s = (cudaStream_t)stream;
+    float* partials = (float*)ss->base;
+    unsigned* tickets = (unsigned*)(ss->base + kStaticTicketOff);
+    int* pos_dev = (int*)(ss->base + kStaticPosOff);
+    // tickets must start at zero whatever an earlier, possibly failed, call left behind
+    AX_CUDA(cudaMemsetAsync(tickets, 0, (size_t)batch * n_heads * sizeof(unsigned), s));
+    AX_CUDA(cudaMemcpyAsync(pos_dev, pos_host, (size_t)batch * sizeof(int), cudaMemcpyHostToDevice, s));
+
+    atlasx_ctx tmp;                       // carries the stream and SM count only; owns nothing
+    tmp.stream = s; tmp.sm_count = ss->sm_count;
+    AxAttnArgs a;
+    a.q = q_dev; a.kc = k_dev; a.vc = v_dev; a.out = out_dev;
+    a.seq_stride = (size_t)max_seq * n_kv_heads * head_dim;
+    a.pos = pos_dev; a.batch = batch; a.n_heads = n_heads; a.n_kv = n_kv_heads; a.hd = head_dim;
+    a.window = window; a.kv_dtype = kv_dtype; a.scale = scale;
+    a.n_splits = ax_attn_pick_splits(&tmp, n_kv_heads, batch, max_rows);
+    while (a.n_splits > 1 && (size_t)batch * n_heads * a.n_splits * (head_dim + 2) > kStaticPartialFloats) a.n_splits--;
+
+    const bool fast = (head_dim == 64 || head_dim == 128) &&
+                      (((uintptr_t)q_dev | (uintptr_t)k_dev | (uintptr_t)v_dev) & 15) == 0 &&
+                      (a.seq_stride * (kv_dtype == ATLASX_BF16 ? 2 : 4)) % 16 == 0;
+    if (!fast) {                          // the generic kernel needs no scratch at all
+        ax_attn_generic_kernel<<<dim3((unsigned)n_heads, (unsigned)batch), 128, 0, s>>>(a);
+        AX_CHECK_LAUNCH("ax_attn_generic_kernel");
+        return ATLASX_OK;
+    }
+    AttnDev dv;
+    dv.a = a; dv.g_real = n_heads / n_kv_heads; dv.chunks = 1;
+    dv.partials = partials; dv.tickets = tickets;
+    if (kv_dtype == ATLASX_BF16) return head_dim == 128 ? dispatch_g<true, 128>(&tmp, dv, false) : dispatch_g<true, 64>(&tmp, dv, false);
+    return head_dim == 128 ? dispatch_g<false, 128>(&tmp, dv, false) : dispatch_g<false, 64>(&tmp, dv, false);
+}

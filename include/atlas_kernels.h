@@ -176,6 +176,20 @@ int atlasx_decode_attention(atlasx_ctx* ctx, const atlasx_kvcache* kv, const flo
                             int n_heads, const int* pos_host, float scale, int window);
 /* algorithmic HBM bytes of one such call (K and V rows read + q + out) */
 size_t atlasx_decode_attention_bytes(const atlasx_kvcache* kv, int n_heads, const int* pos_host, int window);
+/* Same attention for callers that must not allocate (no counterpart in the reference, whose
+ * wrappers never allocate but also never split the sequence).  It takes no context and no cache
+ * object: the caller passes its own stream (cudaStream_t, may be 0) and raw cache pointers
+ * laid out [batch][max_seq × n_kv × hd].  Split partials, tickets and the device copy of pos
+ * live in a fixed 4.5 MiB device array inside the library, so no cudaMalloc / cudaFree (or
+ * any allocating routine) runs.  Limits, rejected with ATLASX_ERR_ARG: batch ≤ 4096 and
+ * batch × n_heads ≤ 4096; the split count is lowered to fit 1 Mi floats of partials.
+ * The first call on a device looks up the array's device address (make that call before any
+ * stream capture).  All calls share the array: two calls whose kernels overlap on the GPU
+ * (different streams, or different host threads) race; serialise them on one stream. */
+int atlasx_decode_attention_static(void* stream, int kv_dtype, const void* k_dev, const void* v_dev,
+                                   int max_seq, int n_kv_heads, int head_dim, int batch,
+                                   const float* q_dev, float* out_dev, int n_heads,
+                                   const int* pos_host, float scale, int window);
 
 /* ── OlmoModel (crates/atlas-model/src/lib.rs:1298-1732) ───────────────────────── */
 typedef struct {
