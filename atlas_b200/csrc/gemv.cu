@@ -17,6 +17,7 @@
 //   * epilogue: plain store (int8: × row scale) or SwiGLU on interleaved gate/up rows.
 // Every wait on an mbarrier is bounded; on expiry the CTA records an error word and leaves.
 #include "gemv.cuh"
+#include <stdlib.h>
 
 namespace {
 
@@ -49,6 +50,7 @@ struct GemvArgs {
     float* y;
     AxPrologue pro;
     int* err;
+    int dbg;                     // experiments only: bit 0 = consumers skip the arithmetic
 };
 
 // ── PTX wrappers ────────────────────────────────────────────────────────────────
@@ -93,28 +95,36 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ── per-format fragment dot: 16 bytes of one weight row against EPC input values ──
-template <int FMT> __device__ __forceinline__ void dot_chunk(const uint4& w, const float4* xv, float& acc);
+// Four independent accumulators per row: with two rows per warp that is eight FMA chains in
+// flight, enough to cover the FMA latency with only two or three warps per scheduler.
+struct Acc4 {
+    float a, b, c, d;
+    __device__ __forceinline__ float sum() const { return (a + b) + (c + d); }
+};
+__device__ __forceinline__ Acc4 acc4_zero() { Acc4 z; z.a = z.b = z.c = z.d = 0.f; return z; }
 
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_F32>(const uint4& w, const float4* xv, float& acc) {
-    acc = fmaf(__uint_as_float(w.x), xv[0].x, acc); acc = fmaf(__uint_as_float(w.y), xv[0].y, acc);
-    acc = fmaf(__uint_as_float(w.z), xv[0].z, acc); acc = fmaf(__uint_as_float(w.w), xv[0].w, acc);
+template <int FMT> __device__ __forceinline__ void dot_chunk(const uint4& w, const float4* xv, Acc4& acc);
+
+template <> __device__ __forceinline__ void dot_chunk<ATLASX_F32>(const uint4& w, const float4* xv, Acc4& acc) {
+    acc.a = fmaf(__uint_as_float(w.x), xv[0].x, acc.a); acc.b = fmaf(__uint_as_float(w.y), xv[0].y, acc.b);
+    acc.c = fmaf(__uint_as_float(w.z), xv[0].z, acc.c); acc.d = fmaf(__uint_as_float(w.w), xv[0].w, acc.d);
 }
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_BF16>(const uint4& w, const float4* xv, float& acc) {
-    acc = fmaf(ax_bf16_lo(w.x), xv[0].x, acc); acc = fmaf(ax_bf16_hi(w.x), xv[0].y, acc);
-    acc = fmaf(ax_bf16_lo(w.y), xv[0].z, acc); acc = fmaf(ax_bf16_hi(w.y), xv[0].w, acc);
-    acc = fmaf(ax_bf16_lo(w.z), xv[1].x, acc); acc = fmaf(ax_bf16_hi(w.z), xv[1].y, acc);
-    acc = fmaf(ax_bf16_lo(w.w), xv[1].z, acc); acc = fmaf(ax_bf16_hi(w.w), xv[1].w, acc);
+template <> __device__ __forceinline__ void dot_chunk<ATLASX_BF16>(const uint4& w, const float4* xv, Acc4& acc) {
+    acc.a = fmaf(ax_bf16_lo(w.x), xv[0].x, acc.a); acc.b = fmaf(ax_bf16_hi(w.x), xv[0].y, acc.b);
+    acc.c = fmaf(ax_bf16_lo(w.y), xv[0].z, acc.c); acc.d = fmaf(ax_bf16_hi(w.y), xv[0].w, acc.d);
+    acc.a = fmaf(ax_bf16_lo(w.z), xv[1].x, acc.a); acc.b = fmaf(ax_bf16_hi(w.z), xv[1].y, acc.b);
+    acc.c = fmaf(ax_bf16_lo(w.w), xv[1].z, acc.c); acc.d = fmaf(ax_bf16_hi(w.w), xv[1].w, acc.d);
 }
 // int8 → f32 without the conversion unit: flip the sign bit, drop the byte into the mantissa
 // of 2^23 with one byte-permute, subtract 2^23+128 (exact).
-__device__ __forceinline__ void dot_i8_word(uint32_t word, const float4& x, float& acc) {
+__device__ __forceinline__ void dot_i8_word(uint32_t word, const float4& x, Acc4& acc) {
     const uint32_t u = word ^ 0x80808080u;
-    acc = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.0f, x.x, acc);
-    acc = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.0f, x.y, acc);
-    acc = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.0f, x.z, acc);
-    acc = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f, x.w, acc);
+    acc.a = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.0f, x.x, acc.a);
+    acc.b = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.0f, x.y, acc.b);
+    acc.c = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.0f, x.z, acc.c);
+    acc.d = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f, x.w, acc.d);
 }
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT8>(const uint4& w, const float4* xv, float& acc) {
+template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT8>(const uint4& w, const float4* xv, Acc4& acc) {
     dot_i8_word(w.x, xv[0], acc); dot_i8_word(w.y, xv[1], acc);
     dot_i8_word(w.z, xv[2], acc); dot_i8_word(w.w, xv[3], acc);
 }
@@ -123,14 +133,14 @@ template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT8>(const uint4& 
 __device__ __forceinline__ float i4_val(uint32_t u, int sh) {
     return __uint_as_float(((u >> sh) & 0xFu) | 0x4B000000u) - 8388616.0f;
 }
-__device__ __forceinline__ void dot_i4_word(uint32_t word, const float4& xa, const float4& xb, float& acc) {
+__device__ __forceinline__ void dot_i4_word(uint32_t word, const float4& xa, const float4& xb, Acc4& acc) {
     const uint32_t u = word ^ 0x88888888u;
-    acc = fmaf(i4_val(u, 4),  xa.x, acc); acc = fmaf(i4_val(u, 0),  xa.y, acc);
-    acc = fmaf(i4_val(u, 12), xa.z, acc); acc = fmaf(i4_val(u, 8),  xa.w, acc);
-    acc = fmaf(i4_val(u, 20), xb.x, acc); acc = fmaf(i4_val(u, 16), xb.y, acc);
-    acc = fmaf(i4_val(u, 28), xb.z, acc); acc = fmaf(i4_val(u, 24), xb.w, acc);
+    acc.a = fmaf(i4_val(u, 4),  xa.x, acc.a); acc.b = fmaf(i4_val(u, 0),  xa.y, acc.b);
+    acc.c = fmaf(i4_val(u, 12), xa.z, acc.c); acc.d = fmaf(i4_val(u, 8),  xa.w, acc.d);
+    acc.a = fmaf(i4_val(u, 20), xb.x, acc.a); acc.b = fmaf(i4_val(u, 16), xb.y, acc.b);
+    acc.c = fmaf(i4_val(u, 28), xb.z, acc.c); acc.d = fmaf(i4_val(u, 24), xb.w, acc.d);
 }
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT4>(const uint4& w, const float4* xv, float& acc) {
+template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT4>(const uint4& w, const float4* xv, Acc4& acc) {
     dot_i4_word(w.x, xv[0], xv[1], acc); dot_i4_word(w.y, xv[2], xv[3], acc);
     dot_i4_word(w.z, xv[4], xv[5], acc); dot_i4_word(w.w, xv[6], xv[7], acc);
 }
@@ -261,6 +271,78 @@ __device__ __forceinline__ void cta_rows(int M, int& lo, int& hi) {
     hi = (int)(units * (blockIdx.x + 1) / gridDim.x) * unit;
 }
 
+// Direct path (no shared-memory ring): every warp streams its two rows with 128-bit loads, four
+// chunks per row per batch, software-pipelined — the loads of batch i+1 are issued before the
+// arithmetic of batch i, and batch 0 is issued before griddepcontrol.wait, i.e. while the previous
+// kernel of the stream is still draining (weights never depend on it).
+template <int FMT>
+__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float* red, int lo, int hi) {
+    constexpr int EPC = Fmt<FMT>::EPC;
+    constexpr int P = EPC / 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nch = a.nchunks;
+    const int nbatch = (nch + 127) >> 7;
+    const int ntiles = (hi - lo + kTileRows - 1) / kTileRows;
+    const int total = ntiles * nbatch;
+    uint4 wa[4], wb[4];
+    auto load = [&](int i, uint4* A, uint4* B) {
+        const int t = i / nbatch, b = i - t * nbatch;
+        const int row0 = lo + t * kTileRows + warp * kRW;
+        if (row0 < hi) {
+            const uint8_t* w0p = a.W + (size_t)row0 * a.row_bytes;
+            const uint8_t* w1p = w0p + (row0 + 1 < hi ? a.row_bytes : 0);
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c = b * 128 + u * 32 + lane;
+                if (c < nch) { A[u] = ax_ldg_stream(w0p + (size_t)c * 16); B[u] = ax_ldg_stream(w1p + (size_t)c * 16); }
+            }
+        }
+    };
+    if (total > 0) load(0, wa, wb);
+    griddep_wait();                       // activations of the previous kernel are complete
+    griddep_launch();
+    stage_input<FMT>(a, xs, red);
+
+    Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
+    float sc0 = 0.f, sc1 = 0.f;
+    for (int i = 0; i < total; i++) {
+        uint4 na[4], nb[4];
+        if (i + 1 < total) load(i + 1, na, nb);
+        const int t = i / nbatch, b = i - t * nbatch;
+        const int row0 = lo + t * kTileRows + warp * kRW;
+        const bool v0 = row0 < hi, v1 = row0 + 1 < hi;
+        if (v0) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int c = b * 128 + u * 32 + lane;
+                if (c < nch) {
+                    float4 xv[P];
+#pragma unroll
+                    for (int p = 0; p < P; p++) xv[p] = xs[p * nch + c];
+                    if (FMT == ATLASX_INT4) {
+                        const size_t e0 = (size_t)row0 * a.K + (size_t)c * EPC;     // flat element index
+                        Acc4 part = acc4_zero(); dot_chunk<FMT>(wa[u], xv, part);
+                        sc0 = fmaf(part.sum(), load_scale_i4(a.scales, (int)(e0 / a.block), a.scales_f16), sc0);
+                        if (v1) {
+                            part = acc4_zero(); dot_chunk<FMT>(wb[u], xv, part);
+                            sc1 = fmaf(part.sum(), load_scale_i4(a.scales, (int)((e0 + a.K) / a.block), a.scales_f16), sc1);
+                        }
+                    } else {
+                        dot_chunk<FMT>(wa[u], xv, acc0);
+                        if (v1) dot_chunk<FMT>(wb[u], xv, acc1);
+                    }
+                }
+            }
+        }
+        if (b == nbatch - 1) {
+            store_rows<FMT>(a, row0, v0, v1, acc0.sum() + sc0, acc1.sum() + sc1);
+            acc0 = acc4_zero(); acc1 = acc4_zero(); sc0 = 0.f; sc1 = 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; u++) { wa[u] = na[u]; wb[u] = nb[u]; }
+    }
+}
+
 template <int FMT, bool TMA>
 __global__ void __launch_bounds__(TMA ? kThreadsTma : kConsumerThreads)
 ax_gemv_stream_kernel(const GemvArgs a) {
@@ -324,9 +406,10 @@ ax_gemv_stream_kernel(const GemvArgs a) {
         return;
     }
 
+    if (!TMA) { consume_direct<FMT>(a, xs, red, lo, hi); return; }
+
     // ── consumers ──────────────────────────────────────────────────────────────────
     griddep_wait();                       // activations of the previous kernel are complete
-    if (!TMA) griddep_launch();
     stage_input<FMT>(a, xs, red);
 
     int fill = 0;
@@ -335,7 +418,8 @@ ax_gemv_stream_kernel(const GemvArgs a) {
         const int r0 = lo + t * kTileRows;
         const int row0 = r0 + warp * kRW;
         const bool v0 = row0 < hi, v1 = row0 + 1 < hi;
-        float acc0 = 0.f, acc1 = 0.f;
+        Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
+        float sc0 = 0.f, sc1 = 0.f;            // int4: sums already multiplied by their block scales
         if (TMA) {
             for (int kc = 0; kc < nk; kc++, fill++) {
                 const int s = fill % a.stages;
@@ -347,7 +431,7 @@ ax_gemv_stream_kernel(const GemvArgs a) {
 #pragma unroll
                 for (int it = 0; it < kSegChunks / 32; it++) {
                     const int c = it * 32 + lane;
-                    if (c < seg_chunks) {
+                    if (c < seg_chunks && !(a.dbg & 1)) {
                         const int cg = kc * kSegChunks + c;
                         float4 xv[P];
 #pragma unroll
@@ -355,15 +439,15 @@ ax_gemv_stream_kernel(const GemvArgs a) {
                         if (v0) {
                             const uint4 w = *reinterpret_cast<const uint4*>(st + c * 16);
                             if (FMT == ATLASX_INT4) {
-                                float part = 0.f; dot_chunk<FMT>(w, xv, part);
-                                acc0 = fmaf(part, load_scale_i4(st + kSeg, (c * EPC) / a.block, a.scales_f16), acc0);
+                                Acc4 part = acc4_zero(); dot_chunk<FMT>(w, xv, part);
+                                sc0 = fmaf(part.sum(), load_scale_i4(st + kSeg, (c * EPC) / a.block, a.scales_f16), sc0);
                             } else dot_chunk<FMT>(w, xv, acc0);
                         }
                         if (v1) {
                             const uint4 w = *reinterpret_cast<const uint4*>(st + a.seg_pitch + c * 16);
                             if (FMT == ATLASX_INT4) {
-                                float part = 0.f; dot_chunk<FMT>(w, xv, part);
-                                acc1 = fmaf(part, load_scale_i4(st + a.seg_pitch + kSeg, (c * EPC) / a.block, a.scales_f16), acc1);
+                                Acc4 part = acc4_zero(); dot_chunk<FMT>(w, xv, part);
+                                sc1 = fmaf(part.sum(), load_scale_i4(st + a.seg_pitch + kSeg, (c * EPC) / a.block, a.scales_f16), sc1);
                             } else dot_chunk<FMT>(w, xv, acc1);
                         }
                     }
@@ -372,42 +456,8 @@ ax_gemv_stream_kernel(const GemvArgs a) {
                 if (lane == 0) mbar_arrive(&empty[s]);
             }
             if (!ok) break;
-        } else if (v0) {
-            // plain path: 128-bit streaming loads, four chunks per row in flight per lane
-            const uint8_t* w0p = a.W + (size_t)row0 * a.row_bytes;
-            const uint8_t* w1p = w0p + (v1 ? a.row_bytes : 0);
-            const int nch = a.nchunks;
-            for (int c0 = lane; c0 < nch; c0 += 128) {
-                uint4 wa[4], wb[4];
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int c = c0 + u * 32;
-                    if (c < nch) { wa[u] = ax_ldg_stream(w0p + (size_t)c * 16); wb[u] = ax_ldg_stream(w1p + (size_t)c * 16); }
-                }
-#pragma unroll
-                for (int u = 0; u < 4; u++) {
-                    const int c = c0 + u * 32;
-                    if (c < nch) {
-                        float4 xv[P];
-#pragma unroll
-                        for (int p = 0; p < P; p++) xv[p] = xs[p * nch + c];
-                        if (FMT == ATLASX_INT4) {
-                            const size_t e0 = (size_t)row0 * a.K + (size_t)c * EPC;     // flat element index
-                            float part = 0.f; dot_chunk<FMT>(wa[u], xv, part);
-                            acc0 = fmaf(part, load_scale_i4(a.scales, (int)(e0 / a.block), a.scales_f16), acc0);
-                            if (v1) {
-                                part = 0.f; dot_chunk<FMT>(wb[u], xv, part);
-                                acc1 = fmaf(part, load_scale_i4(a.scales, (int)((e0 + a.K) / a.block), a.scales_f16), acc1);
-                            }
-                        } else {
-                            dot_chunk<FMT>(wa[u], xv, acc0);
-                            if (v1) dot_chunk<FMT>(wb[u], xv, acc1);
-                        }
-                    }
-                }
-            }
         }
-        store_rows<FMT>(a, row0, v0, v1, acc0, acc1);
+        store_rows<FMT>(a, row0, v0, v1, acc0.sum() + sc0, acc1.sum() + sc1);
     }
 }
 
@@ -519,6 +569,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     a.srow_bytes = w.dtype == ATLASX_INT4 ? (w.cols / w.block) * (w.scales_f16 ? 2 : 4) : 0;
     a.nchunks = a.row_bytes / 16;
     a.epi = epi; a.y = y; a.pro = pro; a.err = ctx->dev_error;
+    { const char* e = getenv("ATLASX_GEMV_DEBUG"); a.dbg = e ? atoi(e) : 0; }
 
     const size_t x_bytes = (((size_t)w.cols * 4 + 127) / 128) * 128;
     const size_t smem_max = ctx->smem_optin ? ctx->smem_optin : 232448;

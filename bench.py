@@ -218,6 +218,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt", type=int, default=2048, help="context length reached before the timed steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -240,6 +241,7 @@ def main():
         torch.cuda.set_device(local_rank)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     ctx = ab.Context(local_rank)
+    ctx.set_gemv_impl(args.gemv_impl)
     if world > 1:
         import ctypes as C
         import torch
