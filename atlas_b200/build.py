@@ -31,13 +31,14 @@ def build(force=False, verbose=False):
     headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     headers.append(os.path.join(HERE, "..", "include", "atlas_kernels.h"))
     nvcc = os.environ.get("NVCC", "nvcc")
+    extra = os.environ.get("AX_EXTRA_NVCC_FLAGS", "").split()
     objs, jobs = [], []
     for src in SOURCES:
         s = os.path.join(CSRC, src)
         o = os.path.join(OUT, src.replace(".cu", ".o"))
         objs.append(o)
         if force or _stale(o, [s] + headers):
-            jobs.append((src, [nvcc] + NVCC_FLAGS + ["-c", s, "-o", o]))
+            jobs.append((src, [nvcc] + NVCC_FLAGS + extra + ["-c", s, "-o", o]))
 
     def run(job):
         name, cmd = job

@@ -1,5 +1,6 @@
 // ctx.cu — context, device buffers, GpuMatrix / GpuKvCache objects and the op-level atlasx_* ABI.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 #include <math.h>
 #include <vector>
@@ -308,7 +309,8 @@ extern "C" size_t atlasx_matrix_bytes(const atlasx_matrix* m) { return m ? ax_we
 extern "C" int atlasx_gemv(atlasx_ctx* c, const atlasx_matrix* m, const float* x, int n, float* y) {
     AX_ARG(c && m && x && y, "null argument");
     AxPrologue pro; pro.base = x;
-    return ax_gemv_launch(c, m->w, pro, AX_EPI_PLAIN, n, y, false);
+    static const bool pdl = getenv("ATLASX_GEMV_PDL") && atoi(getenv("ATLASX_GEMV_PDL"));   // experiments
+    return ax_gemv_launch(c, m->w, pro, AX_EPI_PLAIN, n, y, pdl);
 }
 extern "C" int atlasx_matrix_sgemm(atlasx_ctx* c, const atlasx_matrix* m, const float* rhs, int k, int n, float* out) {
     AX_ARG(c && m && rhs && out, "null argument");

@@ -19,231 +19,9 @@
 #include "gemv.cuh"
 #include <stdlib.h>
 
+#include "gemv_device.cuh"
+
 namespace {
-
-constexpr int kConsumerWarps = 8;
-constexpr int kRW = 2;                                   // rows per consumer warp
-constexpr int kTileRows = kConsumerWarps * kRW;          // 16
-constexpr int kSeg = 2048;                               // weight bytes per row per stage
-constexpr int kSegChunks = kSeg / 16;                    // 128 sixteen-byte chunks
-constexpr int kScaleSegMax = 512;                        // int4 scale bytes per row per stage (f32, block 32)
-constexpr int kMaxStages = 6;
-constexpr int kConsumerThreads = kConsumerWarps * 32;    // 256
-constexpr int kThreadsTma = kConsumerThreads + 32;       // + producer warp
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;   // 2 s
-
-template <int FMT> struct Fmt;
-template <> struct Fmt<ATLASX_F32>  { static constexpr int EPC = 4;  };   // elements per 16-byte chunk
-template <> struct Fmt<ATLASX_BF16> { static constexpr int EPC = 8;  };
-template <> struct Fmt<ATLASX_INT8> { static constexpr int EPC = 16; };
-template <> struct Fmt<ATLASX_INT4> { static constexpr int EPC = 32; };
-
-struct GemvArgs {
-    const uint8_t* W; const uint8_t* scales;
-    int M, K;                    // rows, cols (elements)
-    int row_bytes;               // bytes of one weight row
-    int srow_bytes;              // bytes of one row of int4 scales (0 otherwise)
-    int block; int scales_f16;
-    int stages; int stage_stride; int seg_pitch;   // ring geometry (TMA)
-    int nchunks;                 // 16-byte chunks per row
-    int epi;
-    float* y;
-    AxPrologue pro;
-    int* err;
-    int dbg;                     // experiments only: bit 0 = consumers skip the arithmetic
-};
-
-// ── PTX wrappers ────────────────────────────────────────────────────────────────
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, 1000;\n\t"   // ≤ ~1 µs per try
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
-}
-// Bounded wait: false (and the error word set) when the phase has not completed in 2 s.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    unsigned long long t0 = globaltimer_ns();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; i++) if (mbar_try_wait(bar, parity)) return true;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) { atomicExch(err, code); return false; }
-    }
-}
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-__device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
-
-// ── per-format fragment dot: 16 bytes of one weight row against EPC input values ──
-// Four independent accumulators per row: with two rows per warp that is eight FMA chains in
-// flight, enough to cover the FMA latency with only two or three warps per scheduler.
-struct Acc4 {
-    float a, b, c, d;
-    __device__ __forceinline__ float sum() const { return (a + b) + (c + d); }
-};
-__device__ __forceinline__ Acc4 acc4_zero() { Acc4 z; z.a = z.b = z.c = z.d = 0.f; return z; }
-
-template <int FMT> __device__ __forceinline__ void dot_chunk(const uint4& w, const float4* xv, Acc4& acc);
-
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_F32>(const uint4& w, const float4* xv, Acc4& acc) {
-    acc.a = fmaf(__uint_as_float(w.x), xv[0].x, acc.a); acc.b = fmaf(__uint_as_float(w.y), xv[0].y, acc.b);
-    acc.c = fmaf(__uint_as_float(w.z), xv[0].z, acc.c); acc.d = fmaf(__uint_as_float(w.w), xv[0].w, acc.d);
-}
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_BF16>(const uint4& w, const float4* xv, Acc4& acc) {
-    acc.a = fmaf(ax_bf16_lo(w.x), xv[0].x, acc.a); acc.b = fmaf(ax_bf16_hi(w.x), xv[0].y, acc.b);
-    acc.c = fmaf(ax_bf16_lo(w.y), xv[0].z, acc.c); acc.d = fmaf(ax_bf16_hi(w.y), xv[0].w, acc.d);
-    acc.a = fmaf(ax_bf16_lo(w.z), xv[1].x, acc.a); acc.b = fmaf(ax_bf16_hi(w.z), xv[1].y, acc.b);
-    acc.c = fmaf(ax_bf16_lo(w.w), xv[1].z, acc.c); acc.d = fmaf(ax_bf16_hi(w.w), xv[1].w, acc.d);
-}
-// int8 → f32 without the conversion unit: flip the sign bit, drop the byte into the mantissa
-// of 2^23 with one byte-permute, subtract 2^23+128 (exact).
-__device__ __forceinline__ void dot_i8_word(uint32_t word, const float4& x, Acc4& acc) {
-    const uint32_t u = word ^ 0x80808080u;
-    acc.a = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7540)) - 8388736.0f, x.x, acc.a);
-    acc.b = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7541)) - 8388736.0f, x.y, acc.b);
-    acc.c = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7542)) - 8388736.0f, x.z, acc.c);
-    acc.d = fmaf(__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7543)) - 8388736.0f, x.w, acc.d);
-}
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT8>(const uint4& w, const float4* xv, Acc4& acc) {
-    dot_i8_word(w.x, xv[0], acc); dot_i8_word(w.y, xv[1], acc);
-    dot_i8_word(w.z, xv[2], acc); dot_i8_word(w.w, xv[3], acc);
-}
-// int4: byte b of a word holds element 2b in its high nibble and 2b+1 in its low nibble
-// (atlas-quant/src/lib.rs:137-141).  n ^ 8 = q + 8 goes into the mantissa of 2^23.
-__device__ __forceinline__ float i4_val(uint32_t u, int sh) {
-    return __uint_as_float(((u >> sh) & 0xFu) | 0x4B000000u) - 8388616.0f;
-}
-__device__ __forceinline__ void dot_i4_word(uint32_t word, const float4& xa, const float4& xb, Acc4& acc) {
-    const uint32_t u = word ^ 0x88888888u;
-    acc.a = fmaf(i4_val(u, 4),  xa.x, acc.a); acc.b = fmaf(i4_val(u, 0),  xa.y, acc.b);
-    acc.c = fmaf(i4_val(u, 12), xa.z, acc.c); acc.d = fmaf(i4_val(u, 8),  xa.w, acc.d);
-    acc.a = fmaf(i4_val(u, 20), xb.x, acc.a); acc.b = fmaf(i4_val(u, 16), xb.y, acc.b);
-    acc.c = fmaf(i4_val(u, 28), xb.z, acc.c); acc.d = fmaf(i4_val(u, 24), xb.w, acc.d);
-}
-template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT4>(const uint4& w, const float4* xv, Acc4& acc) {
-    dot_i4_word(w.x, xv[0], xv[1], acc); dot_i4_word(w.y, xv[2], xv[3], acc);
-    dot_i4_word(w.z, xv[4], xv[5], acc); dot_i4_word(w.w, xv[6], xv[7], acc);
-}
-
-// ── block reduction over the 256 consumer threads ────────────────────────────────
-__device__ __forceinline__ float consumer_block_sum(float v, float* red /*[8] + 1*/) {
-    v = ax_warp_sum(v);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    consumer_sync();                       // protect `red` from the previous use
-    if (lane == 0) red[warp] = v;
-    consumer_sync();
-    float t = 0.f;
-#pragma unroll
-    for (int w = 0; w < kConsumerWarps; w++) t += red[w];
-    return t;
-}
-
-// Input staging.  The vector lives in shared memory as P = EPC/4 planes of float4 so that a
-// warp reading one plane for 32 consecutive chunks is conflict-free: element e → plane
-// (e % EPC)/4, slot e / EPC.
-template <int FMT>
-__device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float* red) {
-    constexpr int EPC = Fmt<FMT>::EPC;
-    const AxPrologue& p = a.pro;
-    const int K = a.K, n4 = K >> 2, nch = a.nchunks;
-    const int tid = threadIdx.x;
-    auto slot = [&](int k4) { const int e = k4 << 2; return ((e % EPC) >> 2) * nch + e / EPC; };
-
-    const float* base = p.base;
-    const uint16_t* base16 = nullptr;
-    if (p.embed) {
-        int pos = *p.pos;
-        long long tok = p.seq[pos];
-        if (tok < 0) tok = 0;
-        if (tok > p.vocab - 1) tok = p.vocab - 1;
-        if (p.embed_bf16) base16 = (const uint16_t*)p.embed + (size_t)tok * K;
-        else              base = (const float*)p.embed + (size_t)tok * K;
-    }
-    auto load_base = [&](int k4) -> float4 {
-        if (base16) {
-            const uint2 r = *reinterpret_cast<const uint2*>(base16 + (k4 << 2));
-            return make_float4(ax_bf16_lo(r.x), ax_bf16_hi(r.x), ax_bf16_lo(r.y), ax_bf16_hi(r.y));
-        }
-        return *reinterpret_cast<const float4*>(base + (k4 << 2));
-    };
-
-    if (!p.y && !p.wx) {                                       // plain input
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
-            const float4 v = load_base(k4);
-            xs[slot(k4)] = v;
-            if (p.resid_out && blockIdx.x == 0) reinterpret_cast<float4*>(p.resid_out)[k4] = v;
-        }
-        consumer_sync();
-        return;
-    }
-    float inv_y = 1.f;
-    if (p.y) {
-        float ss = 0.f;
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
-            float4 t = reinterpret_cast<const float4*>(p.y)[k4];
-            for (int r = 1; r < p.nparts; r++) {
-                const float4 u = reinterpret_cast<const float4*>(p.y + (size_t)r * p.part_stride)[k4];
-                t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
-            }
-            xs[slot(k4)] = t;
-            ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
-        }
-        if (p.wy) {
-            ss = consumer_block_sum(ss, red);
-            inv_y = 1.0f / sqrtf(ss / (float)K + p.eps);
-        }
-    }
-    float ss2 = 0.f;
-    for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
-        float4 v = load_base(k4);
-        if (p.y) {
-            float4 t = xs[slot(k4)];
-            if (p.wy) {
-                const float4 w = reinterpret_cast<const float4*>(p.wy)[k4];
-                t.x = t.x * inv_y * w.x; t.y = t.y * inv_y * w.y; t.z = t.z * inv_y * w.z; t.w = t.w * inv_y * w.w;
-            }
-            v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
-        }
-        xs[slot(k4)] = v;
-        if (p.resid_out && blockIdx.x == 0) reinterpret_cast<float4*>(p.resid_out)[k4] = v;
-        ss2 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    }
-    if (p.wx) {
-        ss2 = consumer_block_sum(ss2, red);
-        const float inv_x = 1.0f / sqrtf(ss2 / (float)K + p.eps);
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
-            float4 v = xs[slot(k4)];
-            const float4 w = reinterpret_cast<const float4*>(p.wx)[k4];
-            v.x = v.x * inv_x * w.x; v.y = v.y * inv_x * w.y; v.z = v.z * inv_x * w.z; v.w = v.w * inv_x * w.w;
-            xs[slot(k4)] = v;
-        }
-    }
-    consumer_sync();
-}
-
-__device__ __forceinline__ float load_scale_i4(const void* p, int idx, int f16) {
-    return f16 ? __half2float(reinterpret_cast<const __half*>(p)[idx]) : reinterpret_cast<const float*>(p)[idx];
-}
 
 template <int FMT>
 __device__ __forceinline__ void store_rows(const GemvArgs& a, int row0, bool v0, bool v1, float acc0, float acc1) {
@@ -349,42 +127,44 @@ ax_gemv_stream_kernel(const GemvArgs a) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    // layout: [full[S] | empty[S] | red[16] | pad to 256] [x planes] [ring]
+    // layout: [full[S] | empty[S] | red[16] | pair[16] | pad to 256] [x planes] [ring]
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
     uint64_t* empty = full + kMaxStages;
     float* red = reinterpret_cast<float*>(empty + kMaxStages);
+    float* pair = red + 16;
     float4* xs = reinterpret_cast<float4*>(smem_raw + 256);
     const int x_bytes = ((a.K * 4 + 127) / 128) * 128;
     uint8_t* ring = smem_raw + 256 + x_bytes;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int lo, hi; cta_rows(a.M, lo, hi);
-    const int ntiles = (hi - lo + kTileRows - 1) / kTileRows;
+    if (!TMA) { consume_direct<FMT>(a, xs, red, lo, hi); return; }
+
+    const int ntiles = (hi - lo + kRingRows - 1) / kRingRows;
     const int nk = (a.row_bytes + kSeg - 1) / kSeg;
-
-    if (TMA) {
-        if (tid == 0) {
-            for (int s = 0; s < a.stages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], kConsumerWarps); }
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        }
-        __syncthreads();
+    const int sseg_full = a.seg_pitch - kSeg;                // int4 scale bytes of a full segment
+    if (tid == 0) {
+        for (int s = 0; s < a.stages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], kConsumerWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
+    __syncthreads();
 
-    if (TMA && warp == kConsumerWarps) {
-        // ── producer warp: weights do not depend on the previous kernel, so start at once ──
-        griddep_launch();
+    if (warp == kConsumerWarps) {
+        // ── producer warp: weights do not depend on the previous kernel, so start at once; the
+        //    kernel is sized so that two CTAs fit on an SM, which lets the NEXT kernel of the
+        //    stream become resident and fill its ring while this one is still computing ──
         int fill = 0;
         bool ok = true;
         for (int t = 0; t < ntiles && ok; t++) {
-            const int r0 = lo + t * kTileRows;
-            const int nrows = min(kTileRows, hi - r0);
+            const int r0 = lo + t * kRingRows;
+            const int nrows = min(kRingRows, hi - r0);
             for (int kc = 0; kc < nk && ok; kc++, fill++) {
                 const int s = fill % a.stages;
                 const uint32_t ph = (uint32_t)(fill / a.stages) & 1u;
                 const int seg = min(kSeg, a.row_bytes - kc * kSeg);
                 int sseg = 0;
-                if (FMT == ATLASX_INT4) sseg = min(a.srow_bytes - kc * (a.seg_pitch - kSeg), a.seg_pitch - kSeg);
+                if (FMT == ATLASX_INT4) sseg = min(a.srow_bytes - kc * sseg_full, sseg_full);
                 if (lane == 0) {
                     ok = mbar_wait(&empty[s], ph ^ 1u, a.err, 1);
                     if (ok) mbar_arrive_expect_tx(&full[s], (uint32_t)(nrows * (seg + sseg)));
@@ -395,8 +175,7 @@ ax_gemv_stream_kernel(const GemvArgs a) {
                     const size_t row = (size_t)(r0 + lane);
                     bulk_g2s(dst, a.W + row * a.row_bytes + (size_t)kc * kSeg, (uint32_t)seg, &full[s]);
                     if (FMT == ATLASX_INT4)
-                        bulk_g2s(dst + kSeg, a.scales + row * a.srow_bytes + (size_t)kc * (a.seg_pitch - kSeg),
-                                 (uint32_t)sseg, &full[s]);
+                        bulk_g2s(dst + kSeg, a.scales + row * a.srow_bytes + (size_t)kc * sseg_full, (uint32_t)sseg, &full[s]);
                 }
             }
         }
@@ -406,58 +185,79 @@ ax_gemv_stream_kernel(const GemvArgs a) {
         return;
     }
 
-    if (!TMA) { consume_direct<FMT>(a, xs, red, lo, hi); return; }
-
-    // ── consumers ──────────────────────────────────────────────────────────────────
+    // ── consumers: one row per warp per tile ───────────────────────────────────────
     griddep_wait();                       // activations of the previous kernel are complete
+    // Only now may the next kernel of the stream start (and fill its ring behind this one):
+    // releasing it earlier lets a whole chain of future kernels pile up on the SMs.
+    griddep_launch();
     stage_input<FMT>(a, xs, red);
 
+    const int nch = a.nchunks;
     int fill = 0;
     bool ok = true;
     for (int t = 0; t < ntiles && ok; t++) {
-        const int r0 = lo + t * kTileRows;
-        const int row0 = r0 + warp * kRW;
-        const bool v0 = row0 < hi, v1 = row0 + 1 < hi;
-        Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
-        float sc0 = 0.f, sc1 = 0.f;            // int4: sums already multiplied by their block scales
-        if (TMA) {
-            for (int kc = 0; kc < nk; kc++, fill++) {
-                const int s = fill % a.stages;
-                const uint32_t ph = (uint32_t)(fill / a.stages) & 1u;
-                ok = mbar_wait(&full[s], ph, a.err, 2);
-                if (!ok) break;
-                const int seg_chunks = min(kSeg, a.row_bytes - kc * kSeg) >> 4;
-                const uint8_t* st = ring + (size_t)s * a.stage_stride + (warp * kRW) * a.seg_pitch;
+        const int row = lo + t * kRingRows + warp;
+        const bool valid = row < hi;
+        Acc4 acc = acc4_zero();
+        float sc = 0.f;                   // int4: sums already multiplied by their block scales
+        for (int kc = 0; kc < nk; kc++, fill++) {
+            const int s = fill % a.stages;
+            const uint32_t ph = (uint32_t)(fill / a.stages) & 1u;
+            ok = mbar_wait(&full[s], ph, a.err, 2);
+            if (!ok) break;
+            const int seg_chunks = min(kSeg, a.row_bytes - kc * kSeg) >> 4;
+            const uint8_t* st = ring + (size_t)s * a.stage_stride + warp * a.seg_pitch;
+            if (valid && !(a.dbg & 1)) {
+                const uint4* wp = reinterpret_cast<const uint4*>(st) + lane;
+                const float4* xb = xs + kc * kSegChunks + lane;
+                if (FMT != ATLASX_INT4 && seg_chunks == kSegChunks) {
+                    // full segment: no predicates, addresses are lane base + constants
 #pragma unroll
-                for (int it = 0; it < kSegChunks / 32; it++) {
-                    const int c = it * 32 + lane;
-                    if (c < seg_chunks && !(a.dbg & 1)) {
-                        const int cg = kc * kSegChunks + c;
+                    for (int it = 0; it < kSegChunks / 32; it++) {
                         float4 xv[P];
 #pragma unroll
-                        for (int p = 0; p < P; p++) xv[p] = xs[p * a.nchunks + cg];
-                        if (v0) {
-                            const uint4 w = *reinterpret_cast<const uint4*>(st + c * 16);
+                        for (int p = 0; p < P; p++) xv[p] = xb[p * nch + it * 32];
+                        const uint4 w = wp[it * 32];
+                        dot_chunk<FMT>(w, xv, acc);
+                    }
+                } else {
+#pragma unroll 2
+                    for (int it = 0; it < kSegChunks / 32; it++) {
+                        const int c = it * 32 + lane;
+                        if (c < seg_chunks) {
+                            float4 xv[P];
+#pragma unroll
+                            for (int p = 0; p < P; p++) xv[p] = xb[p * nch + it * 32];
+                            const uint4 w = wp[it * 32];
                             if (FMT == ATLASX_INT4) {
                                 Acc4 part = acc4_zero(); dot_chunk<FMT>(w, xv, part);
-                                sc0 = fmaf(part.sum(), load_scale_i4(st + kSeg, (c * EPC) / a.block, a.scales_f16), sc0);
-                            } else dot_chunk<FMT>(w, xv, acc0);
-                        }
-                        if (v1) {
-                            const uint4 w = *reinterpret_cast<const uint4*>(st + a.seg_pitch + c * 16);
-                            if (FMT == ATLASX_INT4) {
-                                Acc4 part = acc4_zero(); dot_chunk<FMT>(w, xv, part);
-                                sc1 = fmaf(part.sum(), load_scale_i4(st + a.seg_pitch + kSeg, (c * EPC) / a.block, a.scales_f16), sc1);
-                            } else dot_chunk<FMT>(w, xv, acc1);
+                                sc = fmaf(part.sum(), load_scale_i4(st + kSeg, (c * EPC) / a.block, a.scales_f16), sc);
+                            } else dot_chunk<FMT>(w, xv, acc);
                         }
                     }
                 }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[s]);
             }
-            if (!ok) break;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
         }
-        store_rows<FMT>(a, row0, v0, v1, acc0.sum() + sc0, acc1.sum() + sc1);
+        if (!ok) break;
+        float r = ax_warp_sum(acc.sum() + sc);
+        if (FMT == ATLASX_INT8 && valid) r *= reinterpret_cast<const float*>(a.scales)[row];
+        if (a.epi == AX_EPI_SILU_PAIR) {
+            // gate row (even) and up row (odd) sit in neighbouring warps: exchange through shared
+            // memory under a two-warp named barrier; slots alternate with the tile parity
+            float* slot = pair + (t & 1) * kConsumerWarps;
+            if (lane == 0) slot[warp] = r;
+            switch (warp >> 1) {          // immediate ids keep the CTA at six hardware barriers
+                case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+                default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
+            }
+            if (lane == 0 && valid && !(warp & 1)) a.y[row >> 1] = (r / (1.0f + expf(-r))) * slot[warp + 1];
+        } else if (lane == 0 && valid) {
+            a.y[row] = r;
+        }
     }
 }
 
@@ -581,9 +381,15 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         tma_ok = (sseg % 16 == 0) && (a.srow_bytes % 16 == 0) && sseg <= kScaleSegMax && (((uintptr_t)w.scales & 15) == 0);
     }
     a.seg_pitch = kSeg + sseg;
-    a.stage_stride = kTileRows * a.seg_pitch;
-    long long avail = (long long)smem_max - 256 - (long long)x_bytes;
+    a.stage_stride = kRingRows * a.seg_pitch;
+    // Ring depth: first try to stay within half an SM's shared memory so that two CTAs (this
+    // kernel and the next one of the stream, launched programmatically) are resident together;
+    // if the input vector leaves no room for two stages that way, take the whole SM.
+    const long long half_sm = ((long long)smem_max + 1024) / 2 - 1024 - 512;
+    long long avail = half_sm - 256 - (long long)x_bytes;
     int stages = (int)(avail / a.stage_stride);
+    { const char* e = getenv("ATLASX_GEMV_FULLSM"); if (e && atoi(e)) stages = 0; }
+    if (stages < 2) { avail = (long long)smem_max - 256 - (long long)x_bytes; stages = (int)(avail / a.stage_stride); }
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) tma_ok = false;
     a.stages = stages;

@@ -14,6 +14,7 @@
 // and the whole token (plus lm_head, argmax and position advance) is one CUDA graph whose
 // token id and position live in device memory, so replaying it needs no host data.
 #include <limits.h>
+#include <stdlib.h>
 #include <math.h>
 #include <string.h>
 #include <vector>
@@ -262,6 +263,8 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     cudaStream_t s = c->stream;
     const atlasx_model_config& cf = m->cfg;
     const bool pdl = m->use_pdl && !prof;
+    static const int pdl_mask = getenv("ATLASX_PDL_MASK") ? atoi(getenv("ATLASX_PDL_MASK")) : 255;   // experiments
+    auto P = [&](int cls) { return pdl && ((pdl_mask >> cls) & 1); };
     const int d = cf.d_model, L = cf.n_layers;
     const bool post = cf.post_norm != 0;
     int rc = ATLASX_OK, n_launch = 0, cur = 0;
@@ -282,7 +285,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
             p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
         }
-        STEP_LAUNCH(CLS_QKV, gemv_bytes(ly.qkv), ax_gemv_launch(c, ly.qkv, p, AX_EPI_PLAIN, 1, m->qkv, pdl));
+        STEP_LAUNCH(CLS_QKV, gemv_bytes(ly.qkv), ax_gemv_launch(c, ly.qkv, p, AX_EPI_PLAIN, 1, m->qkv, P(CLS_QKV)));
 
         // ── QK-norm, RoPE, cache write ──────────────────────────────────────────
         AxQkPrepArgs qa;
@@ -292,7 +295,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         qa.batch = 1; qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype;
         qa.eps = 1e-6f;                                    // the reference hard-codes 1e-6 here (:850,853)
         STEP_LAUNCH(CLS_QKPREP, 4.0 * (2 * m->q_rows + 2 * m->kv_rows) + (double)2 * m->kv_rows * (cf.kv_dtype == ATLASX_BF16 ? 2 : 4),
-                    ax_qk_prep_launch(c, qa, pdl));
+                    ax_qk_prep_launch(c, qa, P(CLS_QKPREP)));
 
         // ── attention over the cache ────────────────────────────────────────────
         AxAttnArgs aa;
@@ -306,11 +309,11 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             if (ly.window > 0 && rows > ly.window) rows = ly.window;
             abytes = (double)rows * 2 * m->kv_rows * (cf.kv_dtype == ATLASX_BF16 ? 2 : 4) + 8.0 * m->q_rows;
         }
-        STEP_LAUNCH(CLS_ATTN, abytes, ax_attn_launch(c, aa, pdl));
+        STEP_LAUNCH(CLS_ATTN, abytes, ax_attn_launch(c, aa, P(CLS_ATTN)));
 
         // ── output projection (row-parallel under TP) ───────────────────────────
         AxPrologue po; po.base = m->attn;
-        STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, pdl));
+        STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ)));
         if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->o, (size_t)d));
 
         // ── gate/up with SwiGLU epilogue ────────────────────────────────────────
@@ -319,11 +322,11 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = nparts; pg.part_stride = d;
         if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
         pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
-        STEP_LAUNCH(CLS_GATEUP, gemv_bytes(ly.gateup), ax_gemv_launch(c, ly.gateup, pg, AX_EPI_SILU_PAIR, 1, m->h, pdl));
+        STEP_LAUNCH(CLS_GATEUP, gemv_bytes(ly.gateup), ax_gemv_launch(c, ly.gateup, pg, AX_EPI_SILU_PAIR, 1, m->h, P(CLS_GATEUP)));
 
         // ── down projection (row-parallel under TP) ─────────────────────────────
         AxPrologue pd; pd.base = m->h;
-        STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, pdl));
+        STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN)));
         if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->dn, (size_t)d));
     }
     // ── final norm + lm_head ────────────────────────────────────────────────────
@@ -334,7 +337,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     pl.wx = m->final_norm;
     pl.resid_out = m->resid[cur ^ 1]; cur ^= 1;
     m->final_resid = cur;
-    STEP_LAUNCH(CLS_LMHEAD, gemv_bytes(m->lm_head), ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, pdl));
+    STEP_LAUNCH(CLS_LMHEAD, gemv_bytes(m->lm_head), ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, P(CLS_LMHEAD)));
     if (m->world > 1)
         STEP_LAUNCH(CLS_COMM, 4.0 * m->vocab_loc * m->world, ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc));
 

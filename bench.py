@@ -218,6 +218,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--prompt", type=int, default=2048, help="context length reached before the timed steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
+    ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")
     args = ap.parse_args()
 
@@ -256,6 +258,8 @@ def main():
     steps, warm = args.steps, max(args.warmup, 3)
     max_seq = args.prompt + warm + 2 * steps + 16
     m, mc = build_cuda_model(ab, ctx, max_seq, rank, world)
+    if args.no_pdl or args.no_graph:
+        m.set_options(use_graph=not args.no_graph, use_pdl=not args.no_pdl)
     prompt = np.random.default_rng(0).integers(0, mc.vocab_size, size=args.prompt, dtype=np.uint32)
 
     # context: the prompt goes through the decode path token by token, as the reference does
