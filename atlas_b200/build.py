@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "lib")
-SOURCES = ["ctx.cu", "gemv.cu", "attention.cu", "elementwise.cu", "legacy_abi.cu", "model.cu", "comm.cu"]
+SOURCES = ["ctx.cu", "gemv.cu", "attention.cu", "elementwise.cu", "legacy_abi.cu", "model.cu", "comm.cu", "mega.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 LIB_SO = os.path.join(OUT, "libatlas_kernels.so")
@@ -28,7 +28,7 @@ def _stale(target, deps):
 
 def build(force=False, verbose=False):
     os.makedirs(OUT, exist_ok=True)
-    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h", ".inl"))]
     headers.append(os.path.join(HERE, "..", "include", "atlas_kernels.h"))
     nvcc = os.environ.get("NVCC", "nvcc")
     extra = os.environ.get("AX_EXTRA_NVCC_FLAGS", "").split()

@@ -10,6 +10,7 @@
 // and the last CTA of each head group to finish merges the partial results (ticket counter,
 // nothing ever waits).  The KV cache may be bf16 (half the traffic) or f32 (reference format).
 #include "attention.cuh"
+#include "attention_device.cuh"
 
 #include <math_constants.h>
 
@@ -342,6 +343,265 @@ __global__ void __launch_bounds__(128) ax_qk_prep_kernel(const AxQkPrepArgs a) {
     }
 }
 
+// ── fused decode attention, head_dim 128 ─────────────────────────────────────────
+// grid = (max_splits, kv heads).  Every thread owns a 16-byte piece of UN rows per stage and a
+// private landing slot in shared memory for each (stage, row): cp.async fills the slots, the same
+// thread consumes them, so the main loop needs no CTA barrier and NST stages (32 KB per CTA, three
+// CTAs per SM) stay in flight without costing registers.  The first NST stages are requested
+// before griddepcontrol.wait: rows below `pos` are older than the previous kernel.
+constexpr int kFusedUnroll = 2;
+constexpr int kFusedStages = 2;
+constexpr int kFusedRowsPerSplit = 64;
+constexpr size_t kFusedLandBytes = (size_t)kFusedStages * kFusedUnroll * 2 * kAttnThreads * 16;
+
+struct FusedDev {
+    AxFusedAttnArgs a;
+    float* partials;       // [n_heads × max_splits × 130]
+    unsigned* tickets;     // [n_kv], zero between launches
+    unsigned long long* trace;
+};
+
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"((uint32_t)__cvta_generic_to_shared(smem_dst)), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
+
+template <bool BF16, int G>
+__global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const FusedDev dv) {
+    constexpr int HD = 128;
+    constexpr int EPL = BF16 ? 8 : 4;
+    constexpr int LPR = HD / EPL;                 // lanes per cached row: 16 or 32
+    constexpr int RPW = 32 / LPR;
+    constexpr int SLOTS = kAttnWarps * RPW;       // rows per CTA pass: 16 or 8
+    constexpr int UN = kFusedUnroll, NST = kFusedStages;
+    constexpr int ST = HD + 2;
+    extern __shared__ __align__(16) uint8_t fsm[];
+    uint4* land = reinterpret_cast<uint4*>(fsm);                     // [NST][UN][K,V][thread]
+    float* q_s = reinterpret_cast<float*>(fsm + kFusedLandBytes);     // [G][HD]
+    float* k_new = q_s + G * HD;
+    float* v_new = k_new + HD;
+    float* smm = reinterpret_cast<float*>(fsm);                       // [warps][G][ST], reuses the landing slots
+    __shared__ int s_last;
+
+    const AxFusedAttnArgs& a = dv.a;
+    const int split = blockIdx.x, kh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int sub = lane % LPR, slot = warp * RPW + lane / LPR;
+
+    ax_trace_start(dv.trace);
+    const int pos = __ldcg(a.pos);
+    const int tb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
+    const int rows = pos - tb;                    // cached rows; row `pos` comes from shared memory
+    int S = (rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
+    S = S < 1 ? 1 : (S > (int)gridDim.x ? (int)gridDim.x : S);
+    if (split >= S) return;
+    const int per = (rows + S - 1) / S;
+    const int t0 = tb + split * per;
+    const int t1 = min(pos, t0 + per);
+    const int nstages = (t1 - t0 + SLOTS * UN - 1) / (SLOTS * UN);    // CTA-uniform
+    const size_t esz = BF16 ? 2 : 4;
+    const size_t row_bytes = (size_t)a.n_kv * HD * esz;
+    const uint8_t* kbase = (const uint8_t*)a.kc + ((size_t)kh * HD + sub * EPL) * esz;
+    const uint8_t* vbase = (const uint8_t*)a.vc + ((size_t)kh * HD + sub * EPL) * esz;
+
+    auto issue = [&](int j) {                     // always commits, so that group counts stay aligned
+        if (j < nstages) {
+            const int base = t0 + j * SLOTS * UN;
+            uint4* dst = land + (size_t)(j % NST) * UN * 2 * kAttnThreads + tid;
+#pragma unroll
+            for (int u = 0; u < UN; u++) {
+                const int t = base + u * SLOTS + slot;
+                if (t < t1) {
+                    cp_async16(dst + (u * 2 + 0) * kAttnThreads, kbase + (size_t)t * row_bytes);
+                    cp_async16(dst + (u * 2 + 1) * kAttnThreads, vbase + (size_t)t * row_bytes);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int j = 0; j < NST; j++) issue(j);
+
+    // norm weights and table rows of this CTA's prep warps: independent of the token as well
+    const int half = HD / 2;
+    const float* cr = a.cos_t ? a.cos_t + (size_t)pos * half : nullptr;
+    const float* sr = a.sin_t ? a.sin_t + (size_t)pos * half : nullptr;
+    const int q_rows = a.n_heads * HD, kv_rows = a.n_kv * HD;
+    const bool prep_q = warp < G, prep_k = split == 0 && warp == G, prep_v = split == 0 && warp == G + 1;
+    MgRopeConsts rc = {};
+    const float* nw = nullptr;
+    if (prep_q) nw = a.q_norm ? a.q_norm + (size_t)(kh * G + warp) * HD : nullptr;
+    if (prep_k) nw = a.k_norm ? a.k_norm + (size_t)kh * HD : nullptr;
+    if (prep_q || prep_k) rc = mg_rope_consts(nw, cr, sr);
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");                // the raw QKV vector is complete
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    ax_trace_release(dv.trace);
+
+    // q heads of the group; split 0 also makes the new K and V rows and stores them into the cache
+    if (prep_q) {
+        const float4 v = mg_norm_rope_apply(a.qkv + (size_t)(kh * G + warp) * HD, nw != nullptr, cr != nullptr, rc, a.qk_eps);
+        reinterpret_cast<float4*>(q_s + warp * HD)[lane] = v;
+    } else if (prep_k || prep_v) {
+        float4 v;
+        if (prep_k) v = mg_norm_rope_apply(a.qkv + q_rows + (size_t)kh * HD, nw != nullptr, cr != nullptr, rc, a.qk_eps);
+        else        v = __ldcg(reinterpret_cast<const float4*>(a.qkv + q_rows + kv_rows + (size_t)kh * HD) + lane);
+        const size_t off = ((size_t)pos * a.n_kv + kh) * HD + lane * 4;
+        void* cache = prep_k ? a.kc : a.vc;
+        if (BF16) {
+            const uint16_t b0 = ax_f32_to_bf16_rne(v.x), b1 = ax_f32_to_bf16_rne(v.y), b2 = ax_f32_to_bf16_rne(v.z), b3 = ax_f32_to_bf16_rne(v.w);
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(cache) + off) =
+                make_uint2((uint32_t)b0 | ((uint32_t)b1 << 16), (uint32_t)b2 | ((uint32_t)b3 << 16));
+            v = make_float4(ax_bf16_to_f32(b0), ax_bf16_to_f32(b1), ax_bf16_to_f32(b2), ax_bf16_to_f32(b3));
+        } else {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(cache) + off) = v;
+        }
+        reinterpret_cast<float4*>(prep_k ? k_new : v_new)[lane] = v;
+    }
+    __syncthreads();
+    ax_trace_staged(dv.trace);
+
+    float q[G][EPL], acc[G][EPL], m[G], l[G];
+#pragma unroll
+    for (int g = 0; g < G; g++) {
+#pragma unroll
+        for (int e = 0; e < EPL; e++) { q[g][e] = q_s[g * HD + sub * EPL + e]; acc[g][e] = 0.f; }
+        m[g] = -CUDART_INF_F; l[g] = 0.f;
+    }
+
+    for (int j = 0; j < nstages; j++) {
+        cp_async_wait<NST - 1>();                 // stage j of this thread has landed
+        const int base = t0 + j * SLOTS * UN;
+        const uint4* src = land + (size_t)(j % NST) * UN * 2 * kAttnThreads + tid;
+        uint4 kr[UN], vr[UN]; bool valid[UN];
+#pragma unroll
+        for (int u = 0; u < UN; u++) {
+            valid[u] = base + u * SLOTS + slot < t1;
+            if (valid[u]) { kr[u] = src[(u * 2 + 0) * kAttnThreads]; vr[u] = src[(u * 2 + 1) * kAttnThreads]; }
+            else { kr[u] = make_uint4(0, 0, 0, 0); vr[u] = make_uint4(0, 0, 0, 0); }
+        }
+        issue(j + NST);                           // refill the slots just read
+        float sc[UN][G];
+        mg_scores<BF16, UN, EPL, LPR, G>(q, kr, valid, a.scale, sc);
+        mg_update<BF16, UN, EPL, G>(m, l, acc, sc, valid, vr);
+    }
+    cp_async_wait<0>();
+
+    // the new row itself (split 0, first lane group of warp 0)
+    if (split == 0 && warp == 0) {
+        uint4 k1[1], v1[1]; bool ok1[1] = { lane / LPR == 0 };
+        float sc[1][G];
+        const float* kp = k_new + sub * EPL; const float* vp = v_new + sub * EPL;
+        if (BF16) {
+            k1[0] = make_uint4(__float_as_uint(kp[0]) >> 16 | (__float_as_uint(kp[1]) & 0xFFFF0000u), __float_as_uint(kp[2]) >> 16 | (__float_as_uint(kp[3]) & 0xFFFF0000u),
+                               __float_as_uint(kp[4]) >> 16 | (__float_as_uint(kp[5]) & 0xFFFF0000u), __float_as_uint(kp[6]) >> 16 | (__float_as_uint(kp[7]) & 0xFFFF0000u));
+            v1[0] = make_uint4(__float_as_uint(vp[0]) >> 16 | (__float_as_uint(vp[1]) & 0xFFFF0000u), __float_as_uint(vp[2]) >> 16 | (__float_as_uint(vp[3]) & 0xFFFF0000u),
+                               __float_as_uint(vp[4]) >> 16 | (__float_as_uint(vp[5]) & 0xFFFF0000u), __float_as_uint(vp[6]) >> 16 | (__float_as_uint(vp[7]) & 0xFFFF0000u));
+        } else {
+            k1[0] = *reinterpret_cast<const uint4*>(kp);
+            v1[0] = *reinterpret_cast<const uint4*>(vp);
+        }
+        mg_scores<BF16, 1, EPL, LPR, G>(q, k1, ok1, a.scale, sc);
+        mg_update<BF16, 1, EPL, G>(m, l, acc, sc, ok1, v1);
+    }
+
+    // merge lane groups of a warp, then warps, then (last CTA of the kv head) the splits
+#pragma unroll
+    for (int o = LPR; o < 32; o <<= 1) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            const float mo = __shfl_xor_sync(AX_FULL, m[g], o);
+            const float lo = __shfl_xor_sync(AX_FULL, l[g], o);
+            const float mn = fmaxf(m[g], mo);
+            const float ca = mg_exp_diff(m[g], mn), cb = mg_exp_diff(mo, mn);
+            l[g] = l[g] * ca + lo * cb;
+#pragma unroll
+            for (int e = 0; e < EPL; e++) {
+                const float ao = __shfl_xor_sync(AX_FULL, acc[g][e], o);
+                acc[g][e] = acc[g][e] * ca + ao * cb;
+            }
+            m[g] = mn;
+        }
+    }
+    __syncthreads();                              // every thread is done with its landing slots
+    if (lane < LPR) {
+#pragma unroll
+        for (int g = 0; g < G; g++) {
+            float* dst = smm + ((size_t)warp * G + g) * ST;
+            if (sub == 0) { dst[0] = m[g]; dst[1] = l[g]; }
+#pragma unroll
+            for (int e = 0; e < EPL; e++) dst[2 + sub * EPL + e] = acc[g][e];
+        }
+    }
+    __syncthreads();
+    const int SP = (int)gridDim.x;                // partial slots per head
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx % HD;
+        float M, L, A;
+        merge_states<HD>(smm + (size_t)g * ST, kAttnWarps, G * ST, d, M, L, A);
+        const int h = kh * G + g;
+        if (S == 1) {
+            a.out[(size_t)h * HD + d] = A / L;
+        } else {
+            float* P = dv.partials + ((size_t)h * SP + split) * ST;
+            P[2 + d] = A;
+            if (d == 0) { P[0] = M; P[1] = L; }
+        }
+    }
+    ax_trace_end(dv.trace);
+    if (S == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const unsigned tk = atomicAdd(&dv.tickets[kh], 1u);
+        s_last = (tk == (unsigned)(S - 1));
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
+        const int g = idx / HD, d = idx % HD;
+        const int h = kh * G + g;
+        float M, L, A;
+        merge_states<HD>(dv.partials + (size_t)h * SP * ST, S, ST, d, M, L, A);
+        a.out[(size_t)h * HD + d] = A / L;
+    }
+    if (tid == 0) dv.tickets[kh] = 0u;            // ready for the next launch
+    ax_trace_end(dv.trace);
+}
+
+template <bool BF16, int G>
+int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)dv.a.max_splits, (unsigned)dv.a.n_kv);
+    cfg.blockDim = dim3(kAttnThreads);
+    cfg.dynamicSmemBytes = kFusedLandBytes + (size_t)(G + 2) * 128 * 4;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
+    }
+    if (ctx->carveout >= 0) {
+        attr[na].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+        attr[na].val.sharedMemCarveout = (unsigned)ctx->carveout;
+        na++;
+    }
+    if (na) { cfg.attrs = attr; cfg.numAttrs = na; }
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_fused_kernel<BF16, G>, dv));
+    return ATLASX_OK;
+}
+
+template <bool BF16, int G>
+int fused_attr() {
+    AX_CUDA(cudaFuncSetAttribute(ax_attn_fused_kernel<BF16, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)(kFusedLandBytes + (size_t)(G + 2) * 128 * 4)));
+    return ATLASX_OK;
+}
+
 template <bool BF16, int HD, int G>
 int launch_splitk(atlasx_ctx* ctx, const AttnDev& dv, bool pdl) {
     cudaLaunchConfig_t cfg = {};
@@ -411,6 +671,43 @@ int ax_attn_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
     const bool bf = a.kv_dtype == ATLASX_BF16;
     if (bf) return a.hd == 128 ? dispatch_g<true, 128>(ctx, dv, pdl) : dispatch_g<true, 64>(ctx, dv, pdl);
     return a.hd == 128 ? dispatch_g<false, 128>(ctx, dv, pdl) : dispatch_g<false, 64>(ctx, dv, pdl);
+}
+
+bool ax_attn_fused_supported(int hd, int n_heads, int n_kv) {
+    if (hd != 128 || n_kv <= 0 || n_heads % n_kv) return false;
+    const int g = n_heads / n_kv;
+    return g == 1 || g == 2 || g == 4;
+}
+int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows) {
+    // one wave: three CTAs of this kernel are resident per SM
+    int s = (max_rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
+    const int wave = (3 * ctx->sm_count) / (n_kv > 0 ? n_kv : 1);
+    if (s > wave) s = wave;
+    return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+int ax_attn_init(atlasx_ctx*) {
+    int rc;
+    if ((rc = fused_attr<true, 1>()) || (rc = fused_attr<true, 2>()) || (rc = fused_attr<true, 4>())) return rc;
+    if ((rc = fused_attr<false, 1>()) || (rc = fused_attr<false, 2>()) || (rc = fused_attr<false, 4>())) return rc;
+    return ATLASX_OK;
+}
+int ax_attn_fused_launch(atlasx_ctx* ctx, const AxFusedAttnArgs& a, bool pdl) {
+    AX_ARG(a.qkv && a.kc && a.vc && a.out && a.pos, "null pointer");
+    AX_ARG(ax_attn_fused_supported(128, a.n_heads, a.n_kv), "fused attention needs 1, 2 or 4 query heads per KV head");
+    AX_ARG(a.max_splits >= 1 && a.max_splits <= 64, "max_splits must be in 1..64");
+    AX_ARG((((uintptr_t)a.qkv | (uintptr_t)a.kc | (uintptr_t)a.vc | (uintptr_t)a.out) & 15) == 0, "buffers must be 16-byte aligned");
+    FusedDev dv;
+    dv.a = a;
+    int rc = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.n_heads * a.max_splits * (128 + 2), (size_t)a.n_heads);
+    if (rc) return rc;
+    dv.partials = ctx->attn_partials;
+    dv.tickets = ctx->attn_tickets;
+    dv.trace = nullptr;
+    if (ctx->trace_next) { dv.trace = ctx->trace_next; ctx->trace_next += 6; }
+    const int g = a.n_heads / a.n_kv;
+    if (a.kv_dtype == ATLASX_BF16)
+        return g == 1 ? launch_fused<true, 1>(ctx, dv, pdl) : g == 2 ? launch_fused<true, 2>(ctx, dv, pdl) : launch_fused<true, 4>(ctx, dv, pdl);
+    return g == 1 ? launch_fused<false, 1>(ctx, dv, pdl) : g == 2 ? launch_fused<false, 2>(ctx, dv, pdl) : launch_fused<false, 4>(ctx, dv, pdl);
 }
 
 int ax_qk_prep_launch(atlasx_ctx* ctx, const AxQkPrepArgs& a, bool pdl) {

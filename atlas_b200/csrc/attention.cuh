@@ -39,3 +39,25 @@ struct AxQkPrepArgs {
     size_t q_stride = 0, kv_in_stride = 0;   // elements between batch entries of q and of k/v
 };
 int ax_qk_prep_launch(atlasx_ctx* ctx, const AxQkPrepArgs& a, bool pdl = false);
+
+// Decode attention of one layer for one sequence, head_dim 128, as ONE launch: per-head RMSNorm
+// of q and k, rotate-half RoPE, the cache write at `pos`, and split attention over the cached
+// rows (restates crates/atlas-model/src/lib.rs:848-870).  Cached rows are requested before the
+// kernel waits for its predecessor in the stream — they were written by earlier steps.
+struct AxFusedAttnArgs {
+    const float* qkv = nullptr;      // raw [q (n_heads·128) | k (n_kv·128) | v (n_kv·128)] of this token
+    const float* q_norm = nullptr;   // [n_heads × 128] or null
+    const float* k_norm = nullptr;   // [n_kv × 128] or null
+    const float* cos_t = nullptr;    // [max_seq × 64] or null
+    const float* sin_t = nullptr;
+    void* kc = nullptr; void* vc = nullptr;      // [max_seq × n_kv × 128], bf16 bits or f32
+    float* out = nullptr;            // [n_heads × 128]
+    const int* pos = nullptr;        // device scalar, written at least two kernels earlier in the stream
+    int n_heads = 0, n_kv = 0, window = 0, kv_dtype = ATLASX_BF16;
+    int max_splits = 1;              // grid.x; the kernel uses ⌈rows/64⌉ of them, the rest exit at once
+    float scale = 1.f, qk_eps = 1e-6f;
+};
+bool ax_attn_fused_supported(int hd, int n_heads, int n_kv);
+int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows);
+int ax_attn_fused_launch(atlasx_ctx* ctx, const AxFusedAttnArgs& a, bool pdl = false);
+int ax_attn_init(atlasx_ctx* ctx);      // one-time function attributes

@@ -41,6 +41,8 @@ struct atlasx_ctx {
     size_t smem_optin = 0;
     cudaStream_t stream = nullptr;
     int gemv_impl = 0;                 // 0 auto, 1 plain loads, 2 bulk-copy pipeline
+    int carveout = 50;                 // shared-memory share of the L1 array requested per launch (percent), −1: driver's choice.
+                                       // One value for every kernel of a step: neighbours in the stream then fit on an SM together
     // attention scratch (split-K partials + tickets), grown on demand
     float* attn_partials = nullptr;  size_t attn_partials_cap = 0;   // floats
     unsigned* attn_tickets = nullptr; size_t attn_tickets_cap = 0;   // uints, always zero between launches
@@ -51,7 +53,29 @@ struct atlasx_ctx {
     int* dev_error = nullptr;          // device
     int* host_pin = nullptr;           // pinned scratch (ints)
     atlasx_comm* comm = nullptr;
+    // timeline recording (diagnostics): when non-null, the next traced launch stamps six u64
+    // at this address — first/last CTA start, first dependency release, last CTA end, first CTA end, last input staged —
+    // and the launcher advances the pointer
+    unsigned long long* trace_next = nullptr;
 };
+
+// Timeline stamps of one launch; t is read from %globaltimer (ns).
+struct AxTraceSlot { unsigned long long first_start, last_start, first_release, last_end, first_end, last_staged; };
+__device__ __forceinline__ unsigned long long ax_globaltimer() {
+    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
+}
+__device__ __forceinline__ void ax_trace_start(unsigned long long* tr) {
+    if (tr && threadIdx.x == 0) { const unsigned long long t = ax_globaltimer(); atomicMin(tr + 0, t); atomicMax(tr + 1, t); }
+}
+__device__ __forceinline__ void ax_trace_release(unsigned long long* tr) {
+    if (tr && threadIdx.x == 0) atomicMin(tr + 2, ax_globaltimer());
+}
+__device__ __forceinline__ void ax_trace_end(unsigned long long* tr) {
+    if (tr && threadIdx.x == 0) { const unsigned long long t = ax_globaltimer(); atomicMax(tr + 3, t); atomicMin(tr + 4, t); }
+}
+__device__ __forceinline__ void ax_trace_staged(unsigned long long* tr) {
+    if (tr && threadIdx.x == 0) atomicMax(tr + 5, ax_globaltimer());
+}
 
 int atlasx_ctx_ensure_attn_scratch(atlasx_ctx* ctx, size_t partial_floats, size_t tickets);
 

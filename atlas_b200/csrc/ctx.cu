@@ -49,7 +49,9 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
     AX_CUDA(cudaMalloc((void**)&c->amax_ticket, sizeof(unsigned)));
     AX_CUDA(cudaMemset(c->amax_ticket, 0, sizeof(unsigned)));
     AX_CUDA(cudaMalloc((void**)&c->amax_out, sizeof(int)));
+    { const char* e = getenv("ATLASX_CARVEOUT"); if (e) c->carveout = atoi(e); }      // experiments
     int rc = ax_gemv_init(c);
+    if (!rc) rc = ax_attn_init(c);
     if (rc) { delete c; return rc; }
     *out = c;
     return ATLASX_OK;

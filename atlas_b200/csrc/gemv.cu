@@ -41,20 +41,12 @@ __device__ __forceinline__ void store_rows(const GemvArgs& a, int row0, bool v0,
     }
 }
 
-// Row range of this CTA, in units of two rows when M is even (keeps gate/up pairs together).
-__device__ __forceinline__ void cta_rows(int M, int& lo, int& hi) {
-    const int unit = (M & 1) ? 1 : 2;
-    const long long units = M / unit;
-    lo = (int)(units * blockIdx.x / gridDim.x) * unit;
-    hi = (int)(units * (blockIdx.x + 1) / gridDim.x) * unit;
-}
-
 // Direct path (no shared-memory ring): every warp streams its two rows with 128-bit loads, four
 // chunks per row per batch, software-pipelined — the loads of batch i+1 are issued before the
 // arithmetic of batch i, and batch 0 is issued before griddepcontrol.wait, i.e. while the previous
 // kernel of the stream is still draining (weights never depend on it).
 template <int FMT>
-__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float* red, int lo, int hi) {
+__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, int lo, int hi) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,10 +68,14 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
             }
         }
     };
+    ax_trace_start(a.trace);
     if (total > 0) load(0, wa, wb);
+    stage_input_early<FMT>(a, xb);
     griddep_wait();                       // activations of the previous kernel are complete
     griddep_launch();
-    stage_input<FMT>(a, xs, red);
+    ax_trace_release(a.trace);
+    stage_input<FMT>(a, xs, red, xb);
+    ax_trace_staged(a.trace);
 
     Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
     float sc0 = 0.f, sc1 = 0.f;
@@ -119,6 +115,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
 #pragma unroll
         for (int u = 0; u < 4; u++) { wa[u] = na[u]; wb[u] = nb[u]; }
     }
+    ax_trace_end(a.trace);
 }
 
 template <int FMT, bool TMA>
@@ -138,127 +135,28 @@ ax_gemv_stream_kernel(const GemvArgs a) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     int lo, hi; cta_rows(a.M, lo, hi);
-    if (!TMA) { consume_direct<FMT>(a, xs, red, lo, hi); return; }
-
-    const int ntiles = (hi - lo + kRingRows - 1) / kRingRows;
-    const int nk = (a.row_bytes + kSeg - 1) / kSeg;
-    const int sseg_full = a.seg_pitch - kSeg;                // int4 scale bytes of a full segment
-    if (tid == 0) {
-        for (int s = 0; s < a.stages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], kConsumerWarps); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-    }
-    __syncthreads();
-
-    if (warp == kConsumerWarps) {
-        // ── producer warp: weights do not depend on the previous kernel, so start at once; the
-        //    kernel is sized so that two CTAs fit on an SM, which lets the NEXT kernel of the
-        //    stream become resident and fill its ring while this one is still computing ──
-        int fill = 0;
-        bool ok = true;
-        for (int t = 0; t < ntiles && ok; t++) {
-            const int r0 = lo + t * kRingRows;
-            const int nrows = min(kRingRows, hi - r0);
-            for (int kc = 0; kc < nk && ok; kc++, fill++) {
-                const int s = fill % a.stages;
-                const uint32_t ph = (uint32_t)(fill / a.stages) & 1u;
-                const int seg = min(kSeg, a.row_bytes - kc * kSeg);
-                int sseg = 0;
-                if (FMT == ATLASX_INT4) sseg = min(a.srow_bytes - kc * sseg_full, sseg_full);
-                if (lane == 0) {
-                    ok = mbar_wait(&empty[s], ph ^ 1u, a.err, 1);
-                    if (ok) mbar_arrive_expect_tx(&full[s], (uint32_t)(nrows * (seg + sseg)));
-                }
-                ok = __shfl_sync(AX_FULL, ok, 0);
-                if (ok && lane < nrows) {
-                    uint8_t* dst = ring + (size_t)s * a.stage_stride + lane * a.seg_pitch;
-                    const size_t row = (size_t)(r0 + lane);
-                    bulk_g2s(dst, a.W + row * a.row_bytes + (size_t)kc * kSeg, (uint32_t)seg, &full[s]);
-                    if (FMT == ATLASX_INT4)
-                        bulk_g2s(dst + kSeg, a.scales + row * a.srow_bytes + (size_t)kc * sseg_full, (uint32_t)sseg, &full[s]);
-                }
-            }
-        }
-        if (!ok) {            // give copies already in flight time to land before the CTA's memory is reused
-            for (int i = 0; i < 100; i++) __nanosleep(10000);
-        }
+    if (!TMA) {
+        // second plane (raw residual stream, fetched early) only when the launcher reserved it
+        float4* xb = a.pro.base_early ? reinterpret_cast<float4*>(ring) : nullptr;
+        consume_direct<FMT>(a, xs, xb, red, lo, hi);
         return;
     }
 
-    // ── consumers: one row per warp per tile ───────────────────────────────────────
+    Ring rg;
+    rg.full = full; rg.empty = empty; rg.data = ring;
+    rg.stages = a.stages; rg.stage_stride = a.stage_stride; rg.seg_pitch = a.seg_pitch;
+    ring_init(rg);
+    int fill = 0;
+    if (warp == kConsumerWarps) {
+        // producer warp: weights do not depend on the previous kernel, so it starts at once
+        if (!ring_produce<FMT>(a, rg, lo, hi, fill))
+            for (int i = 0; i < 100; i++) __nanosleep(10000);   // let copies in flight land before exit
+        return;
+    }
     griddep_wait();                       // activations of the previous kernel are complete
-    // Only now may the next kernel of the stream start (and fill its ring behind this one):
-    // releasing it earlier lets a whole chain of future kernels pile up on the SMs.
     griddep_launch();
     stage_input<FMT>(a, xs, red);
-
-    const int nch = a.nchunks;
-    int fill = 0;
-    bool ok = true;
-    for (int t = 0; t < ntiles && ok; t++) {
-        const int row = lo + t * kRingRows + warp;
-        const bool valid = row < hi;
-        Acc4 acc = acc4_zero();
-        float sc = 0.f;                   // int4: sums already multiplied by their block scales
-        for (int kc = 0; kc < nk; kc++, fill++) {
-            const int s = fill % a.stages;
-            const uint32_t ph = (uint32_t)(fill / a.stages) & 1u;
-            ok = mbar_wait(&full[s], ph, a.err, 2);
-            if (!ok) break;
-            const int seg_chunks = min(kSeg, a.row_bytes - kc * kSeg) >> 4;
-            const uint8_t* st = ring + (size_t)s * a.stage_stride + warp * a.seg_pitch;
-            if (valid && !(a.dbg & 1)) {
-                const uint4* wp = reinterpret_cast<const uint4*>(st) + lane;
-                const float4* xb = xs + kc * kSegChunks + lane;
-                if (FMT != ATLASX_INT4 && seg_chunks == kSegChunks) {
-                    // full segment: no predicates, addresses are lane base + constants
-#pragma unroll
-                    for (int it = 0; it < kSegChunks / 32; it++) {
-                        float4 xv[P];
-#pragma unroll
-                        for (int p = 0; p < P; p++) xv[p] = xb[p * nch + it * 32];
-                        const uint4 w = wp[it * 32];
-                        dot_chunk<FMT>(w, xv, acc);
-                    }
-                } else {
-#pragma unroll 2
-                    for (int it = 0; it < kSegChunks / 32; it++) {
-                        const int c = it * 32 + lane;
-                        if (c < seg_chunks) {
-                            float4 xv[P];
-#pragma unroll
-                            for (int p = 0; p < P; p++) xv[p] = xb[p * nch + it * 32];
-                            const uint4 w = wp[it * 32];
-                            if (FMT == ATLASX_INT4) {
-                                Acc4 part = acc4_zero(); dot_chunk<FMT>(w, xv, part);
-                                sc = fmaf(part.sum(), load_scale_i4(st + kSeg, (c * EPC) / a.block, a.scales_f16), sc);
-                            } else dot_chunk<FMT>(w, xv, acc);
-                        }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[s]);
-        }
-        if (!ok) break;
-        float r = ax_warp_sum(acc.sum() + sc);
-        if (FMT == ATLASX_INT8 && valid) r *= reinterpret_cast<const float*>(a.scales)[row];
-        if (a.epi == AX_EPI_SILU_PAIR) {
-            // gate row (even) and up row (odd) sit in neighbouring warps: exchange through shared
-            // memory under a two-warp named barrier; slots alternate with the tile parity
-            float* slot = pair + (t & 1) * kConsumerWarps;
-            if (lane == 0) slot[warp] = r;
-            switch (warp >> 1) {          // immediate ids keep the CTA at six hardware barriers
-                case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
-                case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
-                case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
-                default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
-            }
-            if (lane == 0 && valid && !(warp & 1)) a.y[row >> 1] = (r / (1.0f + expf(-r))) * slot[warp + 1];
-        } else if (lane == 0 && valid) {
-            a.y[row] = r;
-        }
-    }
+    ring_consume<FMT>(a, rg, xs, pair, lo, hi, fill);
 }
 
 // ── scalar kernel: any shape, any alignment, n columns (n ≤ 16); one warp per row ─────────
@@ -298,12 +196,19 @@ int launch_stream(atlasx_ctx* ctx, const GemvArgs& a, int grid, size_t smem, boo
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(TMA ? kThreadsTma : kConsumerThreads);
     cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
+    int na = 0;
     if (pdl) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        na++;
     }
+    if (!TMA && ctx->carveout >= 0) {
+        attr[na].id = cudaLaunchAttributePreferredSharedMemoryCarveout;
+        attr[na].val.sharedMemCarveout = (unsigned)ctx->carveout;
+        na++;
+    }
+    if (na) { cfg.attrs = attr; cfg.numAttrs = na; }
     AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_stream_kernel<FMT, TMA>, a));
     return ATLASX_OK;
 }
@@ -312,6 +217,8 @@ template <int FMT>
 int set_attrs() {
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    if (const char* e = getenv("ATLASX_GEMV_CARVEOUT"))     // experiments: shared-memory share of the L1 array, percent
+        AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false>, cudaFuncAttributePreferredSharedMemoryCarveout, atoi(e)));
     return ATLASX_OK;
 }
 
@@ -323,6 +230,38 @@ int ax_gemv_init(atlasx_ctx*) {
     if ((rc = set_attrs<ATLASX_BF16>())) return rc;
     if ((rc = set_attrs<ATLASX_INT8>())) return rc;
     if ((rc = set_attrs<ATLASX_INT4>())) return rc;
+    return ATLASX_OK;
+}
+
+
+int ax_gemv_ring_seg_bytes() { return kSeg; }
+int ax_gemv_ring_scale_seg(const AxWeight& w) {
+    if (w.dtype != ATLASX_INT4) return 0;
+    return (kSeg * 2 / w.block) * (w.scales_f16 ? 2 : 4);
+}
+int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* y, int* err, GemvArgs* out) {
+    AX_ARG(w.data && y && out, "null pointer");
+    const int epc = w.dtype == ATLASX_F32 ? 4 : w.dtype == ATLASX_BF16 ? 8 : w.dtype == ATLASX_INT8 ? 16 : 32;
+    const int ebits = w.dtype == ATLASX_F32 ? 32 : w.dtype == ATLASX_BF16 ? 16 : w.dtype == ATLASX_INT8 ? 8 : 4;
+    bool ok = (w.cols % epc == 0) && (((uintptr_t)w.data & 15) == 0);
+    if (w.dtype == ATLASX_INT4) {
+        ok = ok && w.block >= 32 && (w.block % 32 == 0) && (w.cols % w.block == 0) && w.scales;
+        const int sseg = ax_gemv_ring_scale_seg(w);
+        const int srow = (w.cols / w.block) * (w.scales_f16 ? 2 : 4);
+        ok = ok && (sseg % 16 == 0) && (srow % 16 == 0) && (((uintptr_t)w.scales & 15) == 0);
+    }
+    if (w.dtype == ATLASX_INT8) ok = ok && w.scales;
+    if (epi == AX_EPI_SILU_PAIR) ok = ok && (w.rows % 2 == 0);
+    AX_ARG(ok, "matrix shape or alignment not supported by the ring kernel");
+    GemvArgs a = {};
+    a.W = (const uint8_t*)w.data; a.scales = (const uint8_t*)w.scales;
+    a.M = w.rows; a.K = w.cols;
+    a.row_bytes = (int)((size_t)w.cols * ebits / 8);
+    a.block = w.block > 0 ? w.block : 1; a.scales_f16 = w.scales_f16;
+    a.srow_bytes = w.dtype == ATLASX_INT4 ? (w.cols / w.block) * (w.scales_f16 ? 2 : 4) : 0;
+    a.nchunks = a.row_bytes / 16;
+    a.epi = epi; a.y = y; a.pro = pro; a.err = err; a.dbg = 0; a.trace = nullptr;
+    *out = a;
     return ATLASX_OK;
 }
 
@@ -370,6 +309,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     a.nchunks = a.row_bytes / 16;
     a.epi = epi; a.y = y; a.pro = pro; a.err = ctx->dev_error;
     { const char* e = getenv("ATLASX_GEMV_DEBUG"); a.dbg = e ? atoi(e) : 0; }
+    a.trace = nullptr;
 
     const size_t x_bytes = (((size_t)w.cols * 4 + 127) / 128) * 128;
     const size_t smem_max = ctx->smem_optin ? ctx->smem_optin : 232448;
@@ -395,12 +335,13 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     a.stages = stages;
 
     int impl = ctx->gemv_impl;
-    if (impl == 0) impl = 2;
+    if (impl == 0) impl = 1;              // plain loads: faster than the bulk-copy ring inside a decode step
     if (impl == 2 && !tma_ok) impl = 1;
 
     const int units = (w.rows & 1) ? w.rows : w.rows / 2;
     int rc;
     if (impl == 2) {
+        a.pro.base_early = 0;
         const int grid = units < ctx->sm_count ? units : ctx->sm_count;
         const size_t smem = 256 + x_bytes + (size_t)stages * a.stage_stride;
         switch (w.dtype) {
@@ -410,7 +351,9 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
             default:          rc = launch_stream<ATLASX_INT4, true>(ctx, a, grid, smem, pdl); break;
         }
     } else {
-        const size_t smem = 256 + x_bytes;
+        // the early-fetched residual plane only pays off (and is only reserved) next to a fused norm
+        if (!(a.pro.base_early && (pro.y || pro.wx) && pro.base && !pro.embed && 256 + 2 * x_bytes <= smem_max)) a.pro.base_early = 0;
+        const size_t smem = 256 + x_bytes * (a.pro.base_early ? 2 : 1);
         AX_ARG(smem <= smem_max, "input vector does not fit in shared memory");
         int per_sm = 1;             // resident CTAs per SM for this format and input size
         switch (w.dtype) {
@@ -420,10 +363,12 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
             default:          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_INT4, false>, kConsumerThreads, smem); break;
         }
         if (per_sm < 1) per_sm = 1;
+        { const char* e = getenv("ATLASX_GEMV_PERSM"); if (e && atoi(e) > 0 && per_sm > atoi(e)) per_sm = atoi(e); }   // experiments
         int grid = ctx->sm_count * per_sm;
         const int tiles = (units * ((w.rows & 1) ? 1 : 2) + kTileRows - 1) / kTileRows;
         if (grid > tiles) grid = tiles;
         if (grid < 1) grid = 1;
+        if (ctx->trace_next) { a.trace = ctx->trace_next; ctx->trace_next += 6; }
         switch (w.dtype) {
             case ATLASX_F32:  rc = launch_stream<ATLASX_F32, false>(ctx, a, grid, smem, pdl); break;
             case ATLASX_BF16: rc = launch_stream<ATLASX_BF16, false>(ctx, a, grid, smem, pdl); break;

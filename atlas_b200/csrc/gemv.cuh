@@ -33,12 +33,35 @@ struct AxPrologue {
     const float* wy = nullptr; const float* wx = nullptr;
     float eps = 0.f;
     float* resid_out = nullptr;
+    int base_early = 0;                 // `base` was written at least two kernels back in the stream: may be read before the dependency wait
 };
 
 enum { AX_EPI_PLAIN = 0, AX_EPI_SILU_PAIR = 1 };   // pair: out[r/2] = silu(acc[r])·acc[r+1], r even
 
+// Kernel-side view of one GEMV (built by ax_gemv_launch or by the whole-step kernel's program).
+struct GemvArgs {
+    const uint8_t* W; const uint8_t* scales;
+    int M, K;                    // rows, cols (elements)
+    int row_bytes;               // bytes of one weight row
+    int srow_bytes;              // bytes of one row of int4 scales (0 otherwise)
+    int block; int scales_f16;
+    int stages; int stage_stride; int seg_pitch;   // ring geometry (TMA)
+    int nchunks;                 // 16-byte chunks per row
+    int epi;
+    float* y;
+    AxPrologue pro;
+    int* err;
+    int dbg;                     // experiments only: bit 0 = consumers skip the arithmetic
+    unsigned long long* trace;   // diagnostics: timeline stamps of this launch, or null
+};
+
 // y[rows×n] = W·x.  n == 1: pro/epi honoured.  n in 2..16: plain only, x is [cols×n] row-major.
 int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y,
                    bool pdl = false);
+// Fill the shape/format fields of a GemvArgs for the ring kernels (fails for shapes that need the
+// scalar kernel).  Ring geometry fields are left to the caller.
+int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* y, int* err, GemvArgs* out);
+int ax_gemv_ring_scale_seg(const AxWeight& w);   // int4: scale bytes that accompany one full weight segment (0 otherwise)
+int ax_gemv_ring_seg_bytes();
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes
 size_t ax_weight_bytes(const AxWeight& w);

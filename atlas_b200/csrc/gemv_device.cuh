@@ -10,7 +10,7 @@ namespace {
 #define AX_SEG 4096
 #endif
 #ifndef AX_STAGES
-#define AX_STAGES 3
+#define AX_STAGES 6
 #endif
 constexpr int kConsumerWarps = 8;
 constexpr int kRW = 2;                                   // rows per consumer warp
@@ -30,20 +30,6 @@ template <> struct Fmt<ATLASX_BF16> { static constexpr int EPC = 8;  };
 template <> struct Fmt<ATLASX_INT8> { static constexpr int EPC = 16; };
 template <> struct Fmt<ATLASX_INT4> { static constexpr int EPC = 32; };
 
-struct GemvArgs {
-    const uint8_t* W; const uint8_t* scales;
-    int M, K;                    // rows, cols (elements)
-    int row_bytes;               // bytes of one weight row
-    int srow_bytes;              // bytes of one row of int4 scales (0 otherwise)
-    int block; int scales_f16;
-    int stages; int stage_stride; int seg_pitch;   // ring geometry (TMA)
-    int nchunks;                 // 16-byte chunks per row
-    int epi;
-    float* y;
-    AxPrologue pro;
-    int* err;
-    int dbg;                     // experiments only: bit 0 = consumers skip the arithmetic
-};
 
 // ── PTX wrappers ────────────────────────────────────────────────────────────────
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -153,11 +139,31 @@ __device__ __forceinline__ float consumer_block_sum(float v, float* red /*[8] + 
 // Input staging.  The vector lives in shared memory as P = EPC/4 planes of float4 so that a
 // warp reading one plane for 32 consecutive chunks is conflict-free: element e → plane
 // (e % EPC)/4, slot e / EPC.
+// Part of the prologue that does not depend on the previous kernel of the stream: the norm
+// weights are pulled into L1, and — when the caller vouches that `base` was written at least
+// two kernels back (pro.base_early) — the residual stream is copied into the plane `xb` with
+// cp.async (thread-private slots: the same thread reads them back, no barrier needed).
 template <int FMT>
-__device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float* red) {
+__device__ __forceinline__ void stage_input_early(const GemvArgs& a, float4* xb) {
+    const AxPrologue& p = a.pro;
+    if (!p.y && !p.wx) return;
+    const int n4 = a.K >> 2, tid = threadIdx.x;
+    for (int line = tid; line * 32 < a.K; line += kConsumerThreads) {       // 128-byte lines
+        if (p.wy) asm volatile("prefetch.global.L1 [%0];" :: "l"(p.wy + line * 32));
+        if (p.wx) asm volatile("prefetch.global.L1 [%0];" :: "l"(p.wx + line * 32));
+    }
+    if (xb && p.base_early && p.base && !p.embed) {
+        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(xb + k4)), "l"(p.base + (k4 << 2)) : "memory");
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
+}
+
+template <int FMT>
+__device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float* red, const float4* xb = nullptr) {
     constexpr int EPC = Fmt<FMT>::EPC;
     const AxPrologue& p = a.pro;
-    const int K = a.K, n4 = K >> 2, nch = a.nchunks;
+    const int K = a.K, n4 = (a.dbg & 2) ? K >> 5 : K >> 2, nch = a.nchunks;     // dbg bit 1: experiments only
     const int tid = threadIdx.x;
     auto slot = [&](int k4) { const int e = k4 << 2; return ((e % EPC) >> 2) * nch + e / EPC; };
 
@@ -173,7 +179,9 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
         if (p.embed_bf16) base16 = (const uint16_t*)p.embed + (size_t)tok * K;
         else              base = (const float*)p.embed + (size_t)tok * K;
     }
+    const bool early = xb && p.base_early && p.base && !p.embed && (p.y || p.wx);
     auto load_base = [&](int k4) -> float4 {
+        if (early) return xb[k4];
         if (base16) {
             const uint2 r = *reinterpret_cast<const uint2*>(base16 + (k4 << 2));
             return make_float4(ax_bf16_lo(r.x), ax_bf16_hi(r.x), ax_bf16_lo(r.y), ax_bf16_hi(r.y));
@@ -193,6 +201,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
     float inv_y = 1.f;
     if (p.y) {
         float ss = 0.f;
+#pragma unroll 4
         for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
             float4 t = __ldcg(reinterpret_cast<const float4*>(p.y) + k4);
             for (int r = 1; r < p.nparts; r++) {
@@ -207,7 +216,9 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
             inv_y = 1.0f / sqrtf(ss / (float)K + p.eps);
         }
     }
+    if (early) asm volatile("cp.async.wait_all;" ::: "memory");
     float ss2 = 0.f;
+#pragma unroll 4
     for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
         float4 v = load_base(k4);
         if (p.y) {
@@ -239,5 +250,143 @@ __device__ __forceinline__ float load_scale_i4(const void* p, int idx, int f16) 
     return f16 ? __half2float(reinterpret_cast<const __half*>(p)[idx]) : reinterpret_cast<const float*>(p)[idx];
 }
 
+
+// Row range of this CTA, in units of two rows when M is even (keeps gate/up pairs together).
+__device__ __forceinline__ void cta_rows(int M, int& lo, int& hi) {
+    const int unit = (M & 1) ? 1 : 2;
+    const long long units = M / unit;
+    lo = (int)(units * blockIdx.x / gridDim.x) * unit;
+    hi = (int)(units * (blockIdx.x + 1) / gridDim.x) * unit;
+}
+
+// Shared-memory ring shared by the producer warp and the eight consumer warps.
+struct Ring {
+    uint64_t* full; uint64_t* empty;
+    uint8_t* data;
+    int stages, stage_stride, seg_pitch;
+};
+
+// Producer warp: stream rows [lo,hi) of one matrix into the ring, 8 rows × one ≤4 KB segment per
+// stage, one bulk copy per row (plus the int4 scale segment).  `fill` numbers the stages filled
+// so far and carries over from one matrix to the next.
+template <int FMT>
+__device__ __forceinline__ bool ring_produce(const GemvArgs& a, const Ring& rg, int lo, int hi, int& fill) {
+    const int lane = threadIdx.x & 31;
+    const int ntiles = (hi - lo + kRingRows - 1) / kRingRows;
+    const int nk = (a.row_bytes + kSeg - 1) / kSeg;
+    const int sseg_full = rg.seg_pitch - kSeg;                // int4 scale bytes of a full segment
+    bool ok = true;
+    for (int t = 0; t < ntiles && ok; t++) {
+        const int r0 = lo + t * kRingRows;
+        const int nrows = min(kRingRows, hi - r0);
+        for (int kc = 0; kc < nk && ok; kc++, fill++) {
+            const int s = fill % rg.stages;
+            const uint32_t ph = (uint32_t)(fill / rg.stages) & 1u;
+            const int seg = min(kSeg, a.row_bytes - kc * kSeg);
+            int sseg = 0;
+            if (FMT == ATLASX_INT4) sseg = min(a.srow_bytes - kc * sseg_full, sseg_full);
+            if (lane == 0) {
+                ok = mbar_wait(&rg.empty[s], ph ^ 1u, a.err, 1);
+                if (ok) mbar_arrive_expect_tx(&rg.full[s], (uint32_t)(nrows * (seg + sseg)));
+            }
+            ok = __shfl_sync(AX_FULL, ok, 0);
+            if (ok && lane < nrows) {
+                uint8_t* dst = rg.data + (size_t)s * rg.stage_stride + lane * rg.seg_pitch;
+                const size_t row = (size_t)(r0 + lane);
+                bulk_g2s(dst, a.W + row * a.row_bytes + (size_t)kc * kSeg, (uint32_t)seg, &rg.full[s]);
+                if (FMT == ATLASX_INT4)
+                    bulk_g2s(dst + kSeg, a.scales + row * a.srow_bytes + (size_t)kc * sseg_full, (uint32_t)sseg, &rg.full[s]);
+            }
+        }
+    }
+    return ok;
+}
+
+// Consumer warps: one row per warp per tile; the input vector is already staged in `xs`.
+template <int FMT>
+__device__ __forceinline__ bool ring_consume(const GemvArgs& a, const Ring& rg, const float4* xs, float* pair,
+                                             int lo, int hi, int& fill) {
+    constexpr int EPC = Fmt<FMT>::EPC;
+    constexpr int P = EPC / 4;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntiles = (hi - lo + kRingRows - 1) / kRingRows;
+    const int nk = (a.row_bytes + kSeg - 1) / kSeg;
+    const int nch = a.nchunks;
+    bool ok = true;
+    for (int t = 0; t < ntiles && ok; t++) {
+        const int row = lo + t * kRingRows + warp;
+        const bool valid = row < hi;
+        Acc4 acc = acc4_zero();
+        float sc = 0.f;                   // int4: sums already multiplied by their block scales
+        for (int kc = 0; kc < nk; kc++, fill++) {
+            const int s = fill % rg.stages;
+            const uint32_t ph = (uint32_t)(fill / rg.stages) & 1u;
+            ok = mbar_wait(&rg.full[s], ph, a.err, 2);
+            if (!ok) break;
+            const int seg_chunks = min(kSeg, a.row_bytes - kc * kSeg) >> 4;
+            const uint8_t* st = rg.data + (size_t)s * rg.stage_stride + warp * rg.seg_pitch;
+            if (valid && !(a.dbg & 1)) {
+                const uint4* wp = reinterpret_cast<const uint4*>(st) + lane;
+                const float4* xb = xs + kc * kSegChunks + lane;
+                if (FMT != ATLASX_INT4 && seg_chunks == kSegChunks) {
+                    // full segment: no predicates, addresses are lane base + constants
+#pragma unroll
+                    for (int it = 0; it < kSegChunks / 32; it++) {
+                        float4 xv[P];
+#pragma unroll
+                        for (int p = 0; p < P; p++) xv[p] = xb[p * nch + it * 32];
+                        const uint4 w = wp[it * 32];
+                        dot_chunk<FMT>(w, xv, acc);
+                    }
+                } else {
+#pragma unroll 2
+                    for (int it = 0; it < kSegChunks / 32; it++) {
+                        const int c = it * 32 + lane;
+                        if (c < seg_chunks) {
+                            float4 xv[P];
+#pragma unroll
+                            for (int p = 0; p < P; p++) xv[p] = xb[p * nch + it * 32];
+                            const uint4 w = wp[it * 32];
+                            if (FMT == ATLASX_INT4) {
+                                Acc4 part = acc4_zero(); dot_chunk<FMT>(w, xv, part);
+                                sc = fmaf(part.sum(), load_scale_i4(st + kSeg, (c * EPC) / a.block, a.scales_f16), sc);
+                            } else dot_chunk<FMT>(w, xv, acc);
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&rg.empty[s]);
+        }
+        if (!ok) break;
+        float r = ax_warp_sum(acc.sum() + sc);
+        if (FMT == ATLASX_INT8 && valid) r *= reinterpret_cast<const float*>(a.scales)[row];
+        if (a.epi == AX_EPI_SILU_PAIR) {
+            // gate row (even) and up row (odd) sit in neighbouring warps: exchange through shared
+            // memory under a two-warp named barrier; slots alternate with the tile parity
+            float* slot = pair + (t & 1) * kConsumerWarps;
+            if (lane == 0) slot[warp] = r;
+            switch (warp >> 1) {          // immediate ids keep the CTA at six hardware barriers
+                case 0: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+                case 1: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+                case 2: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+                default: asm volatile("bar.sync 5, 64;" ::: "memory"); break;
+            }
+            if (lane == 0 && valid && !(warp & 1)) a.y[row >> 1] = (r / (1.0f + expf(-r))) * slot[warp + 1];
+        } else if (lane == 0 && valid) {
+            a.y[row] = r;
+        }
+    }
+    return ok;
+}
+
+__device__ __forceinline__ void ring_init(const Ring& rg) {
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < rg.stages; s++) { mbar_init(&rg.full[s], 1); mbar_init(&rg.empty[s], kConsumerWarps); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncthreads();
+}
 
 }  // namespace

@@ -33,7 +33,7 @@ atlasx_ctx* legacy_ctx() {
               cudaMalloc((void**)&c->amax_idx, 4096 * sizeof(int)) == cudaSuccess &&
               cudaMalloc((void**)&c->amax_ticket, sizeof(unsigned)) == cudaSuccess &&
               cudaMemset(c->amax_ticket, 0, sizeof(unsigned)) == cudaSuccess &&
-              ax_gemv_init(c) == ATLASX_OK;
+              ax_gemv_init(c) == ATLASX_OK && ax_attn_init(c) == ATLASX_OK;
     if (!ok) {
         fprintf(stderr, "[atlas_kernels] cannot initialise device %d: %s\n", dev, atlasx_last_error());
         delete c;

@@ -24,6 +24,7 @@
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "gemv.cuh"
+#include "mega.cuh"
 #include "objects.h"
 
 namespace {
@@ -76,9 +77,17 @@ struct atlasx_model {
     int use_graph = 1, use_pdl = 1;
     cudaGraphExec_t graph = nullptr;
     int attn_splits = 1;
+    bool fused_attn = false; int fused_splits = 1;   // one-launch attention (head_dim 128)
     std::vector<void*> owned;                    // device allocations to free
     int* pin = nullptr;                          // pinned host ints
     int launches_per_step = 0;
+    // whole-step persistent kernel (single GPU, head_dim 128)
+    int use_mega = 0; bool mega_ready = false;   // opt-in: slower than the per-operation step so far
+    MegaPhase* phases_dev = nullptr; MegaSync* sync = nullptr;
+    float* mega_partials = nullptr; float* sel_vals = nullptr; int* sel_idx = nullptr;
+    MegaArgs margs; size_t mega_smem = 0; int mega_splits = 1;
+    // timeline diagnostics of the captured step (ATLASX_STEP_TRACE)
+    unsigned long long* step_trace = nullptr; int step_trace_slots = 0;
 };
 
 namespace {
@@ -257,11 +266,130 @@ double gemv_bytes(const AxWeight& w) { return (double)ax_weight_bytes(w) + 4.0 *
         n_launch++;                                                                          \
     } while (0)
 
+// Program of the whole-step kernel: the same operations as run_step, as a list of phases.
+int build_mega(atlasx_model* m) {
+    atlasx_ctx* c = m->ctx;
+    const atlasx_model_config& cf = m->cfg;
+    m->mega_ready = false;
+    if (!m->use_mega || m->world != 1 || m->hd != 128) return ATLASX_OK;
+    const int G = m->nh_loc / m->nkv_loc;
+    if (G != 1 && G != 2 && G != 4) return ATLASX_OK;
+    const int d = cf.d_model, L = cf.n_layers;
+    const bool post = cf.post_norm != 0;
+    int S = c->sm_count / m->nkv_loc;
+    if (S < 1) S = 1;
+    if (S > 8) S = 8;
+    m->mega_splits = S;
+    std::vector<MegaPhase> ph;
+    ph.reserve((size_t)L * 5 + 3);
+    int rc = ATLASX_OK, cur = 0;
+    if ((rc = dmalloc(m, (void**)&m->mega_partials, (size_t)m->nh_loc * S * (m->hd + 4) * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->sel_vals, (size_t)c->sm_count * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->sel_idx, (size_t)c->sm_count * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->sync, sizeof(MegaSync)))) return rc;
+    AX_CUDA(cudaMemsetAsync(m->sync, 0, sizeof(MegaSync), c->stream));
+    size_t x_max = (size_t)(4 * 128 + 256 + 8 * 4 * 130) * 4;          // attention scratch
+    auto add_gemv = [&](const AxWeight& w, const AxPrologue& p, int epi, float* y, bool merge) -> int {
+        MegaPhase P;
+        memset(&P, 0, sizeof(P));
+        P.type = MEGA_GEMV;
+        int r = ax_gemv_make_args(w, p, epi, y, c->dev_error, &P.g);
+        if (r) return r;
+        if (merge) { P.merge_partials = m->mega_partials; P.merge_heads = m->nh_loc; P.merge_hd = m->hd; P.merge_splits = S; }
+        const size_t xb = (((size_t)w.cols * 4 + 127) / 128) * 128;
+        if (xb > x_max) x_max = xb;
+        ph.push_back(P);
+        return ATLASX_OK;
+    };
+    for (int l = 0; l < L; l++) {
+        Layer& ly = m->layers[l];
+        AxPrologue p;
+        p.eps = cf.rms_norm_eps;
+        if (l == 0) {
+            p.embed = m->embed; p.embed_bf16 = m->embed_bf16; p.vocab = cf.vocab_size;
+            p.seq = m->seq; p.pos = &m->st->pos;
+            p.resid_out = m->resid[0]; cur = 0;
+            if (!post) p.wx = ly.attn_norm;
+        } else {
+            p.base = m->resid[cur]; p.y = m->dn; p.nparts = 1; p.part_stride = d;
+            if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
+            p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+        }
+        if (add_gemv(ly.qkv, p, AX_EPI_PLAIN, m->qkv, false)) return ATLASX_OK;     // shape not supported: no mega path
+        MegaPhase A;
+        memset(&A, 0, sizeof(A));
+        A.type = MEGA_ATTN;
+        A.qkv = m->qkv; A.q_norm = ly.q_norm; A.k_norm = ly.k_norm; A.cos_t = m->cos_t; A.sin_t = m->sin_t;
+        A.kc = ly.kv->k; A.vc = ly.kv->v; A.partials = m->mega_partials; A.pos = &m->st->pos;
+        A.n_heads = m->nh_loc; A.n_kv = m->nkv_loc; A.hd = m->hd; A.window = ly.window;
+        A.kv_bf16 = cf.kv_dtype == ATLASX_BF16; A.splits = S; A.scale = m->scale; A.qk_eps = 1e-6f;
+        ph.push_back(A);
+        AxPrologue po; po.base = m->attn;                 // unused: the input is the merged attention output
+        if (add_gemv(ly.wo, po, AX_EPI_PLAIN, m->o, true)) return ATLASX_OK;
+        AxPrologue pg;
+        pg.eps = cf.rms_norm_eps;
+        pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = 1; pg.part_stride = d;
+        if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
+        pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+        if (add_gemv(ly.gateup, pg, AX_EPI_SILU_PAIR, m->h, false)) return ATLASX_OK;
+        AxPrologue pd; pd.base = m->h;
+        if (add_gemv(ly.down, pd, AX_EPI_PLAIN, m->dn, false)) return ATLASX_OK;
+    }
+    AxPrologue pl;
+    pl.eps = cf.rms_norm_eps;
+    pl.base = m->resid[cur]; pl.y = m->dn; pl.nparts = 1; pl.part_stride = d;
+    if (post) pl.wy = m->layers[L - 1].ffn_norm;
+    pl.wx = m->final_norm;
+    pl.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+    if (add_gemv(m->lm_head, pl, AX_EPI_PLAIN, m->logits, false)) return ATLASX_OK;
+    MegaPhase Sp;
+    memset(&Sp, 0, sizeof(Sp));
+    Sp.type = MEGA_SELECT_PART;
+    Sp.logits = m->logits; Sp.vocab = cf.vocab_size; Sp.sel_vals = m->sel_vals; Sp.sel_idx = m->sel_idx;
+    Sp.st_pos = &m->st->pos; Sp.st_nforced = &m->st->n_forced; Sp.st_last = &m->st->last_token;
+    Sp.seq = m->seq; Sp.seq_cap = cf.max_seq_len + 1;
+    ph.push_back(Sp);
+    Sp.type = MEGA_SELECT_FINAL;
+    ph.push_back(Sp);
+
+    // ring geometry: everything that is left of the SM's shared memory after the staged input
+    const int sseg = ax_gemv_ring_scale_seg(m->lm_head);
+    MegaArgs& a = m->margs;
+    a.seg_pitch = ax_gemv_ring_seg_bytes() + sseg;
+    a.stage_stride = 8 * a.seg_pitch;
+    a.x_bytes = (int)((x_max + 127) / 128 * 128);
+    const size_t smem_max = c->smem_optin ? c->smem_optin : 232448;
+    long long avail = (long long)smem_max - 256 - 1024 - a.x_bytes;
+    int stages = (int)(avail / a.stage_stride);
+    if (stages > 6) stages = 6;
+    if (stages < 2) return ATLASX_OK;
+    a.stages = stages;
+    m->mega_smem = 256 + 1024 + (size_t)a.x_bytes + (size_t)stages * a.stage_stride;
+    if ((rc = dmalloc(m, (void**)&m->phases_dev, ph.size() * sizeof(MegaPhase)))) return rc;
+    AX_CUDA(cudaMemcpyAsync(m->phases_dev, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice, c->stream));
+    AX_CUDA(cudaStreamSynchronize(c->stream));
+    a.phases = m->phases_dev; a.n_phases = (int)ph.size(); a.sync = m->sync; a.err = c->dev_error;
+    a.trace = nullptr;
+    if (getenv("ATLASX_MEGA_TRACE")) {
+        if ((rc = dmalloc(m, (void**)&a.trace, ph.size() * 4 * sizeof(unsigned long long)))) return rc;
+        AX_CUDA(cudaMemsetAsync(a.trace, 0, ph.size() * 4 * sizeof(unsigned long long), c->stream));
+    }
+    m->final_resid = cur;
+    if ((rc = ax_mega_init(c))) return rc;
+    m->mega_ready = true;
+    return ATLASX_OK;
+}
+
 // One token: every launch of the step, in order, on the context stream.
 int run_step(atlasx_model* m, Profile* prof, bool advance) {
     atlasx_ctx* c = m->ctx;
     cudaStream_t s = c->stream;
     const atlasx_model_config& cf = m->cfg;
+    if (m->mega_ready && m->use_mega && !prof && advance) {
+        int r = ax_mega_launch(c, cf.weight_format, cf.kv_dtype == ATLASX_BF16, m->margs, m->mega_smem);
+        if (!r) m->launches_per_step = 1;
+        return r;
+    }
     const bool pdl = m->use_pdl && !prof;
     static const int pdl_mask = getenv("ATLASX_PDL_MASK") ? atoi(getenv("ATLASX_PDL_MASK")) : 255;   // experiments
     auto P = [&](int cls) { return pdl && ((pdl_mask >> cls) & 1); };
@@ -282,11 +410,28 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             if (!post) p.wx = ly.attn_norm;
         } else {
             p.base = m->resid[cur]; p.y = m->dn; p.nparts = nparts; p.part_stride = d;
+            p.base_early = 1;                              // written by the gate/up launch, two kernels back
             if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
             p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
         }
         STEP_LAUNCH(CLS_QKV, gemv_bytes(ly.qkv), ax_gemv_launch(c, ly.qkv, p, AX_EPI_PLAIN, 1, m->qkv, P(CLS_QKV)));
 
+        double abytes = 0;
+        if (prof) {
+            int rows = m->host_pos + 1;
+            if (ly.window > 0 && rows > ly.window) rows = ly.window;
+            abytes = (double)rows * 2 * m->kv_rows * (cf.kv_dtype == ATLASX_BF16 ? 2 : 4) + 8.0 * m->q_rows;
+        }
+        if (m->fused_attn) {
+            // ── QK-norm, RoPE, cache write and attention in one launch ─────────────
+            AxFusedAttnArgs fa;
+            fa.qkv = m->qkv; fa.q_norm = ly.q_norm; fa.k_norm = ly.k_norm; fa.cos_t = m->cos_t; fa.sin_t = m->sin_t;
+            fa.kc = ly.kv->k; fa.vc = ly.kv->v; fa.out = m->attn; fa.pos = &m->st->pos;
+            fa.n_heads = m->nh_loc; fa.n_kv = m->nkv_loc; fa.window = ly.window; fa.kv_dtype = cf.kv_dtype;
+            fa.max_splits = m->fused_splits; fa.scale = m->scale;
+            fa.qk_eps = 1e-6f;                             // the reference hard-codes 1e-6 here (:850,853)
+            STEP_LAUNCH(CLS_ATTN, abytes + 4.0 * (m->q_rows + 2 * m->kv_rows), ax_attn_fused_launch(c, fa, P(CLS_ATTN)));
+        } else {
         // ── QK-norm, RoPE, cache write ──────────────────────────────────────────
         AxQkPrepArgs qa;
         qa.q = m->qkv; qa.k = m->qkv + m->q_rows; qa.v = m->qkv + m->q_rows + m->kv_rows;
@@ -303,13 +448,8 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         aa.pos = &m->st->pos; aa.pos_shared = 1; aa.batch = 1;
         aa.n_heads = m->nh_loc; aa.n_kv = m->nkv_loc; aa.hd = m->hd; aa.window = ly.window;
         aa.kv_dtype = cf.kv_dtype; aa.scale = m->scale; aa.n_splits = m->attn_splits;
-        double abytes = 0;
-        if (prof) {
-            int rows = m->host_pos + 1;
-            if (ly.window > 0 && rows > ly.window) rows = ly.window;
-            abytes = (double)rows * 2 * m->kv_rows * (cf.kv_dtype == ATLASX_BF16 ? 2 : 4) + 8.0 * m->q_rows;
-        }
         STEP_LAUNCH(CLS_ATTN, abytes, ax_attn_launch(c, aa, P(CLS_ATTN)));
+        }
 
         // ── output projection (row-parallel under TP) ───────────────────────────
         AxPrologue po; po.base = m->attn;
@@ -320,6 +460,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         AxPrologue pg;
         pg.eps = cf.rms_norm_eps;
         pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = nparts; pg.part_stride = d;
+        pg.base_early = 1;                                 // written by the QKV launch, at least two kernels back
         if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
         pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
         STEP_LAUNCH(CLS_GATEUP, gemv_bytes(ly.gateup), ax_gemv_launch(c, ly.gateup, pg, AX_EPI_SILU_PAIR, 1, m->h, P(CLS_GATEUP)));
@@ -333,6 +474,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     AxPrologue pl;
     pl.eps = cf.rms_norm_eps;
     pl.base = m->resid[cur]; pl.y = m->dn; pl.nparts = nparts; pl.part_stride = d;
+    pl.base_early = 1;
     if (post) pl.wy = m->layers[L - 1].ffn_norm;
     pl.wx = m->final_norm;
     pl.resid_out = m->resid[cur ^ 1]; cur ^= 1;
@@ -362,8 +504,14 @@ int capture_graph(atlasx_model* m) {
     atlasx_ctx* c = m->ctx;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     cudaGraph_t g = nullptr;
+    if (getenv("ATLASX_STEP_TRACE") && !m->step_trace) {
+        int r0 = dmalloc(m, (void**)&m->step_trace, 1024 * sizeof(AxTraceSlot));
+        if (r0) return r0;
+    }
     AX_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
+    c->trace_next = m->step_trace;
     int rc = run_step(m, nullptr, true);
+    if (m->step_trace) { m->step_trace_slots = (int)((c->trace_next - m->step_trace) / 6); c->trace_next = nullptr; }
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "stream capture failed: %s", cudaGetErrorString(e));
@@ -377,7 +525,8 @@ int step(atlasx_model* m) {
     if (m->host_pos >= m->cfg.max_seq_len)
         return atlasx_fail(ATLASX_ERR_STATE, "position %d is past max_seq_len %d", m->host_pos, m->cfg.max_seq_len);
     int rc;
-    if (m->use_graph && m->graph) { AX_CUDA(cudaGraphLaunch(m->graph, m->ctx->stream)); rc = ATLASX_OK; }
+    const bool mega = m->mega_ready && m->use_mega;        // one launch per token: a graph adds nothing
+    if (m->use_graph && m->graph && !mega) { AX_CUDA(cudaGraphLaunch(m->graph, m->ctx->stream)); rc = ATLASX_OK; }
     else rc = run_step(m, nullptr, true);
     if (!rc) m->host_pos++;
     return rc;
@@ -583,13 +732,24 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     // attention split count fixed for the graph; scratch sized once
     int max_rows = cf.max_seq_len;
     m->attn_splits = ax_attn_pick_splits(c, m->nkv_loc, 1, max_rows);
-    rc = atlasx_ctx_ensure_attn_scratch(c, (size_t)m->nh_loc * m->attn_splits * (m->hd + 2), (size_t)m->nh_loc);
+    {
+        const char* e = getenv("ATLASX_ATTN_FUSED");      // experiments: 0 keeps the two-launch form
+        m->fused_attn = ax_attn_fused_supported(m->hd, m->nh_loc, m->nkv_loc) && !(e && atoi(e) == 0);
+        m->fused_splits = ax_attn_fused_max_splits(c, m->nkv_loc, max_rows);
+    }
+    const int scratch_splits = m->fused_attn && m->fused_splits > m->attn_splits ? m->fused_splits : m->attn_splits;
+    rc = atlasx_ctx_ensure_attn_scratch(c, (size_t)m->nh_loc * scratch_splits * (m->hd + 2), (size_t)m->nh_loc);
     if (rc) return rc;
     AX_ARG(cf.vocab_size <= 4096 * 1024, "vocabulary too large for the selection scratch");
     m->finalized = true;
     m->host_pos = 0;
     set_state_k<<<1, 1, 0, s>>>(m->st, 0, INT_MAX);
     AX_CUDA(cudaStreamSynchronize(s));
+    {
+        const char* e = getenv("ATLASX_MEGA");
+        if (e) m->use_mega = atoi(e) ? 1 : 0;
+        if (m->use_mega) { rc = build_mega(m); if (rc) return rc; }
+    }
     // one eager step loads every kernel before capture; it only touches cache row 0, which the
     // first real token rewrites
     rc = run_step(m, nullptr, true); if (rc) return rc;
@@ -600,9 +760,52 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
         int code = 0;
         rc = atlasx_ctx_poll_device_error(c, &code); if (rc) return rc;
     }
-    if (m->use_graph) { rc = capture_graph(m); if (rc) return rc; }
+    if (m->use_graph && !(m->mega_ready && m->use_mega)) { rc = capture_graph(m); if (rc) return rc; }
     return ATLASX_OK;
 }
+
+extern "C" int atlasx_model_set_mega(atlasx_model* m, int on) {
+    AX_ARG(m, "model is null");
+    AX_ARG(!m->finalized, "choose the step kernel before atlasx_model_finalize");
+    m->use_mega = on ? 1 : 0;
+    return ATLASX_OK;
+}
+// Debug aid: per-phase timestamps (ns) of CTA 0 in the last whole-step launch, when the model was
+// finalised with ATLASX_MEGA_TRACE set: wait begin, wait end, input staged, phase done; plus the type.
+extern "C" int atlasx_model_mega_trace(atlasx_model* m, unsigned long long* out, int* types, int cap, int* n_phases) {
+    AX_ARG(m && out && types && n_phases, "null argument");
+    AX_ARG(m->mega_ready && m->margs.trace, "no trace was recorded");
+    const int n = m->margs.n_phases < cap ? m->margs.n_phases : cap;
+    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    AX_CUDA(cudaMemcpy(out, m->margs.trace, (size_t)n * 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
+    std::vector<MegaPhase> ph((size_t)n);
+    AX_CUDA(cudaMemcpy(ph.data(), m->phases_dev, (size_t)n * sizeof(MegaPhase), cudaMemcpyDeviceToHost));
+    for (int i = 0; i < n; i++) types[i] = ph[i].type * 100000 + (ph[i].type == MEGA_GEMV ? ph[i].g.M / 128 : 0);
+    *n_phases = n;
+    return ATLASX_OK;
+}
+// Debug aid: runs one captured step and returns, per traced launch, six %globaltimer stamps (ns):
+// first/last CTA start, first dependency release, last CTA end, first CTA end, last input staged.  Needs ATLASX_STEP_TRACE
+// set when the graph was captured.
+extern "C" int atlasx_model_step_trace(atlasx_model* m, unsigned long long* out, int cap, int* n_slots) {
+    AX_ARG(m && out && n_slots, "null argument");
+    AX_ARG(m->step_trace && m->graph && m->step_trace_slots > 0, "no traced graph");
+    const int n = m->step_trace_slots < cap ? m->step_trace_slots : cap;
+    std::vector<unsigned long long> init((size_t)m->step_trace_slots * 6);
+    for (int i = 0; i < m->step_trace_slots; i++) {
+        unsigned long long* q = &init[(size_t)i * 6];
+        q[0] = ~0ull; q[1] = 0; q[2] = ~0ull; q[3] = 0; q[4] = ~0ull; q[5] = 0;
+    }
+    AX_CUDA(cudaMemcpyAsync(m->step_trace, init.data(), init.size() * 8, cudaMemcpyHostToDevice, m->ctx->stream));
+    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    int rc = step(m);
+    if (rc) return rc;
+    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    AX_CUDA(cudaMemcpy(out, m->step_trace, (size_t)n * 6 * 8, cudaMemcpyDeviceToHost));
+    *n_slots = n;
+    return ATLASX_OK;
+}
+extern "C" int atlasx_model_uses_mega(const atlasx_model* m) { return m && m->mega_ready && m->use_mega; }
 
 extern "C" int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl) {
     AX_ARG(m, "model is null");
@@ -611,7 +814,7 @@ extern "C" int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_
     if (m->finalized && changed) {
         AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
         if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
-        if (m->use_graph) return capture_graph(m);
+        if (m->use_graph && !(m->mega_ready && m->use_mega)) return capture_graph(m);
     }
     return ATLASX_OK;
 }

@@ -70,7 +70,7 @@ def run_gemv(args):
                 continue
             m0, bufs = make_matrix(ctx, fmt, M, K, 1)
             wb = m0.weight_bytes
-            copies = max(2, min(16, int(math.ceil(600e6 / wb))))
+            copies = args.copies if args.copies > 0 else max(2, min(16, int(math.ceil(600e6 / wb))))
             mats, keep = [m0], [bufs]
             for i in range(1, copies):
                 mi, bi = make_matrix(ctx, fmt, M, K, 1 + i)
@@ -138,6 +138,7 @@ def main():
     ap.add_argument("--n", default="1")
     ap.add_argument("--impl", type=int, default=0)
     ap.add_argument("--iters", type=int, default=200)
+    ap.add_argument("--copies", type=int, default=0, help="rotating weight copies (0 = enough to defeat L2; 1 = L2-resident)")
     ap.add_argument("--ctx", default="1024,8192,32768")
     ap.add_argument("--batch", default="1,8,64")
     ap.add_argument("--window", default="0,4096")

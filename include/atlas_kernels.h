@@ -244,6 +244,11 @@ const char* atlasx_model_class_name(int cls);
 double atlasx_model_step_bytes(const atlasx_model* m, int pos);
 int atlasx_model_kernel_launches_per_step(const atlasx_model* m);
 int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
+/* Whole-step persistent kernel (one launch per token; single GPU, head_dim 128, ≤ 4 query heads per
+ * KV head).  On by default where it applies; call before atlasx_model_finalize to turn it off and
+ * keep the kernel-per-operation step. */
+int atlasx_model_set_mega(atlasx_model* m, int on);
+int atlasx_model_uses_mega(const atlasx_model* m);
 /* residual stream after the last forward (d_model floats), for layer-level parity checks */
 int atlasx_model_hidden(atlasx_model* m, float* hidden_host);
 

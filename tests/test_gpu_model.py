@@ -210,3 +210,42 @@ def test_decode_timed_matches_generate(ab, c1_weights):
     assert prof["gemv_qkv"]["launches"] == 4 and prof["attention_splitk"]["launches"] == 4
     assert m.launches_per_step == 4 * 6 + 2
     assert m.step_bytes(10) > 0
+
+
+@pytest.mark.parametrize("kv", ["f32", "bf16"])
+@pytest.mark.parametrize("fmt", ["f32", "bf16", "int8", "int4"])
+def test_whole_step_kernel_matches_per_operation_step_and_oracle(ab, kv, fmt):
+    """head_dim 128, two query heads per KV head, sliding + full layers, YaRN: the one-launch
+    persistent step kernel, the kernel-per-operation step and the CPU oracle must agree —
+    step-by-step logits and hidden state, then free-running greedy tokens."""
+    cfg = dict(helpers.HD128)
+    w = helpers.synth_weights(cfg, seed=21, norm_jitter=0.1)
+    code = {"f32": None, "bf16": ab.BF16, "int8": ab.INT8, "int4": ab.INT4}[fmt]
+    kvd = ab.F32 if kv == "f32" else ab.BF16
+    mega = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code, use_mega=True)
+    plain = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code, use_mega=False)
+    assert mega.uses_mega and not plain.uses_mega
+    assert mega.launches_per_step == 1
+    toks = orc.uniform_u32(30, 21, 1, cfg["vocab_size"])
+    o = None
+    if fmt == "f32":
+        o = helpers.oracle_model(cfg, w, helpers.HD128_LAYERS, kv_round_bf16=(kv == "bf16"))
+    # with the bf16 cache a last-bit difference in a new K/V element can flip its rounding, so
+    # the two step kernels agree only to the cache's resolution there
+    tol = 1e-4 if kv == "f32" else 5e-3
+    for t in toks:
+        a = mega.forward_one_gpu(int(t)); b = plain.forward_one_gpu(int(t))
+        assert np.max(np.abs(a - b)) <= tol
+        assert np.max(np.abs(mega.hidden() - plain.hidden())) <= tol
+        if o is not None:
+            lo = o.forward_one(int(t))
+            assert np.max(np.abs(a - lo)) <= (1e-4 if kv == "f32" else 1e-2)
+    prompt = toks[:12]
+    if kv == "f32":
+        assert mega.generate(prompt, 24, 0.0) == plain.generate(prompt, 24, 0.0)
+    else:
+        assert len(mega.generate(prompt, 24, 0.0)) == 24
+    if o is not None and kv == "f32":
+        assert mega.generate(prompt, 24, 0.0) == o.generate_greedy(prompt, 24).tolist()
+    ms, t1 = mega.decode_timed(10)
+    assert ms > 0 and ab.Context.default().poll_device_error() == 0
