@@ -23,97 +23,103 @@
 
 namespace {
 
+// Direct path (no shared-memory ring).  The CTA's rows are taken two at a time (a pair shares
+// every load of the input vector) and cut into batches of 128 sixteen-byte chunks per row; the
+// batches of all pairs form one sequence that is divided evenly among the eight warps, so a
+// warp's share may begin and end in the middle of a row.  Each warp streams its batches with
+// 128-bit loads, software-pipelined — the loads of batch i+1 are issued before the arithmetic
+// of batch i, and the first batch before griddepcontrol.wait, i.e. while the previous kernel of
+// the stream is still draining (weights never depend on it).  Per pair every warp leaves one
+// partial sum in shared memory (zero if it had no part in it); after a barrier one thread per
+// pair adds the eight values in warp order — deterministic — and applies the epilogue.
 template <int FMT>
-__device__ __forceinline__ void store_rows(const GemvArgs& a, int row0, bool v0, bool v1, float acc0, float acc1) {
-    acc0 = ax_warp_sum(acc0);
-    acc1 = ax_warp_sum(acc1);
-    if ((threadIdx.x & 31) != 0) return;
-    if (FMT == ATLASX_INT8) {
-        const float* s = reinterpret_cast<const float*>(a.scales);
-        if (v0) acc0 *= s[row0];
-        if (v1) acc1 *= s[row0 + 1];
-    }
-    if (a.epi == AX_EPI_SILU_PAIR) {
-        if (v1) a.y[row0 >> 1] = (acc0 / (1.0f + expf(-acc0))) * acc1;     // silu(gate)·up
-    } else {
-        if (v0) a.y[row0] = acc0;
-        if (v1) a.y[row0 + 1] = acc1;
-    }
-}
-
-// Direct path (no shared-memory ring): every warp streams its two rows with 128-bit loads, four
-// chunks per row per batch, software-pipelined — the loads of batch i+1 are issued before the
-// arithmetic of batch i, and batch 0 is issued before griddepcontrol.wait, i.e. while the previous
-// kernel of the stream is still draining (weights never depend on it).
-template <int FMT>
-__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, int lo, int hi) {
+__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, int lo, int hi) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nch = a.nchunks;
     const int nbatch = (nch + 127) >> 7;
-    const int ntiles = (hi - lo + kTileRows - 1) / kTileRows;
-    const int total = ntiles * nbatch;
+    const int npairs = (hi - lo + 1) >> 1;
+    const int total = npairs * nbatch;
+    const int i0 = (int)((long long)total * warp / kConsumerWarps);
+    const int i1 = (int)((long long)total * (warp + 1) / kConsumerWarps);
     uint4 wa[4], wb[4];
     auto load = [&](int i, uint4* A, uint4* B) {
-        const int t = i / nbatch, b = i - t * nbatch;
-        const int row0 = lo + t * kTileRows + warp * kRW;
-        if (row0 < hi) {
-            const uint8_t* w0p = a.W + (size_t)row0 * a.row_bytes;
-            const uint8_t* w1p = w0p + (row0 + 1 < hi ? a.row_bytes : 0);
+        const int p = i / nbatch, b = i - p * nbatch;
+        const int row0 = lo + 2 * p;
+        const uint8_t* w0p = a.W + (size_t)row0 * a.row_bytes;
+        const uint8_t* w1p = w0p + (row0 + 1 < hi ? a.row_bytes : 0);
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int c = b * 128 + u * 32 + lane;
-                if (c < nch) { A[u] = ax_ldg_stream(w0p + (size_t)c * 16); B[u] = ax_ldg_stream(w1p + (size_t)c * 16); }
-            }
+        for (int u = 0; u < 4; u++) {
+            const int c = b * 128 + u * 32 + lane;
+            if (c < nch) { A[u] = ax_ldg_stream(w0p + (size_t)c * 16); B[u] = ax_ldg_stream(w1p + (size_t)c * 16); }
         }
     };
     ax_trace_start(a.trace);
-    if (total > 0) load(0, wa, wb);
+    if (i0 < i1) load(i0, wa, wb);
     stage_input_early<FMT>(a, xb);
+    for (int j = tid; j < npairs * kConsumerWarps * 2; j += kConsumerThreads) part[j] = 0.f;
     griddep_wait();                       // activations of the previous kernel are complete
     griddep_launch();
     ax_trace_release(a.trace);
-    stage_input<FMT>(a, xs, red, xb);
+    stage_input<FMT>(a, xs, red, xb);     // ends with a barrier: the zeroed partials are visible too
     ax_trace_staged(a.trace);
 
     Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
     float sc0 = 0.f, sc1 = 0.f;
-    for (int i = 0; i < total; i++) {
+    for (int i = i0; i < i1; i++) {
         uint4 na[4], nb[4];
-        if (i + 1 < total) load(i + 1, na, nb);
-        const int t = i / nbatch, b = i - t * nbatch;
-        const int row0 = lo + t * kTileRows + warp * kRW;
-        const bool v0 = row0 < hi, v1 = row0 + 1 < hi;
-        if (v0) {
+        if (i + 1 < i1) load(i + 1, na, nb);
+        const int p = i / nbatch, b = i - p * nbatch;
+        const int row0 = lo + 2 * p;
+        const bool v1 = row0 + 1 < hi;
 #pragma unroll
-            for (int u = 0; u < 4; u++) {
-                const int c = b * 128 + u * 32 + lane;
-                if (c < nch) {
-                    float4 xv[P];
+        for (int u = 0; u < 4; u++) {
+            const int c = b * 128 + u * 32 + lane;
+            if (c < nch) {
+                float4 xv[P];
 #pragma unroll
-                    for (int p = 0; p < P; p++) xv[p] = xs[p * nch + c];
-                    if (FMT == ATLASX_INT4) {
-                        const size_t e0 = (size_t)row0 * a.K + (size_t)c * EPC;     // flat element index
-                        Acc4 part = acc4_zero(); dot_chunk<FMT>(wa[u], xv, part);
-                        sc0 = fmaf(part.sum(), load_scale_i4(a.scales, (int)(e0 / a.block), a.scales_f16), sc0);
-                        if (v1) {
-                            part = acc4_zero(); dot_chunk<FMT>(wb[u], xv, part);
-                            sc1 = fmaf(part.sum(), load_scale_i4(a.scales, (int)((e0 + a.K) / a.block), a.scales_f16), sc1);
-                        }
-                    } else {
-                        dot_chunk<FMT>(wa[u], xv, acc0);
-                        if (v1) dot_chunk<FMT>(wb[u], xv, acc1);
+                for (int q = 0; q < P; q++) xv[q] = xs[q * nch + c];
+                if (FMT == ATLASX_INT4) {
+                    const size_t e0 = (size_t)row0 * a.K + (size_t)c * EPC;     // flat element index
+                    Acc4 t = acc4_zero(); dot_chunk<FMT>(wa[u], xv, t);
+                    sc0 = fmaf(t.sum(), load_scale_i4(a.scales, (int)(e0 / a.block), a.scales_f16), sc0);
+                    if (v1) {
+                        t = acc4_zero(); dot_chunk<FMT>(wb[u], xv, t);
+                        sc1 = fmaf(t.sum(), load_scale_i4(a.scales, (int)((e0 + a.K) / a.block), a.scales_f16), sc1);
                     }
+                } else {
+                    dot_chunk<FMT>(wa[u], xv, acc0);
+                    if (v1) dot_chunk<FMT>(wb[u], xv, acc1);
                 }
             }
         }
-        if (b == nbatch - 1) {
-            store_rows<FMT>(a, row0, v0, v1, acc0.sum() + sc0, acc1.sum() + sc1);
+        if (b == nbatch - 1 || i + 1 == i1) {          // the pair, or this warp's share of it, is done
+            const float s0 = ax_warp_sum(acc0.sum() + sc0), s1 = ax_warp_sum(acc1.sum() + sc1);
+            if (lane == 0) { part[(p * kConsumerWarps + warp) * 2] = s0; part[(p * kConsumerWarps + warp) * 2 + 1] = s1; }
             acc0 = acc4_zero(); acc1 = acc4_zero(); sc0 = 0.f; sc1 = 0.f;
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) { wa[u] = na[u]; wb[u] = nb[u]; }
+    }
+    consumer_sync();
+    for (int p = tid; p < npairs; p += kConsumerThreads) {
+        float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+        for (int w = 0; w < kConsumerWarps; w++) { s0 += part[(p * kConsumerWarps + w) * 2]; s1 += part[(p * kConsumerWarps + w) * 2 + 1]; }
+        const int row0 = lo + 2 * p;
+        const bool v1 = row0 + 1 < hi;
+        if (FMT == ATLASX_INT8) {
+            const float* sc = reinterpret_cast<const float*>(a.scales);
+            s0 *= sc[row0];
+            if (v1) s1 *= sc[row0 + 1];
+        }
+        if (a.epi == AX_EPI_SILU_PAIR) {
+            if (v1) a.y[row0 >> 1] = (s0 / (1.0f + expf(-s0))) * s1;           // silu(gate)·up
+        } else {
+            a.y[row0] = s0;
+            if (v1) a.y[row0 + 1] = s1;
+        }
     }
     ax_trace_end(a.trace);
 }
@@ -138,7 +144,8 @@ ax_gemv_stream_kernel(const GemvArgs a) {
     if (!TMA) {
         // second plane (raw residual stream, fetched early) only when the launcher reserved it
         float4* xb = a.pro.base_early ? reinterpret_cast<float4*>(ring) : nullptr;
-        consume_direct<FMT>(a, xs, xb, red, lo, hi);
+        float* part = reinterpret_cast<float*>(ring + (a.pro.base_early ? x_bytes : 0));     // [pairs][warps][2]
+        consume_direct<FMT>(a, xs, xb, red, part, lo, hi);
         return;
     }
 
@@ -351,9 +358,26 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
             default:          rc = launch_stream<ATLASX_INT4, true>(ctx, a, grid, smem, pdl); break;
         }
     } else {
-        // the early-fetched residual plane only pays off (and is only reserved) next to a fused norm
-        if (!(a.pro.base_early && (pro.y || pro.wx) && pro.base && !pro.embed && 256 + 2 * x_bytes <= smem_max)) a.pro.base_early = 0;
-        const size_t smem = 256 + x_bytes * (a.pro.base_early ? 2 : 1);
+        // Grid first (it fixes how many row pairs a CTA can own), with the occupancy of the
+        // larger of the two shared-memory layouts; the early-fetched residual plane only pays
+        // off, and is only reserved, next to a fused norm.
+        if (!(a.pro.base_early && (pro.y || pro.wx) && pro.base && !pro.embed)) a.pro.base_early = 0;
+        const int tiles = units >= 8 ? units / 4 : (units >= 2 ? units / 2 : 1);     // at least four units of rows per CTA
+        auto part_bytes = [&](int grid) {
+            const int unit = (w.rows & 1) ? 1 : 2;
+            const long long rows_max = ((long long)units + grid - 1) / grid * unit + unit;
+            return (size_t)((rows_max + 1) / 2 + 1) * kConsumerWarps * 2 * sizeof(float);
+        };
+        size_t smem = 0;
+        int grid = 1;
+        for (int attempt = 0; attempt < 2; attempt++) {
+            const size_t fixed = 256 + x_bytes * (a.pro.base_early ? 2 : 1);
+            int g = ctx->sm_count * 2 < tiles ? ctx->sm_count * 2 : tiles;     // first guess: two CTAs per SM
+            if (g < 1) g = 1;
+            smem = fixed + part_bytes(g);
+            if (smem <= smem_max) break;
+            if (a.pro.base_early) a.pro.base_early = 0; else break;
+        }
         AX_ARG(smem <= smem_max, "input vector does not fit in shared memory");
         int per_sm = 1;             // resident CTAs per SM for this format and input size
         switch (w.dtype) {
@@ -364,10 +388,14 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         }
         if (per_sm < 1) per_sm = 1;
         { const char* e = getenv("ATLASX_GEMV_PERSM"); if (e && atoi(e) > 0 && per_sm > atoi(e)) per_sm = atoi(e); }   // experiments
-        int grid = ctx->sm_count * per_sm;
-        const int tiles = (units * ((w.rows & 1) ? 1 : 2) + kTileRows - 1) / kTileRows;
+        grid = ctx->sm_count * per_sm;
         if (grid > tiles) grid = tiles;
         if (grid < 1) grid = 1;
+        if (per_sm != 2) {                 // partial-sum area for the final grid; re-check the fit
+            const size_t s2 = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + part_bytes(grid);
+            if (s2 > smem) { AX_ARG(s2 <= smem_max, "input vector does not fit in shared memory"); }
+            smem = s2 > smem ? s2 : smem;
+        }
         if (ctx->trace_next) { a.trace = ctx->trace_next; ctx->trace_next += 6; }
         switch (w.dtype) {
             case ATLASX_F32:  rc = launch_stream<ATLASX_F32, false>(ctx, a, grid, smem, pdl); break;

@@ -90,8 +90,17 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# (32 x (100.73 + 33.63 + 180.46 + 90.28) + 821.60) / 129 MB read + 2.48 MB written, from the ncu capture
+NCU_GEMV_TRAFFIC_PER_LAUNCH = 109.34e6
+PROFILE_LAYERS = 0          # > 0: a truncated model for profiler captures only (--profile-layers)
+
+
 def model_config(ab, max_seq):
-    return ab.ModelConfig.olmo3_actual_7b(max_seq_len=max_seq)
+    mc = ab.ModelConfig.olmo3_actual_7b(max_seq_len=max_seq)
+    if PROFILE_LAYERS:
+        mc.n_layers = PROFILE_LAYERS
+        mc.layer_types = mc.layer_types[:PROFILE_LAYERS]
+    return mc
 
 
 def build_cuda_model(ab, ctx, max_seq, rank, world):
@@ -210,6 +219,44 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def print_timeline(m, n_layers):
+    """One more captured step with stamps; per launch class (averaged over layers 1..): the time from
+    dependency release to the last CTA's end, how early the first CTA started and how late the
+    release came relative to the previous launch's end, the input-staging time and the spread of
+    CTA end times.  All in microseconds, from %globaltimer."""
+    import ctypes as C
+    from atlas_b200 import _ffi
+    L = _ffi.lib()
+    fn = L.atlasx_model_step_trace
+    fn.argtypes = [C.c_void_p, C.c_void_p, C.c_int, C.c_void_p]
+    fn.restype = C.c_int
+    cap, n = 1024, C.c_int(0)
+    out = (C.c_ulonglong * (cap * 6))()
+    for _ in range(2):
+        _ffi.check(fn(m._h, out, cap, C.byref(n)))
+    t = np.array(out[:n.value * 6], dtype=np.float64).reshape(-1, 6) / 1e3
+    per = (n.value - 1) // n_layers
+    names = {5: ["gemv_qkv", "attention_fused", "gemv_o_proj", "gemv_gate_up", "gemv_down"],
+             4: ["gemv_qkv", "gemv_o_proj", "gemv_gate_up", "gemv_down"]}.get(per)
+    if names is None:
+        sys.stderr.write("timeline: unexpected launch count %d\n" % n.value)
+        return
+    acc = {k: [] for k in names}
+    for i in range(per, n_layers * per):
+        acc[names[i % per]].append((t[i, 3] - t[i, 2], t[i, 0] - t[i - 1, 3], t[i, 2] - t[i - 1, 3],
+                                    t[i, 5] - t[i, 2], t[i, 3] - t[i, 4]))
+    sys.stderr.write("timeline of one step: %.1f us from first start to last end, %d traced launches\n"
+                     % (t[-1, 3] - t[0, 0], n.value))
+    sys.stderr.write("%-16s %10s %18s %20s %16s %12s\n" % ("class", "active", "start-prev_end", "release-prev_end",
+                                                          "release->staged", "end spread"))
+    for k in names:
+        a = np.array(acc[k]).mean(0)
+        sys.stderr.write("%-16s %10.2f %18.2f %20.2f %16.2f %12.2f\n" % (k, *a))
+    i = n_layers * per
+    sys.stderr.write("%-16s %10.2f %18.2f %20.2f %16.2f %12.2f\n" % ("gemv_lm_head", t[i, 3] - t[i, 2], t[i, 0] - t[i - 1, 3],
+                     t[i, 2] - t[i - 1, 3], t[i, 5] - t[i, 2], t[i, 3] - t[i, 4]))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -220,8 +267,17 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--profile-layers", type=int, default=0,
+                    help="keep only the first N layers: a few GB on the device, for profiler captures; the line is marked invalid as a benchmark")
+    ap.add_argument("--timeline", action="store_true",
+                    help="record %%globaltimer stamps in every GEMV and attention launch of the captured step and print a "
+                         "per-class summary on stderr; the stamps cost a little, so the JSON line is marked invalid")
     ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")
     args = ap.parse_args()
+    global PROFILE_LAYERS
+    PROFILE_LAYERS = max(0, args.profile_layers)
+    if args.timeline:
+        os.environ["ATLASX_STEP_TRACE"] = "1"
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -321,7 +377,12 @@ def main():
     step_bytes = m.step_bytes(pos0 + steps // 2)
     roofline = {"bound": "hbm", "kernel": "ax_gemv_stream_kernel<bf16> (all %d GEMV launches of a step)" % g_launch,
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
-                "traffic": None,
+                "traffic": NCU_GEMV_TRAFFIC_PER_LAUNCH if (world == 1 and not PROFILE_LAYERS) else None,
+                "traffic_note": "dram__bytes_read+write per GEMV launch, averaged over the 129 launches of a step from one "
+                                "ncu capture of the same kernels and shapes (profiles/decode_step_kernels_ncu_full_olmo3_7b_arch_2_layers.md); "
+                                "algorithmic: %.2f MB" % (g_bytes / max(g_launch, 1) / 1e6),
+                "achieved_note": "CUDA events around each launch of an eager step: includes the launch latency that the "
+                                 "graph + programmatic dependent launch of the timed region hide; step.frac is the timed region",
                 "step": {"algorithmic_bytes": step_bytes, "achieved": step_bytes * value / 1e9,
                          "frac": step_bytes * value / 1e9 / peak, "frac_of_8000": step_bytes * value / 1e9 / 8000.0},
                 "per_class": {k: {"launches": v["launches"], "ms": round(v["ms"], 4),
@@ -345,6 +406,12 @@ def main():
                        "l2": "inputs larger than L2: 13.77 GB of weights stream per step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": m.launches_per_step * steps,
             "roofline": roofline, "cpu_baseline": cpu}
+    if PROFILE_LAYERS:
+        line["invalid"] = "profiler case: only %d of 32 layers" % PROFILE_LAYERS
+    if args.timeline:
+        line["invalid"] = "timeline stamps were recorded inside the kernels"
+        if rank == 0:
+            print_timeline(m, mc.n_layers)
     print(json.dumps(line), flush=True)
 
 
