@@ -6,6 +6,8 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <vector>
+
 #include "common.cuh"
 #include "comm.h"
 
@@ -53,10 +55,18 @@ const char* nccl_err(int e) { return g_nccl.GetErrorString ? g_nccl.GetErrorStri
 struct atlasx_comm {
     nccl_comm_t comm = nullptr;
     int rank = 0, world = 1;
+    AxPeerMail mail; bool mail_ready = false, mail_failed = false;
+    void* mail_local = nullptr;
 };
 
 void atlasx_comm_destroy(atlasx_ctx* ctx) {
     if (ctx && ctx->comm) {
+        atlasx_comm* cm = ctx->comm;
+        if (cm->mail_ready) {
+            for (int p = 0; p < cm->world; p++)
+                if (p != cm->rank && cm->mail.base[p]) cudaIpcCloseMemHandle(cm->mail.base[p]);
+        }
+        if (cm->mail_local) cudaFree(cm->mail_local);
         if (ctx->comm->comm && g_nccl.CommDestroy) g_nccl.CommDestroy(ctx->comm->comm);
         delete ctx->comm;
         ctx->comm = nullptr;
@@ -79,6 +89,72 @@ int ax_comm_allgather(atlasx_ctx* ctx, const float* send, float* recv, size_t n_
     }
     const int e = g_nccl.AllGather(send, recv, n_each, kNcclFloat32, ctx->comm->comm, ctx->stream);
     if (e != kNcclSuccess) return atlasx_fail(ATLASX_ERR_COMM, "ncclAllGather: %s", nccl_err(e));
+    return ATLASX_OK;
+}
+
+// The mailboxes are exchanged as CUDA IPC handles through an NCCL all-gather of raw bytes; every
+// rank must call this at the same point of its program.  A failure to map a peer (no peer access,
+// different IPC namespace) is not an error: all ranks learn of it through a second all-gather and
+// all of them keep the NCCL path.
+int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out) {
+    *out = nullptr;
+    atlasx_comm* cm = ctx->comm;
+    if (!cm || cm->world == 1 || cm->world > kMaxPeers) return ATLASX_OK;
+    if (cm->mail_ready) {
+        if (cm->mail.d < d) return atlasx_fail(ATLASX_ERR_STATE, "peer mailboxes were sized for %d floats, %d asked", cm->mail.d, d);
+        *out = &cm->mail;
+        return ATLASX_OK;
+    }
+    if (cm->mail_failed) return ATLASX_OK;
+    { const char* e = getenv("ATLASX_PEER_ALLREDUCE"); if (e && atoi(e) == 0) { cm->mail_failed = true; return ATLASX_OK; } }
+    const int W = cm->world;
+    const size_t total = (((size_t)2 * W * d * sizeof(uint2)) + 255) / 256 * 256;
+    AX_CUDA(cudaMalloc(&cm->mail_local, total));
+    AX_CUDA(cudaMemset(cm->mail_local, 0, total));
+    AX_CUDA(cudaDeviceSynchronize());
+
+    struct Wire { cudaIpcMemHandle_t h; int ok; int pad[15]; };          // 128 bytes
+    static_assert(sizeof(Wire) == 128, "wire record size");
+    Wire mine = {}; mine.ok = 1;
+    if (cudaIpcGetMemHandle(&mine.h, cm->mail_local) != cudaSuccess) { cudaGetLastError(); mine.ok = 0; }
+    Wire* dev = nullptr;
+    AX_CUDA(cudaMalloc((void**)&dev, sizeof(Wire) * (W + 1)));
+    std::vector<Wire> all((size_t)W);
+    auto gather = [&](const Wire& w) -> int {
+        AX_CUDA(cudaMemcpyAsync(dev + W, &w, sizeof(Wire), cudaMemcpyHostToDevice, ctx->stream));
+        const int e = g_nccl.AllGather(dev + W, dev, sizeof(Wire), /*ncclInt8*/ 0, cm->comm, ctx->stream);
+        if (e != kNcclSuccess) return atlasx_fail(ATLASX_ERR_COMM, "ncclAllGather: %s", nccl_err(e));
+        AX_CUDA(cudaMemcpyAsync(all.data(), dev, sizeof(Wire) * W, cudaMemcpyDeviceToHost, ctx->stream));
+        AX_CUDA(cudaStreamSynchronize(ctx->stream));
+        return ATLASX_OK;
+    };
+    int rc = gather(mine);
+    if (rc) { cudaFree(dev); return rc; }
+    bool ok = true;
+    for (int p = 0; p < W; p++) ok = ok && all[p].ok;
+    AxPeerMail mail;
+    mail.world = W; mail.rank = cm->rank; mail.d = d;
+    if (ok) {
+        for (int p = 0; p < W && ok; p++) {
+            if (p == cm->rank) { mail.base[p] = (uint2*)cm->mail_local; continue; }
+            void* ptr = nullptr;
+            if (cudaIpcOpenMemHandle(&ptr, all[p].h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; }
+            mail.base[p] = (uint2*)ptr;
+        }
+    }
+    Wire verdict = {}; verdict.ok = ok ? 1 : 0;
+    rc = gather(verdict);                                   // second round: did every rank map every peer?
+    cudaFree(dev);
+    if (rc) return rc;
+    for (int p = 0; p < W; p++) ok = ok && all[p].ok;
+    if (!ok) {
+        for (int p = 0; p < W; p++) if (p != cm->rank && mail.base[p]) cudaIpcCloseMemHandle(mail.base[p]);
+        cudaFree(cm->mail_local); cm->mail_local = nullptr;
+        cm->mail_failed = true;
+        return ATLASX_OK;
+    }
+    cm->mail = mail; cm->mail_ready = true;
+    *out = &cm->mail;
     return ATLASX_OK;
 }
 

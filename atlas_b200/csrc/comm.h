@@ -2,8 +2,26 @@
 #pragma once
 #include "common.cuh"
 
+constexpr int kMaxPeers = AX_MAX_PEERS;
+
+// Mailboxes in peer memory for the all-reduce that is fused into the row-parallel GEMVs.
+// Every rank owns one allocation, mapped into every other rank of the node (CUDA IPC):
+//   parts : [2 buffers][world][d] pairs (value bits, sequence number), 8 bytes each — rank r's
+//           partial output lands in slot r of EVERY rank.
+// Buffer 0 carries the o_proj partials, buffer 1 the down-projection partials; two buffers are
+// enough because a rank can only reach its next write into a buffer after it has consumed a
+// part that every peer produced after reading the previous content of that buffer.
+struct AxPeerMail {
+    int world = 1, rank = 0, d = 0;
+    uint2* base[kMaxPeers] = {};        // mailbox of rank p as mapped in this process (own allocation for p == rank)
+    uint2* part(int owner, int buf, int from) const { return base[owner] + ((size_t)buf * world + from) * d; }
+};
+
 int ax_comm_world(const atlasx_ctx* ctx);
 int ax_comm_rank(const atlasx_ctx* ctx);
 int ax_comm_allreduce_sum(atlasx_ctx* ctx, float* buf_dev, size_t n);                         // in place, on ctx->stream
 int ax_comm_allgather(atlasx_ctx* ctx, const float* send_dev, float* recv_dev, size_t n_each);
+// Collective over all ranks: allocates and exchanges the mailboxes for vectors of d floats.
+// Returns ATLASX_OK with *out == nullptr when peer mapping is not possible (the caller keeps NCCL).
+int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out);
 void atlasx_comm_destroy(atlasx_ctx* ctx);

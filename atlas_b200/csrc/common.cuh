@@ -32,6 +32,8 @@ int  atlasx_fail(int code, const char* fmt, ...);
 #define AX_ARG(cond, msg)                                                                 \
     do { if (!(cond)) return atlasx_fail(ATLASX_ERR_ARG, "%s: %s", __func__, msg); } while (0)
 
+#define AX_MAX_PEERS 8
+
 // ── context ─────────────────────────────────────────────────────────────────────
 struct atlasx_comm;   // comm.cpp
 

@@ -114,7 +114,19 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
             s0 *= sc[row0];
             if (v1) s1 *= sc[row0 + 1];
         }
-        if (a.epi == AX_EPI_SILU_PAIR) {
+        if (a.peer.n > 0) {                                                    // push to every rank's mailbox
+            const unsigned seq = __ldcg(a.peer.epoch) * a.peer.mul + a.peer.add;
+            for (int q = 0; q < a.peer.n; q++) {
+                uint2* dst = a.peer.y[q] + row0;
+                if (v1 && (row0 & 1) == 0) {                                       // both pairs in one 16-byte store
+                    asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(dst), "r"(__float_as_uint(s0)), "r"(seq),
+                                 "r"(__float_as_uint(s1)), "r"(seq) : "memory");
+                } else {
+                    asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" :: "l"(dst), "r"(__float_as_uint(s0)), "r"(seq) : "memory");
+                    if (v1) asm volatile("st.volatile.global.v2.u32 [%0], {%1,%2};" :: "l"(dst + 1), "r"(__float_as_uint(s1)), "r"(seq) : "memory");
+                }
+            }
+        } else if (a.epi == AX_EPI_SILU_PAIR) {
             if (v1) a.y[row0 >> 1] = (s0 / (1.0f + expf(-s0))) * s1;           // silu(gate)·up
         } else {
             a.y[row0] = s0;
@@ -283,7 +295,7 @@ size_t ax_weight_bytes(const AxWeight& w) {
     return 0;
 }
 
-int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y, bool pdl) {
+int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y, bool pdl, const AxPeerOut* peer) {
     AX_ARG(w.data && y, "null pointer");
     AX_ARG(w.rows > 0 && w.cols > 0, "empty matrix");
     AX_ARG(n >= 1 && n <= 16, "n must be in 1..16");
@@ -342,6 +354,11 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     a.stages = stages;
 
     int impl = ctx->gemv_impl;
+    if (peer && peer->n > 0) {
+        AX_ARG(vec_ok && epi == AX_EPI_PLAIN, "peer output needs the vectorised kernel and a plain epilogue");
+        a.peer = *peer;
+        impl = 1;
+    }
     if (impl == 0) impl = 1;              // plain loads: faster than the bulk-copy ring inside a decode step
     if (impl == 2 && !tma_ok) impl = 1;
 

@@ -33,7 +33,23 @@ struct AxPrologue {
     const float* wy = nullptr; const float* wx = nullptr;
     float eps = 0.f;
     float* resid_out = nullptr;
+    // Tensor parallel with peer mailboxes: `y` points at ll_n parts of (value, sequence) pairs,
+    // 8 bytes per element, written by the GPUs of the group with single 8-byte stores.  An element
+    // is valid once its sequence word equals *ll_epoch·ll_mul + ll_add; the prologue polls each
+    // element it needs (bounded) — no fence and no separate flag on either side.
+    int ll_n = 0; size_t ll_stride = 0;              // parts, and elements between parts
+    const unsigned* ll_epoch = nullptr; unsigned ll_mul = 0, ll_add = 0;
     int base_early = 0;                 // `base` was written at least two kernels back in the stream: may be read before the dependency wait
+};
+
+// Row-parallel output under tensor parallelism: instead of a local vector the result (this rank's
+// partial sums) goes into slot `rank` of every rank's mailbox over NVLink as (value, sequence)
+// pairs — one 8-byte store per element, so value and sequence number arrive together and the
+// reader needs neither a fence nor a flag (the scheme NCCL calls LL).
+struct AxPeerOut {
+    int n = 0;                           // ranks (0: plain local store into y)
+    uint2* y[AX_MAX_PEERS] = {};         // destination of this rank's part in rank p's mailbox
+    const unsigned* epoch = nullptr; unsigned mul = 0, add = 0;   // sequence word: *epoch·mul + add
 };
 
 enum { AX_EPI_PLAIN = 0, AX_EPI_SILU_PAIR = 1 };   // pair: out[r/2] = silu(acc[r])·acc[r+1], r even
@@ -50,6 +66,7 @@ struct GemvArgs {
     int epi;
     float* y;
     AxPrologue pro;
+    AxPeerOut peer;
     int* err;
     int dbg;                     // experiments only: bit 0 = consumers skip the arithmetic
     unsigned long long* trace;   // diagnostics: timeline stamps of this launch, or null
@@ -57,7 +74,7 @@ struct GemvArgs {
 
 // y[rows×n] = W·x.  n == 1: pro/epi honoured.  n in 2..16: plain only, x is [cols×n] row-major.
 int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y,
-                   bool pdl = false);
+                   bool pdl = false, const AxPeerOut* peer = nullptr);
 // Fill the shape/format fields of a GemvArgs for the ring kernels (fails for shapes that need the
 // scalar kernel).  Ring geometry fields are left to the caller.
 int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* y, int* err, GemvArgs* out);

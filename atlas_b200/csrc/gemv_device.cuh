@@ -201,12 +201,34 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
     float inv_y = 1.f;
     if (p.y) {
         float ss = 0.f;
+        const unsigned seq = p.ll_n ? __ldcg(p.ll_epoch) * p.ll_mul + p.ll_add : 0u;
+        // four (value, sequence) pairs of one part, polled until all four carry this use's number
+        auto load_ll = [&](int r, int k4) -> float4 {
+            const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(p.y) + (size_t)r * p.ll_stride + ((size_t)k4 << 2));
+            uint4 a0, a1;
+            const unsigned long long t0 = ax_globaltimer();
+            for (;;) {
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a0.x), "=r"(a0.y), "=r"(a0.z), "=r"(a0.w) : "l"(q) : "memory");
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(a1.x), "=r"(a1.y), "=r"(a1.z), "=r"(a1.w) : "l"(q + 1) : "memory");
+                if (a0.y == seq && a0.w == seq && a1.y == seq && a1.w == seq) break;
+                // a wait that already expired anywhere on this GPU ends all later ones at once
+                if (*reinterpret_cast<volatile int*>(a.err) != 0) break;
+                if (ax_globaltimer() - t0 > 2000000000ull) { atomicExch(a.err, 3); break; }
+            }
+            return make_float4(__uint_as_float(a0.x), __uint_as_float(a0.z), __uint_as_float(a1.x), __uint_as_float(a1.z));
+        };
 #pragma unroll 4
         for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
-            float4 t = __ldcg(reinterpret_cast<const float4*>(p.y) + k4);
-            for (int r = 1; r < p.nparts; r++) {
-                const float4 u = __ldcg(reinterpret_cast<const float4*>(p.y + (size_t)r * p.part_stride) + k4);
-                t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+            float4 t;
+            if (p.ll_n) {
+                t = load_ll(0, k4);
+                for (int r = 1; r < p.ll_n; r++) { const float4 u = load_ll(r, k4); t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
+            } else {
+                t = __ldcg(reinterpret_cast<const float4*>(p.y) + k4);
+                for (int r = 1; r < p.nparts; r++) {
+                    const float4 u = __ldcg(reinterpret_cast<const float4*>(p.y + (size_t)r * p.part_stride) + k4);
+                    t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w;
+                }
             }
             xs[slot(k4)] = t;
             ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;

@@ -175,17 +175,17 @@ namespace {
 template <int FMT, bool KVBF16>
 __global__ void __launch_bounds__(kThreadsTma, 1) ax_decode_mega_kernel(const MegaArgs ma) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    // layout: [full | empty | red[16] | pair[16] | flag | pad to 256] [phase copy 1 KB] [x / attention scratch] [ring]
+    // layout: [full | empty | red[16] | pair[16] | flag | pad to 256] [two phase records, 2 KB] [x / attention scratch] [ring]
     uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);
     uint64_t* empty = full + kMaxStages;
     float* red = reinterpret_cast<float*>(empty + kMaxStages);
     float* pair = red + 16;
     int* s_flag = reinterpret_cast<int*>(pair + 16);
     MegaPhase* sp = reinterpret_cast<MegaPhase*>(smem_raw + 256);          // two slots
-    static_assert(sizeof(MegaPhase) <= 512, "phase record must fit its shared-memory slot");
-    float4* xs = reinterpret_cast<float4*>(smem_raw + 256 + 1024);
+    static_assert(sizeof(MegaPhase) <= 1024, "phase record must fit its shared-memory slot");
+    float4* xs = reinterpret_cast<float4*>(smem_raw + 256 + 2048);
     Ring rg;
-    rg.full = full; rg.empty = empty; rg.data = smem_raw + 256 + 1024 + ma.x_bytes;
+    rg.full = full; rg.empty = empty; rg.data = smem_raw + 256 + 2048 + ma.x_bytes;
     rg.stages = ma.stages; rg.stage_stride = ma.stage_stride; rg.seg_pitch = ma.seg_pitch;
     ring_init(rg);
 

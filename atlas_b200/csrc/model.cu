@@ -37,6 +37,7 @@ struct StepState {           // device-resident generation state
     int pos;                 // next position to be processed
     int n_forced;            // positions below this hold caller-given tokens
     int last_token;          // argmax of the most recent logits
+    unsigned epoch;          // steps run since the model was finalised (never reset): sequence numbers of the peer mailboxes
 };
 
 struct Layer {
@@ -78,6 +79,7 @@ struct atlasx_model {
     cudaGraphExec_t graph = nullptr;
     int attn_splits = 1;
     bool fused_attn = false; int fused_splits = 1;   // one-launch attention (head_dim 128)
+    const AxPeerMail* mail = nullptr;            // tensor parallel: all-reduce fused into o_proj/down over peer memory
     std::vector<void*> owned;                    // device allocations to free
     int* pin = nullptr;                          // pinned host ints
     int launches_per_step = 0;
@@ -186,7 +188,7 @@ int place_slice(atlasx_model* m, const void* src, int src_dtype, int rows, int c
 // ── argmax of the logits + advance of the device-resident state ─────────────────
 // Last CTA: last_token = argmax; if the next position is not a caller-given one, the token is
 // stored as the next input; pos += 1.
-__global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, AxArgmaxScratch sc, StepState* st, int* seq, int seq_cap, int advance) {
+__global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, AxArgmaxScratch sc, StepState* st, int* seq, int seq_cap, int advance, int bump_epoch) {
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ int s_last;
@@ -224,6 +226,7 @@ __global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, A
         if (idx < 0) idx = n - 1;
         *sc.ticket = 0u;
         st->last_token = idx;
+        if (bump_epoch) st->epoch += 1u;
         if (advance) {
             const int p = st->pos + 1;
             if (p >= st->n_forced && p < seq_cap) seq[p] = idx;
@@ -359,12 +362,12 @@ int build_mega(atlasx_model* m) {
     a.stage_stride = 8 * a.seg_pitch;
     a.x_bytes = (int)((x_max + 127) / 128 * 128);
     const size_t smem_max = c->smem_optin ? c->smem_optin : 232448;
-    long long avail = (long long)smem_max - 256 - 1024 - a.x_bytes;
+    long long avail = (long long)smem_max - 256 - 2048 - a.x_bytes;
     int stages = (int)(avail / a.stage_stride);
     if (stages > 6) stages = 6;
     if (stages < 2) return ATLASX_OK;
     a.stages = stages;
-    m->mega_smem = 256 + 1024 + (size_t)a.x_bytes + (size_t)stages * a.stage_stride;
+    m->mega_smem = 256 + 2048 + (size_t)a.x_bytes + (size_t)stages * a.stage_stride;
     if ((rc = dmalloc(m, (void**)&m->phases_dev, ph.size() * sizeof(MegaPhase)))) return rc;
     AX_CUDA(cudaMemcpyAsync(m->phases_dev, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice, c->stream));
     AX_CUDA(cudaStreamSynchronize(c->stream));
@@ -396,7 +399,23 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     const int d = cf.d_model, L = cf.n_layers;
     const bool post = cf.post_norm != 0;
     int rc = ATLASX_OK, n_launch = 0, cur = 0;
-    const int nparts = 1;                                  // partial sums are reduced by the collective
+    const int nparts = 1;                                  // partial sums are reduced by the collective …
+    // … unless the ranks push them into each other's mailboxes: then the consumer's prologue
+    // waits for the sequence number of (step, layer) and adds the parts itself, in rank order
+    const AxPeerMail* mail = m->mail;
+    auto peer_out = [&](int buf, int l) {
+        AxPeerOut po;
+        po.n = mail->world;
+        for (int q = 0; q < mail->world; q++) po.y[q] = mail->part(q, buf, mail->rank);
+        po.epoch = &m->st->epoch; po.mul = (unsigned)L; po.add = (unsigned)l + 1u;    // use number = step·L + layer + 1
+        return po;
+    };
+    auto peer_in = [&](AxPrologue& p, int buf, int l) {
+        p.y = reinterpret_cast<const float*>(mail->part(mail->rank, buf, 0));
+        p.nparts = mail->world; p.part_stride = (size_t)mail->d;
+        p.ll_n = mail->world; p.ll_stride = (size_t)mail->d;
+        p.ll_epoch = &m->st->epoch; p.ll_mul = (unsigned)L; p.ll_add = (unsigned)l + 1u;
+    };
 
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
@@ -410,6 +429,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             if (!post) p.wx = ly.attn_norm;
         } else {
             p.base = m->resid[cur]; p.y = m->dn; p.nparts = nparts; p.part_stride = d;
+            if (mail) peer_in(p, 1, l - 1);
             p.base_early = 1;                              // written by the gate/up launch, two kernels back
             if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
             p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
@@ -453,13 +473,19 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
 
         // ── output projection (row-parallel under TP) ───────────────────────────
         AxPrologue po; po.base = m->attn;
-        STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ)));
-        if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->o, (size_t)d));
+        if (mail) {
+            const AxPeerOut px = peer_out(0, l);
+            STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ), &px));
+        } else {
+            STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ)));
+            if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->o, (size_t)d));
+        }
 
         // ── gate/up with SwiGLU epilogue ────────────────────────────────────────
         AxPrologue pg;
         pg.eps = cf.rms_norm_eps;
         pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = nparts; pg.part_stride = d;
+        if (mail) peer_in(pg, 0, l);
         pg.base_early = 1;                                 // written by the QKV launch, at least two kernels back
         if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
         pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
@@ -467,13 +493,19 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
 
         // ── down projection (row-parallel under TP) ─────────────────────────────
         AxPrologue pd; pd.base = m->h;
-        STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN)));
-        if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->dn, (size_t)d));
+        if (mail) {
+            const AxPeerOut px = peer_out(1, l);
+            STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN), &px));
+        } else {
+            STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN)));
+            if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->dn, (size_t)d));
+        }
     }
     // ── final norm + lm_head ────────────────────────────────────────────────────
     AxPrologue pl;
     pl.eps = cf.rms_norm_eps;
     pl.base = m->resid[cur]; pl.y = m->dn; pl.nparts = nparts; pl.part_stride = d;
+    if (mail) peer_in(pl, 1, L - 1);
     pl.base_early = 1;
     if (post) pl.wy = m->layers[L - 1].ffn_norm;
     pl.wx = m->final_norm;
@@ -492,7 +524,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         cfg.gridDim = dim3((unsigned)((n + 1023) / 1024)); cfg.blockDim = dim3(256); cfg.stream = s;
         cudaLaunchAttribute attr[1];
         if (pdl) { attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1; cfg.attrs = attr; cfg.numAttrs = 1; }
-        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, (const float*)m->logits, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0));
+        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, (const float*)m->logits, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0, 1));
         if (prof) { cudaEventRecord(prof->ev[2 * prof->n + 1], s); prof->cls[prof->n] = CLS_SELECT; prof->bytes[prof->n] = 4.0 * n; prof->n++; }
         n_launch++;
     }
@@ -745,6 +777,15 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     m->host_pos = 0;
     set_state_k<<<1, 1, 0, s>>>(m->st, 0, INT_MAX);
     AX_CUDA(cudaStreamSynchronize(s));
+    if (m->world > 1) {
+        // collective: every rank finalises its model at the same point of the program.  The small
+        // all-reduce afterwards lines the ranks up, so that the bounded waits of the first step
+        // measure the step and not the difference in set-up time.
+        rc = ax_comm_peer_setup(c, d, &m->mail); if (rc) return rc;
+        AX_CUDA(cudaMemsetAsync(m->o, 0, (size_t)d * 4, s));
+        rc = ax_comm_allreduce_sum(c, m->o, (size_t)d); if (rc) return rc;
+        AX_CUDA(cudaStreamSynchronize(s));
+    }
     {
         const char* e = getenv("ATLASX_MEGA");
         if (e) m->use_mega = atoi(e) ? 1 : 0;
@@ -883,7 +924,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
             if (need_fix)
                 logit_fixups_k<<<1, 32, 0, s>>>(m->logits, V, sup_dev, stepi == 0 ? n_suppress : 0,
                                                 m->seq + n_prompt + start, rep_penalty != 1.0f ? stepi - start : 0, rep_penalty);
-            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0);
+            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0, 0);
             cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return done(atlasx_fail(ATLASX_ERR_CUDA, "selection launch failed: %s", cudaGetErrorString(e)));
         }

@@ -219,7 +219,7 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def print_timeline(m, n_layers):
+def print_timeline(m, n_layers, quiet=False):
     """One more captured step with stamps; per launch class (averaged over layers 1..): the time from
     dependency release to the last CTA's end, how early the first CTA started and how late the
     release came relative to the previous launch's end, the input-staging time and the spread of
@@ -234,6 +234,8 @@ def print_timeline(m, n_layers):
     out = (C.c_ulonglong * (cap * 6))()
     for _ in range(2):
         _ffi.check(fn(m._h, out, cap, C.byref(n)))
+    if quiet:
+        return
     t = np.array(out[:n.value * 6], dtype=np.float64).reshape(-1, 6) / 1e3
     per = (n.value - 1) // n_layers
     names = {5: ["gemv_qkv", "attention_fused", "gemv_o_proj", "gemv_gate_up", "gemv_down"],
@@ -390,6 +392,11 @@ def main():
                               for k, v in prof.items() if v["launches"]},
                 "profiled_at_pos": prof_pos}
 
+    if args.timeline:
+        print_timeline(m, mc.n_layers, quiet=(rank != 0))      # every rank runs the extra steps
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank != 0:
         return
     cpu = None
@@ -405,13 +412,12 @@ def main():
                        "kv_cache": "bf16", "parallelism": "tp%d" % world,
                        "l2": "inputs larger than L2: 13.77 GB of weights stream per step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": m.launches_per_step * steps,
+            "first_tokens": [int(t) for t in toks[:8]],
             "roofline": roofline, "cpu_baseline": cpu}
     if PROFILE_LAYERS:
         line["invalid"] = "profiler case: only %d of 32 layers" % PROFILE_LAYERS
     if args.timeline:
         line["invalid"] = "timeline stamps were recorded inside the kernels"
-        if rank == 0:
-            print_timeline(m, mc.n_layers)
     print(json.dumps(line), flush=True)
 
 
