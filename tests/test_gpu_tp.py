@@ -1,0 +1,57 @@
+"""Two GPUs, one process each: the tensor-parallel step (row-parallel GEMVs pushing their partial
+sums into peer mailboxes, and the NCCL all-reduce it replaces) gives the logits and greedy tokens
+of the single-GPU model and of the CPU oracle."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+import helpers
+from oracle import orc
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _gpu_count():
+    try:
+        import torch
+        return torch.cuda.device_count()
+    except Exception:
+        return 0
+
+
+def _free_port():
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); p = s.getsockname()[1]; s.close(); return p
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+@pytest.mark.parametrize("peer", ["mailbox", "nccl"])
+@pytest.mark.parametrize("kv", ["f32", "bf16"])
+def test_two_gpu_tensor_parallel_matches_single_gpu_and_oracle(tmp_path, kv, peer):
+    import atlas_b200 as ab
+    n_tok = 20
+    out = str(tmp_path / "tp.npz")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", ATLASX_PEER_ALLREDUCE="1" if peer == "mailbox" else "0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+           "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
+           os.path.join(ROOT, "tests", "tp_worker.py"), out, kv, str(n_tok)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=240)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    got = np.load(out)
+
+    cfg = dict(helpers.HD128)
+    w = helpers.synth_weights(cfg, seed=33, norm_jitter=0.1)
+    one = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=ab.F32 if kv == "f32" else ab.BF16)
+    toks = orc.uniform_u32(n_tok, 33, 1, cfg["vocab_size"])
+    ref = np.stack([one.forward_one_gpu(int(t)) for t in toks])
+    tol = 1e-4 if kv == "f32" else 5e-3         # bf16 cache: a last-bit difference can flip a cached element's rounding
+    assert np.max(np.abs(got["logits"] - ref)) <= tol
+    o = helpers.oracle_model(cfg, w, helpers.HD128_LAYERS, kv_round_bf16=(kv == "bf16"))
+    want = np.stack([o.forward_one(int(t)) for t in toks])
+    assert np.max(np.abs(got["logits"] - want)) <= (1e-3 if kv == "f32" else 1e-2)
+    one.reset()
+    assert got["gen"].tolist() == one.generate(toks[:4], 12, 0.0)
