@@ -10,6 +10,7 @@
 // and the last CTA of each head group to finish merges the partial results (ticket counter,
 // nothing ever waits).  The KV cache may be bf16 (half the traffic) or f32 (reference format).
 #include "attention.cuh"
+#include <stdlib.h>
 #include "attention_device.cuh"
 
 #include <math_constants.h>
@@ -350,9 +351,9 @@ __global__ void __launch_bounds__(128) ax_qk_prep_kernel(const AxQkPrepArgs a) {
 // CTAs per SM) stay in flight without costing registers.  The first NST stages are requested
 // before griddepcontrol.wait: rows below `pos` are older than the previous kernel.
 constexpr int kFusedUnroll = 2;
-constexpr int kFusedStages = 2;
+constexpr int kFusedStagesDefault = 2;
 constexpr int kFusedRowsPerSplit = 64;
-constexpr size_t kFusedLandBytes = (size_t)kFusedStages * kFusedUnroll * 2 * kAttnThreads * 16;
+__host__ __device__ constexpr size_t fused_land_bytes(int nst) { return (size_t)nst * kFusedUnroll * 2 * kAttnThreads * 16; }
 
 struct FusedDev {
     AxFusedAttnArgs a;
@@ -367,18 +368,18 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" :: "n"(N) : "memory"); }
 
-template <bool BF16, int G>
+template <bool BF16, int G, int NST>
 __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const FusedDev dv) {
     constexpr int HD = 128;
     constexpr int EPL = BF16 ? 8 : 4;
     constexpr int LPR = HD / EPL;                 // lanes per cached row: 16 or 32
     constexpr int RPW = 32 / LPR;
     constexpr int SLOTS = kAttnWarps * RPW;       // rows per CTA pass: 16 or 8
-    constexpr int UN = kFusedUnroll, NST = kFusedStages;
+    constexpr int UN = kFusedUnroll;
     constexpr int ST = HD + 2;
     extern __shared__ __align__(16) uint8_t fsm[];
     uint4* land = reinterpret_cast<uint4*>(fsm);                     // [NST][UN][K,V][thread]
-    float* q_s = reinterpret_cast<float*>(fsm + kFusedLandBytes);     // [G][HD]
+    float* q_s = reinterpret_cast<float*>(fsm + fused_land_bytes(NST));     // [G][HD]
     float* k_new = q_s + G * HD;
     float* v_new = k_new + HD;
     float* smm = reinterpret_cast<float*>(fsm);                       // [warps][G][ST], reuses the landing slots
@@ -571,12 +572,12 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     ax_trace_end(dv.trace);
 }
 
-template <bool BF16, int G>
-int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
+template <bool BF16, int G, int NST>
+int launch_fused_n(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)dv.a.max_splits, (unsigned)dv.a.n_kv);
     cfg.blockDim = dim3(kAttnThreads);
-    cfg.dynamicSmemBytes = kFusedLandBytes + (size_t)(G + 2) * 128 * 4;
+    cfg.dynamicSmemBytes = fused_land_bytes(NST) + (size_t)(G + 2) * 128 * 4;
     cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -591,14 +592,25 @@ int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
         na++;
     }
     if (na) { cfg.attrs = attr; cfg.numAttrs = na; }
-    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_fused_kernel<BF16, G>, dv));
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_fused_kernel<BF16, G, NST>, dv));
     return ATLASX_OK;
+}
+int g_fused_stages = kFusedStagesDefault;       // 2..4; ATLASX_ATTN_STAGES overrides (experiments)
+
+template <bool BF16, int G>
+int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
+    switch (g_fused_stages) {
+        case 3:  return launch_fused_n<BF16, G, 3>(ctx, dv, pdl);
+        case 4:  return launch_fused_n<BF16, G, 4>(ctx, dv, pdl);
+        default: return launch_fused_n<BF16, G, 2>(ctx, dv, pdl);
+    }
 }
 
 template <bool BF16, int G>
 int fused_attr() {
-    AX_CUDA(cudaFuncSetAttribute(ax_attn_fused_kernel<BF16, G>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)(kFusedLandBytes + (size_t)(G + 2) * 128 * 4)));
+    AX_CUDA(cudaFuncSetAttribute(ax_attn_fused_kernel<BF16, G, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(fused_land_bytes(2) + (size_t)(G + 2) * 128 * 4)));
+    AX_CUDA(cudaFuncSetAttribute(ax_attn_fused_kernel<BF16, G, 3>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(fused_land_bytes(3) + (size_t)(G + 2) * 128 * 4)));
+    AX_CUDA(cudaFuncSetAttribute(ax_attn_fused_kernel<BF16, G, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(fused_land_bytes(4) + (size_t)(G + 2) * 128 * 4)));
     return ATLASX_OK;
 }
 
@@ -687,6 +699,7 @@ int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows) {
 }
 int ax_attn_init(atlasx_ctx*) {
     int rc;
+    if (const char* e = getenv("ATLASX_ATTN_STAGES")) { const int v = atoi(e); if (v >= 2 && v <= 4) g_fused_stages = v; }
     if ((rc = fused_attr<true, 1>()) || (rc = fused_attr<true, 2>()) || (rc = fused_attr<true, 4>())) return rc;
     if ((rc = fused_attr<false, 1>()) || (rc = fused_attr<false, 2>()) || (rc = fused_attr<false, 4>())) return rc;
     return ATLASX_OK;
