@@ -358,8 +358,11 @@ __host__ __device__ constexpr size_t fused_land_bytes(int nst) { return (size_t)
 struct FusedDev {
     AxFusedAttnArgs a;
     float* partials;       // [n_heads × max_splits × 130]
-    unsigned* tickets;     // [n_kv], zero between launches
+    unsigned* tickets;     // [batch × n_kv], zero between launches
     unsigned long long* trace;
+    // operator form (q_ready != null): q is already normed and rotated, the cache already holds row
+    // `pos`, grid.z runs over sequences; nothing is prepared or written besides the output
+    const float* q_ready; size_t seq_stride; const int* pos_b; int pos_shared; int pos_scalar;
 };
 
 __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
@@ -386,25 +389,27 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     __shared__ int s_last;
 
     const AxFusedAttnArgs& a = dv.a;
-    const int split = blockIdx.x, kh = blockIdx.y;
+    const int split = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int sub = lane % LPR, slot = warp * RPW + lane / LPR;
+    const bool prep = dv.q_ready == nullptr;
 
     ax_trace_start(dv.trace);
-    const int pos = __ldcg(a.pos);
+    const int pos = prep ? __ldcg(a.pos) : (dv.pos_b ? __ldcg(dv.pos_b + (dv.pos_shared ? 0 : b)) : dv.pos_scalar);
     const int tb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
-    const int rows = pos - tb;                    // cached rows; row `pos` comes from shared memory
+    const int t_end = prep ? pos : pos + 1;       // fused form: row `pos` comes from shared memory
+    const int rows = t_end - tb;                  // cached rows to stream
     int S = (rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
     S = S < 1 ? 1 : (S > (int)gridDim.x ? (int)gridDim.x : S);
     if (split >= S) return;
     const int per = (rows + S - 1) / S;
     const int t0 = tb + split * per;
-    const int t1 = min(pos, t0 + per);
+    const int t1 = min(t_end, t0 + per);
     const int nstages = (t1 - t0 + SLOTS * UN - 1) / (SLOTS * UN);    // CTA-uniform
     const size_t esz = BF16 ? 2 : 4;
     const size_t row_bytes = (size_t)a.n_kv * HD * esz;
-    const uint8_t* kbase = (const uint8_t*)a.kc + ((size_t)kh * HD + sub * EPL) * esz;
-    const uint8_t* vbase = (const uint8_t*)a.vc + ((size_t)kh * HD + sub * EPL) * esz;
+    const uint8_t* kbase = (const uint8_t*)a.kc + ((size_t)b * dv.seq_stride + (size_t)kh * HD + sub * EPL) * esz;
+    const uint8_t* vbase = (const uint8_t*)a.vc + ((size_t)b * dv.seq_stride + (size_t)kh * HD + sub * EPL) * esz;
 
     auto issue = [&](int j) {                     // always commits, so that group counts stay aligned
         if (j < nstages) {
@@ -429,7 +434,7 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     const float* cr = a.cos_t ? a.cos_t + (size_t)pos * half : nullptr;
     const float* sr = a.sin_t ? a.sin_t + (size_t)pos * half : nullptr;
     const int q_rows = a.n_heads * HD, kv_rows = a.n_kv * HD;
-    const bool prep_q = warp < G, prep_k = split == 0 && warp == G, prep_v = split == 0 && warp == G + 1;
+    const bool prep_q = prep && warp < G, prep_k = prep && split == 0 && warp == G, prep_v = prep && split == 0 && warp == G + 1;
     MgRopeConsts rc = {};
     const float* nw = nullptr;
     if (prep_q) nw = a.q_norm ? a.q_norm + (size_t)(kh * G + warp) * HD : nullptr;
@@ -459,6 +464,9 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
             *reinterpret_cast<float4*>(reinterpret_cast<float*>(cache) + off) = v;
         }
         reinterpret_cast<float4*>(prep_k ? k_new : v_new)[lane] = v;
+    } else if (!prep && warp < G) {
+        reinterpret_cast<float4*>(q_s + warp * HD)[lane] =
+            __ldcg(reinterpret_cast<const float4*>(dv.q_ready + ((size_t)b * a.n_heads + kh * G + warp) * HD) + lane);
     }
     __syncthreads();
     ax_trace_staged(dv.trace);
@@ -490,7 +498,7 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     cp_async_wait<0>();
 
     // the new row itself (split 0, first lane group of warp 0)
-    if (split == 0 && warp == 0) {
+    if (prep && split == 0 && warp == 0) {
         uint4 k1[1], v1[1]; bool ok1[1] = { lane / LPR == 0 };
         float sc[1][G];
         const float* kp = k_new + sub * EPL; const float* vp = v_new + sub * EPL;
@@ -541,11 +549,11 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
         const int g = idx / HD, d = idx % HD;
         float M, L, A;
         merge_states<HD>(smm + (size_t)g * ST, kAttnWarps, G * ST, d, M, L, A);
-        const int h = kh * G + g;
+        const size_t h = (size_t)b * a.n_heads + kh * G + g;
         if (S == 1) {
-            a.out[(size_t)h * HD + d] = A / L;
+            a.out[h * HD + d] = A / L;
         } else {
-            float* P = dv.partials + ((size_t)h * SP + split) * ST;
+            float* P = dv.partials + (h * SP + split) * ST;
             P[2 + d] = A;
             if (d == 0) { P[0] = M; P[1] = L; }
         }
@@ -555,7 +563,7 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        const unsigned tk = atomicAdd(&dv.tickets[kh], 1u);
+        const unsigned tk = atomicAdd(&dv.tickets[b * gridDim.y + kh], 1u);
         s_last = (tk == (unsigned)(S - 1));
     }
     __syncthreads();
@@ -563,19 +571,19 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     __threadfence();
     for (int idx = tid; idx < G * HD; idx += kAttnThreads) {
         const int g = idx / HD, d = idx % HD;
-        const int h = kh * G + g;
+        const size_t h = (size_t)b * a.n_heads + kh * G + g;
         float M, L, A;
-        merge_states<HD>(dv.partials + (size_t)h * SP * ST, S, ST, d, M, L, A);
-        a.out[(size_t)h * HD + d] = A / L;
+        merge_states<HD>(dv.partials + h * SP * ST, S, ST, d, M, L, A);
+        a.out[h * HD + d] = A / L;
     }
-    if (tid == 0) dv.tickets[kh] = 0u;            // ready for the next launch
+    if (tid == 0) dv.tickets[b * gridDim.y + kh] = 0u;            // ready for the next launch
     ax_trace_end(dv.trace);
 }
 
 template <bool BF16, int G, int NST>
-int launch_fused_n(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
+int launch_fused_n(atlasx_ctx* ctx, const FusedDev& dv, bool pdl, int batch) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)dv.a.max_splits, (unsigned)dv.a.n_kv);
+    cfg.gridDim = dim3((unsigned)dv.a.max_splits, (unsigned)dv.a.n_kv, (unsigned)batch);
     cfg.blockDim = dim3(kAttnThreads);
     cfg.dynamicSmemBytes = fused_land_bytes(NST) + (size_t)(G + 2) * 128 * 4;
     cfg.stream = ctx->stream;
@@ -597,12 +605,14 @@ int launch_fused_n(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
 }
 int g_fused_stages = kFusedStagesDefault;       // 2..4; ATLASX_ATTN_STAGES overrides (experiments)
 
+// Inside a decode step two stages are best (the kernel shares the SM with its GEMV neighbours);
+// the stand-alone operator streams with four.
 template <bool BF16, int G>
-int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl) {
-    switch (g_fused_stages) {
-        case 3:  return launch_fused_n<BF16, G, 3>(ctx, dv, pdl);
-        case 4:  return launch_fused_n<BF16, G, 4>(ctx, dv, pdl);
-        default: return launch_fused_n<BF16, G, 2>(ctx, dv, pdl);
+int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl, int batch = 1) {
+    switch (dv.q_ready ? 4 : g_fused_stages) {
+        case 3:  return launch_fused_n<BF16, G, 3>(ctx, dv, pdl, batch);
+        case 4:  return launch_fused_n<BF16, G, 4>(ctx, dv, pdl, batch);
+        default: return launch_fused_n<BF16, G, 2>(ctx, dv, pdl, batch);
     }
 }
 
@@ -641,7 +651,7 @@ int dispatch_g(atlasx_ctx* ctx, AttnDev& dv, bool pdl) {
 }  // namespace
 
 int ax_attn_pick_splits(const atlasx_ctx* ctx, int n_kv, int batch, int max_rows) {
-    const int want = 2 * ctx->sm_count;                 // two CTAs of this kernel fit per SM
+    const int want = 3 * ctx->sm_count;                 // about three CTAs of these kernels fit per SM
     int s = (want + n_kv * batch - 1) / (n_kv * batch);
     const int cap = (max_rows + 63) / 64;               // at least 64 rows per split
     if (s > cap) s = cap;
@@ -668,6 +678,24 @@ int ax_attn_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
         }
         AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_generic_kernel, a));
         return ATLASX_OK;
+    }
+    const int g_real = a.n_heads / a.n_kv;
+    if (a.hd == 128 && (g_real == 1 || g_real == 2 || g_real == 4) && (((uintptr_t)a.out) & 15) == 0) {
+        // head_dim 128: the landing-slot kernel in its operator form
+        FusedDev fd;
+        fd.a.kc = const_cast<void*>(a.kc); fd.a.vc = const_cast<void*>(a.vc); fd.a.out = a.out;
+        fd.a.n_heads = a.n_heads; fd.a.n_kv = a.n_kv; fd.a.window = a.window; fd.a.kv_dtype = a.kv_dtype; fd.a.scale = a.scale;
+        int sp = a.n_splits < 1 ? 1 : (a.n_splits > 64 ? 64 : a.n_splits);
+        fd.a.max_splits = sp;
+        int rc2 = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.batch * a.n_heads * sp * (128 + 2), (size_t)a.batch * a.n_heads);
+        if (rc2) return rc2;
+        fd.partials = ctx->attn_partials; fd.tickets = ctx->attn_tickets; fd.trace = nullptr;
+        fd.q_ready = a.q; fd.seq_stride = a.seq_stride; fd.pos_b = a.pos; fd.pos_shared = a.pos_shared; fd.pos_scalar = a.pos_scalar;
+        if (a.kv_dtype == ATLASX_BF16)
+            return g_real == 1 ? launch_fused<true, 1>(ctx, fd, pdl, a.batch) : g_real == 2 ? launch_fused<true, 2>(ctx, fd, pdl, a.batch)
+                                                                                          : launch_fused<true, 4>(ctx, fd, pdl, a.batch);
+        return g_real == 1 ? launch_fused<false, 1>(ctx, fd, pdl, a.batch) : g_real == 2 ? launch_fused<false, 2>(ctx, fd, pdl, a.batch)
+                                                                                       : launch_fused<false, 4>(ctx, fd, pdl, a.batch);
     }
     AttnDev dv;
     dv.a = a;
@@ -716,6 +744,7 @@ int ax_attn_fused_launch(atlasx_ctx* ctx, const AxFusedAttnArgs& a, bool pdl) {
     dv.partials = ctx->attn_partials;
     dv.tickets = ctx->attn_tickets;
     dv.trace = nullptr;
+    dv.q_ready = nullptr; dv.seq_stride = 0; dv.pos_b = nullptr; dv.pos_shared = 1; dv.pos_scalar = 0;
     if (ctx->trace_next) { dv.trace = ctx->trace_next; ctx->trace_next += 6; }
     const int g = a.n_heads / a.n_kv;
     if (a.kv_dtype == ATLASX_BF16)
