@@ -49,6 +49,7 @@ struct atlasx_ctx {
     float* attn_partials = nullptr;  size_t attn_partials_cap = 0;   // floats
     unsigned* attn_tickets = nullptr; size_t attn_tickets_cap = 0;   // uints, always zero between launches
     int* pos_dev = nullptr; size_t pos_cap = 0;
+    void* split_scratch = nullptr; size_t split_scratch_cap = 0;   // bf16 hi/lo planes of the multi-column input
     // argmax scratch
     float* amax_vals = nullptr; int* amax_idx = nullptr; unsigned* amax_ticket = nullptr; int* amax_out = nullptr;
     // device error word written by bounded waits
@@ -80,6 +81,7 @@ __device__ __forceinline__ void ax_trace_staged(unsigned long long* tr) {
 }
 
 int atlasx_ctx_ensure_attn_scratch(atlasx_ctx* ctx, size_t partial_floats, size_t tickets);
+int atlasx_ctx_ensure_split_scratch(atlasx_ctx* ctx, size_t bytes);
 
 // ── device helpers ──────────────────────────────────────────────────────────────
 #define AX_FULL 0xFFFFFFFFu

@@ -79,7 +79,7 @@ extern "C" int atlasx_ctx_sync(atlasx_ctx* c) {
 extern "C" void* atlasx_ctx_stream(atlasx_ctx* c) { return c ? (void*)c->stream : nullptr; }
 extern "C" int atlasx_ctx_sm_count(atlasx_ctx* c) { return c ? c->sm_count : 0; }
 extern "C" int atlasx_ctx_set_gemv_impl(atlasx_ctx* c, int impl) {
-    AX_ARG(c && impl >= 0 && impl <= 2, "impl must be 0, 1 or 2");
+    AX_ARG(c && impl >= 0 && impl <= 3, "impl must be 0 (automatic), 1 (plain loads), 2 (bulk-copy ring) or 3 (as 1, scalar multi-column kernel)");
     c->gemv_impl = impl;
     return ATLASX_OK;
 }
@@ -91,6 +91,21 @@ extern "C" int atlasx_ctx_poll_device_error(atlasx_ctx* c, int* code_out) {
     if (code) AX_CUDA(cudaMemsetAsync(c->dev_error, 0, sizeof(int), c->stream));
     if (code_out) *code_out = code;
     return code ? atlasx_fail(ATLASX_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", code) : ATLASX_OK;
+}
+
+int atlasx_ctx_ensure_split_scratch(atlasx_ctx* c, size_t bytes) {
+    if (bytes <= c->split_scratch_cap) return ATLASX_OK;
+    cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+    cudaStreamIsCapturing(c->stream, &st);
+    if (st != cudaStreamCaptureStatusNone)
+        return atlasx_fail(ATLASX_ERR_STATE, "multi-column scratch must be sized before stream capture");
+    AX_CUDA(cudaStreamSynchronize(c->stream));
+    cudaFree(c->split_scratch);
+    c->split_scratch = nullptr; c->split_scratch_cap = 0;
+    if (bytes < (1u << 21)) bytes = 1u << 21;
+    AX_CUDA(cudaMalloc(&c->split_scratch, bytes));
+    c->split_scratch_cap = bytes;
+    return ATLASX_OK;
 }
 
 int atlasx_ctx_ensure_attn_scratch(atlasx_ctx* c, size_t partial_floats, size_t tickets) {

@@ -307,6 +307,8 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     if (w.dtype == ATLASX_INT8) vec_ok = vec_ok && w.scales;
     if (vec_ok && pro.base) vec_ok = (((uintptr_t)pro.base & 15) == 0);
 
+    if (n > 1 && !has_pro && epi == AX_EPI_PLAIN && ctx->gemv_impl != 3 && ax_gemv_mma_supported(w, n, pro.base, y))
+        return ax_gemv_mma_launch(ctx, w, pro.base, n, y);             // gemv_impl 3 keeps the scalar kernel (A/B comparison)
     if (!vec_ok) {
         AX_ARG(!has_pro && epi == AX_EPI_PLAIN && pro.base, "fused prologue/epilogue need 16-byte aligned rows and n == 1");
         const int warps = 8;

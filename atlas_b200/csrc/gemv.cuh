@@ -80,5 +80,8 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
 int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* y, int* err, GemvArgs* out);
 int ax_gemv_ring_scale_seg(const AxWeight& w);   // int4: scale bytes that accompany one full weight segment (0 otherwise)
 int ax_gemv_ring_seg_bytes();
+// Tensor-core path for n = 2..16 columns (bf16 / int8 / int4 weights); X [cols×n], Y [rows×n] row-major f32.
+bool ax_gemv_mma_supported(const AxWeight& w, int n, const float* x, const float* y);
+int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y);
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes
 size_t ax_weight_bytes(const AxWeight& w);

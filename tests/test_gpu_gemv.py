@@ -129,6 +129,20 @@ def test_gemv_multi_column(ab, fmt, n, shape):
     assert rel_err(Y[:, 0], y0) <= 1e-5
 
 
+@pytest.mark.parametrize("fmt", ["bf16", "int8", "int4"])
+@pytest.mark.parametrize("n,shape", [(2, (100, 1376)), (5, (100, 1376)), (16, (200, 11008)), (7, (40, 11008)), (13, (1000, 4096))])
+def test_gemv_multi_column_ragged_rows_odd_columns_chunked_k(ab, fmt, n, shape):
+    """Row counts that are no multiple of the 16-row tile, column counts that are no multiple of 8,
+    K long enough that the staged input is cut into several chunks (K = 11008 with 9..16 columns),
+    and K = 1376, which int8 (64-element steps) hands to the scalar kernel."""
+    M, K = shape
+    w = orc.normal_f32(M * K, 46, M + K, 0.02).reshape(M, K)
+    X = orc.normal_f32(K * n, 46, n, 1.0).reshape(K, n)
+    gm, wo = make(ab, fmt, w)
+    Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+    assert rel_err(Y, orc.gemm(wo, X)) <= TOL
+
+
 def test_golden_fixtures(ab, impl):
     g = np.load(os.path.join(G, "gemv.npz"))
     for M, K in [(64, 256), (48, 1376)]:
