@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(128) ax_qk_prep_kernel(const AxQkPrepArgs a) {
 // CTAs per SM) stay in flight without costing registers.  The first NST stages are requested
 // before griddepcontrol.wait: rows below `pos` are older than the previous kernel.
 constexpr int kFusedUnroll = 2;
-constexpr int kFusedStagesDefault = 2;
+constexpr int kFusedStagesDefault = 3;
 constexpr int kFusedRowsPerSplit = 64;
 __host__ __device__ constexpr size_t fused_land_bytes(int nst) { return (size_t)nst * kFusedUnroll * 2 * kAttnThreads * 16; }
 
@@ -605,14 +605,14 @@ int launch_fused_n(atlasx_ctx* ctx, const FusedDev& dv, bool pdl, int batch) {
 }
 int g_fused_stages = kFusedStagesDefault;       // 2..4; ATLASX_ATTN_STAGES overrides (experiments)
 
-// Inside a decode step two stages are best (the kernel shares the SM with its GEMV neighbours);
+// Inside a decode step three stages are best (the kernel shares the SM with its GEMV neighbours);
 // the stand-alone operator streams with four.
 template <bool BF16, int G>
 int launch_fused(atlasx_ctx* ctx, const FusedDev& dv, bool pdl, int batch = 1) {
     switch (dv.q_ready ? 4 : g_fused_stages) {
-        case 3:  return launch_fused_n<BF16, G, 3>(ctx, dv, pdl, batch);
         case 4:  return launch_fused_n<BF16, G, 4>(ctx, dv, pdl, batch);
-        default: return launch_fused_n<BF16, G, 2>(ctx, dv, pdl, batch);
+        case 2:  return launch_fused_n<BF16, G, 2>(ctx, dv, pdl, batch);
+        default: return launch_fused_n<BF16, G, 3>(ctx, dv, pdl, batch);
     }
 }
 
@@ -719,9 +719,11 @@ bool ax_attn_fused_supported(int hd, int n_heads, int n_kv) {
     return g == 1 || g == 2 || g == 4;
 }
 int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows) {
-    // one wave: three CTAs of this kernel are resident per SM
+    // one wave of CTAs
     int s = (max_rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
-    const int wave = (3 * ctx->sm_count) / (n_kv > 0 ? n_kv : 1);
+    int per_sm = 2;                  // measured best with three landing stages (48 KB per CTA)
+    if (const char* e = getenv("ATLASX_ATTN_WAVE")) { const int v = atoi(e); if (v >= 1 && v <= 8) per_sm = v; }   // experiments
+    const int wave = (per_sm * ctx->sm_count) / (n_kv > 0 ? n_kv : 1);
     if (s > wave) s = wave;
     return s < 1 ? 1 : (s > 64 ? 64 : s);
 }
