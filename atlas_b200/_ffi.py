@@ -126,6 +126,7 @@ SIGNATURES = {
     "atlasx_model_kernel_launches_per_step": (ci, [vp]),
     "atlasx_model_set_options": (ci, [vp, ci, ci]),
     "atlasx_model_set_mega": (ci, [vp, ci]),
+    "atlasx_model_set_prefill": (ci, [vp, ci, vp]),
     "atlasx_model_uses_mega": (ci, [vp]),
     "atlasx_model_hidden": (ci, [vp, vp]),
     "atlasx_time_gemv": (ci, [vp, vp, ci, vp, ci, vp, ci, C.POINTER(cf)]),

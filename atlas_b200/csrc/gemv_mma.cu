@@ -39,6 +39,7 @@ struct MmaArgs {
     int kc;                           // k elements staged per chunk (multiple of 64 · 8 warps)
     int pitch;                        // bf16 elements between columns of the staged X
     int tiles;                        // 16-row tiles per row group (1, 2 or 4)
+    int token_major;                  // X is [N][K] and Y is [N][M] (one contiguous vector per column) instead of [K][N] / [M][N]
 };
 
 __device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
@@ -127,13 +128,13 @@ __device__ __forceinline__ void step_mma(float (&acc)[NT][4], const typename Mma
 
 // X [K×N] f32 → two bf16 planes [N+1][kpad] in global memory (hi, lo), column-major, the extra
 // column and the tail past K all zero: what the main kernel copies into shared memory verbatim.
-__global__ void ax_gemv_mma_split_x(const float* X, int K, int N, int kpad, uint16_t* xh, uint16_t* xl) {
+__global__ void ax_gemv_mma_split_x(const float* X, int K, int N, int kpad, int token_major, uint16_t* xh, uint16_t* xl) {
     const int k = blockIdx.x * blockDim.x + threadIdx.x;
     if (k >= kpad) return;
     for (int n = 0; n <= N; n++) {
         uint16_t h = 0, l = 0;
         if (n < N && k < K) {
-            const float x = X[(size_t)k * N + n];
+            const float x = token_major ? X[(size_t)n * K + k] : X[(size_t)k * N + n];
             h = ax_f32_to_bf16_rne(x);
             l = ax_f32_to_bf16_rne(x - ax_bf16_to_f32(h));
         }
@@ -242,7 +243,7 @@ __global__ void __launch_bounds__(kMmaThreads, 2) ax_gemv_mma_kernel(const MmaAr
 #pragma unroll
                         for (int w = 0; w < kMmaWarps; w++) s += red[(size_t)w * 16 * NC + e];
                         if (FMT == ATLASX_INT8) s *= reinterpret_cast<const float*>(a.scales)[row];
-                        float* dst = a.Y + (size_t)row * a.N + n;
+                        float* dst = a.token_major ? a.Y + (size_t)n * a.M + row : a.Y + (size_t)row * a.N + n;
                         *dst = kc0 == 0 ? s : *dst + s;
                     }
                 }
@@ -276,7 +277,7 @@ bool ax_gemv_mma_supported(const AxWeight& w, int n, const float* x, const float
     }
 }
 
-int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y) {
+int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major) {
     AX_ARG(ax_gemv_mma_supported(w, n, x, y), "shape or format not covered by the tensor-core multi-column kernel");
     const int nt = n <= 8 ? 1 : 2;
     const int nc = 8 * nt;
@@ -286,7 +287,7 @@ int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n
     a.M = w.rows; a.K = w.cols; a.N = n;
     a.row_bytes = w.dtype == ATLASX_BF16 ? w.cols * 2 : w.dtype == ATLASX_INT8 ? w.cols : w.cols / 2;
     a.block = w.block > 0 ? w.block : 32; a.scales_f16 = w.scales_f16;
-    a.X = x; a.Y = y;
+    a.X = x; a.Y = y; a.token_major = token_major ? 1 : 0;
     // chunk of K staged at a time: about 100 KB of shared memory, so that two CTAs share an SM
     const size_t red_bytes = (size_t)kMmaWarps * 16 * nc * sizeof(float);
     const long long k_pad = ((long long)w.cols + gran - 1) / gran * gran;
@@ -302,7 +303,7 @@ int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n
     if (rc) return rc;
     uint16_t* xh = reinterpret_cast<uint16_t*>(ctx->split_scratch);
     a.xh = xh; a.xl = xh + plane;
-    ax_gemv_mma_split_x<<<(a.kpad + 255) / 256, 256, 0, ctx->stream>>>(x, w.cols, n, a.kpad, xh, xh + plane);
+    ax_gemv_mma_split_x<<<(a.kpad + 255) / 256, 256, 0, ctx->stream>>>(x, w.cols, n, a.kpad, a.token_major, xh, xh + plane);
     AX_CHECK_LAUNCH("ax_gemv_mma_split_x");
     // rows per CTA pass: as many 16-row tiles (1, 2 or 4) as still give every CTA slot a group
     const int slots = 2 * ctx->sm_count;

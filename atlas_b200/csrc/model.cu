@@ -88,6 +88,11 @@ struct atlasx_model {
     MegaPhase* phases_dev = nullptr; MegaSync* sync = nullptr;
     float* mega_partials = nullptr; float* sel_vals = nullptr; int* sel_idx = nullptr;
     MegaArgs margs; size_t mega_smem = 0; int mega_splits = 1;
+    // prompt ingestion in chunks of up to kPrefillMax tokens through the multi-column kernels
+    int prefill_chunk = 1;                       // 1: token by token (the reference's way)
+    float *pf_r = nullptr, *pf_a = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_o = nullptr,
+          *pf_gu = nullptr, *pf_h = nullptr, *pf_dn = nullptr;
+    int* pf_pos = nullptr;
     // timeline diagnostics of the captured step (ATLASX_STEP_TRACE)
     unsigned long long* step_trace = nullptr; int step_trace_slots = 0;
 };
@@ -532,6 +537,147 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     return ATLASX_OK;
 }
 
+constexpr int kPrefillMax = 16;
+
+// ── prompt ingestion: row-wise helpers, one CTA per token ───────────────────────────
+__global__ void pf_positions_k(const StepState* st, int* pos_arr, int n) {
+    if ((int)threadIdx.x < n) pos_arr[threadIdx.x] = st->pos + threadIdx.x;
+}
+__global__ void pf_embed_rows_k(const void* embed, int bf16, int vocab, const int* seq, const int* pos_arr, int d, float* out) {
+    const int i = blockIdx.x;
+    long long tok = seq[pos_arr[i]];
+    if (tok < 0) tok = 0;
+    if (tok > vocab - 1) tok = vocab - 1;
+    for (int k = threadIdx.x; k < d; k += blockDim.x)
+        out[(size_t)i * d + k] = bf16 ? ax_bf16_to_f32(((const uint16_t*)embed)[(size_t)tok * d + k]) : ((const float*)embed)[(size_t)tok * d + k];
+}
+__device__ __forceinline__ float pf_block_sum(float v, float* red) {
+    v = ax_warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x >> 5); w++) t += red[w];
+    return t;
+}
+// The fused prologue of the GEMVs, row by row:  v = base + (wy ? rmsnorm(y, wy) : y);  resid = v;
+// x = wx ? rmsnorm(v, wx) : v.   y may be null (v = base).  resid may alias base, x may alias resid.
+__global__ void __launch_bounds__(256) pf_rows_norm_add_k(const float* y, const float* base, const float* wy, const float* wx, float eps,
+                                                          int d, float* resid, float* x) {
+    __shared__ float red[8];
+    const size_t o = (size_t)blockIdx.x * d;
+    float inv_y = 1.f;
+    if (y && wy) {
+        float ss = 0.f;
+        for (int k = threadIdx.x; k < d; k += 256) ss = fmaf(y[o + k], y[o + k], ss);
+        inv_y = 1.0f / sqrtf(pf_block_sum(ss, red) / (float)d + eps);
+    }
+    float ss2 = 0.f;
+    for (int k = threadIdx.x; k < d; k += 256) {
+        float v = base[o + k];
+        if (y) { float t = y[o + k]; if (wy) t = t * inv_y * wy[k]; v += t; }
+        resid[o + k] = v;
+        ss2 = fmaf(v, v, ss2);
+    }
+    if (wx) {
+        const float inv_x = 1.0f / sqrtf(pf_block_sum(ss2, red) / (float)d + eps);
+        for (int k = threadIdx.x; k < d; k += 256) x[o + k] = resid[o + k] * inv_x * wx[k];
+    } else if (x != resid) {
+        for (int k = threadIdx.x; k < d; k += 256) x[o + k] = resid[o + k];
+    }
+}
+// gate/up rows are interleaved (even: gate, odd: up): out[i][j] = silu(gu[i][2j]) · gu[i][2j+1]
+__global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out) {
+    const size_t i = blockIdx.y;
+    const int j = blockIdx.x * blockDim.x + threadIdx.x;
+    if (j >= f) return;
+    const float2 v = reinterpret_cast<const float2*>(gu + i * 2 * (size_t)f)[j];
+    out[i * (size_t)f + j] = (v.x / (1.0f + expf(-v.x))) * v.y;
+}
+__global__ void pf_advance_k(StepState* st, int by) { st->pos += by; }
+
+bool prefill_supported(const atlasx_model* m) {
+    if (m->cfg.weight_format == ATLASX_F32) return false;
+    float dummy;
+    for (const Layer& ly : m->layers) {
+        const AxWeight* ws[4] = { &ly.qkv, &ly.wo, &ly.gateup, &ly.down };
+        for (const AxWeight* w : ws) if (!ax_gemv_mma_supported(*w, 2, &dummy, &dummy)) return false;
+    }
+    return true;
+}
+
+// n prompt tokens (2..kPrefillMax) at once: seq[pos .. pos+n) → caches, logits of the last one,
+// selection, pos += n.  Same arithmetic as n single steps (crates/atlas-model/src/lib.rs:1611-1618
+// feeds the prompt token by token); the weights stream once per chunk instead of once per token.
+int run_prefill_chunk(atlasx_model* m, int n) {
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    const atlasx_model_config& cf = m->cfg;
+    const int d = cf.d_model, L = cf.n_layers;
+    const bool post = cf.post_norm != 0;
+    const int qkv_rows = m->q_rows + 2 * m->kv_rows;
+    int rc;
+    pf_positions_k<<<1, 32, 0, s>>>(m->st, m->pf_pos, n);
+    pf_embed_rows_k<<<n, 256, 0, s>>>(m->embed, m->embed_bf16, cf.vocab_size, m->seq, m->pf_pos, d, m->pf_r);
+    const float* a_in = m->pf_r;
+    if (!post) { pf_rows_norm_add_k<<<n, 256, 0, s>>>(nullptr, m->pf_r, nullptr, m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a); a_in = m->pf_a; }
+    for (int l = 0; l < L; l++) {
+        Layer& ly = m->layers[l];
+        if ((rc = ax_gemv_mma_launch(c, ly.qkv, a_in, n, m->pf_qkv, true))) return rc;
+        for (int i = 0; i < n; i++) {
+            float* qkv = m->pf_qkv + (size_t)i * qkv_rows;
+            float* out = m->pf_att + (size_t)i * m->q_rows;
+            if (m->fused_attn) {
+                AxFusedAttnArgs fa;
+                fa.qkv = qkv; fa.q_norm = ly.q_norm; fa.k_norm = ly.k_norm; fa.cos_t = m->cos_t; fa.sin_t = m->sin_t;
+                fa.kc = ly.kv->k; fa.vc = ly.kv->v; fa.out = out; fa.pos = m->pf_pos + i;
+                fa.n_heads = m->nh_loc; fa.n_kv = m->nkv_loc; fa.window = ly.window; fa.kv_dtype = cf.kv_dtype;
+                fa.max_splits = m->fused_splits; fa.scale = m->scale; fa.qk_eps = 1e-6f;
+                if ((rc = ax_attn_fused_launch(c, fa, false))) return rc;
+            } else {
+                AxQkPrepArgs qa;
+                qa.q = qkv; qa.k = qkv + m->q_rows; qa.v = qkv + m->q_rows + m->kv_rows;
+                qa.q_norm = ly.q_norm; qa.k_norm = ly.k_norm; qa.cos_t = m->cos_t; qa.sin_t = m->sin_t;
+                qa.kc = ly.kv->k; qa.vc = ly.kv->v; qa.pos = m->pf_pos + i; qa.pos_shared = 1;
+                qa.batch = 1; qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype; qa.eps = 1e-6f;
+                if ((rc = ax_qk_prep_launch(c, qa, false))) return rc;
+                AxAttnArgs aa;
+                aa.q = qkv; aa.kc = ly.kv->k; aa.vc = ly.kv->v; aa.out = out;
+                aa.pos = m->pf_pos + i; aa.pos_shared = 1; aa.batch = 1;
+                aa.n_heads = m->nh_loc; aa.n_kv = m->nkv_loc; aa.hd = m->hd; aa.window = ly.window;
+                aa.kv_dtype = cf.kv_dtype; aa.scale = m->scale; aa.n_splits = m->attn_splits;
+                if ((rc = ax_attn_launch(c, aa, false))) return rc;
+            }
+        }
+        if ((rc = ax_gemv_mma_launch(c, ly.wo, m->pf_att, n, m->pf_o, true))) return rc;
+        if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
+        pf_rows_norm_add_k<<<n, 256, 0, s>>>(m->pf_o, m->pf_r, post ? ly.attn_norm : nullptr, post ? nullptr : ly.ffn_norm,
+                                             cf.rms_norm_eps, d, m->pf_r, m->pf_a);
+        if ((rc = ax_gemv_mma_launch(c, ly.gateup, m->pf_a, n, m->pf_gu, true))) return rc;
+        pf_silu_pair_rows_k<<<dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)n), 256, 0, s>>>(m->pf_gu, m->ffn_loc, m->pf_h);
+        if ((rc = ax_gemv_mma_launch(c, ly.down, m->pf_h, n, m->pf_dn, true))) return rc;
+        if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_dn, (size_t)n * d))) return rc;
+        const float* next_wx = (post || l == L - 1) ? nullptr : m->layers[l + 1].attn_norm;
+        pf_rows_norm_add_k<<<n, 256, 0, s>>>(m->pf_dn, m->pf_r, post ? ly.ffn_norm : nullptr, next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a);
+        a_in = m->pf_a;
+    }
+    AX_CHECK_LAUNCH("prefill chunk");
+    // logits of the chunk's last token through the single-column path, then selection
+    AxPrologue pl;
+    pl.eps = cf.rms_norm_eps;
+    pl.base = m->pf_r + (size_t)(n - 1) * d;
+    pl.wx = m->final_norm;
+    pl.resid_out = m->resid[m->final_resid];
+    if ((rc = ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, false))) return rc;
+    if (m->world > 1 && (rc = ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc))) return rc;
+    pf_advance_k<<<1, 1, 0, s>>>(m->st, n - 1);
+    AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
+    select_advance_k<<<(cf.vocab_size + 1023) / 1024, 256, 0, s>>>(m->logits, cf.vocab_size, sc, m->st, m->seq, cf.max_seq_len + 1, 1, 1);
+    AX_CHECK_LAUNCH("prefill selection");
+    m->host_pos += n;
+    return ATLASX_OK;
+}
+
 int capture_graph(atlasx_model* m) {
     atlasx_ctx* c = m->ctx;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
@@ -805,6 +951,34 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     return ATLASX_OK;
 }
 
+// Prompt tokens are ingested `chunk` at a time (2..16) through the multi-column kernels; 0 or 1
+// restores the token-by-token path.  Returns the chunk size in effect through *effective: 1 when
+// the weight format or a matrix shape is outside what the multi-column kernel covers.
+extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective) {
+    AX_ARG(m && m->finalized, "model is not finalised");
+    AX_ARG(chunk >= 0 && chunk <= kPrefillMax, "chunk must be in 0..16");
+    int eff = chunk < 2 ? 1 : chunk;
+    if (eff > 1 && !prefill_supported(m)) eff = 1;
+    if (eff > 1 && !m->pf_r) {
+        const size_t P = kPrefillMax;
+        const int d = m->cfg.d_model, qkv_rows = m->q_rows + 2 * m->kv_rows;
+        int rc;
+        if ((rc = dmalloc(m, (void**)&m->pf_r, P * d * 4)) || (rc = dmalloc(m, (void**)&m->pf_a, P * d * 4)) ||
+            (rc = dmalloc(m, (void**)&m->pf_qkv, P * qkv_rows * 4)) || (rc = dmalloc(m, (void**)&m->pf_att, P * m->q_rows * 4)) ||
+            (rc = dmalloc(m, (void**)&m->pf_o, P * d * 4)) || (rc = dmalloc(m, (void**)&m->pf_gu, P * 2 * (size_t)m->ffn_loc * 4)) ||
+            (rc = dmalloc(m, (void**)&m->pf_h, P * (size_t)m->ffn_loc * 4)) || (rc = dmalloc(m, (void**)&m->pf_dn, P * d * 4)) ||
+            (rc = dmalloc(m, (void**)&m->pf_pos, P * sizeof(int)))) return rc;
+        // scratch of the multi-column kernel for the widest input
+        int kmax = d > m->ffn_loc ? d : m->ffn_loc;
+        if (m->q_rows > kmax) kmax = m->q_rows;
+        rc = atlasx_ctx_ensure_split_scratch(m->ctx, (size_t)2 * (kPrefillMax + 1) * ((size_t)kmax + 8192) * sizeof(uint16_t));
+        if (rc) return rc;
+    }
+    m->prefill_chunk = eff;
+    if (effective) *effective = eff;
+    return ATLASX_OK;
+}
+
 extern "C" int atlasx_model_set_mega(atlasx_model* m, int on) {
     AX_ARG(m, "model is null");
     AX_ARG(!m->finalized, "choose the step kernel before atlasx_model_finalize");
@@ -914,7 +1088,13 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         // last_logits starts as zeros (:1609): the first choice is made among equal logits
         AX_CUDA(cudaMemsetAsync(m->logits, 0, (size_t)V * 4, s));
     }
-    for (int i = 0; i < n_prompt; i++) { rc = step(m); if (rc) return done(rc); }
+    for (int i = 0; i < n_prompt;) {
+        const int left = n_prompt - i;
+        const int n = (m->prefill_chunk > 1 && left >= 2) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
+        rc = n > 1 ? run_prefill_chunk(m, n) : step(m);
+        if (rc) return done(rc);
+        i += n;
+    }
     AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
     for (int stepi = 0; stepi < max_new; stepi++) {
         const bool need_fix = fix && ((stepi == 0 && n_suppress > 0) || (rep_penalty != 1.0f && stepi > 0));

@@ -148,6 +148,13 @@ class OlmoModel:
         check(_ffi.lib().atlasx_model_set_options(self._h, int(use_graph), int(use_pdl)))
         check(_ffi.lib().atlasx_model_finalize(self._h))
 
+    def set_prefill(self, chunk=16):
+        """Prompt ingestion `chunk` tokens at a time (the reference's generate feeds one token per
+        forward, :1611-1618).  Returns the chunk size in effect (1 = token by token)."""
+        eff = C.c_int(0)
+        check(_ffi.lib().atlasx_model_set_prefill(self._h, int(chunk), C.byref(eff)))
+        return eff.value
+
     def set_options(self, use_graph=True, use_pdl=True):
         check(_ffi.lib().atlasx_model_set_options(self._h, int(use_graph), int(use_pdl)))
 

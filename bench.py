@@ -274,6 +274,7 @@ def main():
     ap.add_argument("--timeline", action="store_true",
                     help="record %%globaltimer stamps in every GEMV and attention launch of the captured step and print a "
                          "per-class summary on stderr; the stamps cost a little, so the JSON line is marked invalid")
+    ap.add_argument("--prefill", type=int, default=16, help="prompt tokens ingested per chunk before the timed region (1: token by token)")
     ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")
     args = ap.parse_args()
     global PROFILE_LAYERS
@@ -320,8 +321,16 @@ def main():
         m.set_options(use_graph=not args.no_graph, use_pdl=not args.no_pdl)
     prompt = np.random.default_rng(0).integers(0, mc.vocab_size, size=args.prompt, dtype=np.uint32)
 
-    # context: the prompt goes through the decode path token by token, as the reference does
+    # context: the prompt is ingested before the timed region (in chunks through the multi-column
+    # kernels unless --prefill 1; the reference feeds it token by token)
+    chunk = m.set_prefill(args.prefill) if args.prefill > 1 else 1
+    ctx.sync()
+    t_in = time.perf_counter()
     m.generate(prompt, 1, 0.0)
+    ctx.sync()
+    t_in = time.perf_counter() - t_in
+    prompt_ingest = {"tokens": int(args.prompt), "chunk": chunk, "ms": round(t_in * 1e3, 2),
+                     "tok_s": round(args.prompt / t_in, 1) if t_in > 0 else None}
     m.decode_timed(warm)                                   # warm-up steps (untimed)
 
     def barrier():
@@ -412,7 +421,7 @@ def main():
                        "kv_cache": "bf16", "parallelism": "tp%d" % world,
                        "l2": "inputs larger than L2: 13.77 GB of weights stream per step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": m.launches_per_step * steps,
-            "first_tokens": [int(t) for t in toks[:8]],
+            "first_tokens": [int(t) for t in toks[:8]], "prompt_ingest": prompt_ingest,
             "roofline": roofline, "cpu_baseline": cpu}
     if PROFILE_LAYERS:
         line["invalid"] = "profiler case: only %d of 32 layers" % PROFILE_LAYERS

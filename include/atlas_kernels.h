@@ -245,9 +245,16 @@ double atlasx_model_step_bytes(const atlasx_model* m, int pos);
 int atlasx_model_kernel_launches_per_step(const atlasx_model* m);
 int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
 /* Whole-step persistent kernel (one launch per token; single GPU, head_dim 128, ≤ 4 query heads per
- * KV head).  On by default where it applies; call before atlasx_model_finalize to turn it off and
- * keep the kernel-per-operation step. */
+ * KV head).  Off by default (the kernel-per-operation step is faster); call with on = 1 before
+ * atlasx_model_finalize to select it. */
 int atlasx_model_set_mega(atlasx_model* m, int on);
+/* Prompt ingestion in chunks: atlasx_model_generate_greedy feeds the prompt `chunk` tokens at a
+ * time (2..16) through the multi-column kernels, so the weights stream once per chunk instead of
+ * once per token (the reference feeds one token per forward, crates/atlas-model/src/lib.rs:1611-1618).
+ * 0 or 1 restores token-by-token ingestion (the default).  *effective receives the chunk in use:
+ * 1 when a weight format or shape is outside what the multi-column kernel covers (f32 weights,
+ * K not a multiple of 32, or of 64 for int8).  Call after atlasx_model_finalize. */
+int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective);
 int atlasx_model_uses_mega(const atlasx_model* m);
 /* residual stream after the last forward (d_model floats), for layer-level parity checks */
 int atlasx_model_hidden(atlasx_model* m, float* hidden_host);
