@@ -243,6 +243,49 @@ int set_attrs() {
 
 }  // namespace
 
+namespace {
+__global__ void __launch_bounds__(256) ax_mail_reduce_kernel(const uint2* parts, int n_parts, size_t stride, int d,
+                                                             const unsigned* epoch, unsigned mul, unsigned add, float* out, int* err) {
+    // The data polled below arrives through the mailbox from all GPUs (this one included), so the
+    // wait is not needed for it; it keeps the stream's rule that a kernel runs only after
+    // everything before its predecessor is complete, which later launches rely on.
+    griddep_wait();
+    griddep_launch();
+    const unsigned seq = __ldcg(epoch) * mul + add;
+    const int k2 = blockIdx.x * blockDim.x + threadIdx.x;          // two elements (16 bytes of pairs) per thread
+    if (2 * k2 >= d) return;
+    float s0 = 0.f, s1 = 0.f;
+    const unsigned long long t0 = ax_globaltimer();
+    for (int r = 0; r < n_parts; r++) {
+        const uint4* q = reinterpret_cast<const uint4*>(parts + (size_t)r * stride) + k2;
+        uint4 v;
+        for (;;) {
+            asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(q) : "memory");
+            if (v.y == seq && v.w == seq) break;
+            if (*reinterpret_cast<volatile int*>(err) != 0) break;
+            if (ax_globaltimer() - t0 > 2000000000ull) { atomicExch(err, 3); break; }
+        }
+        s0 += __uint_as_float(v.x); s1 += __uint_as_float(v.z);
+    }
+    reinterpret_cast<float2*>(out)[k2] = make_float2(s0, s1);
+}
+}  // namespace
+
+int ax_mail_reduce_launch(atlasx_ctx* ctx, const uint2* parts, int n_parts, size_t stride, int d,
+                          const unsigned* epoch, unsigned mul, unsigned add, float* out, bool pdl) {
+    AX_ARG(parts && out && epoch && n_parts >= 1 && d > 0 && (d & 1) == 0, "bad argument");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)((d / 2 + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_mail_reduce_kernel, parts, n_parts, stride, d, epoch, mul, add, out, ctx->dev_error));
+    return ATLASX_OK;
+}
+
 int ax_gemv_init(atlasx_ctx*) {
     int rc;
     if ((rc = set_attrs<ATLASX_F32>())) return rc;

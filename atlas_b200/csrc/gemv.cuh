@@ -52,6 +52,13 @@ struct AxPeerOut {
     const unsigned* epoch = nullptr; unsigned mul = 0, add = 0;   // sequence word: *epoch·mul + add
 };
 
+// Sum of the n_parts mailbox parts (value, sequence pairs) of one use into a plain f32 vector, in
+// rank order; every pair is polled (bounded) until its sequence word equals *epoch·mul + add.
+// One small kernel between producer and consumer: with many ranks it replaces the polling of all
+// parts by every CTA of the consumer (n_parts × 8·d bytes per CTA) by one pass per GPU.
+int ax_mail_reduce_launch(atlasx_ctx* ctx, const uint2* parts, int n_parts, size_t stride, int d,
+                          const unsigned* epoch, unsigned mul, unsigned add, float* out, bool pdl);
+
 enum { AX_EPI_PLAIN = 0, AX_EPI_SILU_PAIR = 1 };   // pair: out[r/2] = silu(acc[r])·acc[r+1], r even
 
 // Kernel-side view of one GEMV (built by ax_gemv_launch or by the whole-step kernel's program).

@@ -80,6 +80,7 @@ struct atlasx_model {
     int attn_splits = 1;
     bool fused_attn = false; int fused_splits = 1;   // one-launch attention (head_dim 128)
     const AxPeerMail* mail = nullptr;            // tensor parallel: all-reduce fused into o_proj/down over peer memory
+    bool mail_reduce = false;                    // parts are summed by one small kernel per use instead of by every consumer CTA
     std::vector<void*> owned;                    // device allocations to free
     int* pin = nullptr;                          // pinned host ints
     int launches_per_step = 0;
@@ -399,7 +400,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         return r;
     }
     const bool pdl = m->use_pdl && !prof;
-    static const int pdl_mask = getenv("ATLASX_PDL_MASK") ? atoi(getenv("ATLASX_PDL_MASK")) : 255;   // experiments
+    static const int pdl_mask = getenv("ATLASX_PDL_MASK") ? atoi(getenv("ATLASX_PDL_MASK")) : 511;   // experiments
     auto P = [&](int cls) { return pdl && ((pdl_mask >> cls) & 1); };
     const int d = cf.d_model, L = cf.n_layers;
     const bool post = cf.post_norm != 0;
@@ -416,6 +417,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         return po;
     };
     auto peer_in = [&](AxPrologue& p, int buf, int l) {
+        if (m->mail_reduce) return;                        // p.y already names the reduced vector
         p.y = reinterpret_cast<const float*>(mail->part(mail->rank, buf, 0));
         p.nparts = mail->world; p.part_stride = (size_t)mail->d;
         p.ll_n = mail->world; p.ll_stride = (size_t)mail->d;
@@ -481,6 +483,9 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         if (mail) {
             const AxPeerOut px = peer_out(0, l);
             STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ), &px));
+            if (m->mail_reduce)
+                STEP_LAUNCH(CLS_COMM, 8.0 * d * mail->world, ax_mail_reduce_launch(c, mail->part(mail->rank, 0, 0), mail->world, (size_t)mail->d, d,
+                                                                                   &m->st->epoch, (unsigned)L, (unsigned)l + 1u, m->o, P(CLS_COMM)));
         } else {
             STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ)));
             if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->o, (size_t)d));
@@ -501,6 +506,9 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         if (mail) {
             const AxPeerOut px = peer_out(1, l);
             STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN), &px));
+            if (m->mail_reduce)
+                STEP_LAUNCH(CLS_COMM, 8.0 * d * mail->world, ax_mail_reduce_launch(c, mail->part(mail->rank, 1, 0), mail->world, (size_t)mail->d, d,
+                                                                                   &m->st->epoch, (unsigned)L, (unsigned)l + 1u, m->dn, P(CLS_COMM)));
         } else {
             STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN)));
             if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->dn, (size_t)d));
@@ -928,6 +936,10 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
         // all-reduce afterwards lines the ranks up, so that the bounded waits of the first step
         // measure the step and not the difference in set-up time.
         rc = ax_comm_peer_setup(c, d, &m->mail); if (rc) return rc;
+        // every consumer CTA polling every part costs world × 8·d bytes of L2 reads per CTA; one more
+        // small launch per use is cheaper already with two ranks (466 against 462 tok/s)
+        m->mail_reduce = m->mail != nullptr;
+        if (const char* e = getenv("ATLASX_MAIL_REDUCE")) m->mail_reduce = m->mail && atoi(e) != 0;      // experiments
         AX_CUDA(cudaMemsetAsync(m->o, 0, (size_t)d * 4, s));
         rc = ax_comm_allreduce_sum(c, m->o, (size_t)d); if (rc) return rc;
         AX_CUDA(cudaStreamSynchronize(s));
