@@ -134,6 +134,7 @@ SIGNATURES = {
     "atlasx_comm_unique_id": (ci, [vp]),
     "atlasx_comm_init": (ci, [vp, vp, ci, ci]),
     "atlasx_comm_world": (ci, [vp]),
+    "atlasx_comm_selftest_wait_expiry": (ci, [vp, vp]),
     "atlasx_comm_allreduce": (ci, [vp, vp, ci]),
 }
 

@@ -10,6 +10,7 @@
 
 #include "common.cuh"
 #include "comm.h"
+#include "gemv.cuh"
 
 namespace {
 
@@ -182,6 +183,32 @@ extern "C" int atlasx_comm_init(atlasx_ctx* ctx, const void* id128, int rank, in
     return ATLASX_OK;
 }
 extern "C" int atlasx_comm_world(const atlasx_ctx* ctx) { return ax_comm_world(ctx); }
+
+// Self-test of the bounded device-side waits: the mailbox reduction is launched on a zeroed part
+// whose sequence words nothing will ever set.  The kernel must give up after its limit (2 s), set
+// the context's error word and return — the context stays usable.  *code receives the word (3).
+extern "C" int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code) {
+    AX_ARG(ctx && code, "null argument");
+    const int d = 512;
+    uint2* part = nullptr; float* out = nullptr; unsigned* epoch = nullptr;
+    AX_CUDA(cudaMalloc((void**)&part, d * sizeof(uint2)));
+    AX_CUDA(cudaMalloc((void**)&out, d * sizeof(float)));
+    AX_CUDA(cudaMalloc((void**)&epoch, sizeof(unsigned)));
+    AX_CUDA(cudaMemsetAsync(part, 0, d * sizeof(uint2), ctx->stream));
+    AX_CUDA(cudaMemsetAsync(epoch, 0, sizeof(unsigned), ctx->stream));
+    int rc = ax_mail_reduce_launch(ctx, part, 1, (size_t)d, d, epoch, 1u, 7u, out, false);   // waits for sequence 7
+    if (!rc) {
+        cudaError_t e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = atlasx_fail(ATLASX_ERR_CUDA, "self-test kernel failed: %s", cudaGetErrorString(e));
+    }
+    *code = 0;
+    if (!rc) {
+        atlasx_ctx_poll_device_error(ctx, code);          // returns ATLASX_ERR_TIMEOUT when the word is set: expected here
+        rc = ATLASX_OK;
+    }
+    cudaFree(part); cudaFree(out); cudaFree(epoch);
+    return rc;
+}
 extern "C" int atlasx_comm_allreduce(atlasx_ctx* ctx, float* buf, int n) {
     AX_ARG(ctx && buf && n >= 0, "bad argument");
     return ax_comm_allreduce_sum(ctx, buf, (size_t)n);

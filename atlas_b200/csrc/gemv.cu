@@ -81,12 +81,15 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
 #pragma unroll
                 for (int q = 0; q < P; q++) xv[q] = xs[q * nch + c];
                 if (FMT == ATLASX_INT4) {
-                    const size_t e0 = (size_t)row0 * a.K + (size_t)c * EPC;     // flat element index
+                    // a chunk is 32 elements of one row and lies inside one block (block is a multiple
+                    // of 32 and divides the row length): scale index = row · scales_per_row + chunk / (block/32)
+                    const int cb = a.bshift >= 0 ? (c >> a.bshift) : (c * EPC) / a.block;
+                    const int i0 = row0 * a.spr + cb;
                     Acc4 t = acc4_zero(); dot_chunk<FMT>(wa[u], xv, t);
-                    sc0 = fmaf(t.sum(), load_scale_i4(a.scales, (int)(e0 / a.block), a.scales_f16), sc0);
+                    sc0 = fmaf(t.sum(), load_scale_i4(a.scales, i0, a.scales_f16), sc0);
                     if (v1) {
                         t = acc4_zero(); dot_chunk<FMT>(wb[u], xv, t);
-                        sc1 = fmaf(t.sum(), load_scale_i4(a.scales, (int)((e0 + a.K) / a.block), a.scales_f16), sc1);
+                        sc1 = fmaf(t.sum(), load_scale_i4(a.scales, i0 + a.spr, a.scales_f16), sc1);
                     }
                 } else {
                     dot_chunk<FMT>(wa[u], xv, acc0);
@@ -321,6 +324,9 @@ int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* 
     a.row_bytes = (int)((size_t)w.cols * ebits / 8);
     a.block = w.block > 0 ? w.block : 1; a.scales_f16 = w.scales_f16;
     a.srow_bytes = w.dtype == ATLASX_INT4 ? (w.cols / w.block) * (w.scales_f16 ? 2 : 4) : 0;
+    a.spr = w.dtype == ATLASX_INT4 ? w.cols / (w.block > 0 ? w.block : 1) : 0;
+    a.bshift = -1;
+    if (w.dtype == ATLASX_INT4 && w.block >= 32) { const int q = w.block / 32; if ((q & (q - 1)) == 0) { a.bshift = 0; while ((1 << a.bshift) < q) a.bshift++; } }
     a.nchunks = a.row_bytes / 16;
     a.epi = epi; a.y = y; a.pro = pro; a.err = err; a.dbg = 0; a.trace = nullptr;
     *out = a;
@@ -370,6 +376,9 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     a.row_bytes = (int)((size_t)w.cols * ebits / 8);
     a.block = w.block > 0 ? w.block : 1; a.scales_f16 = w.scales_f16;
     a.srow_bytes = w.dtype == ATLASX_INT4 ? (w.cols / w.block) * (w.scales_f16 ? 2 : 4) : 0;
+    a.spr = w.dtype == ATLASX_INT4 ? w.cols / (w.block > 0 ? w.block : 1) : 0;
+    a.bshift = -1;
+    if (w.dtype == ATLASX_INT4 && w.block >= 32) { const int q = w.block / 32; if ((q & (q - 1)) == 0) { a.bshift = 0; while ((1 << a.bshift) < q) a.bshift++; } }
     a.nchunks = a.row_bytes / 16;
     a.epi = epi; a.y = y; a.pro = pro; a.err = ctx->dev_error;
     { const char* e = getenv("ATLASX_GEMV_DEBUG"); a.dbg = e ? atoi(e) : 0; }

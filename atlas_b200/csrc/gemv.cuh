@@ -68,6 +68,8 @@ struct GemvArgs {
     int row_bytes;               // bytes of one weight row
     int srow_bytes;              // bytes of one row of int4 scales (0 otherwise)
     int block; int scales_f16;
+    int spr;                     // int4: scales per row (cols / block)
+    int bshift;                  // int4: log2(block / 32), or −1 when block / 32 is no power of two
     int stages; int stage_stride; int seg_pitch;   // ring geometry (TMA)
     int nchunks;                 // 16-byte chunks per row
     int epi;

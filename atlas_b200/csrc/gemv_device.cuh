@@ -111,12 +111,20 @@ template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT8>(const uint4& 
 __device__ __forceinline__ float i4_val(uint32_t u, int sh) {
     return __uint_as_float(((u >> sh) & 0xFu) | 0x4B000000u) - 8388616.0f;
 }
+// Eight elements of a word: the nibbles are first spread into two words of four bytes each
+// (high nibbles = even elements, low nibbles = odd elements: two logic operations per word), then
+// every byte is dropped into the mantissa of 2^23 with one byte-permute — three operations per
+// element (permute, subtract, FMA) instead of four.
+__device__ __forceinline__ float i4_byte(uint32_t t, uint32_t sel) {
+    return __uint_as_float(__byte_perm(t, 0x4B000000u, sel)) - 8388616.0f;
+}
 __device__ __forceinline__ void dot_i4_word(uint32_t word, const float4& xa, const float4& xb, Acc4& acc) {
     const uint32_t u = word ^ 0x88888888u;
-    acc.a = fmaf(i4_val(u, 4),  xa.x, acc.a); acc.b = fmaf(i4_val(u, 0),  xa.y, acc.b);
-    acc.c = fmaf(i4_val(u, 12), xa.z, acc.c); acc.d = fmaf(i4_val(u, 8),  xa.w, acc.d);
-    acc.a = fmaf(i4_val(u, 20), xb.x, acc.a); acc.b = fmaf(i4_val(u, 16), xb.y, acc.b);
-    acc.c = fmaf(i4_val(u, 28), xb.z, acc.c); acc.d = fmaf(i4_val(u, 24), xb.w, acc.d);
+    const uint32_t hi = (u >> 4) & 0x0F0F0F0Fu, lo = u & 0x0F0F0F0Fu;
+    acc.a = fmaf(i4_byte(hi, 0x7540), xa.x, acc.a); acc.b = fmaf(i4_byte(lo, 0x7540), xa.y, acc.b);
+    acc.c = fmaf(i4_byte(hi, 0x7541), xa.z, acc.c); acc.d = fmaf(i4_byte(lo, 0x7541), xa.w, acc.d);
+    acc.a = fmaf(i4_byte(hi, 0x7542), xb.x, acc.a); acc.b = fmaf(i4_byte(lo, 0x7542), xb.y, acc.b);
+    acc.c = fmaf(i4_byte(hi, 0x7543), xb.z, acc.c); acc.d = fmaf(i4_byte(lo, 0x7543), xb.w, acc.d);
 }
 template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT4>(const uint4& w, const float4* xv, Acc4& acc) {
     dot_i4_word(w.x, xv[0], xv[1], acc); dot_i4_word(w.y, xv[2], xv[3], acc);

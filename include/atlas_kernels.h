@@ -272,6 +272,10 @@ int atlasx_time_attention(atlasx_ctx* ctx, const atlasx_kvcache* kv, const float
 int atlasx_comm_unique_id(void* id128_out);
 int atlasx_comm_init(atlasx_ctx* ctx, const void* id128, int rank, int world);
 int atlasx_comm_world(const atlasx_ctx* ctx);
+/* Diagnostics: launches a mailbox reduction whose data never arrives and reports the device error
+ * word after the kernel gave up (code 3 after its 2 s limit).  Shows that an absent peer ends in
+ * an error status, not in a hang; the context stays usable.  No reference counterpart. */
+int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code);
 /* sum-allreduce of n floats in place on the context stream */
 int atlasx_comm_allreduce(atlasx_ctx* ctx, float* buf_dev, int n);
 

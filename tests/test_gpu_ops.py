@@ -189,3 +189,25 @@ def test_legacy_quantisers_keep_reference_kernel_semantics(ab, ctx):
     assert out.tolist() == [(7 << 4) | 9, (4 << 4) | 2, 0]                 # 3.5→4 (even), 2.5→2 (even)
     for p in (dw, dq, ds, dx, d4, d4s):
         ctx.free(p)
+
+
+def test_bounded_device_wait_expires_with_an_error_status_and_leaves_the_context_usable(ab):
+    """Failure detection on the device: a wait for data that never arrives (a mailbox part whose
+    sequence words nothing sets) runs out after its limit, the kernel returns, the error word reads
+    3, and the same context computes correctly afterwards."""
+    import ctypes as C
+    import time
+    from atlas_b200 import _ffi
+    ctx = ab.Context.default()
+    code = C.c_int(-1)
+    t0 = time.time()
+    _ffi.check(_ffi.lib().atlasx_comm_selftest_wait_expiry(ctx.handle, C.byref(code)))
+    dt = time.time() - t0
+    assert code.value == 3
+    assert 1.5 <= dt <= 10.0
+    # the error word was cleared by the poll and the context still works
+    w = np.arange(32 * 64, dtype=np.float32).reshape(32, 64) / 100.0
+    x = np.ones(64, np.float32)
+    y = ab.GpuMatrix.upload(w, 32, 64, ctx=ctx).sgemm_vec(ab.GpuVec.from_slice(x, ctx=ctx)).download()
+    assert np.allclose(y, w @ x, rtol=1e-5)
+    assert _ffi.lib().atlasx_ctx_poll_device_error(ctx.handle, C.byref(code)) == 0 and code.value == 0
