@@ -127,6 +127,7 @@ SIGNATURES = {
     "atlasx_model_set_options": (ci, [vp, ci, ci]),
     "atlasx_model_set_mega": (ci, [vp, ci]),
     "atlasx_model_set_prefill": (ci, [vp, ci, vp]),
+    "atlasx_model_time_classes": (ci, [vp, C.c_uint, ci, vp, vp, vp]),
     "atlasx_model_uses_mega": (ci, [vp]),
     "atlasx_model_hidden": (ci, [vp, vp]),
     "atlasx_time_gemv": (ci, [vp, vp, ci, vp, ci, vp, ci, C.POINTER(cf)]),

@@ -80,6 +80,7 @@ struct atlasx_model {
     int attn_splits = 1;
     bool fused_attn = false; int fused_splits = 1;   // one-launch attention (head_dim 128)
     const AxPeerMail* mail = nullptr;            // tensor parallel: all-reduce fused into o_proj/down over peer memory
+    int class_mask = (1 << CLS_COUNT) - 1;       // launch classes issued by run_step (all, except while one family is timed)
     bool mail_reduce = false;                    // parts are summed by one small kernel per use instead of by every consumer CTA
     std::vector<void*> owned;                    // device allocations to free
     int* pin = nullptr;                          // pinned host ints
@@ -268,6 +269,7 @@ double gemv_bytes(const AxWeight& w) { return (double)ax_weight_bytes(w) + 4.0 *
 
 #define STEP_LAUNCH(CLS, BYTES, CALL)                                                        \
     do {                                                                                     \
+        if (!((m->class_mask >> (CLS)) & 1)) break;                                          \
         if (prof) cudaEventRecord(prof->ev[2 * prof->n], s);                                 \
         rc = (CALL);                                                                         \
         if (rc) return rc;                                                                   \
@@ -529,7 +531,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         STEP_LAUNCH(CLS_COMM, 4.0 * m->vocab_loc * m->world, ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc));
 
     // ── greedy selection + state advance ────────────────────────────────────────
-    {
+    if ((m->class_mask >> CLS_SELECT) & 1) {
         AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
         const int n = cf.vocab_size;
         if (prof) cudaEventRecord(prof->ev[2 * prof->n], s);
@@ -1154,6 +1156,63 @@ extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, float* elap
     if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "decode failed: %s", cudaGetErrorString(e));
     if (elapsed_ms) *elapsed_ms = ms;
     if (tokens_host) AX_CUDA(cudaMemcpy(tokens_host, m->seq + p0 + 1, (size_t)steps * 4, cudaMemcpyDeviceToHost));
+    return ATLASX_OK;
+}
+
+// Device time of one launch family inside the step's launch conditions: a graph holding only the
+// launches of the classes in `mask` (bit = class index), in step order, with the same programmatic
+// dependent launch attributes, replayed `iters` times between two CUDA events.  Nothing is selected
+// and the position does not advance; activations are left meaningless until the next real step,
+// which starts from the embedding again.  Single GPU only (peer mailboxes would wait for data).
+extern "C" int atlasx_model_time_classes(atlasx_model* m, unsigned mask, int iters, float* ms_per_pass, double* bytes_per_pass, int* launches) {
+    AX_ARG(m && m->finalized && iters > 0 && ms_per_pass, "bad argument");
+    AX_ARG(m->world == 1, "single GPU only");
+    AX_ARG(!(m->mega_ready && m->use_mega), "not available with the whole-step kernel");
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    AX_CUDA(cudaStreamSynchronize(s));
+    const int saved = m->class_mask, saved_launches = m->launches_per_step, saved_resid = m->final_resid;
+    m->class_mask = (int)(mask & ((1u << CLS_COUNT) - 1u)) & ~(1 << CLS_SELECT);
+    // bytes and launch count of the family from one eager, profiled pass
+    {
+        const int cap = m->cfg.n_layers * 8 + 8;
+        Profile pr;
+        pr.ev.resize((size_t)cap * 2); pr.cls.resize(cap); pr.bytes.resize(cap);
+        for (auto& e : pr.ev) cudaEventCreate(&e);
+        int rc0 = run_step(m, &pr, true);
+        cudaStreamSynchronize(s);
+        double b = 0; for (int i = 0; i < pr.n; i++) b += pr.bytes[i];
+        if (bytes_per_pass) *bytes_per_pass = b;
+        if (launches) *launches = pr.n;
+        for (auto& e : pr.ev) cudaEventDestroy(e);
+        if (rc0) { m->class_mask = saved; m->launches_per_step = saved_launches; m->final_resid = saved_resid; return rc0; }
+    }
+    cudaGraph_t g = nullptr; cudaGraphExec_t ge = nullptr;
+    int rc = ATLASX_OK;
+    cudaError_t e = cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal);
+    if (e == cudaSuccess) {
+        rc = run_step(m, nullptr, true);
+        e = cudaStreamEndCapture(s, &g);
+    }
+    m->class_mask = saved; m->launches_per_step = saved_launches; m->final_resid = saved_resid;
+    if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "capture failed: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&ge, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e));
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    for (int i = 0; i < 3; i++) cudaGraphLaunch(ge, s);             // warm-up
+    cudaEventRecord(e0, s);
+    for (int i = 0; i < iters; i++) cudaGraphLaunch(ge, s);
+    cudaEventRecord(e1, s);
+    e = cudaStreamSynchronize(s);
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaGraphExecDestroy(ge);
+    if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "timed replay failed: %s", cudaGetErrorString(e));
+    *ms_per_pass = ms / iters;
     return ATLASX_OK;
 }
 

@@ -148,6 +148,19 @@ class OlmoModel:
         check(_ffi.lib().atlasx_model_set_options(self._h, int(use_graph), int(use_pdl)))
         check(_ffi.lib().atlasx_model_finalize(self._h))
 
+    def time_classes(self, names, iters=32):
+        """Device time per pass (ms), algorithmic bytes and launch count of the named launch classes
+        replayed back to back as one graph (see atlasx_model_time_classes)."""
+        L = _ffi.lib()
+        mask = 0
+        for i in range(32):
+            nm = L.atlasx_model_class_name(i)
+            if nm and nm.decode() in names:
+                mask |= 1 << i
+        ms, by, n = C.c_float(0), C.c_double(0), C.c_int(0)
+        check(L.atlasx_model_time_classes(self._h, mask, int(iters), C.byref(ms), C.byref(by), C.byref(n)))
+        return ms.value, by.value, n.value
+
     def set_prefill(self, chunk=16):
         """Prompt ingestion `chunk` tokens at a time (the reference's generate feeds one token per
         forward, :1611-1618).  Returns the chunk size in effect (1 = token by token)."""

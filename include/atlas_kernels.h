@@ -239,6 +239,11 @@ int atlasx_model_decode_timed(atlasx_model* m, int steps, float* elapsed_ms, uin
 /* one step outside the graph with an event pair around every kernel: per kernel class
  * (see atlasx_model_class_name) launches, milliseconds and algorithmic HBM bytes */
 int atlasx_model_profile_step(atlasx_model* m, int n_classes_max, int* launches, float* ms, double* bytes, int* n_classes);
+/* Device time of the launches of the classes in `mask` (bit = class index as in
+ * atlasx_model_profile_step) in step order, inside one CUDA graph with the step's programmatic
+ * dependent launch attributes, replayed `iters` times between two CUDA events: the family's time
+ * under the launch conditions of the decode loop, without the other families.  Single GPU. */
+int atlasx_model_time_classes(atlasx_model* m, unsigned mask, int iters, float* ms_per_pass, double* bytes_per_pass, int* launches);
 const char* atlasx_model_class_name(int cls);
 /* algorithmic HBM bytes of one decode step at position pos (weights + KV read/write) */
 double atlasx_model_step_bytes(const atlasx_model* m, int pos);
