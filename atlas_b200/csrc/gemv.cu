@@ -32,8 +32,10 @@ namespace {
 // the stream is still draining (weights never depend on it).  Per pair every warp leaves one
 // partial sum in shared memory (zero if it had no part in it); after a barrier one thread per
 // pair adds the eight values in warp order — deterministic — and applies the epilogue.
+constexpr int kScaleLandBytes = 2 * 8 * kConsumerThreads * 4;       // int4 direct path: landing slots of the block scales
+
 template <int FMT>
-__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, int lo, int hi) {
+__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, uint32_t* sland, int lo, int hi) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -55,8 +57,41 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
             if (c < nch) { A[u] = ax_ldg_stream(w0p + (size_t)c * 16); B[u] = ax_ldg_stream(w1p + (size_t)c * 16); }
         }
     };
+    // int4: the block scales of a batch travel with its weights — 4-byte cp.async into thread-private
+    // slots [buffer][row·4 + chunk][thread], so that the arithmetic never waits for a scale from DRAM
+    auto scale_index = [&](int i, int u, int& idx0, int& idx1, bool& ok) {
+        const int p = i / nbatch, b = i - p * nbatch;
+        const int row0 = lo + 2 * p;
+        const int c = b * 128 + u * 32 + lane;
+        ok = c < nch;
+        const int cb = a.bshift >= 0 ? (c >> a.bshift) : (c * EPC) / a.block;
+        idx0 = row0 * a.spr + cb;
+        idx1 = row0 + 1 < hi ? idx0 + a.spr : idx0;
+    };
+    auto load_scales = [&](int i, int buf) {
+        if (FMT == ATLASX_INT4 && i < i1) {
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                int idx0, idx1; bool ok;
+                scale_index(i, u, idx0, idx1, ok);
+                if (ok) {
+                    const uint8_t* s0 = a.scales + (a.scales_f16 ? ((size_t)idx0 * 2 & ~(size_t)3) : (size_t)idx0 * 4);
+                    const uint8_t* s1 = a.scales + (a.scales_f16 ? ((size_t)idx1 * 2 & ~(size_t)3) : (size_t)idx1 * 4);
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(smem_u32(sland + ((buf * 8 + u) * kConsumerThreads + tid))), "l"(s0) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(smem_u32(sland + ((buf * 8 + 4 + u) * kConsumerThreads + tid))), "l"(s1) : "memory");
+                }
+            }
+        }
+        if (FMT == ATLASX_INT4) asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    auto scale_at = [&](int buf, int slot, int idx) -> float {
+        const uint32_t w = sland[(buf * 8 + slot) * kConsumerThreads + tid];
+        if (a.scales_f16) return __half2float(__ushort_as_half((unsigned short)((idx & 1) ? (w >> 16) : (w & 0xFFFFu))));
+        return __uint_as_float(w);
+    };
     ax_trace_start(a.trace);
     if (i0 < i1) load(i0, wa, wb);
+    load_scales(i0, 0);
     stage_input_early<FMT>(a, xb);
     for (int j = tid; j < npairs * kConsumerWarps * 2; j += kConsumerThreads) part[j] = 0.f;
     griddep_wait();                       // activations of the previous kernel are complete
@@ -70,6 +105,9 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     for (int i = i0; i < i1; i++) {
         uint4 na[4], nb[4];
         if (i + 1 < i1) load(i + 1, na, nb);
+        const int sbuf = (i - i0) & 1;
+        load_scales(i + 1, sbuf ^ 1);                          // commits a group even when there is nothing left to fetch
+        if (FMT == ATLASX_INT4) asm volatile("cp.async.wait_group 1;" ::: "memory");     // the scales of batch i have landed
         const int p = i / nbatch, b = i - p * nbatch;
         const int row0 = lo + 2 * p;
         const bool v1 = row0 + 1 < hi;
@@ -83,13 +121,13 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                 if (FMT == ATLASX_INT4) {
                     // a chunk is 32 elements of one row and lies inside one block (block is a multiple
                     // of 32 and divides the row length): scale index = row · scales_per_row + chunk / (block/32)
-                    const int cb = a.bshift >= 0 ? (c >> a.bshift) : (c * EPC) / a.block;
-                    const int i0 = row0 * a.spr + cb;
+                    int idx0, idx1; bool ok;
+                    scale_index(i, u, idx0, idx1, ok);
                     Acc4 t = acc4_zero(); dot_chunk<FMT>(wa[u], xv, t);
-                    sc0 = fmaf(t.sum(), load_scale_i4(a.scales, i0, a.scales_f16), sc0);
+                    sc0 = fmaf(t.sum(), scale_at(sbuf, u, idx0), sc0);
                     if (v1) {
                         t = acc4_zero(); dot_chunk<FMT>(wb[u], xv, t);
-                        sc1 = fmaf(t.sum(), load_scale_i4(a.scales, i0 + a.spr, a.scales_f16), sc1);
+                        sc1 = fmaf(t.sum(), scale_at(sbuf, 4 + u, idx1), sc1);
                     }
                 } else {
                     dot_chunk<FMT>(wa[u], xv, acc0);
@@ -159,8 +197,10 @@ ax_gemv_stream_kernel(const GemvArgs a) {
     if (!TMA) {
         // second plane (raw residual stream, fetched early) only when the launcher reserved it
         float4* xb = a.pro.base_early ? reinterpret_cast<float4*>(ring) : nullptr;
-        float* part = reinterpret_cast<float*>(ring + (a.pro.base_early ? x_bytes : 0));     // [pairs][warps][2]
-        consume_direct<FMT>(a, xs, xb, red, part, lo, hi);
+        uint8_t* after_x = ring + (a.pro.base_early ? x_bytes : 0);
+        uint32_t* sland = reinterpret_cast<uint32_t*>(after_x);                              // int4 only: [2][8][threads] scale slots
+        float* part = reinterpret_cast<float*>(after_x + (FMT == ATLASX_INT4 ? kScaleLandBytes : 0));   // [pairs][warps][2]
+        consume_direct<FMT>(a, xs, xb, red, part, sland, lo, hi);
         return;
     }
 
@@ -442,7 +482,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         size_t smem = 0;
         int grid = 1;
         for (int attempt = 0; attempt < 2; attempt++) {
-            const size_t fixed = 256 + x_bytes * (a.pro.base_early ? 2 : 1);
+            const size_t fixed = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + (w.dtype == ATLASX_INT4 ? kScaleLandBytes : 0);
             int g = ctx->sm_count * 2 < tiles ? ctx->sm_count * 2 : tiles;     // first guess: two CTAs per SM
             if (g < 1) g = 1;
             smem = fixed + part_bytes(g);
@@ -463,7 +503,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         if (grid > tiles) grid = tiles;
         if (grid < 1) grid = 1;
         if (per_sm != 2) {                 // partial-sum area for the final grid; re-check the fit
-            const size_t s2 = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + part_bytes(grid);
+            const size_t s2 = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + (w.dtype == ATLASX_INT4 ? kScaleLandBytes : 0) + part_bytes(grid);
             if (s2 > smem) { AX_ARG(s2 <= smem_max, "input vector does not fit in shared memory"); }
             smem = s2 > smem ? s2 : smem;
         }
