@@ -46,8 +46,9 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     const int i0 = (int)((long long)total * warp / kConsumerWarps);
     const int i1 = (int)((long long)total * (warp + 1) / kConsumerWarps);
     uint4 wa[4], wb[4];
-    auto load = [&](int i, uint4* A, uint4* B) {
-        const int p = i / nbatch, b = i - p * nbatch;
+    // a batch is named by its pair p and its position b inside the pair's row; both are stepped
+    // incrementally (no division in the loop)
+    auto load = [&](int p, int b, uint4* A, uint4* B) {
         const int row0 = lo + 2 * p;
         const uint8_t* w0p = a.W + (size_t)row0 * a.row_bytes;
         const uint8_t* w1p = w0p + (row0 + 1 < hi ? a.row_bytes : 0);
@@ -59,8 +60,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     };
     // int4: the block scales of a batch travel with its weights — 4-byte cp.async into thread-private
     // slots [buffer][row·4 + chunk][thread], so that the arithmetic never waits for a scale from DRAM
-    auto scale_index = [&](int i, int u, int& idx0, int& idx1, bool& ok) {
-        const int p = i / nbatch, b = i - p * nbatch;
+    auto scale_index = [&](int p, int b, int u, int& idx0, int& idx1, bool& ok) {
         const int row0 = lo + 2 * p;
         const int c = b * 128 + u * 32 + lane;
         ok = c < nch;
@@ -68,12 +68,12 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
         idx0 = row0 * a.spr + cb;
         idx1 = row0 + 1 < hi ? idx0 + a.spr : idx0;
     };
-    auto load_scales = [&](int i, int buf) {
-        if (FMT == ATLASX_INT4 && i < i1) {
+    auto load_scales = [&](bool any, int p, int b, int buf) {
+        if (FMT == ATLASX_INT4 && any) {
 #pragma unroll
             for (int u = 0; u < 4; u++) {
                 int idx0, idx1; bool ok;
-                scale_index(i, u, idx0, idx1, ok);
+                scale_index(p, b, u, idx0, idx1, ok);
                 if (ok) {
                     const uint8_t* s0 = a.scales + (a.scales_f16 ? ((size_t)idx0 * 2 & ~(size_t)3) : (size_t)idx0 * 4);
                     const uint8_t* s1 = a.scales + (a.scales_f16 ? ((size_t)idx1 * 2 & ~(size_t)3) : (size_t)idx1 * 4);
@@ -90,8 +90,9 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
         return __uint_as_float(w);
     };
     ax_trace_start(a.trace);
-    if (i0 < i1) load(i0, wa, wb);
-    load_scales(i0, 0);
+    int p = i0 / nbatch, b = i0 - p * nbatch;
+    if (i0 < i1) load(p, b, wa, wb);
+    load_scales(i0 < i1, p, b, 0);
     stage_input_early<FMT>(a, xb);
     for (int j = tid; j < npairs * kConsumerWarps * 2; j += kConsumerThreads) part[j] = 0.f;
     griddep_wait();                       // activations of the previous kernel are complete
@@ -104,11 +105,11 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     float sc0 = 0.f, sc1 = 0.f;
     for (int i = i0; i < i1; i++) {
         uint4 na[4], nb[4];
-        if (i + 1 < i1) load(i + 1, na, nb);
+        const int bn = b + 1 == nbatch ? 0 : b + 1, pn = b + 1 == nbatch ? p + 1 : p;
+        if (i + 1 < i1) load(pn, bn, na, nb);
         const int sbuf = (i - i0) & 1;
-        load_scales(i + 1, sbuf ^ 1);                          // commits a group even when there is nothing left to fetch
+        load_scales(i + 1 < i1, pn, bn, sbuf ^ 1);             // commits a group even when there is nothing left to fetch
         if (FMT == ATLASX_INT4) asm volatile("cp.async.wait_group 1;" ::: "memory");     // the scales of batch i have landed
-        const int p = i / nbatch, b = i - p * nbatch;
         const int row0 = lo + 2 * p;
         const bool v1 = row0 + 1 < hi;
 #pragma unroll
@@ -122,7 +123,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                     // a chunk is 32 elements of one row and lies inside one block (block is a multiple
                     // of 32 and divides the row length): scale index = row · scales_per_row + chunk / (block/32)
                     int idx0, idx1; bool ok;
-                    scale_index(i, u, idx0, idx1, ok);
+                    scale_index(p, b, u, idx0, idx1, ok);
                     Acc4 t = acc4_zero(); dot_chunk<FMT>(wa[u], xv, t);
                     sc0 = fmaf(t.sum(), scale_at(sbuf, u, idx0), sc0);
                     if (v1) {
@@ -142,6 +143,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) { wa[u] = na[u]; wb[u] = nb[u]; }
+        p = pn; b = bn;
     }
     consumer_sync();
     for (int p = tid; p < npairs; p += kConsumerThreads) {
