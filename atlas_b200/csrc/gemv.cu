@@ -103,11 +103,10 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
 
     Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
     float sc0 = 0.f, sc1 = 0.f;
-    // one batch: arithmetic on (ca, cb) while the next batch is fetched into (fa, fb); called with
-    // the two register sets swapped on alternate batches, so nothing is copied between them
-    auto batch = [&](int i, uint4 (&ca)[4], uint4 (&cb)[4], uint4 (&fa)[4], uint4 (&fb)[4]) {
+    for (int i = i0; i < i1; i++) {
+        uint4 na[4], nb[4];
         const int bn = b + 1 == nbatch ? 0 : b + 1, pn = b + 1 == nbatch ? p + 1 : p;
-        if (i + 1 < i1) load(pn, bn, fa, fb);
+        if (i + 1 < i1) load(pn, bn, na, nb);
         const int sbuf = (i - i0) & 1;
         load_scales(i + 1 < i1, pn, bn, sbuf ^ 1);             // commits a group even when there is nothing left to fetch
         if (FMT == ATLASX_INT4) asm volatile("cp.async.wait_group 1;" ::: "memory");     // the scales of batch i have landed
@@ -125,15 +124,15 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                     // of 32 and divides the row length): scale index = row · scales_per_row + chunk / (block/32)
                     int idx0, idx1; bool ok;
                     scale_index(p, b, u, idx0, idx1, ok);
-                    Acc4 t = acc4_zero(); dot_chunk<FMT>(ca[u], xv, t);
+                    Acc4 t = acc4_zero(); dot_chunk<FMT>(wa[u], xv, t);
                     sc0 = fmaf(t.sum(), scale_at(sbuf, u, idx0), sc0);
                     if (v1) {
-                        t = acc4_zero(); dot_chunk<FMT>(cb[u], xv, t);
+                        t = acc4_zero(); dot_chunk<FMT>(wb[u], xv, t);
                         sc1 = fmaf(t.sum(), scale_at(sbuf, 4 + u, idx1), sc1);
                     }
                 } else {
-                    dot_chunk<FMT>(ca[u], xv, acc0);
-                    if (v1) dot_chunk<FMT>(cb[u], xv, acc1);
+                    dot_chunk<FMT>(wa[u], xv, acc0);
+                    if (v1) dot_chunk<FMT>(wb[u], xv, acc1);
                 }
             }
         }
@@ -142,12 +141,9 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
             if (lane == 0) { part[(p * kConsumerWarps + warp) * 2] = s0; part[(p * kConsumerWarps + warp) * 2 + 1] = s1; }
             acc0 = acc4_zero(); acc1 = acc4_zero(); sc0 = 0.f; sc1 = 0.f;
         }
+#pragma unroll
+        for (int u = 0; u < 4; u++) { wa[u] = na[u]; wb[u] = nb[u]; }
         p = pn; b = bn;
-    };
-    uint4 na[4], nb[4];
-    for (int i = i0; i < i1; i += 2) {
-        batch(i, wa, wb, na, nb);
-        if (i + 1 < i1) batch(i + 1, na, nb, wa, wb);
     }
     consumer_sync();
     for (int p = tid; p < npairs; p += kConsumerThreads) {
@@ -184,7 +180,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
 }
 
 template <int FMT, bool TMA>
-__global__ void __launch_bounds__(TMA ? kThreadsTma : kConsumerThreads, TMA ? 1 : 2)
+__global__ void __launch_bounds__(TMA ? kThreadsTma : kConsumerThreads)
 ax_gemv_stream_kernel(const GemvArgs a) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
