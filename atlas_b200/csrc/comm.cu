@@ -143,8 +143,8 @@ int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out) {
             mail.base[p] = (uint2*)ptr;
         }
     }
-    Wire verdict = {}; verdict.ok = ok ? 1 : 0;
-    rc = gather(verdict);                                   // second round: did every rank map every peer?
+    Wire mapped = {}; mapped.ok = ok ? 1 : 0;
+    rc = gather(mapped);                                    // second exchange: did every rank map every peer?
     cudaFree(dev);
     if (rc) return rc;
     for (int p = 0; p < W; p++) ok = ok && all[p].ok;
