@@ -32,9 +32,9 @@ namespace {
 // the stream is still draining (weights never depend on it).  Per pair every warp leaves one
 // partial sum in shared memory (zero if it had no part in it); after a barrier one thread per
 // pair adds the eight values in warp order — deterministic — and applies the epilogue.
-constexpr int kScaleLandBytes = 2 * 8 * kConsumerThreads * 4;       // int4 direct path: landing slots of the block scales
+__host__ __device__ constexpr int scale_land_bytes(int nthr) { return 2 * 8 * nthr * 4; }     // int4 direct path: landing slots of the block scales
 
-template <int FMT>
+template <int FMT, int NTHR>
 __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, uint32_t* sland, int lo, int hi) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
@@ -43,8 +43,8 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     const int nbatch = (nch + 127) >> 7;
     const int npairs = (hi - lo + 1) >> 1;
     const int total = npairs * nbatch;
-    const int i0 = (int)((long long)total * warp / kConsumerWarps);
-    const int i1 = (int)((long long)total * (warp + 1) / kConsumerWarps);
+    const int i0 = (int)((long long)total * warp / (NTHR / 32));
+    const int i1 = (int)((long long)total * (warp + 1) / (NTHR / 32));
     uint4 wa[4], wb[4];
     // a batch is named by its pair p and its position b inside the pair's row; both are stepped
     // incrementally (no division in the loop)
@@ -77,15 +77,15 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                 if (ok) {
                     const uint8_t* s0 = a.scales + (a.scales_f16 ? ((size_t)idx0 * 2 & ~(size_t)3) : (size_t)idx0 * 4);
                     const uint8_t* s1 = a.scales + (a.scales_f16 ? ((size_t)idx1 * 2 & ~(size_t)3) : (size_t)idx1 * 4);
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(smem_u32(sland + ((buf * 8 + u) * kConsumerThreads + tid))), "l"(s0) : "memory");
-                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(smem_u32(sland + ((buf * 8 + 4 + u) * kConsumerThreads + tid))), "l"(s1) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(smem_u32(sland + ((buf * 8 + u) * NTHR + tid))), "l"(s0) : "memory");
+                    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" :: "r"(smem_u32(sland + ((buf * 8 + 4 + u) * NTHR + tid))), "l"(s1) : "memory");
                 }
             }
         }
         if (FMT == ATLASX_INT4) asm volatile("cp.async.commit_group;" ::: "memory");
     };
     auto scale_at = [&](int buf, int slot, int idx) -> float {
-        const uint32_t w = sland[(buf * 8 + slot) * kConsumerThreads + tid];
+        const uint32_t w = sland[(buf * 8 + slot) * NTHR + tid];
         if (a.scales_f16) return __half2float(__ushort_as_half((unsigned short)((idx & 1) ? (w >> 16) : (w & 0xFFFFu))));
         return __uint_as_float(w);
     };
@@ -93,12 +93,12 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     int p = i0 / nbatch, b = i0 - p * nbatch;
     if (i0 < i1) load(p, b, wa, wb);
     load_scales(i0 < i1, p, b, 0);
-    stage_input_early<FMT>(a, xb);
-    for (int j = tid; j < npairs * kConsumerWarps * 2; j += kConsumerThreads) part[j] = 0.f;
+    stage_input_early<FMT, NTHR>(a, xb);
+    for (int j = tid; j < npairs * (NTHR / 32) * 2; j += NTHR) part[j] = 0.f;
     griddep_wait();                       // activations of the previous kernel are complete
     griddep_launch();
     ax_trace_release(a.trace);
-    stage_input<FMT>(a, xs, red, xb);     // ends with a barrier: the zeroed partials are visible too
+    stage_input<FMT, NTHR>(a, xs, red, xb);     // ends with a barrier: the zeroed partials are visible too
     ax_trace_staged(a.trace);
 
     Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
@@ -138,18 +138,18 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
         }
         if (b == nbatch - 1 || i + 1 == i1) {          // the pair, or this warp's share of it, is done
             const float s0 = ax_warp_sum(acc0.sum() + sc0), s1 = ax_warp_sum(acc1.sum() + sc1);
-            if (lane == 0) { part[(p * kConsumerWarps + warp) * 2] = s0; part[(p * kConsumerWarps + warp) * 2 + 1] = s1; }
+            if (lane == 0) { part[(p * (NTHR / 32) + warp) * 2] = s0; part[(p * (NTHR / 32) + warp) * 2 + 1] = s1; }
             acc0 = acc4_zero(); acc1 = acc4_zero(); sc0 = 0.f; sc1 = 0.f;
         }
 #pragma unroll
         for (int u = 0; u < 4; u++) { wa[u] = na[u]; wb[u] = nb[u]; }
         p = pn; b = bn;
     }
-    consumer_sync();
-    for (int p = tid; p < npairs; p += kConsumerThreads) {
+    consumer_sync<NTHR>();
+    for (int p = tid; p < npairs; p += NTHR) {
         float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int w = 0; w < kConsumerWarps; w++) { s0 += part[(p * kConsumerWarps + w) * 2]; s1 += part[(p * kConsumerWarps + w) * 2 + 1]; }
+        for (int w = 0; w < (NTHR / 32); w++) { s0 += part[(p * (NTHR / 32) + w) * 2]; s1 += part[(p * (NTHR / 32) + w) * 2 + 1]; }
         const int row0 = lo + 2 * p;
         const bool v1 = row0 + 1 < hi;
         if (FMT == ATLASX_INT8) {
@@ -179,8 +179,8 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     ax_trace_end(a.trace);
 }
 
-template <int FMT, bool TMA>
-__global__ void __launch_bounds__(TMA ? kThreadsTma : kConsumerThreads)
+template <int FMT, bool TMA, int NTHR = kConsumerThreads>
+__global__ void __launch_bounds__(TMA ? kThreadsTma : NTHR)
 ax_gemv_stream_kernel(const GemvArgs a) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
@@ -201,8 +201,8 @@ ax_gemv_stream_kernel(const GemvArgs a) {
         float4* xb = a.pro.base_early ? reinterpret_cast<float4*>(ring) : nullptr;
         uint8_t* after_x = ring + (a.pro.base_early ? x_bytes : 0);
         uint32_t* sland = reinterpret_cast<uint32_t*>(after_x);                              // int4 only: [2][8][threads] scale slots
-        float* part = reinterpret_cast<float*>(after_x + (FMT == ATLASX_INT4 ? kScaleLandBytes : 0));   // [pairs][warps][2]
-        consume_direct<FMT>(a, xs, xb, red, part, sland, lo, hi);
+        float* part = reinterpret_cast<float*>(after_x + (FMT == ATLASX_INT4 ? scale_land_bytes(NTHR) : 0));   // [pairs][warps][2]
+        consume_direct<FMT, NTHR>(a, xs, xb, red, part, sland, lo, hi);
         return;
     }
 
@@ -255,10 +255,10 @@ __global__ void ax_gemv_scalar_kernel(const uint8_t* W, const uint8_t* scales, i
     }
 }
 
-template <int FMT, bool TMA>
+template <int FMT, bool TMA, int NTHR = kConsumerThreads>
 int launch_stream(atlasx_ctx* ctx, const GemvArgs& a, int grid, size_t smem, bool pdl) {
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(TMA ? kThreadsTma : kConsumerThreads);
+    cfg.gridDim = dim3((unsigned)grid); cfg.blockDim = dim3(TMA ? kThreadsTma : NTHR);
     cfg.dynamicSmemBytes = smem; cfg.stream = ctx->stream;
     cudaLaunchAttribute attr[2];
     int na = 0;
@@ -273,7 +273,7 @@ int launch_stream(atlasx_ctx* ctx, const GemvArgs& a, int grid, size_t smem, boo
         na++;
     }
     if (na) { cfg.attrs = attr; cfg.numAttrs = na; }
-    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_stream_kernel<FMT, TMA>, a));
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_stream_kernel<FMT, TMA, NTHR>, a));
     return ATLASX_OK;
 }
 
@@ -281,6 +281,7 @@ template <int FMT>
 int set_attrs() {
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     if (const char* e = getenv("ATLASX_GEMV_CARVEOUT"))     // experiments: shared-memory share of the L1 array, percent
         AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false>, cudaFuncAttributePreferredSharedMemoryCarveout, atoi(e)));
     return ATLASX_OK;
@@ -476,16 +477,24 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         // off, and is only reserved, next to a fused norm.
         if (!(a.pro.base_early && (pro.y || pro.wx) && pro.base && !pro.embed)) a.pro.base_early = 0;
         const int tiles = units >= 8 ? units / 4 : (units >= 2 ? units / 2 : 1);     // at least four units of rows per CTA
+        // One 512-thread CTA per SM stages the input vector once per SM instead of twice (the same
+        // bytes in flight as two 256-thread CTAs): 2.88 against 2.99 ms per token on the 7B shapes.
+        // Matrices too small to give every SM a CTA keep the 256-thread form.
+        static const int wide_env = getenv("ATLASX_GEMV_THREADS") ? atoi(getenv("ATLASX_GEMV_THREADS")) : 512;   // experiments: 256
+        const bool wide = wide_env == 512 && tiles >= ctx->sm_count;
+        const int nthr = wide ? 512 : kConsumerThreads;
+        const int slots_per_sm = wide ? 1 : 2;
         auto part_bytes = [&](int grid) {
             const int unit = (w.rows & 1) ? 1 : 2;
             const long long rows_max = ((long long)units + grid - 1) / grid * unit + unit;
-            return (size_t)((rows_max + 1) / 2 + 1) * kConsumerWarps * 2 * sizeof(float);
+            return (size_t)((rows_max + 1) / 2 + 1) * (nthr / 32) * 2 * sizeof(float);
         };
+        const size_t land = w.dtype == ATLASX_INT4 ? (size_t)scale_land_bytes(nthr) : 0;
         size_t smem = 0;
         int grid = 1;
         for (int attempt = 0; attempt < 2; attempt++) {
-            const size_t fixed = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + (w.dtype == ATLASX_INT4 ? kScaleLandBytes : 0);
-            int g = ctx->sm_count * 2 < tiles ? ctx->sm_count * 2 : tiles;     // first guess: two CTAs per SM
+            const size_t fixed = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + land;
+            int g = ctx->sm_count * slots_per_sm < tiles ? ctx->sm_count * slots_per_sm : tiles;     // first guess
             if (g < 1) g = 1;
             smem = fixed + part_bytes(g);
             if (smem <= smem_max) break;
@@ -493,28 +502,39 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         }
         AX_ARG(smem <= smem_max, "input vector does not fit in shared memory");
         int per_sm = 1;             // resident CTAs per SM for this format and input size
-        switch (w.dtype) {
-            case ATLASX_F32:  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_F32, false>, kConsumerThreads, smem); break;
-            case ATLASX_BF16: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_BF16, false>, kConsumerThreads, smem); break;
-            case ATLASX_INT8: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_INT8, false>, kConsumerThreads, smem); break;
-            default:          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_INT4, false>, kConsumerThreads, smem); break;
+        if (!wide) {
+            switch (w.dtype) {
+                case ATLASX_F32:  cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_F32, false>, kConsumerThreads, smem); break;
+                case ATLASX_BF16: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_BF16, false>, kConsumerThreads, smem); break;
+                case ATLASX_INT8: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_INT8, false>, kConsumerThreads, smem); break;
+                default:          cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, ax_gemv_stream_kernel<ATLASX_INT4, false>, kConsumerThreads, smem); break;
+            }
         }
         if (per_sm < 1) per_sm = 1;
         { const char* e = getenv("ATLASX_GEMV_PERSM"); if (e && atoi(e) > 0 && per_sm > atoi(e)) per_sm = atoi(e); }   // experiments
         grid = ctx->sm_count * per_sm;
         if (grid > tiles) grid = tiles;
         if (grid < 1) grid = 1;
-        if (per_sm != 2) {                 // partial-sum area for the final grid; re-check the fit
-            const size_t s2 = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + (w.dtype == ATLASX_INT4 ? kScaleLandBytes : 0) + part_bytes(grid);
+        if (per_sm != slots_per_sm) {      // partial-sum area for the final grid; re-check the fit
+            const size_t s2 = 256 + x_bytes * (a.pro.base_early ? 2 : 1) + land + part_bytes(grid);
             if (s2 > smem) { AX_ARG(s2 <= smem_max, "input vector does not fit in shared memory"); }
             smem = s2 > smem ? s2 : smem;
         }
         if (ctx->trace_next) { a.trace = ctx->trace_next; ctx->trace_next += 6; }
-        switch (w.dtype) {
-            case ATLASX_F32:  rc = launch_stream<ATLASX_F32, false>(ctx, a, grid, smem, pdl); break;
-            case ATLASX_BF16: rc = launch_stream<ATLASX_BF16, false>(ctx, a, grid, smem, pdl); break;
-            case ATLASX_INT8: rc = launch_stream<ATLASX_INT8, false>(ctx, a, grid, smem, pdl); break;
-            default:          rc = launch_stream<ATLASX_INT4, false>(ctx, a, grid, smem, pdl); break;
+        if (wide) {
+            switch (w.dtype) {
+                case ATLASX_F32:  rc = launch_stream<ATLASX_F32, false, 512>(ctx, a, grid, smem, pdl); break;
+                case ATLASX_BF16: rc = launch_stream<ATLASX_BF16, false, 512>(ctx, a, grid, smem, pdl); break;
+                case ATLASX_INT8: rc = launch_stream<ATLASX_INT8, false, 512>(ctx, a, grid, smem, pdl); break;
+                default:          rc = launch_stream<ATLASX_INT4, false, 512>(ctx, a, grid, smem, pdl); break;
+            }
+        } else {
+            switch (w.dtype) {
+                case ATLASX_F32:  rc = launch_stream<ATLASX_F32, false>(ctx, a, grid, smem, pdl); break;
+                case ATLASX_BF16: rc = launch_stream<ATLASX_BF16, false>(ctx, a, grid, smem, pdl); break;
+                case ATLASX_INT8: rc = launch_stream<ATLASX_INT8, false>(ctx, a, grid, smem, pdl); break;
+                default:          rc = launch_stream<ATLASX_INT4, false>(ctx, a, grid, smem, pdl); break;
+            }
         }
     }
     return rc;

@@ -68,7 +68,11 @@ __device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t by
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
+template <int NTHR = 256>
+__device__ __forceinline__ void consumer_sync() {
+    if (NTHR == 512) asm volatile("bar.sync 1, 512;" ::: "memory");
+    else asm volatile("bar.sync 1, 256;" ::: "memory");
+}
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
@@ -132,15 +136,16 @@ template <> __device__ __forceinline__ void dot_chunk<ATLASX_INT4>(const uint4& 
 }
 
 // ── block reduction over the 256 consumer threads ────────────────────────────────
-__device__ __forceinline__ float consumer_block_sum(float v, float* red /*[8] + 1*/) {
+template <int NTHR = 256>
+__device__ __forceinline__ float consumer_block_sum(float v, float* red /*[NTHR/32]*/) {
     v = ax_warp_sum(v);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    consumer_sync();                       // protect `red` from the previous use
+    consumer_sync<NTHR>();                       // protect `red` from the previous use
     if (lane == 0) red[warp] = v;
-    consumer_sync();
+    consumer_sync<NTHR>();
     float t = 0.f;
 #pragma unroll
-    for (int w = 0; w < kConsumerWarps; w++) t += red[w];
+    for (int w = 0; w < NTHR / 32; w++) t += red[w];
     return t;
 }
 
@@ -151,23 +156,23 @@ __device__ __forceinline__ float consumer_block_sum(float v, float* red /*[8] + 
 // weights are pulled into L1, and — when the caller vouches that `base` was written at least
 // two kernels back (pro.base_early) — the residual stream is copied into the plane `xb` with
 // cp.async (thread-private slots: the same thread reads them back, no barrier needed).
-template <int FMT>
+template <int FMT, int NTHR = 256>
 __device__ __forceinline__ void stage_input_early(const GemvArgs& a, float4* xb) {
     const AxPrologue& p = a.pro;
     if (!p.y && !p.wx) return;
     const int n4 = a.K >> 2, tid = threadIdx.x;
-    for (int line = tid; line * 32 < a.K; line += kConsumerThreads) {       // 128-byte lines
+    for (int line = tid; line * 32 < a.K; line += NTHR) {       // 128-byte lines
         if (p.wy) asm volatile("prefetch.global.L1 [%0];" :: "l"(p.wy + line * 32));
         if (p.wx) asm volatile("prefetch.global.L1 [%0];" :: "l"(p.wx + line * 32));
     }
     if (xb && p.base_early && p.base && !p.embed) {
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads)
+        for (int k4 = tid; k4 < n4; k4 += NTHR)
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(smem_u32(xb + k4)), "l"(p.base + (k4 << 2)) : "memory");
         asm volatile("cp.async.commit_group;" ::: "memory");
     }
 }
 
-template <int FMT>
+template <int FMT, int NTHR = 256>
 __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float* red, const float4* xb = nullptr) {
     constexpr int EPC = Fmt<FMT>::EPC;
     const AxPrologue& p = a.pro;
@@ -198,12 +203,12 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
     };
 
     if (!p.y && !p.wx) {                                       // plain input
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
+        for (int k4 = tid; k4 < n4; k4 += NTHR) {
             const float4 v = load_base(k4);
             xs[slot(k4)] = v;
             if (p.resid_out && blockIdx.x == 0) reinterpret_cast<float4*>(p.resid_out)[k4] = v;
         }
-        consumer_sync();
+        consumer_sync<NTHR>();
         return;
     }
     float inv_y = 1.f;
@@ -226,7 +231,7 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
             return make_float4(__uint_as_float(a0.x), __uint_as_float(a0.z), __uint_as_float(a1.x), __uint_as_float(a1.z));
         };
 #pragma unroll 4
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
+        for (int k4 = tid; k4 < n4; k4 += NTHR) {
             float4 t;
             if (p.ll_n) {
                 t = load_ll(0, k4);
@@ -242,14 +247,14 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
             ss += t.x * t.x + t.y * t.y + t.z * t.z + t.w * t.w;
         }
         if (p.wy) {
-            ss = consumer_block_sum(ss, red);
+            ss = consumer_block_sum<NTHR>(ss, red);
             inv_y = 1.0f / sqrtf(ss / (float)K + p.eps);
         }
     }
     if (early) asm volatile("cp.async.wait_all;" ::: "memory");
     float ss2 = 0.f;
 #pragma unroll 4
-    for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
+    for (int k4 = tid; k4 < n4; k4 += NTHR) {
         float4 v = load_base(k4);
         if (p.y) {
             float4 t = xs[slot(k4)];
@@ -264,16 +269,16 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
         ss2 += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
     if (p.wx) {
-        ss2 = consumer_block_sum(ss2, red);
+        ss2 = consumer_block_sum<NTHR>(ss2, red);
         const float inv_x = 1.0f / sqrtf(ss2 / (float)K + p.eps);
-        for (int k4 = tid; k4 < n4; k4 += kConsumerThreads) {
+        for (int k4 = tid; k4 < n4; k4 += NTHR) {
             float4 v = xs[slot(k4)];
             const float4 w = reinterpret_cast<const float4*>(p.wx)[k4];
             v.x = v.x * inv_x * w.x; v.y = v.y * inv_x * w.y; v.z = v.z * inv_x * w.z; v.w = v.w * inv_x * w.w;
             xs[slot(k4)] = v;
         }
     }
-    consumer_sync();
+    consumer_sync<NTHR>();
 }
 
 __device__ __forceinline__ float load_scale_i4(const void* p, int idx, int f16) {
