@@ -103,13 +103,17 @@ def model_config(ab, max_seq):
     return mc
 
 
+WEIGHTS = "bf16"            # --weights int8 | int4: informational runs of the quantised formats
+
+
 def build_cuda_model(ab, ctx, max_seq, rank, world):
     """Random-init weights generated on the device from the seeded hash (full tensors, then each
     rank keeps its tensor-parallel slice)."""
     from atlas_b200 import _ffi
     L = _ffi.lib()
     mc = model_config(ab, max_seq)
-    m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.BF16, weight_format=ab.BF16, tp_rank=rank, tp_world=world)
+    fmt = {"bf16": ab.BF16, "int8": ab.INT8, "int4": ab.INT4}[WEIGHTS]
+    m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.BF16, weight_format=fmt, int4_block=32, tp_rank=rank, tp_world=world)
     d, f, V = mc.d_model, mc.ffn_hidden, mc.vocab_size
     shapes = {"wq": (d, d), "wk": (d, d), "wv": (d, d), "wo": (d, d), "gate": (f, d), "up": (f, d), "down": (d, f)}
     big = ctx.malloc(V * d * 2)
@@ -275,10 +279,13 @@ def main():
                     help="record %%globaltimer stamps in every GEMV and attention launch of the captured step and print a "
                          "per-class summary on stderr; the stamps cost a little, so the JSON line is marked invalid")
     ap.add_argument("--prefill", type=int, default=16, help="prompt tokens ingested per chunk before the timed region (1: token by token)")
+    ap.add_argument("--weights", default="bf16", choices=["bf16", "int8", "int4"],
+                    help="weight format held on the device (quantised from the same bf16 tensors); anything but bf16 marks the line invalid as the benchmark")
     ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")
     args = ap.parse_args()
-    global PROFILE_LAYERS
+    global PROFILE_LAYERS, WEIGHTS
     PROFILE_LAYERS = max(0, args.profile_layers)
+    WEIGHTS = args.weights
     if args.timeline:
         os.environ["ATLASX_STEP_TRACE"] = "1"
 
@@ -436,6 +443,9 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu}
     if PROFILE_LAYERS:
         line["invalid"] = "profiler case: only %d of 32 layers" % PROFILE_LAYERS
+    if WEIGHTS != "bf16":
+        line["invalid"] = "weights held as %s (per-row int8 / block-32 int4 with f32 scales), not the benchmark's bf16" % WEIGHTS
+        line["dtype"] = WEIGHTS
     if args.timeline:
         line["invalid"] = "timeline stamps were recorded inside the kernels"
     print(json.dumps(line), flush=True)
