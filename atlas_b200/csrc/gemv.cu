@@ -32,10 +32,96 @@ namespace {
 // the stream is still draining (weights never depend on it).  Per pair every warp leaves one
 // partial sum in shared memory (zero if it had no part in it); after a barrier one thread per
 // pair adds the eight values in warp order — deterministic — and applies the epilogue.
+// ── quantised formats on the integer dot-product unit ─────────────────────────────
+// The f32 input is split once per launch into three int8 digit planes in base 254, with one
+// scale per 32 elements:
+//   x ≈ s_c·(q1 + q2/254 + q3/254²),  s_c = max|x| over the 32 elements / 127,  digits in [−127, 127],
+// leaving |error| ≤ s_c / (2·254²) ≈ 6e-8·max|x| — the size of an f32 rounding, far inside the
+// 1e-3 parity bar.  The weights are then used as they lie in memory (int8 words; int4 nibbles
+// spread to bytes with two logic operations) in dp4a instructions with integer-exact sums:
+// 0.75 (int8) or 1 (int4) instruction per element instead of 3 for convert-subtract-FMA.
+// Scales per 32 elements need no block-wide reduction: eight neighbouring threads own a group.
+constexpr float kDigitBase = 254.0f;
+__host__ __device__ constexpr int digit_plane_bytes(int K) { return (K + 127) / 128 * 128; }
+__host__ __device__ constexpr int digit_groups(int K) { return ((K + 31) / 32 + 31) / 32 * 32; }
+// three planes, the group scales, and for int4 three tables of digit sums per group (the +8 offset of the nibbles)
+__host__ __device__ constexpr int digit_bytes(int fmt, int K) {
+    return fmt == ATLASX_INT8 ? 3 * digit_plane_bytes(K) + digit_groups(K) * 4
+         : fmt == ATLASX_INT4 ? 3 * digit_plane_bytes(K) + 4 * digit_groups(K) * 4 : 0;
+}
+__device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
+    int d; asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {      // a: four unsigned bytes, b: four signed bytes
+    int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
+}
+
+// After stage_input: xs holds the f32 input in natural order.  Writes the digit planes
+// (int8: natural element order; int4: inside every group of eight elements the even ones first,
+// then the odd ones, matching the nibble spread), the scale of every 32 elements and, for int4,
+// the sum of each plane over the same 32 elements.  Ends with a barrier.
+template <int FMT, int NTHR>
+__device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* xs, uint8_t* xq, float* xsc, int* bs) {
+    const int K = a.K, n4 = K >> 2, tid = threadIdx.x;
+    const int pb = digit_plane_bytes(K), ng = digit_groups(K);
+    for (int base = 0; base < n4; base += NTHR) {            // every lane of a warp runs the same trips (shuffles below)
+        const int k4 = base + tid;
+        const bool in = k4 < n4;
+        const float4 v = in ? xs[k4] : make_float4(0.f, 0.f, 0.f, 0.f);
+        float mx = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 2));
+        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 4));     // eight threads = 32 elements
+        if (!(mx < 3.0e38f)) mx = 3.0e38f;                   // inf or NaN in the input: keep the arithmetic finite
+        const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+        const float xv[4] = { v.x, v.y, v.z, v.w };
+        int d1[4], d2[4], d3[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            // round to nearest by adding 1.5·2^23: the integer then sits in the low mantissa bits, so
+            // neither a rounding nor a float-to-int conversion instruction (both quarter-rate) is needed
+            constexpr float M = 12582912.0f;
+            float t = xv[j] * inv;
+            t = fminf(fmaxf(t, -127.f), 127.f);
+            const float a1 = t + M, q1 = a1 - M;
+            const float r1 = (t - q1) * kDigitBase;
+            const float a2 = r1 + M, q2 = a2 - M;
+            const float a3 = (r1 - q2) * kDigitBase + M;
+            d1[j] = __float_as_int(a1) - 0x4B400000; d2[j] = __float_as_int(a2) - 0x4B400000; d3[j] = __float_as_int(a3) - 0x4B400000;
+        }
+        if (FMT == ATLASX_INT4) {
+            int t1 = d1[0] + d1[1] + d1[2] + d1[3], t2 = d2[0] + d2[1] + d2[2] + d2[3], t3 = d3[0] + d3[1] + d3[2] + d3[3];
+#pragma unroll
+            for (int o = 1; o < 8; o <<= 1) {
+                t1 += __shfl_xor_sync(AX_FULL, t1, o); t2 += __shfl_xor_sync(AX_FULL, t2, o); t3 += __shfl_xor_sync(AX_FULL, t3, o);
+            }
+            if (in && (k4 & 7) == 0) { bs[k4 >> 3] = t1; bs[ng + (k4 >> 3)] = t2; bs[2 * ng + (k4 >> 3)] = t3; }
+        }
+        if (!in) continue;
+        if ((k4 & 7) == 0) xsc[k4 >> 3] = mx / 127.0f;
+        if (FMT == ATLASX_INT8) {
+            auto word = [](const int (&d)[4]) { return (uint32_t)(d[0] & 255) | ((uint32_t)(d[1] & 255) << 8) | ((uint32_t)(d[2] & 255) << 16) | ((uint32_t)(d[3] & 255) << 24); };
+            reinterpret_cast<uint32_t*>(xq)[k4] = word(d1);
+            reinterpret_cast<uint32_t*>(xq + pb)[k4] = word(d2);
+            reinterpret_cast<uint32_t*>(xq + 2 * pb)[k4] = word(d3);
+        } else {
+            // elements 4k4..4k4+3 sit at j0..j0+3 of their group of eight (j0 = 0 or 4): the even ones
+            // go to bytes j0/2, j0/2+1 of the group, the odd ones to bytes 4+j0/2, 4+j0/2+1
+            const int g8 = (k4 >> 1) * 8, h = (k4 & 1) * 2;
+            auto half = [](int lo, int hi) { return (uint16_t)((lo & 255) | ((hi & 255) << 8)); };
+            *reinterpret_cast<uint16_t*>(xq + g8 + h) = half(d1[0], d1[2]);           *reinterpret_cast<uint16_t*>(xq + g8 + 4 + h) = half(d1[1], d1[3]);
+            *reinterpret_cast<uint16_t*>(xq + pb + g8 + h) = half(d2[0], d2[2]);      *reinterpret_cast<uint16_t*>(xq + pb + g8 + 4 + h) = half(d2[1], d2[3]);
+            *reinterpret_cast<uint16_t*>(xq + 2 * pb + g8 + h) = half(d3[0], d3[2]);  *reinterpret_cast<uint16_t*>(xq + 2 * pb + g8 + 4 + h) = half(d3[1], d3[3]);
+        }
+    }
+    consumer_sync<NTHR>();
+}
+
 __host__ __device__ constexpr int scale_land_bytes(int nthr) { return 2 * 8 * nthr * 4; }     // int4 direct path: landing slots of the block scales
 
 template <int FMT, int NTHR>
-__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, uint32_t* sland, int lo, int hi) {
+__device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, uint32_t* sland,
+                                               uint8_t* xq, float* xsc, int* bs, int lo, int hi) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -98,8 +184,13 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     griddep_wait();                       // activations of the previous kernel are complete
     griddep_launch();
     ax_trace_release(a.trace);
-    stage_input<FMT, NTHR>(a, xs, red, xb);     // ends with a barrier: the zeroed partials are visible too
+    constexpr bool QUANT = FMT == ATLASX_INT8 || FMT == ATLASX_INT4;
+    stage_input<FMT, NTHR, QUANT>(a, xs, red, xb);     // ends with a barrier: the zeroed partials are visible too
+    if (QUANT) digitize_input<FMT, NTHR>(a, xs, xq, xsc, bs);
     ax_trace_staged(a.trace);
+    const int pb = digit_plane_bytes(a.K);
+    const int nbp = digit_groups(a.K);
+    constexpr float k2 = 1.0f / kDigitBase, k3 = 1.0f / (kDigitBase * kDigitBase);
 
     Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
     float sc0 = 0.f, sc1 = 0.f;
@@ -116,21 +207,51 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
         for (int u = 0; u < 4; u++) {
             const int c = b * 128 + u * 32 + lane;
             if (c < nch) {
-                float4 xv[P];
+                if (FMT == ATLASX_INT8) {
+                    // 16 elements: four weight words against four digit words per plane, then the group's scale
+                    float f0 = 0.f, f1 = 0.f;
 #pragma unroll
-                for (int q = 0; q < P; q++) xv[q] = xs[q * nch + c];
-                if (FMT == ATLASX_INT4) {
+                    for (int pl = 0; pl < 3; pl++) {
+                        const uint4 q = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 16);
+                        int t0 = dp4a_ss(wa[u].x, q.x, 0); t0 = dp4a_ss(wa[u].y, q.y, t0); t0 = dp4a_ss(wa[u].z, q.z, t0); t0 = dp4a_ss(wa[u].w, q.w, t0);
+                        int t1 = 0;
+                        if (v1) { t1 = dp4a_ss(wb[u].x, q.x, 0); t1 = dp4a_ss(wb[u].y, q.y, t1); t1 = dp4a_ss(wb[u].z, q.z, t1); t1 = dp4a_ss(wb[u].w, q.w, t1); }
+                        const float wgt = pl == 0 ? 1.f : pl == 1 ? k2 : k3;
+                        f0 = fmaf((float)t0, wgt, f0); f1 = fmaf((float)t1, wgt, f1);
+                    }
+                    const float xs_c = xsc[c >> 1];
+                    sc0 = fmaf(f0, xs_c, sc0); sc1 = fmaf(f1, xs_c, sc1);
+                } else if (FMT == ATLASX_INT4) {
                     // a chunk is 32 elements of one row and lies inside one block (block is a multiple
                     // of 32 and divides the row length): scale index = row · scales_per_row + chunk / (block/32)
                     int idx0, idx1; bool ok;
                     scale_index(p, b, u, idx0, idx1, ok);
-                    Acc4 t = acc4_zero(); dot_chunk<FMT>(wa[u], xv, t);
-                    sc0 = fmaf(t.sum(), scale_at(sbuf, u, idx0), sc0);
-                    if (v1) {
-                        t = acc4_zero(); dot_chunk<FMT>(wb[u], xv, t);
-                        sc1 = fmaf(t.sum(), scale_at(sbuf, 4 + u, idx1), sc1);
+                    // nibbles (q + 8) spread to bytes: high nibbles = even elements, low nibbles = odd ones
+                    const uint32_t wx[4] = { wa[u].x ^ 0x88888888u, wa[u].y ^ 0x88888888u, wa[u].z ^ 0x88888888u, wa[u].w ^ 0x88888888u };
+                    const uint32_t wy[4] = { wb[u].x ^ 0x88888888u, wb[u].y ^ 0x88888888u, wb[u].z ^ 0x88888888u, wb[u].w ^ 0x88888888u };
+                    float f0 = 0.f, f1 = 0.f;
+#pragma unroll
+                    for (int pl = 0; pl < 3; pl++) {
+                        const uint4 qa = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 32);
+                        const uint4 qb = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 32 + 16);
+                        const uint32_t qe[4] = { qa.x, qa.z, qb.x, qb.z }, qo[4] = { qa.y, qa.w, qb.y, qb.w };
+                        const int off = 8 * bs[pl * nbp + c];
+                        int t0 = -off, t1 = -off;
+#pragma unroll
+                        for (int g = 0; g < 4; g++) {
+                            t0 = dp4a_us((wx[g] >> 4) & 0x0F0F0F0Fu, qe[g], t0); t0 = dp4a_us(wx[g] & 0x0F0F0F0Fu, qo[g], t0);
+                            if (v1) { t1 = dp4a_us((wy[g] >> 4) & 0x0F0F0F0Fu, qe[g], t1); t1 = dp4a_us(wy[g] & 0x0F0F0F0Fu, qo[g], t1); }
+                        }
+                        const float wgt = pl == 0 ? 1.f : pl == 1 ? k2 : k3;
+                        f0 = fmaf((float)t0, wgt, f0); f1 = fmaf((float)t1, wgt, f1);
                     }
+                    const float xs_c = xsc[c];
+                    sc0 = fmaf(f0 * xs_c, scale_at(sbuf, u, idx0), sc0);
+                    if (v1) sc1 = fmaf(f1 * xs_c, scale_at(sbuf, 4 + u, idx1), sc1);
                 } else {
+                float4 xv[P];
+#pragma unroll
+                for (int q = 0; q < P; q++) xv[q] = xs[q * nch + c];
                     dot_chunk<FMT>(wa[u], xv, acc0);
                     if (v1) dot_chunk<FMT>(wb[u], xv, acc1);
                 }
@@ -199,10 +320,14 @@ ax_gemv_stream_kernel(const GemvArgs a) {
     if (!TMA) {
         // second plane (raw residual stream, fetched early) only when the launcher reserved it
         float4* xb = a.pro.base_early ? reinterpret_cast<float4*>(ring) : nullptr;
+        // after the input planes: [int4 scale slots][digit planes + block sums of the quantised formats][partials]
         uint8_t* after_x = ring + (a.pro.base_early ? x_bytes : 0);
         uint32_t* sland = reinterpret_cast<uint32_t*>(after_x);                              // int4 only: [2][8][threads] scale slots
-        float* part = reinterpret_cast<float*>(after_x + (FMT == ATLASX_INT4 ? scale_land_bytes(NTHR) : 0));   // [pairs][warps][2]
-        consume_direct<FMT, NTHR>(a, xs, xb, red, part, sland, lo, hi);
+        uint8_t* xq = after_x + (FMT == ATLASX_INT4 ? scale_land_bytes(NTHR) : 0);
+        float* xsc = reinterpret_cast<float*>(xq + 3 * digit_plane_bytes(a.K));              // scale per 32 input elements
+        int* bs = reinterpret_cast<int*>(xsc + digit_groups(a.K));                           // int4: digit sums per 32 elements
+        float* part = reinterpret_cast<float*>(xq + digit_bytes(FMT, a.K));                  // [pairs][warps][2]
+        consume_direct<FMT, NTHR>(a, xs, xb, red, part, sland, xq, xsc, bs, lo, hi);
         return;
     }
 
@@ -489,7 +614,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
             const long long rows_max = ((long long)units + grid - 1) / grid * unit + unit;
             return (size_t)((rows_max + 1) / 2 + 1) * (nthr / 32) * 2 * sizeof(float);
         };
-        const size_t land = w.dtype == ATLASX_INT4 ? (size_t)scale_land_bytes(nthr) : 0;
+        const size_t land = (w.dtype == ATLASX_INT4 ? (size_t)scale_land_bytes(nthr) : 0) + (size_t)digit_bytes(w.dtype, w.cols);
         size_t smem = 0;
         int grid = 1;
         for (int attempt = 0; attempt < 2; attempt++) {

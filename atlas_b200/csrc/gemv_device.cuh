@@ -172,13 +172,15 @@ __device__ __forceinline__ void stage_input_early(const GemvArgs& a, float4* xb)
     }
 }
 
-template <int FMT, int NTHR = 256>
+// LINEAR: the staged vector keeps its natural order (callers that do not read it in the
+// per-chunk plane layout; no bank conflicts while staging).
+template <int FMT, int NTHR = 256, bool LINEAR = false>
 __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float* red, const float4* xb = nullptr) {
     constexpr int EPC = Fmt<FMT>::EPC;
     const AxPrologue& p = a.pro;
     const int K = a.K, n4 = (a.dbg & 2) ? K >> 5 : K >> 2, nch = a.nchunks;     // dbg bit 1: experiments only
     const int tid = threadIdx.x;
-    auto slot = [&](int k4) { const int e = k4 << 2; return ((e % EPC) >> 2) * nch + e / EPC; };
+    auto slot = [&](int k4) { if (LINEAR) return k4; const int e = k4 << 2; return ((e % EPC) >> 2) * nch + e / EPC; };
 
     const float* base = p.base;
     const uint16_t* base16 = nullptr;
