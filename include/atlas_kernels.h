@@ -92,7 +92,8 @@ int   atlasx_ctx_destroy(atlasx_ctx* ctx);
 int   atlasx_ctx_sync(atlasx_ctx* ctx);
 void* atlasx_ctx_stream(atlasx_ctx* ctx);                 /* cudaStream_t */
 int   atlasx_ctx_sm_count(atlasx_ctx* ctx);
-/* GEMV kernel choice: 0 = automatic, 1 = plain 128-bit loads, 2 = bulk-copy (TMA) pipeline */
+/* GEMV kernel choice: 0 = automatic (plain loads), 1 = plain 128-bit loads, 2 = bulk-copy (TMA) ring,
+ * 3 = as 1 but multi-column products keep the scalar kernel instead of the tensor-core one (A/B comparison) */
 int   atlasx_ctx_set_gemv_impl(atlasx_ctx* ctx, int impl);
 /* nonzero when a device-side bounded wait gave up since the last call (clears it) */
 int   atlasx_ctx_poll_device_error(atlasx_ctx* ctx, int* code_out);
