@@ -84,6 +84,7 @@ struct atlasx_model {
     bool mail_reduce = false;                    // parts are summed by one small kernel per use instead of by every consumer CTA
     std::vector<void*> owned;                    // device allocations to free
     int* pin = nullptr;                          // pinned host ints
+    float* pin_logits = nullptr;                 // pinned staging for logits handed to the host (allocated on first use)
     int launches_per_step = 0;
     // whole-step persistent kernel (single GPU, head_dim 128)
     int use_mega = 0; bool mega_ready = false;   // opt-in: slower than the per-operation step so far
@@ -779,6 +780,7 @@ extern "C" int atlasx_model_free(atlasx_model* m) {
     for (Layer& ly : m->layers) if (ly.kv) atlasx_kvcache_free(ly.kv);
     for (void* p : m->owned) cudaFree(p);
     if (m->pin) cudaFreeHost(m->pin);
+    if (m->pin_logits) cudaFreeHost(m->pin_logits);
     delete m;
     return ATLASX_OK;
 }
@@ -1066,7 +1068,15 @@ extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* 
     AX_CUDA(cudaMemcpyAsync(m->seq + m->host_pos, m->pin, 4, cudaMemcpyHostToDevice, s));
     set_state_k<<<1, 1, 0, s>>>(m->st, m->host_pos, INT_MAX);
     int rc = step(m); if (rc) return rc;
-    if (logits_host) AX_CUDA(cudaMemcpyAsync(logits_host, m->logits, (size_t)m->cfg.vocab_size * 4, cudaMemcpyDeviceToHost, s));
+    if (logits_host) {
+        // through pinned memory: a copy into pageable memory is staged by the driver in small pieces
+        const size_t bytes = (size_t)m->cfg.vocab_size * 4;
+        if (!m->pin_logits) AX_CUDA(cudaMallocHost((void**)&m->pin_logits, bytes));
+        AX_CUDA(cudaMemcpyAsync(m->pin_logits, m->logits, bytes, cudaMemcpyDeviceToHost, s));
+        AX_CUDA(cudaStreamSynchronize(s));
+        memcpy(logits_host, m->pin_logits, bytes);
+        return ATLASX_OK;
+    }
     AX_CUDA(cudaStreamSynchronize(s));
     return ATLASX_OK;
 }
