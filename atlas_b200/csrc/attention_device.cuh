@@ -8,7 +8,7 @@
 namespace {
 
 __device__ __forceinline__ float mg_exp_diff(float m, float m_new) {
-    return (m == -CUDART_INF_F) ? 0.f : expf(m - m_new);
+    return (m == -CUDART_INF_F) ? 0.f : __expf(m - m_new);
 }
 
 template <bool BF16, int EPL>
@@ -77,7 +77,7 @@ __device__ __forceinline__ void mg_update(float (&m)[GT], float (&l)[GT], float 
 #pragma unroll
         for (int e = 0; e < EPL; e++) acc[g][e] *= corr;
 #pragma unroll
-        for (int u = 0; u < N; u++) { p[u][g] = valid[u] ? expf(sc[u][g] - mn) : 0.f; l[g] += p[u][g]; }
+        for (int u = 0; u < N; u++) { p[u][g] = valid[u] ? __expf(sc[u][g] - mn) : 0.f; l[g] += p[u][g]; }
         m[g] = mn;
     }
 #pragma unroll
