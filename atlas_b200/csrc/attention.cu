@@ -492,8 +492,12 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
         }
         issue(j + NST);                           // refill the slots just read
         float sc[UN][G];
-        mg_scores<BF16, UN, EPL, LPR, G>(q, kr, valid, a.scale, sc);
-        mg_update<BF16, UN, EPL, G>(m, l, acc, sc, valid, vr);
+        if constexpr (G == 4 && BF16) {
+            mg_step_g4<UN, EPL>(q, kr, vr, valid, a.scale, m[0], l[0], acc);          // m[0], l[0]: this lane's own head
+        } else {
+            mg_scores<BF16, UN, EPL, LPR, G>(q, kr, valid, a.scale, sc);
+            mg_update<BF16, UN, EPL, G>(m, l, acc, sc, valid, vr);
+        }
     }
     cp_async_wait<0>();
 
@@ -511,8 +515,16 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
             k1[0] = *reinterpret_cast<const uint4*>(kp);
             v1[0] = *reinterpret_cast<const uint4*>(vp);
         }
-        mg_scores<BF16, 1, EPL, LPR, G>(q, k1, ok1, a.scale, sc);
-        mg_update<BF16, 1, EPL, G>(m, l, acc, sc, ok1, v1);
+        if constexpr (G == 4 && BF16) {
+            mg_step_g4<1, EPL>(q, k1, v1, ok1, a.scale, m[0], l[0], acc);
+        } else {
+            mg_scores<BF16, 1, EPL, LPR, G>(q, k1, ok1, a.scale, sc);
+            mg_update<BF16, 1, EPL, G>(m, l, acc, sc, ok1, v1);
+        }
+    }
+    if constexpr (G == 4 && BF16) {
+        const float mo = m[0], lo = l[0];
+        mg_expand_g4(mo, lo, m, l);
     }
 
     // merge lane groups of a warp, then warps, then (last CTA of the kv head) the splits

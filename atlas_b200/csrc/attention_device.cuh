@@ -109,4 +109,68 @@ __device__ __forceinline__ void mg_scores(const float (&q)[GT][EPL], const uint4
     }
 }
 
+// Four query heads per KV head, 16 lanes per cached row (bf16): scores and online softmax with the
+// work divided instead of repeated.  A segmented butterfly (5 shuffles per row instead of 16)
+// leaves each lane with the finished dot product of ONE head — head (sub >> 2), sub = lane % 16 —
+// so that lane alone keeps that head's running maximum and sum and computes its exponentials;
+// the probabilities and the rescale factor are then handed to the other lanes by shuffles.
+// m_own / l_own: state of this lane's head.  acc: all four heads' partial outputs, as elsewhere.
+template <int N, int EPL>
+__device__ __forceinline__ void mg_step_g4(const float (&q)[4][EPL], const uint4 (&kr)[N], const uint4 (&vr)[N], const bool (&valid)[N],
+                                           float scale, float& m_own, float& l_own, float (&acc)[4][EPL]) {
+    const int lane = threadIdx.x & 31;
+    const bool b3 = (lane & 8) != 0, b2 = (lane & 4) != 0;
+    float s[N];
+#pragma unroll
+    for (int u = 0; u < N; u++) {
+        float kf[EPL]; mg_unpack<true, EPL>(kr[u], kf);
+        float d[4];
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            float t = 0.f;
+#pragma unroll
+            for (int e = 0; e < EPL; e++) t = fmaf(q[g][e], kf[e], t);
+            d[g] = t;
+        }
+        const float e0 = (b3 ? d[2] : d[0]) + __shfl_xor_sync(AX_FULL, b3 ? d[0] : d[2], 8);
+        const float e1 = (b3 ? d[3] : d[1]) + __shfl_xor_sync(AX_FULL, b3 ? d[1] : d[3], 8);
+        float f = (b2 ? e1 : e0) + __shfl_xor_sync(AX_FULL, b2 ? e0 : e1, 4);
+        f += __shfl_xor_sync(AX_FULL, f, 2);
+        f += __shfl_xor_sync(AX_FULL, f, 1);
+        s[u] = valid[u] ? f * scale : -CUDART_INF_F;
+    }
+    float mn = m_own;
+#pragma unroll
+    for (int u = 0; u < N; u++) mn = fmaxf(mn, s[u]);
+    const float corr = (mn == -CUDART_INF_F) ? 1.f : mg_exp_diff(m_own, mn);
+    float p[N];
+    l_own *= corr;
+#pragma unroll
+    for (int u = 0; u < N; u++) { p[u] = valid[u] ? __expf(s[u] - mn) : 0.f; l_own += p[u]; }
+    m_own = mn;
+    const int half = lane & 16;                            // which 16-lane group of the warp
+#pragma unroll
+    for (int g = 0; g < 4; g++) {
+        const float cg = __shfl_sync(AX_FULL, corr, half | (g << 2));
+#pragma unroll
+        for (int e = 0; e < EPL; e++) acc[g][e] *= cg;
+    }
+#pragma unroll
+    for (int u = 0; u < N; u++) {
+        float vf[EPL]; mg_unpack<true, EPL>(vr[u], vf);
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const float pg = __shfl_sync(AX_FULL, p[u], half | (g << 2));
+#pragma unroll
+            for (int e = 0; e < EPL; e++) acc[g][e] = fmaf(pg, vf[e], acc[g][e]);
+        }
+    }
+}
+// hands every lane the state of all four heads (for the merges that follow the row loop)
+__device__ __forceinline__ void mg_expand_g4(float m_own, float l_own, float (&m)[4], float (&l)[4]) {
+    const int half = threadIdx.x & 16;
+#pragma unroll
+    for (int g = 0; g < 4; g++) { m[g] = __shfl_sync(AX_FULL, m_own, half | (g << 2)); l[g] = __shfl_sync(AX_FULL, l_own, half | (g << 2)); }
+}
+
 }  // namespace
