@@ -119,23 +119,21 @@ SIGNATURES = {
     "atlasx_model_pos": (ci, [vp]),
     "atlasx_model_forward_one": (ci, [vp, C.c_uint32, vp]),
     "atlasx_model_generate_greedy": (ci, [vp, vp, ci, ci, vp, ci, cf, ci, vp, ci, vp, pi]),
-    "atlasx_model_decode_timed": (ci, [vp, ci, C.POINTER(cf), vp]),
+    "atlasx_model_decode_timed": (ci, [vp, ci, ci, C.POINTER(cf), vp]),
     "atlasx_model_profile_step": (ci, [vp, ci, vp, vp, vp, pi]),
     "atlasx_model_class_name": (C.c_char_p, [ci]),
     "atlasx_model_step_bytes": (C.c_double, [vp, ci]),
     "atlasx_model_kernel_launches_per_step": (ci, [vp]),
     "atlasx_model_set_options": (ci, [vp, ci, ci]),
-    "atlasx_model_set_mega": (ci, [vp, ci]),
     "atlasx_model_set_prefill": (ci, [vp, ci, vp]),
     "atlasx_model_time_classes": (ci, [vp, C.c_uint, ci, vp, vp, vp]),
-    "atlasx_model_uses_mega": (ci, [vp]),
     "atlasx_model_hidden": (ci, [vp, vp]),
     "atlasx_time_gemv": (ci, [vp, vp, ci, vp, ci, vp, ci, C.POINTER(cf)]),
     "atlasx_time_attention": (ci, [vp, vp, vp, vp, ci, vp, cf, ci, ci, C.POINTER(cf)]),
     "atlasx_comm_unique_id": (ci, [vp]),
     "atlasx_comm_init": (ci, [vp, vp, ci, ci]),
     "atlasx_comm_world": (ci, [vp]),
-    "atlasx_comm_selftest_wait_expiry": (ci, [vp, vp]),
+    "atlasx_comm_selftest_wait_expiry": (ci, [vp, vp, ci]),
     "atlasx_comm_allreduce": (ci, [vp, vp, ci]),
 }
 

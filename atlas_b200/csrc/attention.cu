@@ -10,7 +10,6 @@
 // and the last CTA of each head group to finish merges the partial results (ticket counter,
 // nothing ever waits).  The KV cache may be bf16 (half the traffic) or f32 (reference format).
 #include "attention.cuh"
-#include <stdlib.h>
 #include "attention_device.cuh"
 
 #include <math_constants.h>
@@ -699,9 +698,13 @@ int ax_attn_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
         fd.a.n_heads = a.n_heads; fd.a.n_kv = a.n_kv; fd.a.window = a.window; fd.a.kv_dtype = a.kv_dtype; fd.a.scale = a.scale;
         int sp = a.n_splits < 1 ? 1 : (a.n_splits > 64 ? 64 : a.n_splits);
         fd.a.max_splits = sp;
-        int rc2 = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.batch * a.n_heads * sp * (128 + 2), (size_t)a.batch * a.n_heads);
-        if (rc2) return rc2;
-        fd.partials = ctx->attn_partials; fd.tickets = ctx->attn_tickets; fd.trace = nullptr;
+        if (a.scratch_partials && a.scratch_tickets) { fd.partials = a.scratch_partials; fd.tickets = a.scratch_tickets; }
+        else {
+            int rc2 = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.batch * a.n_heads * sp * (128 + 2), (size_t)a.batch * a.n_heads);
+            if (rc2) return rc2;
+            fd.partials = ctx->attn_partials; fd.tickets = ctx->attn_tickets;
+        }
+        fd.trace = nullptr;
         fd.q_ready = a.q; fd.seq_stride = a.seq_stride; fd.pos_b = a.pos; fd.pos_shared = a.pos_shared; fd.pos_scalar = a.pos_scalar;
         if (a.kv_dtype == ATLASX_BF16)
             return g_real == 1 ? launch_fused<true, 1>(ctx, fd, pdl, a.batch) : g_real == 2 ? launch_fused<true, 2>(ctx, fd, pdl, a.batch)
@@ -716,10 +719,13 @@ int ax_attn_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
     dv.chunks = 1;
     const size_t need_p = (size_t)a.batch * a.n_heads * dv.a.n_splits * (a.hd + 2);
     const size_t need_t = (size_t)a.batch * a.n_heads;      // ≥ batch × groups
-    int rc = atlasx_ctx_ensure_attn_scratch(ctx, need_p, need_t);
-    if (rc) return rc;
-    dv.partials = ctx->attn_partials;
-    dv.tickets = ctx->attn_tickets;
+    if (a.scratch_partials && a.scratch_tickets) { dv.partials = a.scratch_partials; dv.tickets = a.scratch_tickets; }
+    else {
+        int rc = atlasx_ctx_ensure_attn_scratch(ctx, need_p, need_t);
+        if (rc) return rc;
+        dv.partials = ctx->attn_partials;
+        dv.tickets = ctx->attn_tickets;
+    }
     const bool bf = a.kv_dtype == ATLASX_BF16;
     if (bf) return a.hd == 128 ? dispatch_g<true, 128>(ctx, dv, pdl) : dispatch_g<true, 64>(ctx, dv, pdl);
     return a.hd == 128 ? dispatch_g<false, 128>(ctx, dv, pdl) : dispatch_g<false, 64>(ctx, dv, pdl);
@@ -733,15 +739,14 @@ bool ax_attn_fused_supported(int hd, int n_heads, int n_kv) {
 int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows) {
     // one wave of CTAs
     int s = (max_rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
-    int per_sm = 2;                  // measured best with three landing stages (48 KB per CTA)
-    if (const char* e = getenv("ATLASX_ATTN_WAVE")) { const int v = atoi(e); if (v >= 1 && v <= 8) per_sm = v; }   // experiments
+    const int per_sm = ctx->tune.attn_wave;      // 2 measured best with three landing stages (48 KB per CTA)
     const int wave = (per_sm * ctx->sm_count) / (n_kv > 0 ? n_kv : 1);
     if (s > wave) s = wave;
     return s < 1 ? 1 : (s > 64 ? 64 : s);
 }
-int ax_attn_init(atlasx_ctx*) {
+int ax_attn_init(atlasx_ctx* ctx) {
     int rc;
-    if (const char* e = getenv("ATLASX_ATTN_STAGES")) { const int v = atoi(e); if (v >= 2 && v <= 4) g_fused_stages = v; }
+    g_fused_stages = ctx->tune.attn_stages;
     if ((rc = fused_attr<true, 1>()) || (rc = fused_attr<true, 2>()) || (rc = fused_attr<true, 4>())) return rc;
     if ((rc = fused_attr<false, 1>()) || (rc = fused_attr<false, 2>()) || (rc = fused_attr<false, 4>())) return rc;
     return ATLASX_OK;
@@ -753,10 +758,13 @@ int ax_attn_fused_launch(atlasx_ctx* ctx, const AxFusedAttnArgs& a, bool pdl) {
     AX_ARG((((uintptr_t)a.qkv | (uintptr_t)a.kc | (uintptr_t)a.vc | (uintptr_t)a.out) & 15) == 0, "buffers must be 16-byte aligned");
     FusedDev dv;
     dv.a = a;
-    int rc = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.n_heads * a.max_splits * (128 + 2), (size_t)a.n_heads);
-    if (rc) return rc;
-    dv.partials = ctx->attn_partials;
-    dv.tickets = ctx->attn_tickets;
+    if (a.scratch_partials && a.scratch_tickets) { dv.partials = a.scratch_partials; dv.tickets = a.scratch_tickets; }
+    else {
+        int rc = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.n_heads * a.max_splits * (128 + 2), (size_t)a.n_heads);
+        if (rc) return rc;
+        dv.partials = ctx->attn_partials;
+        dv.tickets = ctx->attn_tickets;
+    }
     dv.trace = nullptr;
     dv.q_ready = nullptr; dv.seq_stride = 0; dv.pos_b = nullptr; dv.pos_shared = 1; dv.pos_scalar = 0;
     if (ctx->trace_next) { dv.trace = ctx->trace_next; ctx->trace_next += 6; }

@@ -15,6 +15,9 @@ struct AxAttnArgs {
     int kv_dtype = ATLASX_BF16;
     float scale = 1.f;
     int n_splits = 1;
+    // split partials [batch × n_heads × n_splits × (hd + 2)] floats and tickets [batch × n_heads] (zero
+    // between launches) owned by the caller; null: context scratch, grown on demand (never inside a graph)
+    float* scratch_partials = nullptr; unsigned* scratch_tickets = nullptr;
 };
 
 // Chooses the split count for a launch that must fill the GPU whatever the position is.
@@ -56,6 +59,10 @@ struct AxFusedAttnArgs {
     int n_heads = 0, n_kv = 0, window = 0, kv_dtype = ATLASX_BF16;
     int max_splits = 1;              // grid.x; the kernel uses ⌈rows/64⌉ of them, the rest exit at once
     float scale = 1.f, qk_eps = 1e-6f;
+    // split partials [n_heads × max_splits × 130] floats and tickets [n_heads] (zero between launches)
+    // owned by the caller — a captured graph must not depend on context scratch that a later call may
+    // re-allocate; null: context scratch
+    float* scratch_partials = nullptr; unsigned* scratch_tickets = nullptr;
 };
 bool ax_attn_fused_supported(int hd, int n_heads, int n_kv);
 int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows);

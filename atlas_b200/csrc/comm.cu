@@ -6,6 +6,7 @@
 #include <stdlib.h>
 #include <string.h>
 
+#include <chrono>
 #include <vector>
 
 #include "common.cuh"
@@ -93,6 +94,28 @@ int ax_comm_allgather(atlasx_ctx* ctx, const float* send, float* recv, size_t n_
     return ATLASX_OK;
 }
 
+int ax_comm_stream_sync(atlasx_ctx* ctx) {
+    atlasx_comm* cm = ctx->comm;
+    if (!cm || cm->world == 1) { AX_CUDA(cudaStreamSynchronize(ctx->stream)); return ATLASX_OK; }
+    const auto t0 = std::chrono::steady_clock::now();
+    for (unsigned spin = 0;; spin++) {
+        const cudaError_t q = cudaStreamQuery(ctx->stream);
+        if (q == cudaSuccess) return ATLASX_OK;
+        if (q != cudaErrorNotReady) return atlasx_fail(ATLASX_ERR_CUDA, "stream failed: %s", cudaGetErrorString(q));
+        if ((spin & 63) != 63) continue;                     // the checks below every 64th poll
+        if (g_nccl.CommGetAsyncError) {
+            int async_err = 0;
+            const int e = g_nccl.CommGetAsyncError(cm->comm, &async_err);
+            if (e != kNcclSuccess || async_err != kNcclSuccess)
+                return atlasx_fail(ATLASX_ERR_COMM, "NCCL reported an asynchronous error: %s", nccl_err(e != kNcclSuccess ? e : async_err));
+        }
+        const long long ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms > ctx->tune.comm_timeout_ms)
+            return atlasx_fail(ATLASX_ERR_TIMEOUT, "the tensor-parallel step did not complete within %d ms (a rank that never joined?); "
+                                                   "the work is still queued: destroy the context", ctx->tune.comm_timeout_ms);
+    }
+}
+
 // The mailboxes are exchanged as CUDA IPC handles through an NCCL all-gather of raw bytes; every
 // rank must call this at the same point of its program.  A failure to map a peer (no peer access,
 // different IPC namespace) is not an error: all ranks learn of it through a second all-gather and
@@ -107,9 +130,10 @@ int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out) {
         return ATLASX_OK;
     }
     if (cm->mail_failed) return ATLASX_OK;
-    { const char* e = getenv("ATLASX_PEER_ALLREDUCE"); if (e && atoi(e) == 0) { cm->mail_failed = true; return ATLASX_OK; } }
+    if (!ctx->tune.peer_allreduce) { cm->mail_failed = true; return ATLASX_OK; }
     const int W = cm->world;
-    const size_t total = (((size_t)2 * W * d * sizeof(uint2)) + 255) / 256 * 256;
+    const size_t mail_bytes = (((size_t)2 * W * d * sizeof(uint2)) + 255) / 256 * 256;
+    const size_t total = mail_bytes + 256;                  // + the use counter
     AX_CUDA(cudaMalloc(&cm->mail_local, total));
     AX_CUDA(cudaMemset(cm->mail_local, 0, total));
     AX_CUDA(cudaDeviceSynchronize());
@@ -135,6 +159,7 @@ int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out) {
     for (int p = 0; p < W; p++) ok = ok && all[p].ok;
     AxPeerMail mail;
     mail.world = W; mail.rank = cm->rank; mail.d = d;
+    mail.useq = reinterpret_cast<unsigned*>((uint8_t*)cm->mail_local + mail_bytes);
     if (ok) {
         for (int p = 0; p < W && ok; p++) {
             if (p == cm->rank) { mail.base[p] = (uint2*)cm->mail_local; continue; }
@@ -187,7 +212,9 @@ extern "C" int atlasx_comm_world(const atlasx_ctx* ctx) { return ax_comm_world(c
 // Self-test of the bounded device-side waits: the mailbox reduction is launched on a zeroed part
 // whose sequence words nothing will ever set.  The kernel must give up after its limit (2 s), set
 // the context's error word and return — the context stays usable.  *code receives the word (3).
-extern "C" int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code) {
+// keep != 0 leaves the word set (the state a real expiry leaves behind) for the caller to clear
+// with atlasx_ctx_poll_device_error.
+extern "C" int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code, int keep) {
     AX_ARG(ctx && code, "null argument");
     const int d = 512;
     uint2* part = nullptr; float* out = nullptr; unsigned* epoch = nullptr;
@@ -202,7 +229,12 @@ extern "C" int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code) {
         if (e != cudaSuccess) rc = atlasx_fail(ATLASX_ERR_CUDA, "self-test kernel failed: %s", cudaGetErrorString(e));
     }
     *code = 0;
-    if (!rc) {
+    if (!rc && keep) {                                    // report the word and leave it set
+        cudaError_t e = cudaMemcpyAsync(ctx->host_pin, ctx->dev_error, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream);
+        if (e == cudaSuccess) e = cudaStreamSynchronize(ctx->stream);
+        if (e != cudaSuccess) rc = atlasx_fail(ATLASX_ERR_CUDA, "reading the error word failed: %s", cudaGetErrorString(e));
+        else *code = ctx->host_pin[0];
+    } else if (!rc) {
         atlasx_ctx_poll_device_error(ctx, code);          // returns ATLASX_ERR_TIMEOUT when the word is set: expected here
         rc = ATLASX_OK;
     }

@@ -13,6 +13,11 @@ constexpr int kMaxPeers = AX_MAX_PEERS;
 // part that every peer produced after reading the previous content of that buffer.
 struct AxPeerMail {
     int world = 1, rank = 0, d = 0;
+    // Device word beside this rank's mailbox: number of mailbox uses so far.  It belongs to the
+    // mailbox, not to a model — every model of the context stamps its partial sums with
+    // *useq + layer + 1 and advances the word by its layer count per step, so sequence numbers
+    // never repeat while the mailbox lives, whatever models come and go on the context.
+    unsigned* useq = nullptr;
     uint2* base[kMaxPeers] = {};        // mailbox of rank p as mapped in this process (own allocation for p == rank)
     uint2* part(int owner, int buf, int from) const { return base[owner] + ((size_t)buf * world + from) * d; }
 };
@@ -21,6 +26,11 @@ int ax_comm_world(const atlasx_ctx* ctx);
 int ax_comm_rank(const atlasx_ctx* ctx);
 int ax_comm_allreduce_sum(atlasx_ctx* ctx, float* buf_dev, size_t n);                         // in place, on ctx->stream
 int ax_comm_allgather(atlasx_ctx* ctx, const float* send_dev, float* recv_dev, size_t n_each);
+// Host wait for the context stream.  Single GPU: cudaStreamSynchronize.  With a communicator the
+// host polls instead — stream completion, ncclCommGetAsyncError, and a deadline
+// (ATLASX_COMM_TIMEOUT_MS, default 30 s) — so that a peer that never joins a collective ends in
+// ATLASX_ERR_COMM / ATLASX_ERR_TIMEOUT on the host instead of an endless wait.
+int ax_comm_stream_sync(atlasx_ctx* ctx);
 // Collective over all ranks: allocates and exchanges the mailboxes for vectors of d floats.
 // Returns ATLASX_OK with *out == nullptr when peer mapping is not possible (the caller keeps NCCL).
 int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out);

@@ -45,6 +45,18 @@ struct atlasx_ctx {
     int gemv_impl = 0;                 // 0 auto, 1 plain loads, 2 bulk-copy pipeline
     int carveout = 50;                 // shared-memory share of the L1 array requested per launch (percent), −1: driver's choice.
                                        // One value for every kernel of a step: neighbours in the stream then fit on an SM together
+    // Experiment switches, read from the environment once when the context is created (never on a launch path)
+    struct Tuning {
+        int gemv_threads = 512;        // ATLASX_GEMV_THREADS=256: two 256-thread CTAs per SM instead of one 512-thread CTA
+        int pdl_mask = 0x7FFFFFFF;     // ATLASX_PDL_MASK: bit per launch class of the decode step
+        int attn_fused = 1;            // ATLASX_ATTN_FUSED=0: QK-norm/RoPE/cache write and attention as two launches
+        int attn_stages = 3;           // ATLASX_ATTN_STAGES: landing stages of the one-launch attention inside a step (2..4)
+        int attn_wave = 2;             // ATLASX_ATTN_WAVE: attention CTAs per SM that one wave of splits may fill
+        int peer_allreduce = 1;        // ATLASX_PEER_ALLREDUCE=0: ncclAllReduce instead of the peer mailboxes
+        int mail_reduce = -1;          // ATLASX_MAIL_REDUCE: 1 = mailbox parts summed by a kernel of their own, 0 = by the consumer, −1 = automatic
+        int step_trace = 0;            // ATLASX_STEP_TRACE=1: timeline stamps in the captured step
+        int comm_timeout_ms = 30000;   // ATLASX_COMM_TIMEOUT_MS: host deadline for a tensor-parallel step to complete
+    } tune;
     // attention scratch (split-K partials + tickets), grown on demand
     float* attn_partials = nullptr;  size_t attn_partials_cap = 0;   // floats
     unsigned* attn_tickets = nullptr; size_t attn_tickets_cap = 0;   // uints, always zero between launches

@@ -49,7 +49,21 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
     AX_CUDA(cudaMalloc((void**)&c->amax_ticket, sizeof(unsigned)));
     AX_CUDA(cudaMemset(c->amax_ticket, 0, sizeof(unsigned)));
     AX_CUDA(cudaMalloc((void**)&c->amax_out, sizeof(int)));
-    { const char* e = getenv("ATLASX_CARVEOUT"); if (e) c->carveout = atoi(e); }      // experiments
+    {   // experiment switches: the only place the library reads its environment (besides ATLAS_NCCL_LIB at NCCL load)
+        auto env_int = [](const char* name, int* dst) { const char* e = getenv(name); if (e && *e) *dst = atoi(e); };
+        env_int("ATLASX_CARVEOUT", &c->carveout);
+        env_int("ATLASX_GEMV_THREADS", &c->tune.gemv_threads);
+        env_int("ATLASX_PDL_MASK", &c->tune.pdl_mask);
+        env_int("ATLASX_ATTN_FUSED", &c->tune.attn_fused);
+        env_int("ATLASX_ATTN_STAGES", &c->tune.attn_stages);
+        env_int("ATLASX_ATTN_WAVE", &c->tune.attn_wave);
+        env_int("ATLASX_PEER_ALLREDUCE", &c->tune.peer_allreduce);
+        env_int("ATLASX_MAIL_REDUCE", &c->tune.mail_reduce);
+        env_int("ATLASX_STEP_TRACE", &c->tune.step_trace);
+        env_int("ATLASX_COMM_TIMEOUT_MS", &c->tune.comm_timeout_ms);
+        if (c->tune.attn_stages < 2 || c->tune.attn_stages > 4) c->tune.attn_stages = 3;
+        if (c->tune.attn_wave < 1 || c->tune.attn_wave > 8) c->tune.attn_wave = 2;
+    }
     int rc = ax_gemv_init(c);
     if (!rc) rc = ax_attn_init(c);
     if (rc) { delete c; return rc; }
@@ -64,7 +78,7 @@ extern "C" int atlasx_ctx_destroy(atlasx_ctx* c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     atlasx_comm_destroy(c);
-    cudaFree(c->attn_partials); cudaFree(c->attn_tickets); cudaFree(c->pos_dev);
+    cudaFree(c->attn_partials); cudaFree(c->attn_tickets); cudaFree(c->pos_dev); cudaFree(c->split_scratch);
     cudaFree(c->amax_vals); cudaFree(c->amax_idx); cudaFree(c->amax_ticket); cudaFree(c->amax_out);
     cudaFree(c->dev_error); cudaFreeHost(c->host_pin);
     cudaStreamDestroy(c->stream);
@@ -326,8 +340,7 @@ extern "C" size_t atlasx_matrix_bytes(const atlasx_matrix* m) { return m ? ax_we
 extern "C" int atlasx_gemv(atlasx_ctx* c, const atlasx_matrix* m, const float* x, int n, float* y) {
     AX_ARG(c && m && x && y, "null argument");
     AxPrologue pro; pro.base = x;
-    static const bool pdl = getenv("ATLASX_GEMV_PDL") && atoi(getenv("ATLASX_GEMV_PDL"));   // experiments
-    return ax_gemv_launch(c, m->w, pro, AX_EPI_PLAIN, n, y, pdl);
+    return ax_gemv_launch(c, m->w, pro, AX_EPI_PLAIN, n, y, false);
 }
 extern "C" int atlasx_matrix_sgemm(atlasx_ctx* c, const atlasx_matrix* m, const float* rhs, int k, int n, float* out) {
     AX_ARG(c && m && rhs && out, "null argument");

@@ -17,8 +17,6 @@
 //   * epilogue: plain store (int8: × row scale) or SwiGLU on interleaved gate/up rows.
 // Every wait on an mbarrier is bounded; on expiry the CTA records an error word and leaves.
 #include "gemv.cuh"
-#include <stdlib.h>
-
 #include "gemv_device.cuh"
 
 namespace {
@@ -72,7 +70,14 @@ __device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* 
         mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 1));
         mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 2));
         mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 4));     // eight threads = 32 elements
-        if (!(mx < 3.0e38f)) mx = 3.0e38f;                   // inf or NaN in the input: keep the arithmetic finite
+        // NaN or inf anywhere in the group: the digits below stay finite (the clamp swallows NaN), so the
+        // group's scale carries the fault instead — it becomes NaN, and with it every output row, as in
+        // the float formats.  0·x is NaN exactly for x = NaN or ±inf; NaN survives the additions.
+        float bad = v.x * 0.f + v.y * 0.f + v.z * 0.f + v.w * 0.f;
+        bad += __shfl_xor_sync(AX_FULL, bad, 1);
+        bad += __shfl_xor_sync(AX_FULL, bad, 2);
+        bad += __shfl_xor_sync(AX_FULL, bad, 4);
+        if (!(mx < 3.0e38f)) mx = 3.0e38f;
         const float inv = mx > 0.f ? 127.0f / mx : 0.f;
         const float xv[4] = { v.x, v.y, v.z, v.w };
         int d1[4], d2[4], d3[4];
@@ -98,7 +103,7 @@ __device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* 
             if (in && (k4 & 7) == 0) { bs[k4 >> 3] = t1; bs[ng + (k4 >> 3)] = t2; bs[2 * ng + (k4 >> 3)] = t3; }
         }
         if (!in) continue;
-        if ((k4 & 7) == 0) xsc[k4 >> 3] = mx / 127.0f;
+        if ((k4 & 7) == 0) xsc[k4 >> 3] = mx / 127.0f + bad;
         if (FMT == ATLASX_INT8) {
             auto word = [](const int (&d)[4]) { return (uint32_t)(d[0] & 255) | ((uint32_t)(d[1] & 255) << 8) | ((uint32_t)(d[2] & 255) << 16) | ((uint32_t)(d[3] & 255) << 24); };
             reinterpret_cast<uint32_t*>(xq)[k4] = word(d1);
@@ -407,8 +412,6 @@ int set_attrs() {
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false, 512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
-    if (const char* e = getenv("ATLASX_GEMV_CARVEOUT"))     // experiments: shared-memory share of the L1 array, percent
-        AX_CUDA(cudaFuncSetAttribute(ax_gemv_stream_kernel<FMT, false>, cudaFuncAttributePreferredSharedMemoryCarveout, atoi(e)));
     return ATLASX_OK;
 }
 
@@ -467,40 +470,6 @@ int ax_gemv_init(atlasx_ctx*) {
 }
 
 
-int ax_gemv_ring_seg_bytes() { return kSeg; }
-int ax_gemv_ring_scale_seg(const AxWeight& w) {
-    if (w.dtype != ATLASX_INT4) return 0;
-    return (kSeg * 2 / w.block) * (w.scales_f16 ? 2 : 4);
-}
-int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* y, int* err, GemvArgs* out) {
-    AX_ARG(w.data && y && out, "null pointer");
-    const int epc = w.dtype == ATLASX_F32 ? 4 : w.dtype == ATLASX_BF16 ? 8 : w.dtype == ATLASX_INT8 ? 16 : 32;
-    const int ebits = w.dtype == ATLASX_F32 ? 32 : w.dtype == ATLASX_BF16 ? 16 : w.dtype == ATLASX_INT8 ? 8 : 4;
-    bool ok = (w.cols % epc == 0) && (((uintptr_t)w.data & 15) == 0);
-    if (w.dtype == ATLASX_INT4) {
-        ok = ok && w.block >= 32 && (w.block % 32 == 0) && (w.cols % w.block == 0) && w.scales;
-        const int sseg = ax_gemv_ring_scale_seg(w);
-        const int srow = (w.cols / w.block) * (w.scales_f16 ? 2 : 4);
-        ok = ok && (sseg % 16 == 0) && (srow % 16 == 0) && (((uintptr_t)w.scales & 15) == 0);
-    }
-    if (w.dtype == ATLASX_INT8) ok = ok && w.scales;
-    if (epi == AX_EPI_SILU_PAIR) ok = ok && (w.rows % 2 == 0);
-    AX_ARG(ok, "matrix shape or alignment not supported by the ring kernel");
-    GemvArgs a = {};
-    a.W = (const uint8_t*)w.data; a.scales = (const uint8_t*)w.scales;
-    a.M = w.rows; a.K = w.cols;
-    a.row_bytes = (int)((size_t)w.cols * ebits / 8);
-    a.block = w.block > 0 ? w.block : 1; a.scales_f16 = w.scales_f16;
-    a.srow_bytes = w.dtype == ATLASX_INT4 ? (w.cols / w.block) * (w.scales_f16 ? 2 : 4) : 0;
-    a.spr = w.dtype == ATLASX_INT4 ? w.cols / (w.block > 0 ? w.block : 1) : 0;
-    a.bshift = -1;
-    if (w.dtype == ATLASX_INT4 && w.block >= 32) { const int q = w.block / 32; if ((q & (q - 1)) == 0) { a.bshift = 0; while ((1 << a.bshift) < q) a.bshift++; } }
-    a.nchunks = a.row_bytes / 16;
-    a.epi = epi; a.y = y; a.pro = pro; a.err = err; a.dbg = 0; a.trace = nullptr;
-    *out = a;
-    return ATLASX_OK;
-}
-
 size_t ax_weight_bytes(const AxWeight& w) {
     const size_t n = (size_t)w.rows * w.cols;
     switch (w.dtype) {
@@ -549,7 +518,6 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     if (w.dtype == ATLASX_INT4 && w.block >= 32) { const int q = w.block / 32; if ((q & (q - 1)) == 0) { a.bshift = 0; while ((1 << a.bshift) < q) a.bshift++; } }
     a.nchunks = a.row_bytes / 16;
     a.epi = epi; a.y = y; a.pro = pro; a.err = ctx->dev_error;
-    { const char* e = getenv("ATLASX_GEMV_DEBUG"); a.dbg = e ? atoi(e) : 0; }
     a.trace = nullptr;
 
     const size_t x_bytes = (((size_t)w.cols * 4 + 127) / 128) * 128;
@@ -569,7 +537,6 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     const long long half_sm = ((long long)smem_max + 1024) / 2 - 1024 - 512;
     long long avail = half_sm - 256 - (long long)x_bytes;
     int stages = (int)(avail / a.stage_stride);
-    { const char* e = getenv("ATLASX_GEMV_FULLSM"); if (e && atoi(e)) stages = 0; }
     if (stages < 2) { avail = (long long)smem_max - 256 - (long long)x_bytes; stages = (int)(avail / a.stage_stride); }
     if (stages > kMaxStages) stages = kMaxStages;
     if (stages < 2) tma_ok = false;
@@ -605,8 +572,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         // One 512-thread CTA per SM stages the input vector once per SM instead of twice (the same
         // bytes in flight as two 256-thread CTAs): 2.88 against 2.99 ms per token on the 7B shapes.
         // Matrices too small to give every SM a CTA keep the 256-thread form.
-        static const int wide_env = getenv("ATLASX_GEMV_THREADS") ? atoi(getenv("ATLASX_GEMV_THREADS")) : 512;   // experiments: 256
-        const bool wide = wide_env == 512 && tiles >= ctx->sm_count;
+        const bool wide = ctx->tune.gemv_threads == 512 && tiles >= ctx->sm_count;
         const int nthr = wide ? 512 : kConsumerThreads;
         const int slots_per_sm = wide ? 1 : 2;
         auto part_bytes = [&](int grid) {
@@ -636,7 +602,6 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
             }
         }
         if (per_sm < 1) per_sm = 1;
-        { const char* e = getenv("ATLASX_GEMV_PERSM"); if (e && atoi(e) > 0 && per_sm > atoi(e)) per_sm = atoi(e); }   // experiments
         grid = ctx->sm_count * per_sm;
         if (grid > tiles) grid = tiles;
         if (grid < 1) grid = 1;

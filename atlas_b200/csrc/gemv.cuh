@@ -61,7 +61,7 @@ int ax_mail_reduce_launch(atlasx_ctx* ctx, const uint2* parts, int n_parts, size
 
 enum { AX_EPI_PLAIN = 0, AX_EPI_SILU_PAIR = 1 };   // pair: out[r/2] = silu(acc[r])·acc[r+1], r even
 
-// Kernel-side view of one GEMV (built by ax_gemv_launch or by the whole-step kernel's program).
+// Kernel-side view of one GEMV (built by ax_gemv_launch).
 struct GemvArgs {
     const uint8_t* W; const uint8_t* scales;
     int M, K;                    // rows, cols (elements)
@@ -77,18 +77,12 @@ struct GemvArgs {
     AxPrologue pro;
     AxPeerOut peer;
     int* err;
-    int dbg;                     // experiments only: bit 0 = consumers skip the arithmetic
     unsigned long long* trace;   // diagnostics: timeline stamps of this launch, or null
 };
 
 // y[rows×n] = W·x.  n == 1: pro/epi honoured.  n in 2..16: plain only, x is [cols×n] row-major.
 int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y,
                    bool pdl = false, const AxPeerOut* peer = nullptr);
-// Fill the shape/format fields of a GemvArgs for the ring kernels (fails for shapes that need the
-// scalar kernel).  Ring geometry fields are left to the caller.
-int ax_gemv_make_args(const AxWeight& w, const AxPrologue& pro, int epi, float* y, int* err, GemvArgs* out);
-int ax_gemv_ring_scale_seg(const AxWeight& w);   // int4: scale bytes that accompany one full weight segment (0 otherwise)
-int ax_gemv_ring_seg_bytes();
 // Tensor-core path for n = 2..16 columns (bf16 / int8 / int4 weights); X [cols×n], Y [rows×n] row-major f32.
 bool ax_gemv_mma_supported(const AxWeight& w, int n, const float* x, const float* y);
 // token_major: X is [n][cols] and Y is [n][rows] (one contiguous vector per column).

@@ -1,6 +1,6 @@
-// gemv_device.cuh — device-side building blocks of the weight-streaming GEMV, shared by the
-// per-matrix kernels (gemv.cu) and the whole-step persistent kernel (mega.cu): ring geometry,
-// mbarrier / bulk-copy wrappers, per-format fragment dot products, input staging (prologue).
+// gemv_device.cuh — device-side building blocks of the weight-streaming GEMV kernels (gemv.cu):
+// ring geometry, mbarrier / bulk-copy wrappers, per-format fragment dot products, input staging
+// (prologue).
 #pragma once
 #include "gemv.cuh"
 
@@ -178,15 +178,14 @@ template <int FMT, int NTHR = 256, bool LINEAR = false>
 __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float* red, const float4* xb = nullptr) {
     constexpr int EPC = Fmt<FMT>::EPC;
     const AxPrologue& p = a.pro;
-    const int K = a.K, n4 = (a.dbg & 2) ? K >> 5 : K >> 2, nch = a.nchunks;     // dbg bit 1: experiments only
+    const int K = a.K, n4 = K >> 2, nch = a.nchunks;
     const int tid = threadIdx.x;
     auto slot = [&](int k4) { if (LINEAR) return k4; const int e = k4 << 2; return ((e % EPC) >> 2) * nch + e / EPC; };
 
     const float* base = p.base;
     const uint16_t* base16 = nullptr;
     if (p.embed) {
-        // activations and generation state are read past L1 (__ldcg): inside the persistent
-        // whole-step kernel they are rewritten by other SMs while this CTA stays resident
+        // activations and generation state are read past L1 (__ldcg): other SMs wrote them
         int pos = __ldcg(p.pos);
         long long tok = __ldcg(p.seq + pos);
         if (tok < 0) tok = 0;
@@ -362,7 +361,7 @@ __device__ __forceinline__ bool ring_consume(const GemvArgs& a, const Ring& rg, 
             if (!ok) break;
             const int seg_chunks = min(kSeg, a.row_bytes - kc * kSeg) >> 4;
             const uint8_t* st = rg.data + (size_t)s * rg.stage_stride + warp * rg.seg_pitch;
-            if (valid && !(a.dbg & 1)) {
+            if (valid) {
                 const uint4* wp = reinterpret_cast<const uint4*>(st) + lane;
                 const float4* xb = xs + kc * kSegChunks + lane;
                 if (FMT != ATLASX_INT4 && seg_chunks == kSegChunks) {

@@ -24,7 +24,6 @@
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "gemv.cuh"
-#include "mega.cuh"
 #include "objects.h"
 
 namespace {
@@ -37,7 +36,6 @@ struct StepState {           // device-resident generation state
     int pos;                 // next position to be processed
     int n_forced;            // positions below this hold caller-given tokens
     int last_token;          // argmax of the most recent logits
-    unsigned epoch;          // steps run since the model was finalised (never reset): sequence numbers of the peer mailboxes
 };
 
 struct Layer {
@@ -79,6 +77,7 @@ struct atlasx_model {
     cudaGraphExec_t graph = nullptr;
     int attn_splits = 1;
     bool fused_attn = false; int fused_splits = 1;   // one-launch attention (head_dim 128)
+    float* attn_partials = nullptr; unsigned* attn_tickets = nullptr;   // split-attention scratch of this model's step graph
     const AxPeerMail* mail = nullptr;            // tensor parallel: all-reduce fused into o_proj/down over peer memory
     int class_mask = (1 << CLS_COUNT) - 1;       // launch classes issued by run_step (all, except while one family is timed)
     bool mail_reduce = false;                    // parts are summed by one small kernel per use instead of by every consumer CTA
@@ -86,11 +85,6 @@ struct atlasx_model {
     int* pin = nullptr;                          // pinned host ints
     float* pin_logits = nullptr;                 // pinned staging for logits handed to the host (allocated on first use)
     int launches_per_step = 0;
-    // whole-step persistent kernel (single GPU, head_dim 128)
-    int use_mega = 0; bool mega_ready = false;   // opt-in: slower than the per-operation step so far
-    MegaPhase* phases_dev = nullptr; MegaSync* sync = nullptr;
-    float* mega_partials = nullptr; float* sel_vals = nullptr; int* sel_idx = nullptr;
-    MegaArgs margs; size_t mega_smem = 0; int mega_splits = 1;
     // prompt ingestion in chunks of up to kPrefillMax tokens through the multi-column kernels
     int prefill_chunk = 1;                       // 1: token by token (the reference's way)
     float *pf_r = nullptr, *pf_a = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_o = nullptr,
@@ -196,7 +190,9 @@ int place_slice(atlasx_model* m, const void* src, int src_dtype, int rows, int c
 // ── argmax of the logits + advance of the device-resident state ─────────────────
 // Last CTA: last_token = argmax; if the next position is not a caller-given one, the token is
 // stored as the next input; pos += 1.
-__global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, AxArgmaxScratch sc, StepState* st, int* seq, int seq_cap, int advance, int bump_epoch) {
+// useq (may be null): the mailbox use counter of the tensor-parallel group, advanced by `bump` per step.
+__global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, AxArgmaxScratch sc, StepState* st, int* seq, int seq_cap, int advance,
+                                                        unsigned* useq, unsigned bump) {
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ int s_last;
@@ -234,7 +230,7 @@ __global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, A
         if (idx < 0) idx = n - 1;
         *sc.ticket = 0u;
         st->last_token = idx;
-        if (bump_epoch) st->epoch += 1u;
+        if (useq) *useq += bump;
         if (advance) {
             const int p = st->pos + 1;
             if (p >= st->n_forced && p < seq_cap) seq[p] = idx;
@@ -278,133 +274,13 @@ double gemv_bytes(const AxWeight& w) { return (double)ax_weight_bytes(w) + 4.0 *
         n_launch++;                                                                          \
     } while (0)
 
-// Program of the whole-step kernel: the same operations as run_step, as a list of phases.
-int build_mega(atlasx_model* m) {
-    atlasx_ctx* c = m->ctx;
-    const atlasx_model_config& cf = m->cfg;
-    m->mega_ready = false;
-    if (!m->use_mega || m->world != 1 || m->hd != 128) return ATLASX_OK;
-    const int G = m->nh_loc / m->nkv_loc;
-    if (G != 1 && G != 2 && G != 4) return ATLASX_OK;
-    const int d = cf.d_model, L = cf.n_layers;
-    const bool post = cf.post_norm != 0;
-    int S = c->sm_count / m->nkv_loc;
-    if (S < 1) S = 1;
-    if (S > 8) S = 8;
-    m->mega_splits = S;
-    std::vector<MegaPhase> ph;
-    ph.reserve((size_t)L * 5 + 3);
-    int rc = ATLASX_OK, cur = 0;
-    if ((rc = dmalloc(m, (void**)&m->mega_partials, (size_t)m->nh_loc * S * (m->hd + 4) * 4))) return rc;
-    if ((rc = dmalloc(m, (void**)&m->sel_vals, (size_t)c->sm_count * 4))) return rc;
-    if ((rc = dmalloc(m, (void**)&m->sel_idx, (size_t)c->sm_count * 4))) return rc;
-    if ((rc = dmalloc(m, (void**)&m->sync, sizeof(MegaSync)))) return rc;
-    AX_CUDA(cudaMemsetAsync(m->sync, 0, sizeof(MegaSync), c->stream));
-    size_t x_max = (size_t)(4 * 128 + 256 + 8 * 4 * 130) * 4;          // attention scratch
-    auto add_gemv = [&](const AxWeight& w, const AxPrologue& p, int epi, float* y, bool merge) -> int {
-        MegaPhase P;
-        memset(&P, 0, sizeof(P));
-        P.type = MEGA_GEMV;
-        int r = ax_gemv_make_args(w, p, epi, y, c->dev_error, &P.g);
-        if (r) return r;
-        if (merge) { P.merge_partials = m->mega_partials; P.merge_heads = m->nh_loc; P.merge_hd = m->hd; P.merge_splits = S; }
-        const size_t xb = (((size_t)w.cols * 4 + 127) / 128) * 128;
-        if (xb > x_max) x_max = xb;
-        ph.push_back(P);
-        return ATLASX_OK;
-    };
-    for (int l = 0; l < L; l++) {
-        Layer& ly = m->layers[l];
-        AxPrologue p;
-        p.eps = cf.rms_norm_eps;
-        if (l == 0) {
-            p.embed = m->embed; p.embed_bf16 = m->embed_bf16; p.vocab = cf.vocab_size;
-            p.seq = m->seq; p.pos = &m->st->pos;
-            p.resid_out = m->resid[0]; cur = 0;
-            if (!post) p.wx = ly.attn_norm;
-        } else {
-            p.base = m->resid[cur]; p.y = m->dn; p.nparts = 1; p.part_stride = d;
-            if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
-            p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
-        }
-        if (add_gemv(ly.qkv, p, AX_EPI_PLAIN, m->qkv, false)) return ATLASX_OK;     // shape not supported: no mega path
-        MegaPhase A;
-        memset(&A, 0, sizeof(A));
-        A.type = MEGA_ATTN;
-        A.qkv = m->qkv; A.q_norm = ly.q_norm; A.k_norm = ly.k_norm; A.cos_t = m->cos_t; A.sin_t = m->sin_t;
-        A.kc = ly.kv->k; A.vc = ly.kv->v; A.partials = m->mega_partials; A.pos = &m->st->pos;
-        A.n_heads = m->nh_loc; A.n_kv = m->nkv_loc; A.hd = m->hd; A.window = ly.window;
-        A.kv_bf16 = cf.kv_dtype == ATLASX_BF16; A.splits = S; A.scale = m->scale; A.qk_eps = 1e-6f;
-        ph.push_back(A);
-        AxPrologue po; po.base = m->attn;                 // unused: the input is the merged attention output
-        if (add_gemv(ly.wo, po, AX_EPI_PLAIN, m->o, true)) return ATLASX_OK;
-        AxPrologue pg;
-        pg.eps = cf.rms_norm_eps;
-        pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = 1; pg.part_stride = d;
-        if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
-        pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
-        if (add_gemv(ly.gateup, pg, AX_EPI_SILU_PAIR, m->h, false)) return ATLASX_OK;
-        AxPrologue pd; pd.base = m->h;
-        if (add_gemv(ly.down, pd, AX_EPI_PLAIN, m->dn, false)) return ATLASX_OK;
-    }
-    AxPrologue pl;
-    pl.eps = cf.rms_norm_eps;
-    pl.base = m->resid[cur]; pl.y = m->dn; pl.nparts = 1; pl.part_stride = d;
-    if (post) pl.wy = m->layers[L - 1].ffn_norm;
-    pl.wx = m->final_norm;
-    pl.resid_out = m->resid[cur ^ 1]; cur ^= 1;
-    if (add_gemv(m->lm_head, pl, AX_EPI_PLAIN, m->logits, false)) return ATLASX_OK;
-    MegaPhase Sp;
-    memset(&Sp, 0, sizeof(Sp));
-    Sp.type = MEGA_SELECT_PART;
-    Sp.logits = m->logits; Sp.vocab = cf.vocab_size; Sp.sel_vals = m->sel_vals; Sp.sel_idx = m->sel_idx;
-    Sp.st_pos = &m->st->pos; Sp.st_nforced = &m->st->n_forced; Sp.st_last = &m->st->last_token;
-    Sp.seq = m->seq; Sp.seq_cap = cf.max_seq_len + 1;
-    ph.push_back(Sp);
-    Sp.type = MEGA_SELECT_FINAL;
-    ph.push_back(Sp);
-
-    // ring geometry: everything that is left of the SM's shared memory after the staged input
-    const int sseg = ax_gemv_ring_scale_seg(m->lm_head);
-    MegaArgs& a = m->margs;
-    a.seg_pitch = ax_gemv_ring_seg_bytes() + sseg;
-    a.stage_stride = 8 * a.seg_pitch;
-    a.x_bytes = (int)((x_max + 127) / 128 * 128);
-    const size_t smem_max = c->smem_optin ? c->smem_optin : 232448;
-    long long avail = (long long)smem_max - 256 - 2048 - a.x_bytes;
-    int stages = (int)(avail / a.stage_stride);
-    if (stages > 6) stages = 6;
-    if (stages < 2) return ATLASX_OK;
-    a.stages = stages;
-    m->mega_smem = 256 + 2048 + (size_t)a.x_bytes + (size_t)stages * a.stage_stride;
-    if ((rc = dmalloc(m, (void**)&m->phases_dev, ph.size() * sizeof(MegaPhase)))) return rc;
-    AX_CUDA(cudaMemcpyAsync(m->phases_dev, ph.data(), ph.size() * sizeof(MegaPhase), cudaMemcpyHostToDevice, c->stream));
-    AX_CUDA(cudaStreamSynchronize(c->stream));
-    a.phases = m->phases_dev; a.n_phases = (int)ph.size(); a.sync = m->sync; a.err = c->dev_error;
-    a.trace = nullptr;
-    if (getenv("ATLASX_MEGA_TRACE")) {
-        if ((rc = dmalloc(m, (void**)&a.trace, ph.size() * 4 * sizeof(unsigned long long)))) return rc;
-        AX_CUDA(cudaMemsetAsync(a.trace, 0, ph.size() * 4 * sizeof(unsigned long long), c->stream));
-    }
-    m->final_resid = cur;
-    if ((rc = ax_mega_init(c))) return rc;
-    m->mega_ready = true;
-    return ATLASX_OK;
-}
-
 // One token: every launch of the step, in order, on the context stream.
 int run_step(atlasx_model* m, Profile* prof, bool advance) {
     atlasx_ctx* c = m->ctx;
     cudaStream_t s = c->stream;
     const atlasx_model_config& cf = m->cfg;
-    if (m->mega_ready && m->use_mega && !prof && advance) {
-        int r = ax_mega_launch(c, cf.weight_format, cf.kv_dtype == ATLASX_BF16, m->margs, m->mega_smem);
-        if (!r) m->launches_per_step = 1;
-        return r;
-    }
     const bool pdl = m->use_pdl && !prof;
-    static const int pdl_mask = getenv("ATLASX_PDL_MASK") ? atoi(getenv("ATLASX_PDL_MASK")) : 511;   // experiments
-    auto P = [&](int cls) { return pdl && ((pdl_mask >> cls) & 1); };
+    auto P = [&](int cls) { return pdl && ((c->tune.pdl_mask >> cls) & 1); };
     const int d = cf.d_model, L = cf.n_layers;
     const bool post = cf.post_norm != 0;
     int rc = ATLASX_OK, n_launch = 0, cur = 0;
@@ -416,7 +292,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         AxPeerOut po;
         po.n = mail->world;
         for (int q = 0; q < mail->world; q++) po.y[q] = mail->part(q, buf, mail->rank);
-        po.epoch = &m->st->epoch; po.mul = (unsigned)L; po.add = (unsigned)l + 1u;    // use number = step·L + layer + 1
+        po.epoch = mail->useq; po.mul = 1u; po.add = (unsigned)l + 1u;                // use number = uses so far + layer + 1
         return po;
     };
     auto peer_in = [&](AxPrologue& p, int buf, int l) {
@@ -424,7 +300,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         p.y = reinterpret_cast<const float*>(mail->part(mail->rank, buf, 0));
         p.nparts = mail->world; p.part_stride = (size_t)mail->d;
         p.ll_n = mail->world; p.ll_stride = (size_t)mail->d;
-        p.ll_epoch = &m->st->epoch; p.ll_mul = (unsigned)L; p.ll_add = (unsigned)l + 1u;
+        p.ll_epoch = mail->useq; p.ll_mul = 1u; p.ll_add = (unsigned)l + 1u;
     };
 
     for (int l = 0; l < L; l++) {
@@ -460,6 +336,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             fa.n_heads = m->nh_loc; fa.n_kv = m->nkv_loc; fa.window = ly.window; fa.kv_dtype = cf.kv_dtype;
             fa.max_splits = m->fused_splits; fa.scale = m->scale;
             fa.qk_eps = 1e-6f;                             // the reference hard-codes 1e-6 here (:850,853)
+            fa.scratch_partials = m->attn_partials; fa.scratch_tickets = m->attn_tickets;
             STEP_LAUNCH(CLS_ATTN, abytes + 4.0 * (m->q_rows + 2 * m->kv_rows), ax_attn_fused_launch(c, fa, P(CLS_ATTN)));
         } else {
         // ── QK-norm, RoPE, cache write ──────────────────────────────────────────
@@ -478,6 +355,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         aa.pos = &m->st->pos; aa.pos_shared = 1; aa.batch = 1;
         aa.n_heads = m->nh_loc; aa.n_kv = m->nkv_loc; aa.hd = m->hd; aa.window = ly.window;
         aa.kv_dtype = cf.kv_dtype; aa.scale = m->scale; aa.n_splits = m->attn_splits;
+        aa.scratch_partials = m->attn_partials; aa.scratch_tickets = m->attn_tickets;
         STEP_LAUNCH(CLS_ATTN, abytes, ax_attn_launch(c, aa, P(CLS_ATTN)));
         }
 
@@ -488,7 +366,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ), &px));
             if (m->mail_reduce)
                 STEP_LAUNCH(CLS_COMM, 8.0 * d * mail->world, ax_mail_reduce_launch(c, mail->part(mail->rank, 0, 0), mail->world, (size_t)mail->d, d,
-                                                                                   &m->st->epoch, (unsigned)L, (unsigned)l + 1u, m->o, P(CLS_COMM)));
+                                                                                   mail->useq, 1u, (unsigned)l + 1u, m->o, P(CLS_COMM)));
         } else {
             STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ)));
             if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->o, (size_t)d));
@@ -511,7 +389,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
             STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN), &px));
             if (m->mail_reduce)
                 STEP_LAUNCH(CLS_COMM, 8.0 * d * mail->world, ax_mail_reduce_launch(c, mail->part(mail->rank, 1, 0), mail->world, (size_t)mail->d, d,
-                                                                                   &m->st->epoch, (unsigned)L, (unsigned)l + 1u, m->dn, P(CLS_COMM)));
+                                                                                   mail->useq, 1u, (unsigned)l + 1u, m->dn, P(CLS_COMM)));
         } else {
             STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN)));
             if (m->world > 1) STEP_LAUNCH(CLS_COMM, 4.0 * d, ax_comm_allreduce_sum(c, m->dn, (size_t)d));
@@ -540,7 +418,8 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         cfg.gridDim = dim3((unsigned)((n + 1023) / 1024)); cfg.blockDim = dim3(256); cfg.stream = s;
         cudaLaunchAttribute attr[1];
         if (pdl) { attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1; cfg.attrs = attr; cfg.numAttrs = 1; }
-        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, (const float*)m->logits, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0, 1));
+        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, (const float*)m->logits, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0,
+                                   mail ? mail->useq : (unsigned*)nullptr, (unsigned)L));
         if (prof) { cudaEventRecord(prof->ev[2 * prof->n + 1], s); prof->cls[prof->n] = CLS_SELECT; prof->bytes[prof->n] = 4.0 * n; prof->n++; }
         n_launch++;
     }
@@ -644,6 +523,7 @@ int run_prefill_chunk(atlasx_model* m, int n) {
                 fa.kc = ly.kv->k; fa.vc = ly.kv->v; fa.out = out; fa.pos = m->pf_pos + i;
                 fa.n_heads = m->nh_loc; fa.n_kv = m->nkv_loc; fa.window = ly.window; fa.kv_dtype = cf.kv_dtype;
                 fa.max_splits = m->fused_splits; fa.scale = m->scale; fa.qk_eps = 1e-6f;
+                fa.scratch_partials = m->attn_partials; fa.scratch_tickets = m->attn_tickets;
                 if ((rc = ax_attn_fused_launch(c, fa, false))) return rc;
             } else {
                 AxQkPrepArgs qa;
@@ -657,6 +537,7 @@ int run_prefill_chunk(atlasx_model* m, int n) {
                 aa.pos = m->pf_pos + i; aa.pos_shared = 1; aa.batch = 1;
                 aa.n_heads = m->nh_loc; aa.n_kv = m->nkv_loc; aa.hd = m->hd; aa.window = ly.window;
                 aa.kv_dtype = cf.kv_dtype; aa.scale = m->scale; aa.n_splits = m->attn_splits;
+                aa.scratch_partials = m->attn_partials; aa.scratch_tickets = m->attn_tickets;
                 if ((rc = ax_attn_launch(c, aa, false))) return rc;
             }
         }
@@ -683,7 +564,8 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     if (m->world > 1 && (rc = ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc))) return rc;
     pf_advance_k<<<1, 1, 0, s>>>(m->st, n - 1);
     AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
-    select_advance_k<<<(cf.vocab_size + 1023) / 1024, 256, 0, s>>>(m->logits, cf.vocab_size, sc, m->st, m->seq, cf.max_seq_len + 1, 1, 1);
+    // the chunk used NCCL, not the mailboxes: the use counter stays where it is
+    select_advance_k<<<(cf.vocab_size + 1023) / 1024, 256, 0, s>>>(m->logits, cf.vocab_size, sc, m->st, m->seq, cf.max_seq_len + 1, 1, nullptr, 0u);
     AX_CHECK_LAUNCH("prefill selection");
     m->host_pos += n;
     return ATLASX_OK;
@@ -693,7 +575,7 @@ int capture_graph(atlasx_model* m) {
     atlasx_ctx* c = m->ctx;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
     cudaGraph_t g = nullptr;
-    if (getenv("ATLASX_STEP_TRACE") && !m->step_trace) {
+    if (c->tune.step_trace && !m->step_trace) {
         int r0 = dmalloc(m, (void**)&m->step_trace, 1024 * sizeof(AxTraceSlot));
         if (r0) return r0;
     }
@@ -714,8 +596,7 @@ int step(atlasx_model* m) {
     if (m->host_pos >= m->cfg.max_seq_len)
         return atlasx_fail(ATLASX_ERR_STATE, "position %d is past max_seq_len %d", m->host_pos, m->cfg.max_seq_len);
     int rc;
-    const bool mega = m->mega_ready && m->use_mega;        // one launch per token: a graph adds nothing
-    if (m->use_graph && m->graph && !mega) { AX_CUDA(cudaGraphLaunch(m->graph, m->ctx->stream)); rc = ATLASX_OK; }
+    if (m->use_graph && m->graph) { AX_CUDA(cudaGraphLaunch(m->graph, m->ctx->stream)); rc = ATLASX_OK; }
     else rc = run_step(m, nullptr, true);
     if (!rc) m->host_pos++;
     return rc;
@@ -922,14 +803,14 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     // attention split count fixed for the graph; scratch sized once
     int max_rows = cf.max_seq_len;
     m->attn_splits = ax_attn_pick_splits(c, m->nkv_loc, 1, max_rows);
-    {
-        const char* e = getenv("ATLASX_ATTN_FUSED");      // experiments: 0 keeps the two-launch form
-        m->fused_attn = ax_attn_fused_supported(m->hd, m->nh_loc, m->nkv_loc) && !(e && atoi(e) == 0);
-        m->fused_splits = ax_attn_fused_max_splits(c, m->nkv_loc, max_rows);
-    }
+    m->fused_attn = ax_attn_fused_supported(m->hd, m->nh_loc, m->nkv_loc) && c->tune.attn_fused != 0;
+    m->fused_splits = ax_attn_fused_max_splits(c, m->nkv_loc, max_rows);
     const int scratch_splits = m->fused_attn && m->fused_splits > m->attn_splits ? m->fused_splits : m->attn_splits;
-    rc = atlasx_ctx_ensure_attn_scratch(c, (size_t)m->nh_loc * scratch_splits * (m->hd + 2), (size_t)m->nh_loc);
-    if (rc) return rc;
+    // the model's own scratch: its captured graph holds these pointers, so they must not move when
+    // another model or an operator call on the same context needs more
+    if ((rc = dmalloc(m, (void**)&m->attn_partials, (size_t)m->nh_loc * scratch_splits * (m->hd + 2) * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->attn_tickets, (size_t)m->nh_loc * sizeof(unsigned)))) return rc;
+    AX_CUDA(cudaMemsetAsync(m->attn_tickets, 0, (size_t)m->nh_loc * sizeof(unsigned), s));
     AX_ARG(cf.vocab_size <= 4096 * 1024, "vocabulary too large for the selection scratch");
     m->finalized = true;
     m->host_pos = 0;
@@ -943,15 +824,10 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
         // every consumer CTA polling every part costs world × 8·d bytes of L2 reads per CTA; one more
         // small launch per use is cheaper already with two ranks (466 against 462 tok/s)
         m->mail_reduce = m->mail != nullptr;
-        if (const char* e = getenv("ATLASX_MAIL_REDUCE")) m->mail_reduce = m->mail && atoi(e) != 0;      // experiments
+        if (c->tune.mail_reduce >= 0) m->mail_reduce = m->mail && c->tune.mail_reduce != 0;
         AX_CUDA(cudaMemsetAsync(m->o, 0, (size_t)d * 4, s));
         rc = ax_comm_allreduce_sum(c, m->o, (size_t)d); if (rc) return rc;
         AX_CUDA(cudaStreamSynchronize(s));
-    }
-    {
-        const char* e = getenv("ATLASX_MEGA");
-        if (e) m->use_mega = atoi(e) ? 1 : 0;
-        if (m->use_mega) { rc = build_mega(m); if (rc) return rc; }
     }
     // one eager step loads every kernel before capture; it only touches cache row 0, which the
     // first real token rewrites
@@ -963,7 +839,7 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
         int code = 0;
         rc = atlasx_ctx_poll_device_error(c, &code); if (rc) return rc;
     }
-    if (m->use_graph && !(m->mega_ready && m->use_mega)) { rc = capture_graph(m); if (rc) return rc; }
+    if (m->use_graph) { rc = capture_graph(m); if (rc) return rc; }
     return ATLASX_OK;
 }
 
@@ -995,26 +871,6 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
     return ATLASX_OK;
 }
 
-extern "C" int atlasx_model_set_mega(atlasx_model* m, int on) {
-    AX_ARG(m, "model is null");
-    AX_ARG(!m->finalized, "choose the step kernel before atlasx_model_finalize");
-    m->use_mega = on ? 1 : 0;
-    return ATLASX_OK;
-}
-// Debug aid: per-phase timestamps (ns) of CTA 0 in the last whole-step launch, when the model was
-// finalised with ATLASX_MEGA_TRACE set: wait begin, wait end, input staged, phase done; plus the type.
-extern "C" int atlasx_model_mega_trace(atlasx_model* m, unsigned long long* out, int* types, int cap, int* n_phases) {
-    AX_ARG(m && out && types && n_phases, "null argument");
-    AX_ARG(m->mega_ready && m->margs.trace, "no trace was recorded");
-    const int n = m->margs.n_phases < cap ? m->margs.n_phases : cap;
-    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
-    AX_CUDA(cudaMemcpy(out, m->margs.trace, (size_t)n * 4 * sizeof(unsigned long long), cudaMemcpyDeviceToHost));
-    std::vector<MegaPhase> ph((size_t)n);
-    AX_CUDA(cudaMemcpy(ph.data(), m->phases_dev, (size_t)n * sizeof(MegaPhase), cudaMemcpyDeviceToHost));
-    for (int i = 0; i < n; i++) types[i] = ph[i].type * 100000 + (ph[i].type == MEGA_GEMV ? ph[i].g.M / 128 : 0);
-    *n_phases = n;
-    return ATLASX_OK;
-}
 // Debug aid: runs one captured step and returns, per traced launch, six %globaltimer stamps (ns):
 // first/last CTA start, first dependency release, last CTA end, first CTA end, last input staged.  Needs ATLASX_STEP_TRACE
 // set when the graph was captured.
@@ -1036,7 +892,6 @@ extern "C" int atlasx_model_step_trace(atlasx_model* m, unsigned long long* out,
     *n_slots = n;
     return ATLASX_OK;
 }
-extern "C" int atlasx_model_uses_mega(const atlasx_model* m) { return m && m->mega_ready && m->use_mega; }
 
 extern "C" int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl) {
     AX_ARG(m, "model is null");
@@ -1045,7 +900,7 @@ extern "C" int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_
     if (m->finalized && changed) {
         AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
         if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
-        if (m->use_graph && !(m->mega_ready && m->use_mega)) return capture_graph(m);
+        if (m->use_graph) return capture_graph(m);
     }
     return ATLASX_OK;
 }
@@ -1060,6 +915,22 @@ extern "C" int atlasx_model_reset(atlasx_model* m) {
 }
 extern "C" int atlasx_model_pos(const atlasx_model* m) { return m ? m->host_pos : -1; }
 
+// Bounded device-side waits (peer mailbox polls, bulk-copy barriers) that gave up set the context's
+// error word and let the step run on with whatever was in memory.  The entry points that hand
+// results to the host fetch the word beside their own read-back (queue_wait_status before the
+// host synchronisation, wait_status after it) and fail with ATLASX_ERR_TIMEOUT instead of returning
+// such results.  The word stays set — every later call fails too — until the caller clears it with
+// atlasx_ctx_poll_device_error.
+static int queue_wait_status(atlasx_model* m) {
+    AX_CUDA(cudaMemcpyAsync(m->pin + 1, m->ctx->dev_error, sizeof(int), cudaMemcpyDeviceToHost, m->ctx->stream));
+    return ATLASX_OK;
+}
+static int wait_status(const atlasx_model* m) {
+    const int code = m->pin[1];
+    return code ? atlasx_fail(ATLASX_ERR_TIMEOUT, "a bounded device-side wait expired during the step (code %d): results are not valid; "
+                                                  "clear with atlasx_ctx_poll_device_error", code) : ATLASX_OK;
+}
+
 extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* logits_host) {
     AX_ARG(m && m->finalized, "model is not finalised");
     cudaStream_t s = m->ctx->stream;
@@ -1068,17 +939,19 @@ extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* 
     AX_CUDA(cudaMemcpyAsync(m->seq + m->host_pos, m->pin, 4, cudaMemcpyHostToDevice, s));
     set_state_k<<<1, 1, 0, s>>>(m->st, m->host_pos, INT_MAX);
     int rc = step(m); if (rc) return rc;
+    if ((rc = queue_wait_status(m))) return rc;
     if (logits_host) {
         // through pinned memory: a copy into pageable memory is staged by the driver in small pieces
         const size_t bytes = (size_t)m->cfg.vocab_size * 4;
         if (!m->pin_logits) AX_CUDA(cudaMallocHost((void**)&m->pin_logits, bytes));
         AX_CUDA(cudaMemcpyAsync(m->pin_logits, m->logits, bytes, cudaMemcpyDeviceToHost, s));
-        AX_CUDA(cudaStreamSynchronize(s));
+        if ((rc = ax_comm_stream_sync(m->ctx))) return rc;
+        if ((rc = wait_status(m))) return rc;
         memcpy(logits_host, m->pin_logits, bytes);
         return ATLASX_OK;
     }
-    AX_CUDA(cudaStreamSynchronize(s));
-    return ATLASX_OK;
+    if ((rc = ax_comm_stream_sync(m->ctx))) return rc;
+    return wait_status(m);
 }
 
 extern "C" int atlasx_model_hidden(atlasx_model* m, float* hidden_host) {
@@ -1101,13 +974,18 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
     int rc = atlasx_model_reset(m); if (rc) return rc;
     if (n_prompt > 0) AX_CUDA(cudaMemcpyAsync(m->seq, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s));
     set_state_k<<<1, 1, 0, s>>>(m->st, 0, n_prompt);
-    int *sup_dev = nullptr;
+    struct DevInts {                    // freed on every way out, after the stream has drained
+        int* p = nullptr; cudaStream_t s;
+        ~DevInts() { if (p) { cudaStreamSynchronize(s); cudaFree(p); } }
+    } sup_guard;
+    sup_guard.s = s;
     const bool fix = n_suppress > 0 || rep_penalty != 1.0f;
     if (n_suppress > 0) {
-        AX_CUDA(cudaMalloc((void**)&sup_dev, (size_t)n_suppress * 4));
-        AX_CUDA(cudaMemcpyAsync(sup_dev, suppress, (size_t)n_suppress * 4, cudaMemcpyHostToDevice, s));
+        AX_CUDA(cudaMalloc((void**)&sup_guard.p, (size_t)n_suppress * 4));
+        AX_CUDA(cudaMemcpyAsync(sup_guard.p, suppress, (size_t)n_suppress * 4, cudaMemcpyHostToDevice, s));
     }
-    auto done = [&](int r) { cudaStreamSynchronize(s); cudaFree(sup_dev); return r; };
+    int* const sup_dev = sup_guard.p;
+    auto done = [&](int r) { cudaStreamSynchronize(s); return r; };
     if (n_prompt == 0) {
         // last_logits starts as zeros (:1609): the first choice is made among equal logits
         AX_CUDA(cudaMemsetAsync(m->logits, 0, (size_t)V * 4, s));
@@ -1128,12 +1006,14 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
             if (need_fix)
                 logit_fixups_k<<<1, 32, 0, s>>>(m->logits, V, sup_dev, stepi == 0 ? n_suppress : 0,
                                                 m->seq + n_prompt + start, rep_penalty != 1.0f ? stepi - start : 0, rep_penalty);
-            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0, 0);
+            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0, nullptr, 0u);
             cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return done(atlasx_fail(ATLASX_ERR_CUDA, "selection launch failed: %s", cudaGetErrorString(e)));
         }
         AX_CUDA(cudaMemcpyAsync(m->pin, &m->st->last_token, 4, cudaMemcpyDeviceToHost, s));
-        AX_CUDA(cudaStreamSynchronize(s));
+        if ((rc = queue_wait_status(m))) return rc;
+        if ((rc = ax_comm_stream_sync(c))) return rc;
+        if ((rc = wait_status(m))) return rc;
         const uint32_t tok = (uint32_t)m->pin[0];
         if (m->cfg.eos_token_id >= 0 && tok == (uint32_t)m->cfg.eos_token_id) break;
         bool stop = false;
@@ -1145,27 +1025,36 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
     return done(ATLASX_OK);
 }
 
-extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, float* elapsed_ms, uint32_t* tokens_host) {
-    AX_ARG(m && m->finalized && steps > 0, "bad argument");
-    AX_ARG(m->host_pos + steps <= m->cfg.max_seq_len, "steps run past max_seq_len");
+extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, int lead, float* elapsed_ms, uint32_t* tokens_host) {
+    AX_ARG(m && m->finalized && steps > 0 && lead >= 0, "bad argument");
+    AX_ARG(m->host_pos + lead + steps <= m->cfg.max_seq_len, "steps run past max_seq_len");
     cudaStream_t s = m->ctx->stream;
     const int p0 = m->host_pos;
     set_state_k<<<1, 1, 0, s>>>(m->st, p0, p0, m->seq);      // every token from here on is generated
     cudaEvent_t e0, e1;
     AX_CUDA(cudaEventCreate(&e0)); AX_CUDA(cudaEventCreate(&e1));
     AX_CUDA(cudaStreamSynchronize(s));
-    AX_CUDA(cudaEventRecord(e0, s));
     int rc = ATLASX_OK;
+    // untimed lead-in steps, queued without a host synchronisation before the first event: the ranks
+    // of a tensor-parallel group leave them coupled through their mailboxes, so the timed region
+    // starts at the same moment on every GPU however far apart the hosts got here
+    for (int i = 0; i < lead && !rc; i++) rc = step(m);
+    if (!rc) AX_CUDA(cudaEventRecord(e0, s));
     for (int i = 0; i < steps && !rc; i++) rc = step(m);
     cudaEventRecord(e1, s);
-    cudaError_t e = cudaStreamSynchronize(s);
+    const int rq = queue_wait_status(m);
+    const int rs = ax_comm_stream_sync(m->ctx);
+    cudaError_t e = rs ? cudaSuccess : cudaStreamSynchronize(s);
     float ms = 0.f;
-    cudaEventElapsedTime(&ms, e0, e1);
+    if (!rs) cudaEventElapsedTime(&ms, e0, e1);
     cudaEventDestroy(e0); cudaEventDestroy(e1);
+    if (rs) return rs;
     if (rc) return rc;
     if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "decode failed: %s", cudaGetErrorString(e));
+    if (rq) return rq;
+    if ((rc = wait_status(m))) return rc;
     if (elapsed_ms) *elapsed_ms = ms;
-    if (tokens_host) AX_CUDA(cudaMemcpy(tokens_host, m->seq + p0 + 1, (size_t)steps * 4, cudaMemcpyDeviceToHost));
+    if (tokens_host) AX_CUDA(cudaMemcpy(tokens_host, m->seq + p0 + 1, (size_t)(lead + steps) * 4, cudaMemcpyDeviceToHost));
     return ATLASX_OK;
 }
 
@@ -1177,7 +1066,6 @@ extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, float* elap
 extern "C" int atlasx_model_time_classes(atlasx_model* m, unsigned mask, int iters, float* ms_per_pass, double* bytes_per_pass, int* launches) {
     AX_ARG(m && m->finalized && iters > 0 && ms_per_pass, "bad argument");
     AX_ARG(m->world == 1, "single GPU only");
-    AX_ARG(!(m->mega_ready && m->use_mega), "not available with the whole-step kernel");
     atlasx_ctx* c = m->ctx;
     cudaStream_t s = c->stream;
     AX_CUDA(cudaStreamSynchronize(s));

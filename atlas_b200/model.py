@@ -139,12 +139,10 @@ class OlmoModel:
             self._create(fmt)
         check(_ffi.lib().atlasx_model_set_tensor(self._h, int(layer), int(which), C.c_void_p(ptr), dt, int(bool(on_device))))
 
-    def init_gpu_resources(self, use_graph=True, use_pdl=True, use_mega=False):
-        """:1360-1386.  use_mega=True selects the one-launch persistent step kernel where it applies
-        (single GPU, head_dim 128); the default is the kernel-per-operation step, which is faster."""
+    def init_gpu_resources(self, use_graph=True, use_pdl=True):
+        """:1360-1386"""
         if self._h is None:
             raise AtlasError("no tensors were given")
-        check(_ffi.lib().atlasx_model_set_mega(self._h, int(use_mega)))
         check(_ffi.lib().atlasx_model_set_options(self._h, int(use_graph), int(use_pdl)))
         check(_ffi.lib().atlasx_model_finalize(self._h))
 
@@ -213,11 +211,12 @@ class OlmoModel:
         return out[:n.value].tolist()
 
     # measurement helpers -----------------------------------------------------------------
-    def decode_timed(self, steps):
+    def decode_timed(self, steps, lead=0):
+        """Device time (ms) of `steps` greedy steps and their tokens; `lead` untimed steps run first."""
         ms = C.c_float(0)
-        toks = np.zeros(steps, np.uint32)
-        check(_ffi.lib().atlasx_model_decode_timed(self._h, int(steps), C.byref(ms), toks.ctypes.data))
-        return ms.value, toks
+        toks = np.zeros(lead + steps, np.uint32)
+        check(_ffi.lib().atlasx_model_decode_timed(self._h, int(steps), int(lead), C.byref(ms), toks.ctypes.data))
+        return ms.value, toks[lead:]
 
     def profile_step(self):
         n = 16
@@ -228,10 +227,6 @@ class OlmoModel:
 
     def step_bytes(self, pos):
         return float(_ffi.lib().atlasx_model_step_bytes(self._h, int(pos)))
-
-    @property
-    def uses_mega(self):
-        return bool(_ffi.lib().atlasx_model_uses_mega(self._h))
 
     @property
     def launches_per_step(self):

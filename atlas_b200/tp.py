@@ -59,3 +59,63 @@ def init_comm(ctx, rank, world, broadcast_bytes):
     data = broadcast_bytes(bytes(ident) if rank == 0 else None)
     ident = (C.c_ubyte * 128)(*data)
     _ffi.check(_ffi.lib().atlasx_comm_init(ctx.handle, ident, rank, world))
+
+
+class StepGuard:
+    """Host-side failure detection for a tensor-parallel group (no counterpart in the reference).
+
+    The fused all-reduce makes every decode step a rendezvous of all ranks: a rank that raised,
+    exited or simply never reached the step would leave the others waiting in their mailbox
+    polls until the device-side limit.  The guard moves that discovery to the host, before the
+    launch: every rank counts its steps in a shared key-value store (anything with the
+    `add(key, n) -> int` call of torch.distributed's stores) and, before it launches step s,
+    checks that every peer has announced step s too.  A peer that does not show up within
+    `deadline_s`, or that said goodbye with leave(), ends the step with AtlasError on the ranks
+    that are still there — no kernel or collective is in flight at that point, so the GPU and
+    the context stay usable.
+    """
+
+    def __init__(self, store, rank, world, deadline_s=5.0, prefix="atlasx/tp"):
+        self.store, self.rank, self.world = store, int(rank), int(world)
+        self.deadline_s, self.prefix = float(deadline_s), prefix
+        self.step = 0
+
+    def _key(self, what, r):
+        return "%s/%s/%d" % (self.prefix, what, r)
+
+    def arrive(self):
+        """Announce that this rank is about to run its next step; returns the step number."""
+        self.step = int(self.store.add(self._key("step", self.rank), 1))
+        return self.step
+
+    def leave(self):
+        """Announce that this rank runs no more steps (call between steps, nothing in flight)."""
+        self.store.add(self._key("left", self.rank), 1)
+
+    def check(self, poll_s=0.002):
+        """Block until every peer has announced this rank's current step.  Raises AtlasError naming
+        the ranks that left or did not arrive before the deadline."""
+        import time
+        t_end = time.monotonic() + self.deadline_s
+        while True:
+            late, gone = [], []
+            for r in range(self.world):
+                if r == self.rank:
+                    continue
+                if int(self.store.add(self._key("step", r), 0)) >= self.step:
+                    continue
+                (gone if int(self.store.add(self._key("left", r), 0)) > 0 else late).append(r)
+            if gone:
+                raise _ffi.AtlasError("tensor-parallel rank(s) %s left the group before step %d" % (gone, self.step))
+            if not late:
+                return
+            if time.monotonic() >= t_end:
+                raise _ffi.AtlasError("tensor-parallel rank(s) %s did not reach step %d within %.1f s"
+                                      % (late, self.step, self.deadline_s))
+            time.sleep(poll_s)
+
+    def step_barrier(self):
+        """arrive() + check(): call right before launching a step."""
+        self.arrive()
+        self.check()
+        return self.step

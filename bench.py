@@ -160,13 +160,15 @@ def cpu_reference_model(n_layers, max_seq):
     return m
 
 
-def cpu_baseline_sample():
+def cpu_baseline_sample(context=2049):
     """Bounded sample for the default run: one layer of the model plus lm_head through the
-    oracle's forward_one, all host threads; tokens/s extrapolated to 32 layers."""
+    oracle's forward_one at the benchmark's context length, all host threads; tokens/s
+    extrapolated to 32 layers."""
     from oracle import orc
     cores = os.cpu_count() or 1
     orc.set_threads(cores)
-    m = cpu_reference_model(1, 16)
+    m = cpu_reference_model(1, context + 16)
+    m.seed_context(context)                                 # cache rows below `context` hold seeded values
     m.forward_one(1)                                        # warm-up
     t0 = time.perf_counter(); n = 3
     for i in range(n):
@@ -182,8 +184,8 @@ def cpu_baseline_sample():
     t_layer = max(t_tok - t_head, 1e-9)
     full = 32 * t_layer + t_head
     return {"value": 1.0 / full, "unit": UNIT, "cores": cores, "kind": "port",
-            "sample": "oracle forward_one on 1 of 32 layers + lm_head at pos<4, %d tokens; per-token time = 32*layer + head = %.3f s"
-                      % (n, full)}
+            "sample": "oracle forward_one on 1 of 32 layers + lm_head at pos %d.., %d tokens; per-token time = 32*layer + head = %.3f s"
+                      % (context + 1, n, full)}
 
 
 def run_reference(args, rank):
@@ -197,9 +199,11 @@ def run_reference(args, rank):
         avail_gb = os.sysconf("SC_AVPHYS_PAGES") * os.sysconf("SC_PAGE_SIZE") / 1e9
     except Exception:
         avail_gb = 0
-    steps, warm = args.steps, max(args.warmup, 1)
+    steps, warm = args.steps, max(args.warmup, 3)
+    pos0 = args.prompt + 1 + warm                            # the position the GPU arm's timed region starts at
     if avail_gb > 40:
-        m = cpu_reference_model(32, steps + warm + 8)
+        m = cpu_reference_model(32, pos0 + steps + 8)
+        m.seed_context(args.prompt + 1)                     # cache rows of the context: seeded values instead of an ingested prompt
         for i in range(warm):
             m.forward_one(7 + i)
         t0 = time.perf_counter()
@@ -208,15 +212,18 @@ def run_reference(args, rank):
             tok = orc.argmax(m.forward_one(int(tok)))
         dt = time.perf_counter() - t0
         value = steps / dt
-        sample = "full model, %d greedy tokens from pos %d on %d host threads (OpenMP over output rows)" % (steps, warm, cores)
+        sample = ("full model, %d greedy tokens from pos %d (cache rows below %d seeded) on %d host threads (OpenMP over output rows; "
+                  "the reference's forward_one is single-threaded)" % (steps, pos0, args.prompt + 1, cores))
         ms = dt / steps * 1e3
     else:
-        b = cpu_baseline_sample()
+        b = cpu_baseline_sample(args.prompt + 1)
         value, sample, ms = b["value"], b["sample"] + " (host RAM too small for the full model)", 1e3 / b["value"]
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps, "warmup": warm,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic", "impl": "reference",
-            "config": {"workload": WORKLOAD, "context": "pos %d.." % warm, "l2": "weights (13.77 GB) exceed any cache"},
+            "config": {"workload": WORKLOAD, "context": "pos %d..%d (context of %d tokens, then warm-up)" % (pos0, pos0 + steps, args.prompt + 1),
+                       "kv_cache": "f32 (the reference's format)", "parallelism": "cpu x%d threads" % cores,
+                       "l2": "inputs larger than any cache: 13.77 GB of weights stream per step"},
             "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "gpu_launches": 0}
@@ -269,8 +276,10 @@ def main():
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=3, help="timed regions of --steps tokens taken back to back; the median is reported")
     ap.add_argument("--prompt", type=int, default=2048, help="context length reached before the timed steps")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tp-check", action="store_true", help="N > 1: skip rebuilding the model on one GPU to compare tokens")
     ap.add_argument("--no-pdl", action="store_true", help="launch without programmatic dependent launch")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--profile-layers", type=int, default=0,
@@ -322,7 +331,9 @@ def main():
         _ffi.check(_ffi.lib().atlasx_comm_init(ctx.handle, ident, rank, world))
 
     steps, warm = args.steps, max(args.warmup, 3)
-    max_seq = args.prompt + warm + 2 * steps + 16
+    reps = max(1, args.repeats)
+    lead = 2 if world > 1 else 0                           # untimed lock-step steps in front of every timed region
+    max_seq = args.prompt + warm + reps * (steps + lead) + 2 * steps + 16
     m, mc = build_cuda_model(ab, ctx, max_seq, rank, world)
     if args.no_pdl or args.no_graph:
         m.set_options(use_graph=not args.no_graph, use_pdl=not args.no_pdl)
@@ -345,19 +356,29 @@ def main():
         if dist is not None:
             dist.barrier()
 
+    # The timed region is EXACTLY `steps` tokens between two CUDA events on the launching stream; it
+    # is taken `reps` times back to back (each behind a barrier) and the median region is reported.
+    # The clock sampler starts before the barrier, so that forking it delays no rank inside a region.
     sampler = ClockSampler(local_rank)
-    barrier()
     if rank == 0:
         sampler.start()
+        time.sleep(0.3)
     pos0 = m.pos
-    ms, toks = m.decode_timed(steps)                        # CUDA events on the launching stream
+    all_ms, toks = [], None
+    for _ in range(reps):
+        barrier()
+        ms_r, t_r = m.decode_timed(steps, lead)            # `lead` untimed lock-step steps, then the events
+        if dist is not None:
+            import torch
+            tt = torch.tensor([ms_r], device="cuda")
+            dist.all_reduce(tt, op=dist.ReduceOp.MAX)      # max over ranks
+            ms_r = float(tt.item())
+        all_ms.append(ms_r)
+        if toks is None:
+            toks = t_r
     barrier()
     clocks = sampler.stop() if rank == 0 else None
-    if dist is not None:
-        import torch
-        tt = torch.tensor([ms], device="cuda")
-        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-        ms = float(tt.item())
+    ms = float(np.median(all_ms))
     value = steps / (ms / 1e3)
 
     # end to end through the reference-facing call: token in, logits out, host argmax
@@ -392,12 +413,12 @@ def main():
     g_ms = sum(prof[k]["ms"] for k in gemv)
     g_launch = sum(prof[k]["launches"] for k in gemv)
     eager = g_bytes / (g_ms / 1e3) / 1e9
-    step_bytes = m.step_bytes(pos0 + steps // 2)
+    step_bytes = m.step_bytes(pos0 + (reps * (steps + lead)) // 2)
     # The same launches under the conditions of the timed region: one CUDA graph holding only the
     # GEMV launches of a step, in order, with their programmatic-dependent-launch attributes,
     # replayed between two CUDA events (the attention and selection launches are left out).
     fam_ms, fam_bytes, fam_n = None, None, None
-    if world == 1 and not m.uses_mega:
+    if world == 1:
         fam_ms, fam_bytes, fam_n = m.time_classes(set(gemv), iters=max(8, min(steps, 64)))
     achieved = (fam_bytes / (fam_ms / 1e3) / 1e9) if fam_ms else eager
     roofline = {"bound": "hbm", "kernel": "ax_gemv_stream_kernel<bf16> (all %d GEMV launches of a step)" % g_launch,
@@ -410,7 +431,7 @@ def main():
                                              "launch: includes ~4 us of launch latency per kernel that the decode loop hides"},
                 "traffic": NCU_GEMV_TRAFFIC_PER_LAUNCH if (world == 1 and not PROFILE_LAYERS) else None,
                 "traffic_note": "dram__bytes_read+write per GEMV launch, averaged over the 129 launches of a step from one "
-                                "ncu capture of the same kernels and shapes (profiles/decode_step_kernels_ncu_full_olmo3_7b_arch_2_layers.md); "
+                                "ncu capture of the same kernels and shapes on a 2-layer model; "
                                 "algorithmic: %.2f MB" % (g_bytes / max(g_launch, 1) / 1e6),
                 "step": {"algorithmic_bytes": step_bytes, "achieved": step_bytes * value / 1e9,
                          "frac": step_bytes * value / 1e9 / peak, "frac_of_8000": step_bytes * value / 1e9 / 8000.0},
@@ -421,6 +442,24 @@ def main():
 
     if args.timeline:
         print_timeline(m, mc.n_layers, quiet=(rank != 0))      # every rank runs the extra steps
+    # Parity inside a tensor-parallel run: rank 0 rebuilds the model on its GPU alone (second context,
+    # no communicator) and regenerates the same tokens; the first tokens of the timed region must agree.
+    tp_parity = None
+    if world > 1 and rank == 0 and not args.no_tp_check:
+        ctx1 = ab.Context(local_rank)
+        m1, _ = build_cuda_model(ab, ctx1, max_seq, 0, 1)
+        if args.prefill > 1:
+            m1.set_prefill(args.prefill)
+        m1.generate(prompt, 1, 0.0)
+        m1.decode_timed(warm)
+        _, t1 = m1.decode_timed(min(steps, 32), lead)
+        n_cmp = min(len(t1), len(toks))
+        same = [int(a) == int(b) for a, b in zip(t1[:n_cmp], toks[:n_cmp])]
+        tp_parity = {"tokens_compared": n_cmp, "match_single_gpu": all(same),
+                     "first_mismatch": None if all(same) else same.index(False)}
+        if not all(same):
+            sys.stderr.write("tensor-parallel tokens differ from the single-GPU model at step %d\n" % same.index(False))
+        del m1
     if dist is not None:
         dist.barrier()
         dist.destroy_process_group()
@@ -429,17 +468,19 @@ def main():
     cpu = None
     if not args.no_cpu_baseline and world == 1:
         try:
-            cpu = cpu_baseline_sample()
+            cpu = cpu_baseline_sample(args.prompt + 1)
         except Exception as e:       # the baseline is reported, never required
             cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": "failed: %s" % e}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "context": "pos %d..%d after a %d-token random prompt" % (pos0, pos0 + steps, args.prompt),
+            "config": {"workload": WORKLOAD, "context": "pos %d..%d (context of %d tokens, then warm-up)" % (pos0 + lead, pos0 + lead + steps, args.prompt + 1),
                        "kv_cache": "bf16", "parallelism": "tp%d" % world,
+                       "timing": "median of %d regions of %d steps, CUDA events, max over ranks; regions (ms): %s"
+                                 % (reps, steps, ", ".join("%.2f" % x for x in all_ms)),
                        "l2": "inputs larger than L2: 13.77 GB of weights stream per step"},
             "clocks": clocks, "e2e": e2e, "gpu_launches": m.launches_per_step * steps,
-            "first_tokens": [int(t) for t in toks[:8]], "prompt_ingest": prompt_ingest,
+            "first_tokens": [int(t) for t in toks[:8]], "tp_parity": tp_parity, "prompt_ingest": prompt_ingest,
             "roofline": roofline, "cpu_baseline": cpu}
     if PROFILE_LAYERS:
         line["invalid"] = "profiler case: only %d of 32 layers" % PROFILE_LAYERS

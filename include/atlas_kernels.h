@@ -234,9 +234,11 @@ int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* logits_host
 int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* prompt, int n_prompt, int max_new,
                                  const uint32_t* suppress, int n_suppress, float rep_penalty, int rep_window,
                                  const uint32_t* stops, int n_stops, uint32_t* out_tokens, int* n_out);
-/* device-resident decode for timing: runs `steps` greedy steps from the current state with no
- * host round trip per token; returns the elapsed device time (CUDA events) */
-int atlasx_model_decode_timed(atlasx_model* m, int steps, float* elapsed_ms, uint32_t* tokens_host);
+/* device-resident decode for timing: runs `lead` + `steps` greedy steps from the current state
+ * with no host round trip per token; returns the device time of the last `steps` of them (CUDA
+ * events; the lead-in steps line the ranks of a tensor-parallel group up before the first
+ * event).  tokens_host receives lead + steps tokens. */
+int atlasx_model_decode_timed(atlasx_model* m, int steps, int lead, float* elapsed_ms, uint32_t* tokens_host);
 /* one step outside the graph with an event pair around every kernel: per kernel class
  * (see atlasx_model_class_name) launches, milliseconds and algorithmic HBM bytes */
 int atlasx_model_profile_step(atlasx_model* m, int n_classes_max, int* launches, float* ms, double* bytes, int* n_classes);
@@ -250,10 +252,6 @@ const char* atlasx_model_class_name(int cls);
 double atlasx_model_step_bytes(const atlasx_model* m, int pos);
 int atlasx_model_kernel_launches_per_step(const atlasx_model* m);
 int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
-/* Whole-step persistent kernel (one launch per token; single GPU, head_dim 128, ≤ 4 query heads per
- * KV head).  Off by default (the kernel-per-operation step is faster); call with on = 1 before
- * atlasx_model_finalize to select it. */
-int atlasx_model_set_mega(atlasx_model* m, int on);
 /* Prompt ingestion in chunks: atlasx_model_generate_greedy feeds the prompt `chunk` tokens at a
  * time (2..16) through the multi-column kernels, so the weights stream once per chunk instead of
  * once per token (the reference feeds one token per forward, crates/atlas-model/src/lib.rs:1611-1618).
@@ -261,7 +259,6 @@ int atlasx_model_set_mega(atlasx_model* m, int on);
  * 1 when a weight format or shape is outside what the multi-column kernel covers (f32 weights,
  * K not a multiple of 32, or of 64 for int8).  Call after atlasx_model_finalize. */
 int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective);
-int atlasx_model_uses_mega(const atlasx_model* m);
 /* residual stream after the last forward (d_model floats), for layer-level parity checks */
 int atlasx_model_hidden(atlasx_model* m, float* hidden_host);
 
@@ -280,8 +277,11 @@ int atlasx_comm_init(atlasx_ctx* ctx, const void* id128, int rank, int world);
 int atlasx_comm_world(const atlasx_ctx* ctx);
 /* Diagnostics: launches a mailbox reduction whose data never arrives and reports the device error
  * word after the kernel gave up (code 3 after its 2 s limit).  Shows that an absent peer ends in
- * an error status, not in a hang; the context stays usable.  No reference counterpart. */
-int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code);
+ * an error status, not in a hang; the context stays usable.  keep = 0 clears the word again;
+ * keep != 0 leaves it set, as a real expiry does: atlasx_model_forward_one / _generate_greedy /
+ * _decode_timed then fail with ATLASX_ERR_TIMEOUT until atlasx_ctx_poll_device_error clears it.
+ * No reference counterpart. */
+int atlasx_comm_selftest_wait_expiry(atlasx_ctx* ctx, int* code, int keep);
 /* sum-allreduce of n floats in place on the context stream */
 int atlasx_comm_allreduce(atlasx_ctx* ctx, float* buf_dev, int n);
 

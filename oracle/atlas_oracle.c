@@ -405,6 +405,16 @@ void orc_model_init_reference_random(orc_model* m) {
 void orc_model_set_kv_round_bf16(orc_model* m, int on) { m->kv_round_bf16 = on; }
 void orc_model_reset(orc_model* m) { m->pos = 0; }   /* caches are not cleared, :872-880 */
 int  orc_model_pos(const orc_model* m) { return m->pos; }
+void orc_model_seed_context(orc_model* m, int pos, uint64_t seed) {
+    if (pos < 0) pos = 0;
+    if (pos > m->cfg.max_seq_len) pos = m->cfg.max_seq_len;
+    size_t n = (size_t)pos * m->cfg.n_kv_heads * m->head_dim;
+    for (int l = 0; l < m->cfg.n_layers; l++) {
+        orc_fill_normal_f32(m->layers[l].kc, n, seed, (uint64_t)(2 * l), 1.0f);
+        orc_fill_normal_f32(m->layers[l].vc, n, seed, (uint64_t)(2 * l + 1), 1.0f);
+    }
+    m->pos = pos;
+}
 
 static void linear(orc_w w, const float* x, float* y, size_t out_dim, size_t in_dim) {
     if (w.dtype) orc_linear_bf16((const uint16_t*)w.p, x, y, out_dim, in_dim);

@@ -111,6 +111,10 @@ void       orc_model_init_reference_random(orc_model* m);
 void       orc_model_set_kv_round_bf16(orc_model* m, int on);
 void       orc_model_reset(orc_model* m);                         /* :1389-1392 */
 int        orc_model_pos(const orc_model* m);
+/* Measurement aid (no reference counterpart): pretend `pos` tokens were already processed — the
+ * cache rows [0,pos) of every layer are filled with seeded N(0,1) values and the position is set,
+ * so that a timed forward_one reads as much context as a run that really ingested a prompt. */
+void       orc_model_seed_context(orc_model* m, int pos, uint64_t seed);
 /* forward_one_hooked, :1425-1445.  hidden_out (optional) receives the residual
  * stream after every layer, n_layers × d_model. */
 void       orc_forward_one(orc_model* m, uint32_t token, float* logits, float* hidden_out);

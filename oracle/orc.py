@@ -37,7 +37,8 @@ def build(force=False):
     if force or not os.path.exists(ORACLE_SO) or \
             os.path.getmtime(ORACLE_SO) < os.path.getmtime(os.path.join(HERE, "atlas_oracle.c")):
         subprocess.run(["make", "-C", HERE, "_build/liboracle.so"], check=True, capture_output=True)
-    ref_src = os.environ.get("ATLAS_REF", "/root/reference")
+    # the reference checkout: ATLAS_REF, else a `reference` directory beside this repository
+    ref_src = os.environ.get("ATLAS_REF") or os.path.abspath(os.path.join(HERE, "..", "..", "reference"))
     if os.path.exists(os.path.join(ref_src, "kernels", "matmul.cu")):
         subprocess.run(["make", "-C", HERE, "ref", "REF=" + ref_src], check=True, capture_output=True)
 
@@ -89,6 +90,7 @@ def lib():
     L.orc_model_set_kv_round_bf16.argtypes = [C.c_void_p, C.c_int]
     L.orc_model_reset.argtypes = [C.c_void_p]
     L.orc_model_pos.restype = C.c_int; L.orc_model_pos.argtypes = [C.c_void_p]
+    L.orc_model_seed_context.argtypes = [C.c_void_p, C.c_int, u64]
     L.orc_forward_one.argtypes = [C.c_void_p, C.c_uint32, f32p, f32p]
     L.orc_generate_greedy.restype = C.c_int
     L.orc_generate_greedy.argtypes = [C.c_void_p, C.POINTER(C.c_uint32), C.c_int, C.c_int,
@@ -294,6 +296,10 @@ class OracleModel:
     @property
     def pos(self):
         return lib().orc_model_pos(self._h)
+
+    def seed_context(self, pos, seed=0):
+        """Measurement aid: cache rows [0,pos) filled with seeded N(0,1) values, position set to pos."""
+        lib().orc_model_seed_context(self._h, int(pos), int(seed))
 
     def forward_one(self, token, want_hidden=False):
         logits = np.empty(self.cfg.vocab_size, dtype=np.float32)

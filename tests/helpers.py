@@ -19,7 +19,7 @@ SMALL_SWA = dict(vocab_size=1000, d_model=256, n_layers=4, n_heads=4, n_kv_heads
                  yarn_attn_factor=1.2079441541679836, yarn_beta_fast=32.0, yarn_beta_slow=1.0)
 SMALL_SWA_LAYERS = [1, 1, 1, 0]
 
-# head_dim 128 with two query heads per KV head: the shape class the whole-step kernel covers
+# head_dim 128 with two query heads per KV head: the shape class of the one-launch attention
 HD128 = dict(vocab_size=2000, d_model=512, n_layers=3, n_heads=4, n_kv_heads=2, ffn_hidden=1024,
              max_seq_len=80, rope_theta=500000.0, rms_norm_eps=1e-6, post_norm=1,
              sliding_window=8, rope_scaling=1, yarn_factor=8.0, yarn_orig_max_pos=32,
@@ -87,7 +87,7 @@ def oracle_model(cfg, w, layer_sliding=None, kv_round_bf16=False):
 
 
 def cuda_model(cfg, w, layer_sliding=None, kv_dtype=None, weight_format=None, int4_block=32, ctx=None,
-               use_graph=True, use_pdl=True, use_mega=False):
+               use_graph=True, use_pdl=True):
     import atlas_b200 as ab
     mc = ab.ModelConfig(cfg["vocab_size"], cfg["d_model"], cfg["n_layers"], cfg["n_heads"], cfg["n_kv_heads"],
                         cfg["ffn_hidden"], cfg["max_seq_len"], cfg["rope_theta"], cfg["rms_norm_eps"],
@@ -101,7 +101,7 @@ def cuda_model(cfg, w, layer_sliding=None, kv_dtype=None, weight_format=None, in
     m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.BF16 if kv_dtype is None else kv_dtype,
                      weight_format=weight_format, int4_block=int4_block)
     give(m, w)
-    m.init_gpu_resources(use_graph=use_graph, use_pdl=use_pdl, use_mega=use_mega)
+    m.init_gpu_resources(use_graph=use_graph, use_pdl=use_pdl)
     return m
 
 

@@ -129,6 +129,49 @@ def test_gemv_multi_column(ab, fmt, n, shape):
     assert rel_err(Y[:, 0], y0) <= 1e-5
 
 
+@pytest.mark.parametrize("fmt", ["int8", "int4"])
+@pytest.mark.parametrize("shape", SWEEP + [(100352, 4096)], ids=lambda s: "%dx%d" % s)
+def test_config3_quantised_shapes_all_column_counts(ab, fmt, shape):
+    """BASELINE config 3 in full: the four sweep shapes (lm_head included), weights quantised by the
+    atlas-quant recipe (int8 per row, int4 block 32), N ∈ {1, 4, 8, 16}; every output element against
+    the oracle's dequantise-then-dot product."""
+    M, K = shape
+    w = orc.normal_f32(M * K, 47, M + K, 0.02).reshape(M, K)
+    gm, wo = make(ab, fmt, w)
+    del w
+    for n in (1, 4, 8, 16):
+        X = orc.normal_f32(K * n, 47, 100 + n, 1.0).reshape(K, n)
+        Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+        ref = orc.gemm(wo, X) if n > 1 else orc.linear(wo, X[:, 0]).reshape(M, 1)
+        assert rel_err(Y, ref) <= TOL, n
+    assert ab.Context.default().poll_device_error() == 0
+
+
+@pytest.mark.parametrize("n", [4, 8, 16])
+def test_config3_lm_head_shape_bf16_multi_column(ab, n):
+    M, K = 100352, 4096
+    w16 = orc.normal_bf16(M * K, 48, 1, 0.02).reshape(M, K)
+    X = orc.normal_f32(K * n, 48, n, 1.0).reshape(K, n)
+    Y = ab.GpuMatrix.upload_bf16(w16, M, K).sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+    assert rel_err(Y, orc.gemm(w16, X)) <= TOL
+
+
+@pytest.mark.parametrize("fmt", ["int8", "int4"])
+def test_quantised_gemv_propagates_nan_and_inf_in_the_input(ab, fmt):
+    """A NaN (or inf) in the input vector must not be masked by the integer dot-product path: every
+    output is NaN, as with the float formats (a corrupted activation has to stay visible)."""
+    M, K = 256, 512
+    w = orc.normal_f32(M * K, 49, 1, 0.02).reshape(M, K)
+    gm, _ = make(ab, fmt, w)
+    for bad in (np.nan, np.inf):
+        x = orc.normal_f32(K, 49, 2, 1.0)
+        x[137] = bad
+        y = gm.sgemm_vec(ab.GpuVec.from_slice(x), 1).download()
+        assert np.all(np.isnan(y))
+    x = orc.normal_f32(K, 49, 2, 1.0)
+    assert np.all(np.isfinite(gm.sgemm_vec(ab.GpuVec.from_slice(x), 1).download()))
+
+
 @pytest.mark.parametrize("fmt", ["bf16", "int8", "int4"])
 @pytest.mark.parametrize("n,shape", [(2, (100, 1376)), (5, (100, 1376)), (16, (200, 11008)), (7, (40, 11008)), (13, (1000, 4096))])
 def test_gemv_multi_column_ragged_rows_odd_columns_chunked_k(ab, fmt, n, shape):

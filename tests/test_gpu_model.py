@@ -212,43 +212,48 @@ def test_decode_timed_matches_generate(ab, c1_weights):
     assert m.step_bytes(10) > 0
 
 
+def _requantised(w, fmt):
+    """The weights as the library stores them in format `fmt`, dequantised for the oracle."""
+    def requant(a):
+        if fmt == "f32":
+            return a
+        if fmt == "bf16":
+            return orc.bf16_to_f32((a.view(np.uint32) >> 16).astype(np.uint16)).reshape(a.shape)
+        if fmt == "int8":
+            q, s = orc.int8_quantize(a); return orc.int8_dequantize(q, s)
+        q, s = orc.int4_quantize(a, 32); return orc.int4_dequantize(q, s, a.size, 32).reshape(a.shape)
+    wq = {"embed": w["embed"], "final_norm": w["final_norm"], "lm_head": requant(w["lm_head"]), "layers": []}
+    for L in w["layers"]:
+        Lq = dict(L)
+        for name, _ in helpers.PER_LAYER:
+            Lq[name] = requant(L[name])
+        wq["layers"].append(Lq)
+    return wq
+
+
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
 @pytest.mark.parametrize("fmt", ["f32", "bf16", "int8", "int4"])
-def test_whole_step_kernel_matches_per_operation_step_and_oracle(ab, kv, fmt):
-    """head_dim 128, two query heads per KV head, sliding + full layers, YaRN: the one-launch
-    persistent step kernel, the kernel-per-operation step and the CPU oracle must agree —
-    step-by-step logits and hidden state, then free-running greedy tokens."""
+def test_head_dim_128_one_launch_attention_against_oracle(ab, kv, fmt):
+    """head_dim 128, two query heads per KV head, sliding + full layers, YaRN — the shape class
+    whose QK-norm, RoPE, cache write and attention run as one launch: step-by-step logits and
+    hidden state against the CPU oracle (on the weights as stored), then free-running tokens."""
     cfg = dict(helpers.HD128)
     w = helpers.synth_weights(cfg, seed=21, norm_jitter=0.1)
     code = {"f32": None, "bf16": ab.BF16, "int8": ab.INT8, "int4": ab.INT4}[fmt]
     kvd = ab.F32 if kv == "f32" else ab.BF16
-    mega = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code, use_mega=True)
-    plain = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code, use_mega=False)
-    assert mega.uses_mega and not plain.uses_mega
-    assert mega.launches_per_step == 1
+    m = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code)
+    assert m.launches_per_step == 3 * 5 + 2
+    o = helpers.oracle_model(cfg, _requantised(w, fmt), helpers.HD128_LAYERS, kv_round_bf16=(kv == "bf16"))
     toks = orc.uniform_u32(30, 21, 1, cfg["vocab_size"])
-    o = None
-    if fmt == "f32":
-        o = helpers.oracle_model(cfg, w, helpers.HD128_LAYERS, kv_round_bf16=(kv == "bf16"))
-    # with the bf16 cache a last-bit difference in a new K/V element can flip its rounding, so
-    # the two step kernels agree only to the cache's resolution there
-    tol = 1e-4 if kv == "f32" else 5e-3
+    tol = 1e-3 if kv == "f32" else 1e-2
     for t in toks:
-        a = mega.forward_one_gpu(int(t)); b = plain.forward_one_gpu(int(t))
-        assert np.max(np.abs(a - b)) <= tol
-        assert np.max(np.abs(mega.hidden() - plain.hidden())) <= tol
-        if o is not None:
-            lo = o.forward_one(int(t))
-            assert np.max(np.abs(a - lo)) <= (1e-4 if kv == "f32" else 1e-2)
-    prompt = toks[:12]
-    if kv == "f32":
-        assert mega.generate(prompt, 24, 0.0) == plain.generate(prompt, 24, 0.0)
-    else:
-        assert len(mega.generate(prompt, 24, 0.0)) == 24
-    if o is not None and kv == "f32":
-        assert mega.generate(prompt, 24, 0.0) == o.generate_greedy(prompt, 24).tolist()
-    ms, t1 = mega.decode_timed(10)
-    assert ms > 0 and ab.Context.default().poll_device_error() == 0
+        lo, hid = o.forward_one(int(t), want_hidden=True)
+        assert np.max(np.abs(m.forward_one_gpu(int(t)) - lo)) <= tol
+        assert np.max(np.abs(m.hidden() - hid[-1])) <= tol
+    if kv == "f32" and fmt == "f32":
+        prompt = toks[:12]
+        assert m.generate(prompt, 24, 0.0) == o.generate_greedy(prompt, 24).tolist()
+    assert ab.Context.default().poll_device_error() == 0
 
 
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
@@ -284,8 +289,72 @@ def test_chunked_prompt_ingestion_matches_token_by_token(ab, kv, fmt):
             continue
         assert m.pos == plain.pos - 1
         assert np.max(np.abs(m.forward_one_gpu(int(want[-1])) - want_next)) <= tol
+    # against the CPU oracle (weights as stored, cache rounded as stored): free-running tokens — a
+    # divergence only where the oracle's own top-2 margin is inside twice the logit bound — and
+    # teacher-forced logits after the chunked prompt plus the generated tokens
+    o = helpers.oracle_model(cfg, _requantised(w, fmt), helpers.HD128_LAYERS, kv_round_bf16=(kv == "bf16"))
+    otoks, _, margins = o.generate_greedy(prompt, 10, want_logits=True)
+    m = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code)
+    assert m.set_prefill(16) == 16
+    got = m.generate(prompt, 10, 0.0)
+    if got != otoks.tolist():
+        i = next(j for j in range(10) if got[j] != otoks[j])
+        assert margins[i] <= 2 * LOGIT_TOL, (i, float(margins[i]))
+    o.reset()
+    for t in list(prompt) + got + [got[-1]]:
+        lo = o.forward_one(int(t))
+    assert np.max(np.abs(m.forward_one_gpu(int(got[-1])) - lo)) <= LOGIT_TOL
 
 
 def test_chunked_prompt_ingestion_declines_unsupported_formats(ab, c1_weights):
     m = helpers.cuda_model(helpers.C1, c1_weights, kv_dtype=ab.F32)        # f32 weights
     assert m.set_prefill(16) == 1
+
+
+def test_step_graph_survives_growth_of_the_context_attention_scratch(ab):
+    """A finalised model keeps its split-attention scratch to itself: an operator-level attention call
+    on the same context that needs far more scratch (and so re-allocates the context's) must not
+    disturb the model's captured step graph."""
+    import math
+    cfg = dict(helpers.HD128)
+    w = helpers.synth_weights(cfg, seed=31, norm_jitter=0.1)
+    o = helpers.oracle_model(cfg, w, helpers.HD128_LAYERS)
+    m = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=ab.F32)
+    toks = orc.uniform_u32(40, 31, 1, cfg["vocab_size"])
+    for t in toks[:12]:
+        assert np.max(np.abs(m.forward_one_gpu(int(t)) - o.forward_one(int(t)))) <= 1e-3
+    for batch, nh in ((4, 32), (16, 64)):                      # each call needs more context scratch than the last
+        kv = ab.GpuKvCache(4096, 8, 128, dtype=ab.BF16, batch=batch)
+        q = ab.GpuVec.from_slice(orc.normal_f32(batch * nh * 128, 31, 2, 1.0))
+        kv.decode_attention(q, nh, [4095] * batch, 1.0 / math.sqrt(128), 0).download()
+        for t in toks[12:26] if batch == 4 else toks[26:]:
+            assert np.max(np.abs(m.forward_one_gpu(int(t)) - o.forward_one(int(t)))) <= 1e-3
+    assert ab.Context.default().poll_device_error() == 0
+
+
+def test_expired_device_wait_fails_the_next_model_calls_until_cleared(ab):
+    """Failure detection, host side of it: once a bounded device-side wait has given up (made here by
+    the self-test, whose awaited data never arrives — no fault, the kernel returns by itself), the
+    calls that hand results to the host report it instead of returning what the step computed, and
+    keep doing so until the error word is cleared."""
+    import ctypes as C
+    from atlas_b200 import _ffi
+    cfg = dict(helpers.SMALL_SWA)
+    w = helpers.synth_weights(cfg, seed=33)
+    m = helpers.cuda_model(cfg, w, helpers.SMALL_SWA_LAYERS, kv_dtype=ab.F32)
+    o = helpers.oracle_model(cfg, w, helpers.SMALL_SWA_LAYERS)
+    ctx = ab.Context.default()
+    code = C.c_int(0)
+    _ffi.check(_ffi.lib().atlasx_comm_selftest_wait_expiry(ctx.handle, C.byref(code), 1))
+    assert code.value == 3
+    for _ in range(2):
+        with pytest.raises(ab.AtlasError, match="bounded device-side wait"):
+            m.forward_one_gpu(5)
+    with pytest.raises(ab.AtlasError, match="bounded device-side wait"):
+        m.generate([1, 2, 3], 4, 0.0)
+    with pytest.raises(ab.AtlasError):
+        ctx.poll_device_error()                                 # reports once more and clears
+    assert ctx.poll_device_error() == 0
+    m.reset()
+    for t in (5, 9, 11):
+        assert np.max(np.abs(m.forward_one_gpu(t) - o.forward_one(t))) <= 1e-3

@@ -201,7 +201,7 @@ def test_bounded_device_wait_expires_with_an_error_status_and_leaves_the_context
     ctx = ab.Context.default()
     code = C.c_int(-1)
     t0 = time.time()
-    _ffi.check(_ffi.lib().atlasx_comm_selftest_wait_expiry(ctx.handle, C.byref(code)))
+    _ffi.check(_ffi.lib().atlasx_comm_selftest_wait_expiry(ctx.handle, C.byref(code), 0))
     dt = time.time() - t0
     assert code.value == 3
     assert 1.5 <= dt <= 10.0

@@ -112,3 +112,61 @@ def test_slices_cover_every_tensor_once():
         assert tp.local_dims(mc, world)["vocab"] * world >= mc.vocab_size
     with pytest.raises(ab.AtlasError):
         tp.local_dims(ab.ModelConfig(100, 96, 1, 3, 3, 64, 8), 2)
+
+
+def _guard_worker(rank, world, port, store_port, scenario, out):
+    """Failure made on the host, CPU ranks over gloo: rank 1 skips a step, or leaves between steps;
+    rank 0 must get an error status within the deadline instead of entering the collective."""
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    import torch
+    import torch.distributed as dist
+    import atlas_b200 as ab
+    from atlas_b200 import tp
+    os.environ["MASTER_ADDR"] = "127.0.0.1"; os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    store = dist.TCPStore("127.0.0.1", store_port, world, rank == 0, timeout=datetime.timedelta(seconds=20))
+    guard = tp.StepGuard(store, rank, world, deadline_s=1.0)
+    done, err, waited = 0, "", 0.0
+    try:
+        for s in range(1, 7):
+            if rank == 1 and s == 4:
+                if scenario == "leave":
+                    guard.leave()                   # between steps, nothing in flight
+                else:
+                    time.sleep(3.0)                 # never announces step 4 in time: "skips" it
+                break
+            t0 = time.monotonic()
+            guard.step_barrier()
+            waited = time.monotonic() - t0
+            t = torch.ones(4) * (rank + 1)
+            dist.all_reduce(t)                      # stands for the step's collective
+            assert float(t[0]) == 3.0
+            done = s
+    except ab.AtlasError as e:
+        err = str(e)
+        waited = time.monotonic() - t0
+    out.put((rank, done, err, waited))
+    time.sleep(0.5 if rank == 0 else 0.0)           # rank 0 owns the store: let the peer finish its last reads
+    # no destroy_process_group: it would be a collective with a rank that has gone
+
+
+@pytest.mark.parametrize("scenario", ["skip", "leave"])
+def test_step_guard_turns_a_missing_rank_into_an_error_within_the_deadline(scenario):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port, store_port = _free_port(), _free_port()
+    procs = [ctx.Process(target=_guard_worker, args=(r, 2, port, store_port, scenario, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict((r, (done, err, waited)) for r, done, err, waited in [q.get(timeout=120) for _ in procs])
+    for p in procs:
+        p.join(60)
+    done0, err0, waited0 = res[0]
+    assert done0 == 3 and res[1][0] == 3                      # three good steps on both ranks
+    if scenario == "leave":
+        assert "left the group before step 4" in err0 and waited0 < 1.0     # learnt at once, no deadline needed
+    else:
+        assert "did not reach step 4 within" in err0 and 0.9 <= waited0 < 2.5

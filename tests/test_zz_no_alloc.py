@@ -2,9 +2,9 @@
 allocate device memory while serving (a fully pre-partitioned memory pool, a plugin living
 inside another allocator, a loop where cudaMalloc's implicit synchronisation is unacceptable).
 Its split-K scratch is a fixed array inside the library.  The output must equal that of the
-regular entry point (atlasx_decode_attention, scratch in context memory) within the 1e-3
-attention tolerance of these tests, on two calls in a row: the second call reuses the array
-the first one left behind.  Collected last so that a stop-at-first-failure run has already run
+regular entry point (atlasx_decode_attention, scratch in context memory) and that of the CPU
+oracle within the 1e-3 attention tolerance of these tests, on two calls in a row: the second
+call reuses the array the first one left behind.  Collected last so that a stop-at-first-failure run has already run
 everything else."""
 import ctypes as C
 import math
@@ -28,9 +28,16 @@ def _case(ab, nh, nkv, hd, max_seq, batch, dtype, positions, window, seed):
     fill = L.atlasx_fill_normal_bf16 if dtype == ab.BF16 else L.atlasx_fill_normal_f32
     _ffi.check(fill(ctx.handle, kp, n, seed, 1, 0, 1.0))
     _ffi.check(fill(ctx.handle, vp, n, seed, 2, 0, 1.0))
-    q = ab.GpuVec.from_slice(orc.normal_f32(batch * nh * hd, seed, 3, 1.0))
+    q_host = orc.normal_f32(batch * nh * hd, seed, 3, 1.0)
+    q = ab.GpuVec.from_slice(q_host)
     scale = 1.0 / math.sqrt(hd)
     want = kv.decode_attention(q, nh, positions, scale, window).download()
+    # the regular entry point itself against the CPU oracle fed the same cache contents
+    gen = (lambda st: orc.bf16_to_f32(orc.normal_bf16(n, seed, st, 1.0))) if dtype == ab.BF16 else (lambda st: orc.normal_f32(n, seed, st, 1.0))
+    k_host, v_host = gen(1).reshape(batch, -1), gen(2).reshape(batch, -1)
+    oracle = np.concatenate([orc.decode_attention(q_host[b * nh * hd:(b + 1) * nh * hd], k_host[b], v_host[b], nh, nkv, hd,
+                                                  positions[b], scale, window) for b in range(batch)])
+    assert rel_err(want, oracle) <= 1e-3
     out = ab.GpuVec.zeros(batch * nh * hd)
     pos = np.ascontiguousarray(positions, dtype=np.int32)
     stream = L.atlasx_ctx_stream(ctx.handle)
@@ -41,6 +48,7 @@ def _case(ab, nh, nkv, hd, max_seq, batch, dtype, positions, window, seed):
         got = out.download()
         assert np.all(np.isfinite(got)), call
         assert rel_err(got, want) <= 1e-3, call
+        assert rel_err(got, oracle) <= 1e-3, call
         _ffi.check(L.atlasx_memset(ctx.handle, out.ptr, 0, 4 * out.len))
     return kv
 

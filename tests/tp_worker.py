@@ -37,6 +37,19 @@ def main():
                         layer_types=list(helpers.HD128_LAYERS), sliding_window=cfg["sliding_window"], post_norm=True)
     mc.rope_scaling = ab.Yarn(cfg["yarn_factor"], cfg["yarn_orig_max_pos"], cfg["yarn_attn_factor"],
                               cfg["yarn_beta_fast"], cfg["yarn_beta_slow"])
+    # A first tensor-parallel model with fewer layers runs a few steps on the same context and is
+    # freed: its sequence numbers stay behind in the peer mailboxes, and the model under test must
+    # not take them for its own (the use counter belongs to the mailbox, not to a model).
+    cfg0 = dict(cfg, n_layers=2)
+    mc0 = ab.ModelConfig(cfg0["vocab_size"], cfg0["d_model"], 2, cfg0["n_heads"], cfg0["n_kv_heads"], cfg0["ffn_hidden"],
+                         cfg0["max_seq_len"], cfg0["rope_theta"], cfg0["rms_norm_eps"], layer_types=[1, 0],
+                         sliding_window=cfg0["sliding_window"], post_norm=True)
+    m0 = ab.OlmoModel(mc0, ctx=ctx, kv_dtype=ab.F32, tp_rank=rank, tp_world=world)
+    helpers.give(m0, dict(w, layers=w["layers"][:2]))
+    m0.init_gpu_resources()
+    for tk in range(9):
+        m0.forward_one_gpu(tk)
+    del m0
     m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.F32 if kv == "f32" else ab.BF16, tp_rank=rank, tp_world=world)
     helpers.give(m, w)                       # full tensors: the library keeps this rank's slices
     m.init_gpu_resources()
