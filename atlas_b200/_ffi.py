@@ -10,7 +10,8 @@ import os
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "lib", "libatlas_kernels.so")
 
-F32, BF16, INT8, INT4 = 0, 1, 2, 3
+F32, BF16, INT8, INT4, F16 = 0, 1, 2, 3, 4
+AUTO = -1
 
 T_EMBED, T_FINAL_NORM, T_LM_HEAD = 0, 1, 2
 T_WQ, T_WK, T_WV, T_WO, T_GATE, T_UP, T_DOWN = 10, 11, 12, 13, 14, 15, 16
@@ -31,6 +32,18 @@ class ModelConfigC(C.Structure):
         ("post_norm", C.c_int), ("eos_token_id", C.c_int), ("kv_dtype", C.c_int),
         ("weight_format", C.c_int), ("int4_block", C.c_int), ("tp_rank", C.c_int), ("tp_world", C.c_int),
     ]
+
+
+class SamplingConfigC(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("repetition_penalty", C.c_float), ("repetition_window", C.c_int),
+                ("frequency_penalty", C.c_float), ("presence_penalty", C.c_float), ("top_p", C.c_float),
+                ("top_k", C.c_int), ("min_p", C.c_float)]
+
+
+class LoadStatsC(C.Structure):
+    _fields_ = [("seconds", C.c_double), ("file_bytes_read", C.c_size_t), ("bytes_uploaded", C.c_size_t),
+                ("peak_host_rss_bytes", C.c_size_t), ("n_tensors_used", C.c_int), ("post_norm", C.c_int),
+                ("tied_lm_head", C.c_int), ("weight_format", C.c_int)]
 
 
 _lib = None
@@ -114,11 +127,25 @@ SIGNATURES = {
     "atlasx_model_create": (ci, [vp, C.POINTER(ModelConfigC), vp, pvp]),
     "atlasx_model_free": (ci, [vp]),
     "atlasx_model_set_tensor": (ci, [vp, ci, ci, vp, ci, ci]),
+    "atlasx_model_tensor_slice": (ci, [vp, ci, C.POINTER(sz), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz), C.POINTER(sz), pi]),
+    "atlasx_model_set_tensor_slice": (ci, [vp, ci, ci, vp, ci, ci]),
     "atlasx_model_finalize": (ci, [vp]),
+    "atlasx_safetensors_open": (ci, [C.c_char_p, pvp]),
+    "atlasx_safetensors_close": (ci, [vp]),
+    "atlasx_safetensors_count": (ci, [vp]),
+    "atlasx_safetensors_find": (ci, [vp, C.c_char_p]),
+    "atlasx_safetensors_tensor": (ci, [vp, ci, C.POINTER(C.c_char_p), pi, pi, C.POINTER(sz), C.POINTER(sz)]),
+    "atlasx_safetensors_read": (ci, [vp, ci, sz, sz, sz, sz, ci, vp]),
+    "atlasx_safetensors_write": (ci, [C.c_char_p, ci, vp, vp, vp, vp, vp]),
+    "atlasx_model_load_safetensors": (ci, [vp, vp, ci, C.POINTER(ModelConfigC), vp, pvp, C.POINTER(LoadStatsC)]),
+    "atlasx_config_patch_from_json": (ci, [C.c_char_p, C.POINTER(ModelConfigC), vp, pi]),
+    "atlasx_model_load_dir": (ci, [vp, C.c_char_p, C.POINTER(ModelConfigC), vp, pvp, C.POINTER(LoadStatsC)]),
     "atlasx_model_reset": (ci, [vp]),
     "atlasx_model_pos": (ci, [vp]),
     "atlasx_model_forward_one": (ci, [vp, C.c_uint32, vp]),
     "atlasx_model_generate_greedy": (ci, [vp, vp, ci, ci, vp, ci, cf, ci, vp, ci, vp, pi]),
+    "atlasx_sample_token": (ci, [vp, vp, ci, C.POINTER(SamplingConfigC), ci, vp, ci, vp, ci, C.POINTER(u64), pi, vp]),
+    "atlasx_model_generate_sampling": (ci, [vp, vp, ci, ci, C.POINTER(SamplingConfigC), vp, ci, vp, ci, u64, ci, vp, pi]),
     "atlasx_model_decode_timed": (ci, [vp, ci, ci, C.POINTER(cf), vp]),
     "atlasx_model_profile_step": (ci, [vp, ci, vp, vp, vp, pi]),
     "atlasx_model_class_name": (C.c_char_p, [ci]),

@@ -37,6 +37,15 @@ int  atlasx_fail(int code, const char* fmt, ...);
 // ── context ─────────────────────────────────────────────────────────────────────
 struct atlasx_comm;   // comm.cpp
 
+// scratch of the device sampling pipeline (sampling.cu), sized for the largest vocabulary seen
+struct AxSampleScratch {
+    int cap = 0;
+    float* work = nullptr; float* cval = nullptr; int* cidx = nullptr; float* skey = nullptr; int* sval = nullptr;
+    int* cnt_all = nullptr; int* cnt_win = nullptr;
+    unsigned long long* rng = nullptr; int* token = nullptr;
+    unsigned* list = nullptr; int list_cap = 0;        // suppress list + history of the operator form
+};
+
 struct atlasx_ctx {
     int device = 0;
     int sm_count = 148;
@@ -68,6 +77,7 @@ struct atlasx_ctx {
     int* dev_error = nullptr;          // device
     int* host_pin = nullptr;           // pinned scratch (ints)
     atlasx_comm* comm = nullptr;
+    AxSampleScratch sample;
     // timeline recording (diagnostics): when non-null, the next traced launch stamps six u64
     // at this address — first/last CTA start, first dependency release, last CTA end, first CTA end, last input staged —
     // and the launcher advances the pointer

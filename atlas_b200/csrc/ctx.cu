@@ -10,6 +10,7 @@
 #include "elementwise.cuh"
 #include "gemv.cuh"
 #include "objects.h"
+#include "sampling.cuh"
 
 // ── error text ───────────────────────────────────────────────────────────────────
 static thread_local char g_err[512] = "";
@@ -78,6 +79,7 @@ extern "C" int atlasx_ctx_destroy(atlasx_ctx* c) {
     cudaSetDevice(c->device);
     cudaStreamSynchronize(c->stream);
     atlasx_comm_destroy(c);
+    ax_sample_free_scratch(c);
     cudaFree(c->attn_partials); cudaFree(c->attn_tickets); cudaFree(c->pos_dev); cudaFree(c->split_scratch);
     cudaFree(c->amax_vals); cudaFree(c->amax_idx); cudaFree(c->amax_ticket); cudaFree(c->amax_out);
     cudaFree(c->dev_error); cudaFreeHost(c->host_pin);

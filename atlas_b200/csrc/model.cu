@@ -25,6 +25,8 @@
 #include "elementwise.cuh"
 #include "gemv.cuh"
 #include "objects.h"
+#include "sampling.cuh"
+#include <time.h>
 
 namespace {
 
@@ -612,7 +614,7 @@ extern "C" int atlasx_model_create(atlasx_ctx* ctx, const atlasx_model_config* c
            cfg->vocab_size > 0 && cfg->max_seq_len > 0, "dimensions must be positive");
     AX_ARG(cfg->d_model % cfg->n_heads == 0 && cfg->n_heads % cfg->n_kv_heads == 0, "head counts do not divide");
     AX_ARG(cfg->kv_dtype == ATLASX_BF16 || cfg->kv_dtype == ATLASX_F32, "kv_dtype must be bf16 or f32");
-    AX_ARG(cfg->weight_format >= ATLASX_F32 && cfg->weight_format <= ATLASX_INT4, "unknown weight_format");
+    AX_ARG(cfg->weight_format >= ATLASX_F32 && cfg->weight_format <= ATLASX_INT4, "unknown weight_format (ATLASX_AUTO is for the loaders)");
     const int world = cfg->tp_world > 0 ? cfg->tp_world : 1;
     AX_ARG(cfg->tp_rank >= 0 && cfg->tp_rank < world, "tp_rank out of range");
     AX_ARG(cfg->n_heads % world == 0 && cfg->n_kv_heads % world == 0 && cfg->ffn_hidden % world == 0,
@@ -673,38 +675,69 @@ static int set_vector(atlasx_model* m, float** dst, const void* src_dev, int dty
     return ATLASX_OK;
 }
 
-extern "C" int atlasx_model_set_tensor(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device) {
+namespace {
+// Shape of the full tensor `which` and the part [r0,r0+nr) × [c0,c0+nc) of it this tensor-parallel
+// rank keeps.  whole = 1 when the rank must be handed the full tensor all the same: replicated
+// tensors, and int8 weights that are split by columns (their per-row scale is the maximum over the
+// FULL row, so the row has to be quantised before it is cut).
+struct TensorPart { int rows = 0, cols = 0, r0 = 0, nr = 0, c0 = 0, nc = 0, whole = 1; };
+int tensor_part(const atlasx_model* m, int which, TensorPart* tp) {
+    const atlasx_model_config& cf = m->cfg;
+    const int d = cf.d_model, hd = m->hd, r = m->rank;
+    TensorPart t;
+    auto rows_of = [&](int rows, int cols, int r0, int nr) { t.rows = rows; t.cols = cols; t.r0 = r0; t.nr = nr; t.c0 = 0; t.nc = cols; t.whole = m->world == 1; };
+    auto cols_of = [&](int rows, int cols, int c0, int nc) {
+        t.rows = rows; t.cols = cols; t.r0 = 0; t.nr = rows; t.c0 = c0; t.nc = nc;
+        t.whole = m->world == 1 || cf.weight_format == ATLASX_INT8;
+    };
+    auto all_of = [&](int rows, int cols) { t.rows = rows; t.cols = cols; t.r0 = 0; t.nr = rows; t.c0 = 0; t.nc = cols; t.whole = 1; };
+    switch (which) {
+        case ATLASX_T_EMBED: all_of(cf.vocab_size, d); break;
+        case ATLASX_T_LM_HEAD: {
+            const int r0 = r * m->vocab_loc < cf.vocab_size ? r * m->vocab_loc : cf.vocab_size;
+            int nr = cf.vocab_size - r0; if (nr > m->vocab_loc) nr = m->vocab_loc;
+            rows_of(cf.vocab_size, d, r0, nr); break;
+        }
+        case ATLASX_T_FINAL_NORM: case ATLASX_T_ATTN_NORM: case ATLASX_T_FFN_NORM: all_of(1, d); break;
+        case ATLASX_T_WQ: rows_of(cf.n_heads * hd, d, r * m->q_rows, m->q_rows); break;
+        case ATLASX_T_WK: case ATLASX_T_WV: rows_of(cf.n_kv_heads * hd, d, r * m->kv_rows, m->kv_rows); break;
+        case ATLASX_T_WO: cols_of(d, cf.n_heads * hd, r * m->q_rows, m->q_rows); break;
+        case ATLASX_T_GATE: case ATLASX_T_UP: rows_of(cf.ffn_hidden, d, r * m->ffn_loc, m->ffn_loc); break;
+        case ATLASX_T_DOWN: cols_of(d, cf.ffn_hidden, r * m->ffn_loc, m->ffn_loc); break;
+        case ATLASX_T_Q_NORM: all_of(1, cf.n_heads * hd); break;                    // small: given whole, the slice is cut on the device
+        case ATLASX_T_K_NORM: all_of(1, cf.n_kv_heads * hd); break;
+        default: return atlasx_fail(ATLASX_ERR_ARG, "unknown tensor id %d", which);
+    }
+    *tp = t;
+    return ATLASX_OK;
+}
+
+// is_part: `data` holds exactly the part tensor_part() names (row-major nr × nc) instead of the full tensor.
+int set_tensor_impl(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device, bool is_part) {
     AX_ARG(m && data, "null argument");
     AX_ARG(dtype == ATLASX_F32 || dtype == ATLASX_BF16, "tensors are given as f32 or bf16");
     AX_ARG(!m->finalized, "model already finalised");
     const atlasx_model_config& cf = m->cfg;
-    const int d = cf.d_model, hd = m->hd;
-    int rows = 0, cols = 0;
-    switch (which) {
-        case ATLASX_T_EMBED: case ATLASX_T_LM_HEAD: rows = cf.vocab_size; cols = d; break;
-        case ATLASX_T_FINAL_NORM: case ATLASX_T_ATTN_NORM: case ATLASX_T_FFN_NORM: rows = 1; cols = d; break;
-        case ATLASX_T_WQ: rows = cf.n_heads * hd; cols = d; break;
-        case ATLASX_T_WK: case ATLASX_T_WV: rows = cf.n_kv_heads * hd; cols = d; break;
-        case ATLASX_T_WO: rows = d; cols = cf.n_heads * hd; break;
-        case ATLASX_T_GATE: case ATLASX_T_UP: rows = cf.ffn_hidden; cols = d; break;
-        case ATLASX_T_DOWN: rows = d; cols = cf.ffn_hidden; break;
-        case ATLASX_T_Q_NORM: rows = 1; cols = cf.n_heads * hd; break;
-        case ATLASX_T_K_NORM: rows = 1; cols = cf.n_kv_heads * hd; break;
-        default: return atlasx_fail(ATLASX_ERR_ARG, "unknown tensor id %d", which);
-    }
+    const int d = cf.d_model;
+    TensorPart tp;
+    int rc = tensor_part(m, which, &tp);
+    if (rc) return rc;
     if (which >= ATLASX_T_WQ) AX_ARG(layer >= 0 && layer < cf.n_layers, "layer out of range");
+    if (tp.whole) is_part = false;
+    // the tensor as handed over: the full one, or the rank's part standing in for it
+    const int rows = is_part ? tp.nr : tp.rows, cols = is_part ? tp.nc : tp.cols;
+    const int r0 = is_part ? 0 : tp.r0, c0 = is_part ? 0 : tp.c0;
     const size_t n = (size_t)rows * cols, esz = dtype == ATLASX_BF16 ? 2 : 4;
     cudaStream_t s = m->ctx->stream;
     void* staged = nullptr;
     const void* src = data;
     if (!on_device) {
-        AX_CUDA(cudaMalloc(&staged, n * esz));
+        AX_CUDA(cudaMalloc(&staged, n * esz ? n * esz : 16));
         cudaError_t e = cudaMemcpyAsync(staged, data, n * esz, cudaMemcpyHostToDevice, s);
         if (e == cudaSuccess) e = cudaStreamSynchronize(s);
         if (e != cudaSuccess) { cudaFree(staged); return atlasx_fail(ATLASX_ERR_CUDA, "upload failed: %s", cudaGetErrorString(e)); }
         src = staged;
     }
-    int rc = ATLASX_OK;
     const int r = m->rank;
     Layer* ly = which >= ATLASX_T_WQ ? &m->layers[layer] : nullptr;
     switch (which) {
@@ -714,30 +747,51 @@ extern "C" int atlasx_model_set_tensor(atlasx_model* m, int layer, int which, co
             if (!rc) { m->embed_bf16 = dtype == ATLASX_BF16; cudaMemcpyAsync(m->embed, src, n * esz, cudaMemcpyDeviceToDevice, s); m->have_embed = true; }
             break;
         }
-        case ATLASX_T_LM_HEAD: {
-            const int r0 = r * m->vocab_loc;
-            int nr = cf.vocab_size - r0; if (nr > m->vocab_loc) nr = m->vocab_loc; if (nr < 0) nr = 0;
-            if (nr > 0) rc = place_slice(m, src, dtype, rows, cols, r0, nr, 0, d, m->lm_head, 0, 1);
+        case ATLASX_T_LM_HEAD:
+            if (tp.nr > 0) rc = place_slice(m, src, dtype, rows, cols, r0, tp.nr, 0, d, m->lm_head, 0, 1);
             m->have_lm_head = true;
             break;
-        }
         case ATLASX_T_FINAL_NORM: rc = set_vector(m, &m->final_norm, src, dtype, 0, d); break;
         case ATLASX_T_ATTN_NORM: rc = set_vector(m, &ly->attn_norm, src, dtype, 0, d); break;
         case ATLASX_T_FFN_NORM: rc = set_vector(m, &ly->ffn_norm, src, dtype, 0, d); break;
         case ATLASX_T_Q_NORM: rc = set_vector(m, &ly->q_norm, src, dtype, r * m->q_rows, m->q_rows); break;
         case ATLASX_T_K_NORM: rc = set_vector(m, &ly->k_norm, src, dtype, r * m->kv_rows, m->kv_rows); break;
-        case ATLASX_T_WQ: rc = place_slice(m, src, dtype, rows, cols, r * m->q_rows, m->q_rows, 0, d, ly->qkv, 0, 1); break;
-        case ATLASX_T_WK: rc = place_slice(m, src, dtype, rows, cols, r * m->kv_rows, m->kv_rows, 0, d, ly->qkv, m->q_rows, 1); break;
-        case ATLASX_T_WV: rc = place_slice(m, src, dtype, rows, cols, r * m->kv_rows, m->kv_rows, 0, d, ly->qkv, m->q_rows + m->kv_rows, 1); break;
-        case ATLASX_T_WO: rc = place_slice(m, src, dtype, rows, cols, 0, d, r * m->q_rows, m->q_rows, ly->wo, 0, 1); break;
-        case ATLASX_T_GATE: rc = place_slice(m, src, dtype, rows, cols, r * m->ffn_loc, m->ffn_loc, 0, d, ly->gateup, 0, 2); break;
-        case ATLASX_T_UP: rc = place_slice(m, src, dtype, rows, cols, r * m->ffn_loc, m->ffn_loc, 0, d, ly->gateup, 1, 2); break;
-        case ATLASX_T_DOWN: rc = place_slice(m, src, dtype, rows, cols, 0, d, r * m->ffn_loc, m->ffn_loc, ly->down, 0, 1); break;
+        case ATLASX_T_WQ: rc = place_slice(m, src, dtype, rows, cols, r0, tp.nr, 0, d, ly->qkv, 0, 1); break;
+        case ATLASX_T_WK: rc = place_slice(m, src, dtype, rows, cols, r0, tp.nr, 0, d, ly->qkv, m->q_rows, 1); break;
+        case ATLASX_T_WV: rc = place_slice(m, src, dtype, rows, cols, r0, tp.nr, 0, d, ly->qkv, m->q_rows + m->kv_rows, 1); break;
+        case ATLASX_T_WO: rc = place_slice(m, src, dtype, rows, cols, 0, d, c0, tp.nc, ly->wo, 0, 1); break;
+        case ATLASX_T_GATE: rc = place_slice(m, src, dtype, rows, cols, r0, tp.nr, 0, d, ly->gateup, 0, 2); break;
+        case ATLASX_T_UP: rc = place_slice(m, src, dtype, rows, cols, r0, tp.nr, 0, d, ly->gateup, 1, 2); break;
+        case ATLASX_T_DOWN: rc = place_slice(m, src, dtype, rows, cols, 0, d, c0, tp.nc, ly->down, 0, 1); break;
     }
     if (ly && !rc) ly->have[which - ATLASX_T_WQ] = true;
     cudaStreamSynchronize(s);
     cudaFree(staged);
     return rc;
+}
+}  // namespace
+
+extern "C" int atlasx_model_set_tensor(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device) {
+    return set_tensor_impl(m, layer, which, data, dtype, on_device, false);
+}
+extern "C" int atlasx_model_set_tensor_slice(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device) {
+    return set_tensor_impl(m, layer, which, data, dtype, on_device, true);
+}
+extern "C" int atlasx_model_tensor_slice(const atlasx_model* m, int which, size_t* full_rows, size_t* full_cols,
+                                         size_t* r0, size_t* r1, size_t* c0, size_t* c1, int* whole) {
+    AX_ARG(m, "model is null");
+    TensorPart tp;
+    int rc = tensor_part(m, which, &tp);
+    if (rc) return rc;
+    if (full_rows) *full_rows = (size_t)tp.rows;
+    if (full_cols) *full_cols = (size_t)tp.cols;
+    // what the caller has to hand over: the kept part, or everything
+    if (r0) *r0 = tp.whole ? 0 : (size_t)tp.r0;
+    if (r1) *r1 = tp.whole ? (size_t)tp.rows : (size_t)(tp.r0 + tp.nr);
+    if (c0) *c0 = tp.whole ? 0 : (size_t)tp.c0;
+    if (c1) *c1 = tp.whole ? (size_t)tp.cols : (size_t)(tp.c0 + tp.nc);
+    if (whole) *whole = tp.whole;
+    return ATLASX_OK;
 }
 
 extern "C" int atlasx_model_finalize(atlasx_model* m) {
@@ -1023,6 +1077,79 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         rc = step(m); if (rc) return done(rc);
     }
     return done(ATLASX_OK);
+}
+
+// generate_with_sampling, sampling branch (:1599-1732): the prompt and every step run exactly as in
+// the greedy call; between steps one launch of the sampling kernel picks the next token from the
+// logits on the device (penalties, temperature, top-k, top-p, min-p, one XorShift64 draw) and makes
+// it the input of the next position.  Per token only the 4-byte id crosses to the host (for the
+// EOS / stop test).  temperature ≤ 0 takes the greedy call.
+extern "C" int atlasx_model_generate_sampling(atlasx_model* m, const uint32_t* prompt, int n_prompt, int max_new,
+                                              const atlasx_sampling_config* cfg, const uint32_t* suppress, int n_suppress,
+                                              const uint32_t* stops, int n_stops, uint64_t seed, int seed_from_time,
+                                              uint32_t* out_tokens, int* n_out) {
+    AX_ARG(m && m->finalized && n_out && cfg, "bad argument");
+    if (cfg->temperature <= 0.0f || cfg->temperature < 1e-6f)
+        return atlasx_model_generate_greedy(m, prompt, n_prompt, max_new, suppress, n_suppress, cfg->repetition_penalty,
+                                            cfg->repetition_window, stops, n_stops, out_tokens, n_out);
+    AX_ARG(n_prompt >= 0 && max_new >= 0 && (n_prompt == 0 || prompt) && (max_new == 0 || out_tokens) && n_suppress >= 0, "bad argument");
+    AX_ARG(n_prompt + max_new <= m->cfg.max_seq_len, "prompt + max_new exceeds max_seq_len");
+    AX_ARG(cfg->repetition_window >= 0 && cfg->top_k >= 0, "repetition_window and top_k must not be negative");
+    atlasx_ctx* c = m->ctx;
+    cudaStream_t s = c->stream;
+    const int V = m->cfg.vocab_size;
+    *n_out = 0;
+    int rc = atlasx_model_reset(m); if (rc) return rc;
+    if ((rc = ax_sample_ensure_scratch(c, V))) return rc;
+    AxSampleScratch& sc = c->sample;
+    AX_ARG(n_suppress <= sc.list_cap, "suppress list too long");
+    if ((rc = ax_sample_reset_counts(c, V))) return rc;
+    if (n_suppress) AX_CUDA(cudaMemcpyAsync(sc.list, suppress, (size_t)n_suppress * 4, cudaMemcpyHostToDevice, s));
+    // Rng::from_entropy (:1196-1203) or a fixed seed as Rng::from_seed (:1205-1207)
+    unsigned long long state = seed | 1ull;
+    if (seed_from_time) {
+        struct timespec ts; clock_gettime(CLOCK_REALTIME, &ts);
+        state = ((unsigned long long)ts.tv_sec * 1000000000ull + (unsigned long long)ts.tv_nsec) ^ 0x517cc1b727220a95ull;
+    }
+    AX_CUDA(cudaMemcpyAsync(sc.rng, &state, 8, cudaMemcpyHostToDevice, s));
+    if (n_prompt > 0) AX_CUDA(cudaMemcpyAsync(m->seq, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s));
+    set_state_k<<<1, 1, 0, s>>>(m->st, 0, n_prompt);
+    AX_CUDA(cudaStreamSynchronize(s));                        // `state` and the caller's lists may go out of scope
+    if (n_prompt == 0) AX_CUDA(cudaMemsetAsync(m->logits, 0, (size_t)V * 4, s));      // last_logits starts as zeros (:1609)
+    for (int i = 0; i < n_prompt;) {
+        const int left = n_prompt - i;
+        const int n = (m->prefill_chunk > 1 && left >= 2) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
+        rc = n > 1 ? run_prefill_chunk(m, n) : step(m);
+        if (rc) { cudaStreamSynchronize(s); return rc; }
+        i += n;
+    }
+    AxSampleArgs a = {};
+    a.logits = m->logits; a.n = V; a.cfg = ax_sampling_params(*cfg);
+    a.suppress = sc.list; a.n_suppress = n_suppress;
+    a.hist = nullptr; a.n_hist = 0; a.win_len = 0;
+    a.work = sc.work; a.cval = sc.cval; a.cidx = sc.cidx; a.skey = sc.skey; a.sval = sc.sval;
+    a.cnt_all = sc.cnt_all; a.cnt_win = sc.cnt_win; a.rng = sc.rng; a.token_out = sc.token; a.probs_out = nullptr;
+    a.last_token = &m->st->last_token; a.seq = m->seq; a.pos = &m->st->pos; a.seq_cap = m->cfg.max_seq_len + 1;
+    const int W = cfg->repetition_window;
+    for (int stepi = 0; stepi < max_new; stepi++) {
+        a.step = stepi;
+        a.tok_in = stepi > 0 ? (int)out_tokens[stepi - 1] : -1;               // joins the history and the window …
+        a.tok_out = stepi - 1 - W >= 0 ? (int)out_tokens[stepi - 1 - W] : -1;   // … whose oldest member leaves
+        if ((rc = ax_sample_launch(c, a))) break;
+        AX_CUDA(cudaMemcpyAsync(m->pin, sc.token, 4, cudaMemcpyDeviceToHost, s));
+        if ((rc = queue_wait_status(m))) break;
+        if ((rc = ax_comm_stream_sync(c))) break;
+        if ((rc = wait_status(m))) break;
+        const uint32_t tok = (uint32_t)m->pin[0];
+        if (m->cfg.eos_token_id >= 0 && tok == (uint32_t)m->cfg.eos_token_id) break;
+        bool stop = false;
+        for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
+        if (stop) break;
+        out_tokens[(*n_out)++] = tok;
+        if ((rc = step(m))) break;
+    }
+    cudaStreamSynchronize(s);
+    return rc;
 }
 
 extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, int lead, float* elapsed_ms, uint32_t* tokens_host) {

@@ -1,8 +1,8 @@
 """Host-side mirror of the decode surface of the reference's atlas-model crate
 (crates/atlas-model/src/lib.rs): ModelConfig :58-329, SamplingConfig :1223-1295 and
 OlmoModel {new, init_gpu_resources, reset, forward_one_gpu, generate, generate_with_sampling}
-:1298-1732 — over the fused sm_100a decode step.  Greedy decoding only (temperature ≤ 0), which
-is the path the library accelerates; there is no CPU fallback.
+:1298-1732 — over the fused sm_100a decode step, greedy or with the sampling pipeline on the
+device; there is no CPU fallback.
 """
 import ctypes as C
 from dataclasses import dataclass, field
@@ -68,7 +68,7 @@ class ModelConfig:
 
 @dataclass
 class SamplingConfig:
-    """:1223-1248 (only the fields the greedy branch reads are honoured)."""
+    """:1223-1248"""
     temperature: float = 1.0
     repetition_penalty: float = 1.0
     repetition_window: int = 64
@@ -78,6 +78,30 @@ class SamplingConfig:
     top_k: int = 0
     min_p: float = 0.0
     suppress_initial_tokens: List[int] = field(default_factory=list)
+
+    @classmethod
+    def olmo3(cls):
+        """:1278-1294"""
+        return cls(temperature=0.6, repetition_penalty=1.15, repetition_window=256, frequency_penalty=0.0,
+                   presence_penalty=0.0, top_p=0.95, top_k=50, min_p=0.05, suppress_initial_tokens=[14023])
+
+
+def sampling_struct(config: SamplingConfig):
+    return _ffi.SamplingConfigC(config.temperature, config.repetition_penalty, config.repetition_window, config.frequency_penalty,
+                                config.presence_penalty, config.top_p, config.top_k, config.min_p)
+
+
+def sample_token(logits_dev, n, config: SamplingConfig, step, history, rng_state, ctx=None, probs_dev=None):
+    """One selection of the sampling pipeline from `n` logits on the device (atlasx_sample_token).
+    Returns (token, new rng state)."""
+    ctx = ctx or Context.default()
+    sup = np.ascontiguousarray(config.suppress_initial_tokens, dtype=np.uint32)
+    hist = np.ascontiguousarray(history, dtype=np.uint32)
+    st, tok = C.c_uint64(int(rng_state)), C.c_int(-1)
+    check(_ffi.lib().atlasx_sample_token(ctx.handle, C.c_void_p(int(logits_dev)), int(n), C.byref(sampling_struct(config)), int(step),
+                                         sup.ctypes.data, sup.size, hist.ctypes.data, hist.size, C.byref(st), C.byref(tok),
+                                         C.c_void_p(int(probs_dev)) if probs_dev else None))
+    return tok.value, st.value
 
 
 class OlmoModel:
@@ -95,8 +119,9 @@ class OlmoModel:
         self._h = None
         self._kv_dtype, self._int4_block, self._tp = kv_dtype, int4_block, (tp_rank, tp_world)
 
-    def _create(self, weight_format):
-        cfg = self.config
+    @staticmethod
+    def config_struct(cfg, kv_dtype, weight_format, int4_block, tp_rank, tp_world):
+        """(atlasx_model_config, layer_sliding array or None) for a ModelConfig."""
         c = ModelConfigC()
         c.vocab_size, c.d_model, c.n_layers = cfg.vocab_size, cfg.d_model, cfg.n_layers
         c.n_heads, c.n_kv_heads, c.ffn_hidden, c.max_seq_len = cfg.n_heads, cfg.n_kv_heads, cfg.ffn_hidden, cfg.max_seq_len
@@ -108,12 +133,17 @@ class OlmoModel:
             c.yarn_attn_factor, c.yarn_beta_fast, c.yarn_beta_slow = y.attn_factor, y.beta_fast, y.beta_slow
         c.post_norm = int(cfg.post_norm)
         c.eos_token_id = -1          # EOS is passed with the stop tokens at generate() time (it is a pub field there)
-        c.kv_dtype, c.weight_format, c.int4_block = self._kv_dtype, weight_format, self._int4_block
-        c.tp_rank, c.tp_world = self._tp
+        c.kv_dtype, c.weight_format, c.int4_block = kv_dtype, weight_format, int4_block
+        c.tp_rank, c.tp_world = tp_rank, tp_world
         sliding = None
         if cfg.layer_types:
             assert len(cfg.layer_types) == cfg.n_layers
             sliding = (C.c_int * cfg.n_layers)(*[int(t == LAYER_SLIDING) for t in cfg.layer_types])
+        return c, sliding
+
+    def _create(self, weight_format):
+        cfg = self.config
+        c, sliding = self.config_struct(cfg, self._kv_dtype, weight_format, self._int4_block, *self._tp)
         h = C.c_void_p()
         check(_ffi.lib().atlasx_model_create(self.ctx.handle, C.byref(c), sliding, C.byref(h)))
         self._h = h
@@ -194,10 +224,12 @@ class OlmoModel:
         """:1584-1590"""
         return self.generate_with_sampling(prompt, max_new, SamplingConfig(temperature=temperature))
 
-    def generate_with_sampling(self, prompt, max_new, config: SamplingConfig):
-        """:1599-1732, greedy branch."""
+    def generate_with_sampling(self, prompt, max_new, config: SamplingConfig, seed=None):
+        """:1599-1732.  temperature ≤ 0: the greedy branch.  Otherwise the sampling pipeline runs on the
+        device between steps (only the 4-byte token id is read back per step); the XorShift64 generator is
+        seeded from the clock as the reference does, or from `seed` (Rng::from_seed) for repeatable runs."""
         if not (config.temperature <= 0.0 or config.temperature < 1e-6):
-            raise AtlasError("only greedy decoding (temperature <= 0) runs on the GPU path")
+            return self._generate_sampling(prompt, max_new, config, seed)
         p = np.ascontiguousarray(prompt, dtype=np.uint32)
         sup = np.ascontiguousarray(config.suppress_initial_tokens, dtype=np.uint32)
         stop_list = list(self.extra_stop_tokens) + ([int(self.eos_token_id)] if self.eos_token_id is not None else [])
@@ -208,6 +240,18 @@ class OlmoModel:
             self._h, p.ctypes.data, p.size, int(max_new), sup.ctypes.data, sup.size,
             float(config.repetition_penalty), int(config.repetition_window),
             stops.ctypes.data, stops.size, out.ctypes.data, C.byref(n)))
+        return out[:n.value].tolist()
+
+    def _generate_sampling(self, prompt, max_new, config, seed):
+        p = np.ascontiguousarray(prompt, dtype=np.uint32)
+        sup = np.ascontiguousarray(config.suppress_initial_tokens, dtype=np.uint32)
+        stop_list = list(self.extra_stop_tokens) + ([int(self.eos_token_id)] if self.eos_token_id is not None else [])
+        stops = np.ascontiguousarray(stop_list, dtype=np.uint32)
+        out = np.zeros(max(max_new, 1), np.uint32)
+        n = C.c_int(0)
+        check(_ffi.lib().atlasx_model_generate_sampling(
+            self._h, p.ctypes.data, p.size, int(max_new), C.byref(sampling_struct(config)), sup.ctypes.data, sup.size,
+            stops.ctypes.data, stops.size, int(seed or 0), int(seed is None), out.ctypes.data, C.byref(n)))
         return out[:n.value].tolist()
 
     # measurement helpers -----------------------------------------------------------------

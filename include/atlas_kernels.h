@@ -79,7 +79,9 @@ void atlas_quantize_int4(const float* input, uint8_t* output, float* scale, int 
 #define ATLASX_ERR_TIMEOUT  (-5)   /* a bounded device-side wait ran out */
 #define ATLASX_ERR_STATE    (-6)
 
-enum atlasx_dtype { ATLASX_F32 = 0, ATLASX_BF16 = 1, ATLASX_INT8 = 2, ATLASX_INT4 = 3 };
+enum atlasx_dtype { ATLASX_F32 = 0, ATLASX_BF16 = 1, ATLASX_INT8 = 2, ATLASX_INT4 = 3,
+                    ATLASX_F16 = 4 /* a file dtype only: converted to f32 while loading */ };
+#define ATLASX_AUTO (-1)      /* weight_format for the loaders: bf16 when the file's linear weights are BF16, else f32 */
 
 /* message of the last failing atlasx_* call on this thread ("" if none) */
 const char* atlasx_last_error(void);
@@ -192,6 +194,29 @@ int atlasx_decode_attention_static(void* stream, int kv_dtype, const void* k_dev
                                    const float* q_dev, float* out_dev, int n_heads,
                                    const int* pos_host, float scale, int window);
 
+/* ── SamplingConfig and the sampling pipeline (crates/atlas-model/src/lib.rs:1223-1294, 2581-2717) ── */
+typedef struct {
+    float temperature;          /* <= 0 (or < 1e-6): greedy                      */
+    float repetition_penalty;   /* 1.0 = off                                     */
+    int   repetition_window;
+    float frequency_penalty;    /* 0.0 = off                                     */
+    float presence_penalty;     /* 0.0 = off                                     */
+    float top_p;                /* 1.0 = off                                     */
+    int   top_k;                /* 0 = off                                       */
+    float min_p;                /* 0.0 = off                                     */
+} atlasx_sampling_config;
+/* One selection of generate_with_sampling's sampling branch (:1650-1710) from `n` logits on the device:
+ * first-token suppression (step == 0), repetition / frequency / presence penalties over `history` (the
+ * tokens generated so far; the last repetition_window of them for the repetition penalty), temperature,
+ * top-k, top-p, min-p, softmax, and one draw of the XorShift64 generator whose state *rng_state holds
+ * (Rng :1190-1216; advanced by the call).  Only the token comes back; probs_dev_out (optional, n floats
+ * on the device) receives the final distribution.  The RNG stream, the top-k set and all tie rules are
+ * bit-exact with the reference; probabilities agree to the last bits of expf.  Equal probabilities in
+ * top-p — ordered by an unstable sort in the reference, so unspecified there — keep index order. */
+int atlasx_sample_token(atlasx_ctx* ctx, const float* logits_dev, int n, const atlasx_sampling_config* cfg, int step,
+                        const uint32_t* suppress_host, int n_suppress, const uint32_t* history_host, int n_hist,
+                        uint64_t* rng_state, int* token_out, float* probs_dev_out);
+
 /* ── OlmoModel (crates/atlas-model/src/lib.rs:1298-1732) ───────────────────────── */
 typedef struct {
     int   vocab_size, d_model, n_layers, n_heads, n_kv_heads, ffn_hidden, max_seq_len;
@@ -222,6 +247,15 @@ int atlasx_model_free(atlasx_model* m);
 /* Give the FULL (unsharded) tensor, f32 or bf16 bits, from host (on_device 0) or device
  * memory (1); the model keeps its tensor-parallel slice in its own layout. */
 int atlasx_model_set_tensor(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device);
+/* Tensor-parallel loading without the detour through the full tensor: atlasx_model_tensor_slice
+ * names the rows [r0,r1) × columns [c0,c1) of the full [full_rows × full_cols] tensor `which` that
+ * this rank keeps; atlasx_model_set_tensor_slice takes exactly that part (row-major).  whole = 1
+ * means the rank needs the full tensor (replicated tensors; int8 weights split by columns, whose
+ * per-row scale is defined over the full row): hand it to atlasx_model_set_tensor.  With one rank
+ * every tensor is whole. */
+int atlasx_model_tensor_slice(const atlasx_model* m, int which, size_t* full_rows, size_t* full_cols,
+                              size_t* r0, size_t* r1, size_t* c0, size_t* c1, int* whole);
+int atlasx_model_set_tensor_slice(atlasx_model* m, int layer, int which, const void* data, int dtype, int on_device);
 /* init_gpu_resources (:1360-1386): RoPE tables, KV caches, step graph.  Call once after the tensors. */
 int atlasx_model_finalize(atlasx_model* m);
 int atlasx_model_reset(atlasx_model* m);                                            /* reset :1389 */
@@ -234,6 +268,15 @@ int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* logits_host
 int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* prompt, int n_prompt, int max_new,
                                  const uint32_t* suppress, int n_suppress, float rep_penalty, int rep_window,
                                  const uint32_t* stops, int n_stops, uint32_t* out_tokens, int* n_out);
+/* generate_with_sampling, sampling branch (:1599-1732): as atlasx_model_generate_greedy, with the next token
+ * picked on the device by the pipeline of atlasx_sample_token — only the 4-byte token id crosses to the
+ * host per step.  The generator is seeded as Rng::from_seed(seed) (seed | 1), or from the clock as
+ * Rng::from_entropy does when seed_from_time != 0 (the reference's behaviour for every call).
+ * temperature <= 0 runs the greedy call (repetition penalty and suppression still apply, :1625-1646). */
+int atlasx_model_generate_sampling(atlasx_model* m, const uint32_t* prompt, int n_prompt, int max_new,
+                                   const atlasx_sampling_config* cfg, const uint32_t* suppress, int n_suppress,
+                                   const uint32_t* stops, int n_stops, uint64_t seed, int seed_from_time,
+                                   uint32_t* out_tokens, int* n_out);
 /* device-resident decode for timing: runs `lead` + `steps` greedy steps from the current state
  * with no host round trip per token; returns the device time of the last `steps` of them (CUDA
  * events; the lead-in steps line the ranks of a tensor-parallel group up before the first
@@ -261,6 +304,54 @@ int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
 int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective);
 /* residual stream after the last forward (d_model floats), for layer-level parity checks */
 int atlasx_model_hidden(atlasx_model* m, float* hidden_host);
+
+/* ── safetensors (crates/atlas-model/src/lib.rs: SafetensorsFile :2046-2240, loaders :2283-2570) ──
+ * A file is mapped, not read: opening costs the header only. */
+typedef struct atlasx_safetensors atlasx_safetensors;
+int atlasx_safetensors_open(const char* path, atlasx_safetensors** out);            /* open / from_bytes :2071-2125 */
+int atlasx_safetensors_close(atlasx_safetensors* st);
+int atlasx_safetensors_count(const atlasx_safetensors* st);                         /* len :2133 */
+int atlasx_safetensors_find(const atlasx_safetensors* st, const char* name);        /* index or -1; contains / get_desc :2143-2150 */
+/* descriptor of tensor `index` (header order): name, dtype (ATLASX_F32 / _BF16 / _F16, -1 = a dtype the
+ * path cannot read), number of dimensions, the first four extents (1-padded), bytes in the file */
+int atlasx_safetensors_tensor(const atlasx_safetensors* st, int index, const char** name, int* dtype,
+                              int* n_dims, size_t* dims4, size_t* nbytes);
+/* rows [r0,r1) × columns [c0,c1) of the tensor seen as [product of leading extents × last extent], into host
+ * memory as f32 (get_f32 :2205-2240: F32 as is, BF16 as the upper half of an f32, F16 converted) or as raw
+ * bf16 bits (get_bf16 :2187-2202, BF16 tensors only) */
+int atlasx_safetensors_read(const atlasx_safetensors* st, int index, size_t r0, size_t r1, size_t c0, size_t c1,
+                            int out_dtype, void* dst_host);
+/* the synthetic writer of the reference's tests (build_f32 :2154-2185; same header text), F32 and BF16 tensors;
+ * dims4 holds four extents per tensor */
+int atlasx_safetensors_write(const char* path, int n, const char* const* names, const int* dtypes,
+                             const int* n_dims, const size_t* dims4, const void* const* data_host);
+
+typedef struct {
+    double seconds;               /* open → model finalised */
+    size_t file_bytes_read;       /* bytes of the files this rank touched */
+    size_t bytes_uploaded;        /* host → device */
+    size_t peak_host_rss_bytes;   /* getrusage maximum resident set of the process */
+    int    n_tensors_used;
+    int    post_norm;             /* detected from the tensor names (:2508-2515) */
+    int    tied_lm_head;          /* no lm_head.weight in the files: lm_head = embedding (:2493-2497) */
+    int    weight_format;         /* the format in effect (ATLASX_AUTO resolved) */
+} atlasx_load_stats;
+/* load_model_from_safetensors (:2283-2360) over one or several files: creates the model, places every
+ * known tensor (names :2300-2346; unknown ones ignored; post-norm and a separate lm_head detected from the
+ * names first), finalises it.  BF16 tensors go to the device as stored, F32 as stored, F16 as f32; each
+ * tensor-parallel rank reads only its part; cfg->weight_format INT8 / INT4 quantises on the device while
+ * loading, ATLASX_AUTO follows the file.  cfg->post_norm is overridden by the detection.  stats may be NULL. */
+int atlasx_model_load_safetensors(atlasx_ctx* ctx, const char* const* paths, int n_paths, const atlasx_model_config* cfg,
+                                  const int* layer_sliding, atlasx_model** out, atlasx_load_stats* stats);
+/* patch_config_from_hf_json (:2367-2432): layer_types, sliding_window, rope_scaling (yarn), rope_theta,
+ * rms_norm_eps, eos_token_id — only fields present in the file change; max_seq_len never.
+ * sliding_out (n_layers ints, may be NULL) is filled and *have_layer_types set to the array length when the
+ * file has layer_types. */
+int atlasx_config_patch_from_json(const char* config_json_path, atlasx_model_config* cfg, int* sliding_out, int* have_layer_types);
+/* load_model_from_dir (:2437-2570): config.json overlay when present, the shards named in
+ * model.safetensors.index.json (sorted), else model.safetensors */
+int atlasx_model_load_dir(atlasx_ctx* ctx, const char* dir, const atlasx_model_config* cfg, const int* layer_sliding,
+                          atlasx_model** out, atlasx_load_stats* stats);
 
 /* ── measurement helpers: `iters` launches back to back between two CUDA events on the context
  *    stream; elapsed device time in milliseconds.  GEMV launches rotate over n_mats matrices so

@@ -548,3 +548,142 @@ int orc_generate_greedy(orc_model* m, const uint32_t* prompt, int n_prompt, int 
     free(last); free(work);
     return n_out;
 }
+
+/* ── sampling ──────────────────────────────────────────────────────────────── */
+uint64_t orc_rng_from_seed(uint64_t seed) { return seed | 1u; }
+float orc_rng_next_f32(uint64_t* st) {
+    uint64_t x = *st;
+    x ^= x << 13; x ^= x >> 7; x ^= x << 17;
+    *st = x;
+    return (float)(x >> 33) / (float)(1ull << 31);
+}
+void orc_apply_repetition_penalty(float* logits, size_t n, const uint32_t* toks, int nt, float theta) {
+    repetition_penalty(logits, n, toks, nt, theta);
+}
+void orc_apply_frequency_penalty(float* logits, size_t n, const uint32_t* history, int nh, float penalty) {
+    /* (token, count) pairs in order of first occurrence, one subtraction per distinct token */
+    for (int i = 0; i < nh; i++) {
+        int first = 1;
+        for (int j = 0; j < i; j++) if (history[j] == history[i]) { first = 0; break; }
+        if (!first) continue;
+        size_t count = 0;
+        for (int j = i; j < nh; j++) if (history[j] == history[i]) count++;
+        size_t idx = history[i];
+        if (idx < n) logits[idx] -= penalty * (float)count;
+    }
+}
+void orc_apply_presence_penalty(float* logits, size_t n, const uint32_t* history, int nh, float penalty) {
+    for (int i = 0; i < nh; i++) {
+        int first = 1;
+        for (int j = 0; j < i; j++) if (history[j] == history[i]) { first = 0; break; }
+        size_t idx = history[i];
+        if (first && idx < n) logits[idx] -= penalty;
+    }
+}
+static int cmp_desc_f32(const void* a, const void* b) {
+    float x = *(const float*)a, y = *(const float*)b;
+    return (y > x) - (y < x);
+}
+void orc_apply_top_k(float* logits, size_t n, size_t k) {
+    if (k == 0 || k >= n) return;
+    float* sorted = (float*)malloc(sizeof(float) * n);
+    memcpy(sorted, logits, sizeof(float) * n);
+    qsort(sorted, n, sizeof(float), cmp_desc_f32);
+    float threshold = sorted[k - 1];
+    free(sorted);
+    size_t at_or_above = 0, above = 0;
+    for (size_t i = 0; i < n; i++) { if (logits[i] >= threshold) at_or_above++; if (logits[i] > threshold) above++; }
+    if (at_or_above <= k) {
+        for (size_t i = 0; i < n; i++) if (logits[i] < threshold) logits[i] = -INFINITY;
+    } else {                                   /* ties at the threshold: the first ones in index order are kept */
+        size_t need = k - above, kept = 0;
+        for (size_t i = 0; i < n; i++) {
+            if (logits[i] > threshold) continue;
+            if (logits[i] == threshold && kept < need) { kept++; continue; }
+            logits[i] = -INFINITY;
+        }
+    }
+}
+typedef struct { size_t idx; float p; } orc_ip;
+static int cmp_ip_desc(const void* a, const void* b) {
+    const orc_ip* x = (const orc_ip*)a; const orc_ip* y = (const orc_ip*)b;
+    if (y->p > x->p) return 1;
+    if (y->p < x->p) return -1;
+    return (x->idx > y->idx) - (x->idx < y->idx);
+}
+void orc_apply_top_p(float* logits, size_t n, float p) {
+    if (n == 0) return;
+    float max_l = -INFINITY;
+    for (size_t i = 0; i < n; i++) max_l = fmaxf(max_l, logits[i]);
+    orc_ip* pr = (orc_ip*)malloc(sizeof(orc_ip) * n);
+    float sum = 0.0f;
+    for (size_t i = 0; i < n; i++) { pr[i].idx = i; pr[i].p = expf(logits[i] - max_l); }
+    for (size_t i = 0; i < n; i++) sum += pr[i].p;
+    if (sum <= 0.0f) { free(pr); return; }
+    for (size_t i = 0; i < n; i++) pr[i].p /= sum;
+    qsort(pr, n, sizeof(orc_ip), cmp_ip_desc);
+    float cum = 0.0f; size_t cutoff = n;
+    for (size_t i = 0; i < n; i++) { cum += pr[i].p; if (cum >= p) { cutoff = i + 1; break; } }
+    for (size_t i = cutoff; i < n; i++) logits[pr[i].idx] = -INFINITY;
+    free(pr);
+}
+void orc_apply_min_p(float* logits, size_t n, float min_p) {
+    if (min_p <= 0.0f) return;
+    float max_l = -INFINITY;
+    for (size_t i = 0; i < n; i++) max_l = fmaxf(max_l, logits[i]);
+    float threshold = max_l + logf(min_p);
+    for (size_t i = 0; i < n; i++) if (logits[i] < threshold) logits[i] = -INFINITY;
+}
+size_t orc_sample_from_probs(const float* probs, size_t n, float r) {
+    float cum = 0.0f;
+    for (size_t i = 0; i < n; i++) { cum += probs[i]; if (r < cum) return i; }
+    return n - 1;
+}
+size_t orc_sample_token(const float* last_logits, size_t n, const orc_sampling* cfg, int step,
+                        const uint32_t* suppress, int n_suppress, const uint32_t* history, int n_hist,
+                        uint64_t* rng, float* probs_out) {
+    float* l = (float*)malloc(sizeof(float) * n);
+    memcpy(l, last_logits, sizeof(float) * n);
+    if (step == 0) for (int i = 0; i < n_suppress; i++) if ((size_t)suppress[i] < n) l[suppress[i]] = -INFINITY;
+    if (cfg->repetition_penalty != 1.0f && n_hist > 0) {
+        int start = n_hist > cfg->repetition_window ? n_hist - cfg->repetition_window : 0;
+        repetition_penalty(l, n, history + start, n_hist - start, cfg->repetition_penalty);
+    }
+    size_t next;
+    if (cfg->temperature <= 0.0f || cfg->temperature < 1e-6f) {
+        next = orc_argmax(l, n);
+    } else {
+        if (cfg->frequency_penalty != 0.0f && n_hist > 0) orc_apply_frequency_penalty(l, n, history, n_hist, cfg->frequency_penalty);
+        if (cfg->presence_penalty != 0.0f && n_hist > 0) orc_apply_presence_penalty(l, n, history, n_hist, cfg->presence_penalty);
+        for (size_t i = 0; i < n; i++) l[i] /= cfg->temperature;
+        if (cfg->top_k > 0) orc_apply_top_k(l, n, (size_t)cfg->top_k);
+        if (cfg->top_p < 1.0f) orc_apply_top_p(l, n, cfg->top_p);
+        if (cfg->min_p > 0.0f) orc_apply_min_p(l, n, cfg->min_p);
+        orc_softmax_inplace(l, n);
+        if (probs_out) memcpy(probs_out, l, sizeof(float) * n);
+        next = orc_sample_from_probs(l, n, orc_rng_next_f32(rng));
+    }
+    free(l);
+    return next;
+}
+int orc_generate_sampling(orc_model* m, const uint32_t* prompt, int n_prompt, int max_new, const orc_sampling* cfg,
+                          const uint32_t* suppress, int n_suppress, const uint32_t* stops, int n_stops,
+                          uint64_t seed, uint32_t* out_tokens) {
+    size_t V = (size_t)m->cfg.vocab_size;
+    orc_model_reset(m);
+    uint64_t rng = orc_rng_from_seed(seed);
+    float* last = (float*)calloc(V, sizeof(float));
+    for (int i = 0; i < n_prompt; i++) orc_forward_one(m, prompt[i], last, NULL);
+    int n_out = 0;
+    for (int step = 0; step < max_new; step++) {
+        uint32_t tok = (uint32_t)orc_sample_token(last, V, cfg, step, suppress, n_suppress, out_tokens, n_out, &rng, NULL);
+        if (m->cfg.eos_token_id >= 0 && tok == (uint32_t)m->cfg.eos_token_id) break;
+        int stop = 0;
+        for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = 1;
+        if (stop) break;
+        out_tokens[n_out++] = tok;
+        orc_forward_one(m, tok, last, NULL);
+    }
+    free(last);
+    return n_out;
+}

@@ -128,6 +128,40 @@ int        orc_generate_greedy(orc_model* m, const uint32_t* prompt, int n_promp
                                const uint32_t* stops, int n_stops,
                                uint32_t* out_tokens, float* logits_trace, float* margin_trace);
 
+/* ── sampling (atlas-model/src/lib.rs: Rng :1190-1216, SamplingConfig :1223-1294, primitives
+ *    :2581-2717, generate_with_sampling :1599-1732) ─────────────────────────────────────────── */
+typedef struct {
+    float temperature;          /* ≤ 0 or < 1e-6: greedy */
+    float repetition_penalty;   /* 1.0 = off */
+    int   repetition_window;
+    float frequency_penalty, presence_penalty;
+    float top_p;                /* 1.0 = off */
+    int   top_k;                /* 0 = off */
+    float min_p;                /* 0.0 = off */
+} orc_sampling;
+uint64_t orc_rng_from_seed(uint64_t seed);                       /* Rng::from_seed :1205-1207: seed | 1 */
+float    orc_rng_next_f32(uint64_t* state);                      /* xorshift 13/7/17, top 31 bits / 2^31 :1210-1215 */
+void   orc_apply_repetition_penalty(float* logits, size_t n, const uint32_t* toks, int nt, float theta);   /* :2581-2592 */
+void   orc_apply_frequency_penalty(float* logits, size_t n, const uint32_t* history, int nh, float penalty); /* counts as built at :1662-1670, then :2598-2605 */
+void   orc_apply_presence_penalty(float* logits, size_t n, const uint32_t* history, int nh, float penalty);  /* :1675-1680, :2610-2617 */
+void   orc_apply_top_k(float* logits, size_t n, size_t k);       /* :2657-2686 */
+/* :2625-2655.  The reference orders equal probabilities with an unstable sort (unspecified);
+ * here ties keep index order. */
+void   orc_apply_top_p(float* logits, size_t n, float p);
+void   orc_apply_min_p(float* logits, size_t n, float min_p);    /* :2692-2699 */
+size_t orc_sample_from_probs(const float* probs, size_t n, float r);   /* :2710-2717 */
+/* One selection as generate_with_sampling makes it (:1625-1710) from the logits of the last forward:
+ * step-0 suppression, penalties over `history` (the tokens generated so far), temperature, top-k,
+ * top-p, min-p, softmax, sample with one draw from *rng — or the greedy branch.  probs_out
+ * (optional, n floats) receives the final distribution (sampling branch only). */
+size_t orc_sample_token(const float* last_logits, size_t n, const orc_sampling* cfg, int step,
+                        const uint32_t* suppress, int n_suppress, const uint32_t* history, int n_hist,
+                        uint64_t* rng, float* probs_out);
+/* generate_with_sampling with a fixed seed instead of the system time.  Returns the token count. */
+int    orc_generate_sampling(orc_model* m, const uint32_t* prompt, int n_prompt, int max_new, const orc_sampling* cfg,
+                             const uint32_t* suppress, int n_suppress, const uint32_t* stops, int n_stops,
+                             uint64_t seed, uint32_t* out_tokens);
+
 void orc_set_threads(int n);
 int  orc_get_threads(void);
 

@@ -32,6 +32,18 @@ class OrcConfig(C.Structure):
     ]
 
 
+class OrcSampling(C.Structure):
+    _fields_ = [("temperature", C.c_float), ("repetition_penalty", C.c_float), ("repetition_window", C.c_int),
+                ("frequency_penalty", C.c_float), ("presence_penalty", C.c_float), ("top_p", C.c_float),
+                ("top_k", C.c_int), ("min_p", C.c_float)]
+
+
+def sampling(temperature=1.0, repetition_penalty=1.0, repetition_window=64, frequency_penalty=0.0, presence_penalty=0.0,
+             top_p=1.0, top_k=0, min_p=0.0):
+    """SamplingConfig (defaults of :1250-1263)."""
+    return OrcSampling(temperature, repetition_penalty, repetition_window, frequency_penalty, presence_penalty, top_p, top_k, min_p)
+
+
 def build(force=False):
     """Compile the CPU oracle (and the reference kernels when the checkout is present)."""
     if force or not os.path.exists(ORACLE_SO) or \
@@ -97,6 +109,20 @@ def lib():
                                       C.POINTER(C.c_uint32), C.c_int, C.c_float, C.c_int,
                                       C.POINTER(C.c_uint32), C.c_int,
                                       C.POINTER(C.c_uint32), f32p, f32p]
+    u32p = C.POINTER(C.c_uint32)
+    L.orc_rng_from_seed.restype = u64; L.orc_rng_from_seed.argtypes = [u64]
+    L.orc_rng_next_f32.restype = C.c_float; L.orc_rng_next_f32.argtypes = [C.POINTER(u64)]
+    L.orc_apply_repetition_penalty.argtypes = [f32p, sz, u32p, C.c_int, C.c_float]
+    L.orc_apply_frequency_penalty.argtypes = [f32p, sz, u32p, C.c_int, C.c_float]
+    L.orc_apply_presence_penalty.argtypes = [f32p, sz, u32p, C.c_int, C.c_float]
+    L.orc_apply_top_k.argtypes = [f32p, sz, sz]
+    L.orc_apply_top_p.argtypes = [f32p, sz, C.c_float]
+    L.orc_apply_min_p.argtypes = [f32p, sz, C.c_float]
+    L.orc_sample_from_probs.restype = sz; L.orc_sample_from_probs.argtypes = [f32p, sz, C.c_float]
+    L.orc_sample_token.restype = sz
+    L.orc_sample_token.argtypes = [f32p, sz, C.POINTER(OrcSampling), C.c_int, u32p, C.c_int, u32p, C.c_int, C.POINTER(u64), f32p]
+    L.orc_generate_sampling.restype = C.c_int
+    L.orc_generate_sampling.argtypes = [C.c_void_p, u32p, C.c_int, C.c_int, C.POINTER(OrcSampling), u32p, C.c_int, u32p, C.c_int, u64, u32p]
     L.orc_set_threads.argtypes = [C.c_int]
     L.orc_get_threads.restype = C.c_int
     _lib = L
@@ -254,6 +280,67 @@ def decode_attention(q, kc, vc, n_heads, n_kv, hd, pos, scale, window):
     return out
 
 
+# ── sampling primitives (each returns a new array) ────────────────────────────────
+class Rng:
+    """Rng::from_seed + next_f32 (:1205-1215)."""
+
+    def __init__(self, seed):
+        self.state = C.c_uint64(lib().orc_rng_from_seed(int(seed)))
+
+    def next_f32(self):
+        return float(lib().orc_rng_next_f32(C.byref(self.state)))
+
+
+def _u32(a):
+    return np.ascontiguousarray(a, dtype=np.uint32)
+
+
+def _apply(fn, logits, *args):
+    l = np.array(logits, dtype=np.float32)
+    fn(_p(l, C.c_float), l.size, *args)
+    return l
+
+
+def apply_repetition_penalty(logits, toks, theta):
+    t = _u32(toks); return _apply(lib().orc_apply_repetition_penalty, logits, _p(t, C.c_uint32), t.size, theta)
+
+
+def apply_frequency_penalty(logits, history, penalty):
+    t = _u32(history); return _apply(lib().orc_apply_frequency_penalty, logits, _p(t, C.c_uint32), t.size, penalty)
+
+
+def apply_presence_penalty(logits, history, penalty):
+    t = _u32(history); return _apply(lib().orc_apply_presence_penalty, logits, _p(t, C.c_uint32), t.size, penalty)
+
+
+def apply_top_k(logits, k):
+    return _apply(lib().orc_apply_top_k, logits, int(k))
+
+
+def apply_top_p(logits, p):
+    return _apply(lib().orc_apply_top_p, logits, p)
+
+
+def apply_min_p(logits, min_p):
+    return _apply(lib().orc_apply_min_p, logits, min_p)
+
+
+def sample_from_probs(probs, r):
+    pr = np.ascontiguousarray(probs, dtype=np.float32)
+    return int(lib().orc_sample_from_probs(_p(pr, C.c_float), pr.size, r))
+
+
+def sample_token(last_logits, cfg, step, history, rng, suppress=(), want_probs=False):
+    """One selection of generate_with_sampling (:1625-1710); rng is an orc.Rng (advanced by one draw)."""
+    l = np.ascontiguousarray(last_logits, dtype=np.float32)
+    sup, hist = _u32(suppress), _u32(history)
+    probs = np.zeros(l.size, np.float32) if want_probs else None
+    tok = int(lib().orc_sample_token(_p(l, C.c_float), l.size, C.byref(cfg), int(step), _p(sup, C.c_uint32), sup.size,
+                                     _p(hist, C.c_uint32), hist.size, C.byref(rng.state),
+                                     _p(probs, C.c_float) if probs is not None else None))
+    return (tok, probs) if want_probs else tok
+
+
 # ── model ───────────────────────────────────────────────────────────────────────
 class OracleModel:
     """CPU twin of OlmoModel (forward_one / greedy generate)."""
@@ -325,4 +412,12 @@ class OracleModel:
                                       _p(margins, C.c_float))
         if want_logits:
             return out[:n].copy(), trace[:n], margins[:n]
+        return out[:n].copy()
+
+    def generate_sampling(self, prompt, max_new, cfg, seed, suppress=(), stops=()):
+        """generate_with_sampling (:1599-1732) with Rng::from_seed(seed) in place of the system time."""
+        prompt, sup, stp = _u32(prompt), _u32(suppress), _u32(stops)
+        out = np.zeros(max(max_new, 1), dtype=np.uint32)
+        n = lib().orc_generate_sampling(self._h, _p(prompt, C.c_uint32), prompt.size, max_new, C.byref(cfg),
+                                        _p(sup, C.c_uint32), sup.size, _p(stp, C.c_uint32), stp.size, int(seed), _p(out, C.c_uint32))
         return out[:n].copy()

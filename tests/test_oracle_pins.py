@@ -306,3 +306,178 @@ def test_synthetic_generator_statistics():
     assert not np.array_equal(z[:100], orc.normal_f32(100, 0, 2, 1.0))
     b = orc.normal_bf16(1000, 3, 4, 0.02)
     assert np.array_equal(b, orc.f32_to_bf16_rne(orc.normal_f32(1000, 3, 4, 0.02)))
+
+
+# ── sampling: the reference's own unit expectations (crates/atlas-model/src/lib.rs:2846-2990) plus an
+#    independent numpy restatement of every primitive ─────────────────────────────────────────────
+def test_rng_xorshift_stream():
+    # :2846-2866: values in range and not constant; and the exact stream, recomputed here with
+    # Python integers: state = seed | 1; x ^= x << 13; x ^= x >> 7; x ^= x << 17 (64-bit);
+    # value = (x >> 33) as f32 / 2^31
+    rng = orc.Rng(42)
+    x = 42 | 1
+    seen = set()
+    for _ in range(1000):
+        x ^= (x << 13) & 0xFFFFFFFFFFFFFFFF
+        x ^= x >> 7
+        x ^= (x << 17) & 0xFFFFFFFFFFFFFFFF
+        want = np.float32(np.float32(x >> 33) / np.float32(2 ** 31))
+        v = rng.next_f32()
+        assert v == float(want) and 0.0 <= v < 2.0
+        seen.add(v)
+    assert len(seen) > 900
+    assert orc.Rng(0).state.value == 1                      # from_seed avoids the all-zero state
+
+
+def test_sample_from_probs_basic():
+    # :2869-2876
+    probs = [0.1, 0.2, 0.3, 0.4]
+    assert [orc.sample_from_probs(probs, r) for r in (0.0, 0.05, 0.15, 0.35, 0.95)] == [0, 0, 1, 2, 3]
+    assert orc.sample_from_probs(probs, 1.5) == 3            # past the total: the last index (:2716)
+
+
+def test_penalties_known_answers():
+    # :2881-2900 repetition, :2961-2981 frequency and presence
+    l = orc.apply_repetition_penalty([1.0, 2.0, 3.0, -1.0], [1, 3], 1.5)
+    assert abs(l[1] - 1.333) < 0.01 and abs(l[3] + 1.5) < 0.01 and l[0] == 1.0 and l[2] == 3.0
+    assert l[1] == np.float32(2.0) / np.float32(1.5) and l[3] == np.float32(-1.5)
+    orig = [1.0, 2.0, 3.0, -1.0]
+    assert orc.apply_repetition_penalty(orig, [0, 1, 2, 3], 1.0).tolist() == orig
+    # a token seen twice in the window is penalised twice (:2582 loops over occurrences)
+    assert orc.apply_repetition_penalty([4.0], [0, 0], 2.0)[0] == 1.0
+    l = orc.apply_frequency_penalty([1.0, 2.0, 3.0], [1, 2, 1, 1], 0.5)            # counts (1,3), (2,1)
+    assert abs(l[1] - 0.5) < 0.01 and abs(l[2] - 2.5) < 0.01 and l[0] == 1.0
+    l = orc.apply_presence_penalty([1.0, 2.0, 3.0], [2, 0, 2], 0.5)                # seen {0, 2}
+    assert abs(l[0] - 0.5) < 0.01 and l[1] == 2.0 and abs(l[2] - 2.5) < 0.01
+    assert orc.apply_presence_penalty([1.0], [5, 9], 0.5)[0] == 1.0                # ids past the vocabulary are skipped
+
+
+def test_top_k_top_p_min_p_known_answers():
+    ninf = -np.inf
+    # :2926-2944
+    l = orc.apply_top_k([1.0, 5.0, 3.0, 2.0, 4.0], 3)
+    assert l.tolist() == [ninf, 5.0, 3.0, ninf, 4.0]
+    orig = [1.0, 5.0, 3.0, 2.0, 4.0]
+    assert orc.apply_top_k(orig, 0).tolist() == orig and orc.apply_top_k(orig, 5).tolist() == orig
+    # ties at the threshold: exactly k survive, the first ones in index order (:2670-2684)
+    assert orc.apply_top_k([2.0, 7.0, 2.0, 2.0, 1.0], 3).tolist() == [2.0, 7.0, 2.0, ninf, ninf]
+    # :2903-2923
+    l = orc.apply_top_p([-1.0, 0.0, 0.7, 1.7], 0.5)
+    assert l[3] > ninf and int(np.sum(l == ninf)) >= 1
+    assert l.tolist() == [ninf, ninf, ninf, np.float32(1.7)]                       # p(token 3) ≈ 0.60 ≥ 0.5 alone
+    assert np.all(orc.apply_top_p([1.0, 2.0, 3.0, 4.0], 1.0) > ninf)
+    # :2947-2958
+    l = orc.apply_min_p([10.0, 0.0, -5.0, 9.0], 0.1)
+    assert l.tolist() == [10.0, ninf, ninf, 9.0]
+
+
+def _np_pipeline(logits, cfg, step, history, suppress, r):
+    """numpy restatement of the sampling branch (:1650-1710), written from the reference text
+    independently of the C oracle: f32 throughout, sequential sums."""
+    f = np.float32
+    l = np.array(logits, dtype=np.float32)
+    if step == 0:
+        for t in suppress:
+            if t < l.size:
+                l[t] = -np.inf
+    if cfg.repetition_penalty != 1.0 and len(history):
+        for t in history[max(0, len(history) - cfg.repetition_window):]:
+            if t < l.size:
+                l[t] = l[t] / f(cfg.repetition_penalty) if l[t] > 0 else l[t] * f(cfg.repetition_penalty)
+    if cfg.frequency_penalty != 0.0 and len(history):
+        for t in dict.fromkeys(history):
+            if t < l.size:
+                l[t] = l[t] - f(cfg.frequency_penalty) * f(list(history).count(t))
+    if cfg.presence_penalty != 0.0 and len(history):
+        for t in sorted(set(history)):
+            if t < l.size:
+                l[t] = l[t] - f(cfg.presence_penalty)
+    l = l / f(cfg.temperature)
+    k = cfg.top_k
+    if 0 < k < l.size:
+        thr = np.sort(l)[::-1][k - 1]
+        if np.sum(l >= thr) <= k:
+            l[l < thr] = -np.inf
+        else:
+            need = k - int(np.sum(l > thr))
+            ties = np.flatnonzero(l == thr)
+            l[l < thr] = -np.inf
+            l[ties[need:]] = -np.inf
+
+    def seqsum(a):
+        s = f(0.0)
+        for v in a:
+            s = f(s + v)
+        return s
+    if cfg.top_p < 1.0:
+        e = np.exp((l - l.max()).astype(np.float32)).astype(np.float32)
+        s = seqsum(e)
+        if s > 0:
+            pr = (e / s).astype(np.float32)
+            order = sorted(range(l.size), key=lambda i: (-pr[i], i))
+            cum, cut = f(0.0), l.size
+            for j, i in enumerate(order):
+                cum = f(cum + pr[i])
+                if cum >= f(cfg.top_p):
+                    cut = j + 1
+                    break
+            for i in order[cut:]:
+                l[i] = -np.inf
+    if cfg.min_p > 0.0:
+        l[l < f(l.max() + np.log(f(cfg.min_p)))] = -np.inf
+    e = np.exp((l - l.max()).astype(np.float32)).astype(np.float32)
+    pr = (e * f(f(1.0) / seqsum(e))).astype(np.float32)
+    cum = f(0.0)
+    for i, p in enumerate(pr):
+        cum = f(cum + p)
+        if f(r) < cum:
+            return i, pr
+    return l.size - 1, pr
+
+
+@pytest.mark.parametrize("case", ["olmo3", "plain", "penalties", "top_p_only", "min_p_only", "top_k_ties"])
+def test_sampling_pipeline_matches_numpy_restatement(case):
+    cfgs = {"olmo3": orc.sampling(0.6, 1.15, 256, 0.0, 0.0, 0.95, 50, 0.05),        # SamplingConfig::olmo3 (:1278-1294)
+            "plain": orc.sampling(1.0), "penalties": orc.sampling(0.8, 1.3, 4, 0.2, 0.4, 1.0, 0, 0.0),
+            "top_p_only": orc.sampling(1.2, top_p=0.7), "min_p_only": orc.sampling(0.9, min_p=0.2),
+            "top_k_ties": orc.sampling(1.0, top_k=5)}
+    cfg = cfgs[case]
+    n = 997
+    hist = [int(t) for t in orc.uniform_u32(40, 77, 1, 60)]
+    for trial in range(25):
+        logits = orc.normal_f32(n, 77, 10 + trial, 2.0)
+        if case == "top_k_ties":
+            logits = np.round(logits)                        # many exact ties around the k-th value
+        rng = orc.Rng(1000 + trial)
+        probe = orc.Rng(1000 + trial)
+        r = probe.next_f32()
+        step = 0 if trial % 5 == 0 else trial
+        tok, probs = orc.sample_token(logits, cfg, step, hist[:trial * 2], rng, suppress=[3, 14023], want_probs=True)
+        want_tok, want_probs = _np_pipeline(logits, cfg, step, hist[:trial * 2], [3, 14023], r)
+        assert rng.state.value == probe.state.value          # exactly one draw
+        # the survivor set is bit-exact; probabilities agree to a few ulp (numpy's exp vs libm's expf)
+        assert np.array_equal(probs > 0, want_probs > 0)
+        assert np.max(np.abs(probs - want_probs)) <= 1e-6
+        assert tok == want_tok
+
+
+def test_sampling_config_defaults_and_olmo3():
+    # :2984-3010
+    import atlas_b200 as ab
+    c = ab.SamplingConfig()
+    assert (c.repetition_penalty, c.top_p, c.top_k, c.min_p, c.temperature) == (1.0, 1.0, 0, 0.0, 1.0)
+    c = ab.SamplingConfig.olmo3()
+    assert abs(c.temperature - 0.6) < 0.01 and abs(c.repetition_penalty - 1.15) < 0.01 and abs(c.top_p - 0.95) < 0.01
+    assert c.top_k == 50 and abs(c.min_p - 0.05) < 0.01 and c.repetition_window == 256 and c.frequency_penalty == 0.0
+    assert c.suppress_initial_tokens == [14023]
+
+
+def test_greedy_branch_of_sample_token_equals_generate_greedy():
+    m = _tiny()
+    want = m.generate_greedy([0, 1], 8, rep_penalty=1.3, rep_window=4)
+    got = m.generate_sampling([0, 1], 8, orc.sampling(0.0, 1.3, 4), seed=5)
+    assert np.array_equal(want, got)
+    a = m.generate_sampling([0, 1], 12, orc.sampling(1.0, top_k=20), seed=5)
+    b = m.generate_sampling([0, 1], 12, orc.sampling(1.0, top_k=20), seed=5)
+    c = m.generate_sampling([0, 1], 12, orc.sampling(1.0, top_k=20), seed=6)
+    assert np.array_equal(a, b) and not np.array_equal(a, c) and a.size == 12

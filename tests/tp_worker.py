@@ -50,9 +50,15 @@ def main():
     for tk in range(9):
         m0.forward_one_gpu(tk)
     del m0
-    m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.F32 if kv == "f32" else ab.BF16, tp_rank=rank, tp_world=world)
-    helpers.give(m, w)                       # full tensors: the library keeps this rank's slices
-    m.init_gpu_resources()
+    if len(sys.argv) > 4:
+        # from a safetensors file: each rank maps the file and reads only its rows / columns
+        m = ab.load_model_from_safetensors(sys.argv[4], mc, ctx=ctx, kv_dtype=ab.F32 if kv == "f32" else ab.BF16,
+                                           weight_format={"auto": ab.AUTO, "int8": ab.INT8, "int4": ab.INT4}[sys.argv[5]],
+                                           tp_rank=rank, tp_world=world)
+    else:
+        m = ab.OlmoModel(mc, ctx=ctx, kv_dtype=ab.F32 if kv == "f32" else ab.BF16, tp_rank=rank, tp_world=world)
+        helpers.give(m, w)                   # full tensors: the library keeps this rank's slices
+        m.init_gpu_resources()
     toks = orc.uniform_u32(n_tok, 33, 1, cfg["vocab_size"])
     logits = np.stack([m.forward_one_gpu(int(tk)) for tk in toks])
     m.reset()
