@@ -5,6 +5,6 @@ from .tensor import (Context, GpuKvCache, GpuMatrix, GpuRopeTables, GpuVec, devi
                      qk_norm_inplace_gpu, rope_tables, silu_mul_gpu)
 from .quant import INT4_BLOCK_SIZE, Int4Tensor, Int8Tensor  # noqa: F401
 from .model import LAYER_FULL, LAYER_SLIDING, ModelConfig, OlmoModel, SamplingConfig, Yarn, sample_token  # noqa: F401
-from .infer import InferEngine  # noqa: F401
+from .infer import InferEngine, PheromoneDeposit, StigmergicHook  # noqa: F401
 from .safetensors import (LoadStats, SafetensorsFile, TensorDesc, load_model_from_dir, load_model_from_safetensors,  # noqa: F401
                           patch_config_from_hf_json)

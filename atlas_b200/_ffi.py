@@ -46,6 +46,8 @@ class LoadStatsC(C.Structure):
                 ("tied_lm_head", C.c_int), ("weight_format", C.c_int)]
 
 
+LAYER_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_float))
+
 _lib = None
 
 vp, sz, u64, ci, cf = C.c_void_p, C.c_size_t, C.c_uint64, C.c_int, C.c_float
@@ -155,6 +157,9 @@ SIGNATURES = {
     "atlasx_model_set_prefill": (ci, [vp, ci, vp]),
     "atlasx_model_time_classes": (ci, [vp, C.c_uint, ci, vp, vp, vp]),
     "atlasx_model_hidden": (ci, [vp, vp]),
+    "atlasx_model_layer_hidden": (ci, [vp, ci, vp]),
+    "atlasx_model_set_layer_hook": (ci, [vp, vp, vp]),
+    "atlasx_model_deposits": (ci, [vp, vp, vp, vp, ci, pi]),
     "atlasx_time_gemv": (ci, [vp, vp, ci, vp, ci, vp, ci, C.POINTER(cf)]),
     "atlasx_time_attention": (ci, [vp, vp, vp, vp, ci, vp, cf, ci, ci, C.POINTER(cf)]),
     "atlasx_comm_unique_id": (ci, [vp]),

@@ -72,7 +72,16 @@ struct atlasx_model {
     float *resid[2] = { nullptr, nullptr }, *qkv = nullptr, *attn = nullptr, *o = nullptr, *h = nullptr, *dn = nullptr;
     float *logits_loc = nullptr, *logits = nullptr;
     int* seq = nullptr; StepState* st = nullptr;
-    int final_resid = 0;                         // which resid buffer holds the stream after a step
+    // Residual stream: resid[0] holds the embedding of the token, resid[1] the stream after each
+    // attention sub-layer, taps[l] the stream after layer l — one buffer per layer instead of a
+    // ping-pong pair, so that every layer's output survives the step and can be handed to a hook.
+    float* taps = nullptr;                       // [n_layers][d_model]
+    // per-layer hook (StigmergicHook, crates/atlas-infer/src/hook.rs): the taps of a forward are copied to
+    // pinned host memory behind it and the hook runs on the host while the next forward executes
+    atlasx_layer_hook hook_fn = nullptr; void* hook_user = nullptr;
+    float* tap_host[2] = { nullptr, nullptr }; cudaEvent_t tap_ev[2] = { nullptr, nullptr };
+    int tap_k = 0; bool tap_pending = false; long long tap_tok[2] = { -1, -1 };
+    std::vector<uint32_t> dep_tok, dep_fired; std::vector<float> dep_delta;
     int host_pos = 0;
     bool finalized = false;
     int use_graph = 1, use_pdl = 1;
@@ -285,7 +294,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     auto P = [&](int cls) { return pdl && ((c->tune.pdl_mask >> cls) & 1); };
     const int d = cf.d_model, L = cf.n_layers;
     const bool post = cf.post_norm != 0;
-    int rc = ATLASX_OK, n_launch = 0, cur = 0;
+    int rc = ATLASX_OK, n_launch = 0;
     const int nparts = 1;                                  // partial sums are reduced by the collective …
     // … unless the ranks push them into each other's mailboxes: then the consumer's prologue
     // waits for the sequence number of (step, layer) and adds the parts itself, in rank order
@@ -313,14 +322,14 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         if (l == 0) {
             p.embed = m->embed; p.embed_bf16 = m->embed_bf16; p.vocab = cf.vocab_size;
             p.seq = m->seq; p.pos = &m->st->pos;
-            p.resid_out = m->resid[0]; cur = 0;
+            p.resid_out = m->resid[0];
             if (!post) p.wx = ly.attn_norm;
         } else {
-            p.base = m->resid[cur]; p.y = m->dn; p.nparts = nparts; p.part_stride = d;
+            p.base = m->resid[1]; p.y = m->dn; p.nparts = nparts; p.part_stride = d;
             if (mail) peer_in(p, 1, l - 1);
             p.base_early = 1;                              // written by the gate/up launch, two kernels back
             if (post) p.wy = m->layers[l - 1].ffn_norm; else p.wx = ly.attn_norm;
-            p.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+            p.resid_out = m->taps + (size_t)(l - 1) * d;                         // output of layer l−1
         }
         STEP_LAUNCH(CLS_QKV, gemv_bytes(ly.qkv), ax_gemv_launch(c, ly.qkv, p, AX_EPI_PLAIN, 1, m->qkv, P(CLS_QKV)));
 
@@ -377,11 +386,11 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         // ── gate/up with SwiGLU epilogue ────────────────────────────────────────
         AxPrologue pg;
         pg.eps = cf.rms_norm_eps;
-        pg.base = m->resid[cur]; pg.y = m->o; pg.nparts = nparts; pg.part_stride = d;
+        pg.base = l == 0 ? m->resid[0] : m->taps + (size_t)(l - 1) * d; pg.y = m->o; pg.nparts = nparts; pg.part_stride = d;
         if (mail) peer_in(pg, 0, l);
         pg.base_early = 1;                                 // written by the QKV launch, at least two kernels back
         if (post) pg.wy = ly.attn_norm; else pg.wx = ly.ffn_norm;
-        pg.resid_out = m->resid[cur ^ 1]; cur ^= 1;
+        pg.resid_out = m->resid[1];
         STEP_LAUNCH(CLS_GATEUP, gemv_bytes(ly.gateup), ax_gemv_launch(c, ly.gateup, pg, AX_EPI_SILU_PAIR, 1, m->h, P(CLS_GATEUP)));
 
         // ── down projection (row-parallel under TP) ─────────────────────────────
@@ -400,13 +409,12 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     // ── final norm + lm_head ────────────────────────────────────────────────────
     AxPrologue pl;
     pl.eps = cf.rms_norm_eps;
-    pl.base = m->resid[cur]; pl.y = m->dn; pl.nparts = nparts; pl.part_stride = d;
+    pl.base = m->resid[1]; pl.y = m->dn; pl.nparts = nparts; pl.part_stride = d;
     if (mail) peer_in(pl, 1, L - 1);
     pl.base_early = 1;
     if (post) pl.wy = m->layers[L - 1].ffn_norm;
     pl.wx = m->final_norm;
-    pl.resid_out = m->resid[cur ^ 1]; cur ^= 1;
-    m->final_resid = cur;
+    pl.resid_out = m->taps + (size_t)(L - 1) * d;
     STEP_LAUNCH(CLS_LMHEAD, gemv_bytes(m->lm_head), ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, P(CLS_LMHEAD)));
     if (m->world > 1)
         STEP_LAUNCH(CLS_COMM, 4.0 * m->vocab_loc * m->world, ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc));
@@ -561,7 +569,7 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     pl.eps = cf.rms_norm_eps;
     pl.base = m->pf_r + (size_t)(n - 1) * d;
     pl.wx = m->final_norm;
-    pl.resid_out = m->resid[m->final_resid];
+    pl.resid_out = m->taps + (size_t)(L - 1) * d;
     if ((rc = ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, false))) return rc;
     if (m->world > 1 && (rc = ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc))) return rc;
     pf_advance_k<<<1, 1, 0, s>>>(m->st, n - 1);
@@ -604,7 +612,74 @@ int step(atlasx_model* m) {
     return rc;
 }
 
+// ── per-layer hook ───────────────────────────────────────────────────────────────────
+// Runs the hook over the layer outputs of the forward whose taps were copied into host buffer k
+// (the reference's accumulate, crates/atlas-infer/src/hook.rs:60-67: negative deltas count as 0).
+int run_hooks(atlasx_model* m, int k) {
+    AX_CUDA(cudaEventSynchronize(m->tap_ev[k]));
+    const int L = m->cfg.n_layers, d = m->cfg.d_model;
+    float acc = 0.f; uint32_t fired = 0;
+    for (int l = 0; l < L; l++) {
+        float delta = 0.f;
+        if (m->hook_fn(m->hook_user, l, m->tap_host[k] + (size_t)l * d, d, &delta)) { acc += delta > 0.f ? delta : 0.f; fired++; }
+    }
+    if (m->tap_tok[k] >= 0) { m->dep_tok.push_back((uint32_t)m->tap_tok[k]); m->dep_delta.push_back(acc); m->dep_fired.push_back(fired); }
+    return ATLASX_OK;
+}
+// One forward inside generate: the step, then — with a hook attached — the copy of its layer outputs
+// to the host, and the hook calls of the PREVIOUS forward while this one runs on the GPU.
+// tok: the generated token this forward processes (−1 for a prompt token: hook results are dropped).
+int gen_step(atlasx_model* m, long long tok) {
+    int rc = step(m);
+    if (rc || !m->hook_fn) return rc;
+    const int k = m->tap_k;
+    AX_CUDA(cudaMemcpyAsync(m->tap_host[k], m->taps, (size_t)m->cfg.n_layers * m->cfg.d_model * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    AX_CUDA(cudaEventRecord(m->tap_ev[k], m->ctx->stream));
+    m->tap_tok[k] = tok;
+    if (m->tap_pending && (rc = run_hooks(m, k ^ 1))) return rc;
+    m->tap_pending = true; m->tap_k = k ^ 1;
+    return ATLASX_OK;
+}
+int flush_hooks(atlasx_model* m) {
+    if (!m->hook_fn || !m->tap_pending) return ATLASX_OK;
+    m->tap_pending = false;
+    return run_hooks(m, m->tap_k ^ 1);
+}
+
 }  // namespace
+
+// StigmergicHook on the GPU path (crates/atlas-infer/src/hook.rs:31-33; the reference runs hooked
+// generation on its CPU model, engine.rs:144-162).  fn = NULL detaches.
+extern "C" int atlasx_model_set_layer_hook(atlasx_model* m, atlasx_layer_hook fn, void* user) {
+    AX_ARG(m && m->finalized, "model is not finalised");
+    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    m->hook_fn = fn; m->hook_user = user; m->tap_pending = false; m->tap_k = 0;
+    if (fn && !m->tap_host[0]) {
+        const size_t bytes = (size_t)m->cfg.n_layers * m->cfg.d_model * 4;
+        for (int k = 0; k < 2; k++) {
+            AX_CUDA(cudaMallocHost((void**)&m->tap_host[k], bytes));
+            AX_CUDA(cudaEventCreateWithFlags(&m->tap_ev[k], cudaEventDisableTiming));
+        }
+    }
+    return ATLASX_OK;
+}
+extern "C" int atlasx_model_deposits(atlasx_model* m, uint32_t* token_ids, float* total_delta, uint32_t* layers_fired, int cap, int* n) {
+    AX_ARG(m && n, "null argument");
+    const int have = (int)m->dep_tok.size();
+    *n = have;
+    for (int i = 0; i < have && i < cap; i++) {
+        if (token_ids) token_ids[i] = m->dep_tok[(size_t)i];
+        if (total_delta) total_delta[i] = m->dep_delta[(size_t)i];
+        if (layers_fired) layers_fired[i] = m->dep_fired[(size_t)i];
+    }
+    return ATLASX_OK;
+}
+extern "C" int atlasx_model_layer_hidden(atlasx_model* m, int layer, float* hidden_host) {
+    AX_ARG(m && m->finalized && hidden_host && layer >= 0 && layer < m->cfg.n_layers, "bad argument");
+    AX_CUDA(cudaMemcpyAsync(hidden_host, m->taps + (size_t)layer * m->cfg.d_model, (size_t)m->cfg.d_model * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
+    return ATLASX_OK;
+}
 
 extern "C" const char* atlasx_model_class_name(int cls) { return (cls >= 0 && cls < CLS_COUNT) ? kClassNames[cls] : ""; }
 
@@ -662,6 +737,7 @@ extern "C" int atlasx_model_free(atlasx_model* m) {
     if (m->graph) cudaGraphExecDestroy(m->graph);
     for (Layer& ly : m->layers) if (ly.kv) atlasx_kvcache_free(ly.kv);
     for (void* p : m->owned) cudaFree(p);
+    for (int k = 0; k < 2; k++) { if (m->tap_host[k]) cudaFreeHost(m->tap_host[k]); if (m->tap_ev[k]) cudaEventDestroy(m->tap_ev[k]); }
     if (m->pin) cudaFreeHost(m->pin);
     if (m->pin_logits) cudaFreeHost(m->pin_logits);
     delete m;
@@ -840,6 +916,7 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     const size_t vocab_pad = (size_t)m->vocab_loc * m->world;
     if ((rc = dmalloc(m, (void**)&m->resid[0], (size_t)d * 4))) return rc;
     if ((rc = dmalloc(m, (void**)&m->resid[1], (size_t)d * 4))) return rc;
+    if ((rc = dmalloc(m, (void**)&m->taps, (size_t)cf.n_layers * d * 4))) return rc;
     if ((rc = dmalloc(m, (void**)&m->qkv, (size_t)(m->q_rows + 2 * m->kv_rows) * 4))) return rc;
     if ((rc = dmalloc(m, (void**)&m->attn, (size_t)m->q_rows * 4))) return rc;
     if ((rc = dmalloc(m, (void**)&m->o, (size_t)d * 4))) return rc;
@@ -993,6 +1070,13 @@ extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* 
     AX_CUDA(cudaMemcpyAsync(m->seq + m->host_pos, m->pin, 4, cudaMemcpyHostToDevice, s));
     set_state_k<<<1, 1, 0, s>>>(m->st, m->host_pos, INT_MAX);
     int rc = step(m); if (rc) return rc;
+    if (m->hook_fn) {                     // forward_one_gpu_hooked (:1524-1557): the hook sees every layer's output of this token
+        m->tap_pending = false;
+        AX_CUDA(cudaMemcpyAsync(m->tap_host[0], m->taps, (size_t)m->cfg.n_layers * m->cfg.d_model * 4, cudaMemcpyDeviceToHost, s));
+        AX_CUDA(cudaEventRecord(m->tap_ev[0], s));
+        m->tap_tok[0] = -1;
+        if ((rc = run_hooks(m, 0))) return rc;
+    }
     if ((rc = queue_wait_status(m))) return rc;
     if (logits_host) {
         // through pinned memory: a copy into pageable memory is staged by the driver in small pieces
@@ -1010,7 +1094,8 @@ extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* 
 
 extern "C" int atlasx_model_hidden(atlasx_model* m, float* hidden_host) {
     AX_ARG(m && m->finalized && hidden_host, "bad argument");
-    AX_CUDA(cudaMemcpyAsync(hidden_host, m->resid[m->final_resid], (size_t)m->cfg.d_model * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
+    AX_CUDA(cudaMemcpyAsync(hidden_host, m->taps + (size_t)(m->cfg.n_layers - 1) * m->cfg.d_model, (size_t)m->cfg.d_model * 4,
+                            cudaMemcpyDeviceToHost, m->ctx->stream));
     AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
     return ATLASX_OK;
 }
@@ -1026,6 +1111,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
     const int V = m->cfg.vocab_size;
     *n_out = 0;
     int rc = atlasx_model_reset(m); if (rc) return rc;
+    m->dep_tok.clear(); m->dep_delta.clear(); m->dep_fired.clear(); m->tap_pending = false;
     if (n_prompt > 0) AX_CUDA(cudaMemcpyAsync(m->seq, prompt, (size_t)n_prompt * 4, cudaMemcpyHostToDevice, s));
     set_state_k<<<1, 1, 0, s>>>(m->st, 0, n_prompt);
     struct DevInts {                    // freed on every way out, after the stream has drained
@@ -1039,15 +1125,16 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         AX_CUDA(cudaMemcpyAsync(sup_guard.p, suppress, (size_t)n_suppress * 4, cudaMemcpyHostToDevice, s));
     }
     int* const sup_dev = sup_guard.p;
-    auto done = [&](int r) { cudaStreamSynchronize(s); return r; };
+    auto done = [&](int r) { cudaStreamSynchronize(s); const int rh = flush_hooks(m); return r ? r : rh; };
     if (n_prompt == 0) {
         // last_logits starts as zeros (:1609): the first choice is made among equal logits
         AX_CUDA(cudaMemsetAsync(m->logits, 0, (size_t)V * 4, s));
     }
     for (int i = 0; i < n_prompt;) {
         const int left = n_prompt - i;
-        const int n = (m->prefill_chunk > 1 && left >= 2) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
-        rc = n > 1 ? run_prefill_chunk(m, n) : step(m);
+        // with a hook every prompt token is a forward of its own: the hook sees each token's layers
+        const int n = (m->prefill_chunk > 1 && left >= 2 && !m->hook_fn) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
+        rc = n > 1 ? run_prefill_chunk(m, n) : gen_step(m, -1);
         if (rc) return done(rc);
         i += n;
     }
@@ -1074,7 +1161,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
         if (stop) break;
         out_tokens[(*n_out)++] = tok;
-        rc = step(m); if (rc) return done(rc);
+        rc = gen_step(m, (long long)tok); if (rc) return done(rc);
     }
     return done(ATLASX_OK);
 }
@@ -1100,6 +1187,7 @@ extern "C" int atlasx_model_generate_sampling(atlasx_model* m, const uint32_t* p
     const int V = m->cfg.vocab_size;
     *n_out = 0;
     int rc = atlasx_model_reset(m); if (rc) return rc;
+    m->dep_tok.clear(); m->dep_delta.clear(); m->dep_fired.clear(); m->tap_pending = false;
     if ((rc = ax_sample_ensure_scratch(c, V))) return rc;
     AxSampleScratch& sc = c->sample;
     AX_ARG(n_suppress <= sc.list_cap, "suppress list too long");
@@ -1118,8 +1206,8 @@ extern "C" int atlasx_model_generate_sampling(atlasx_model* m, const uint32_t* p
     if (n_prompt == 0) AX_CUDA(cudaMemsetAsync(m->logits, 0, (size_t)V * 4, s));      // last_logits starts as zeros (:1609)
     for (int i = 0; i < n_prompt;) {
         const int left = n_prompt - i;
-        const int n = (m->prefill_chunk > 1 && left >= 2) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
-        rc = n > 1 ? run_prefill_chunk(m, n) : step(m);
+        const int n = (m->prefill_chunk > 1 && left >= 2 && !m->hook_fn) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
+        rc = n > 1 ? run_prefill_chunk(m, n) : gen_step(m, -1);
         if (rc) { cudaStreamSynchronize(s); return rc; }
         i += n;
     }
@@ -1146,10 +1234,11 @@ extern "C" int atlasx_model_generate_sampling(atlasx_model* m, const uint32_t* p
         for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
         if (stop) break;
         out_tokens[(*n_out)++] = tok;
-        if ((rc = step(m))) break;
+        if ((rc = gen_step(m, (long long)tok))) break;
     }
     cudaStreamSynchronize(s);
-    return rc;
+    const int rh = flush_hooks(m);
+    return rc ? rc : rh;
 }
 
 extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, int lead, float* elapsed_ms, uint32_t* tokens_host) {
@@ -1196,7 +1285,7 @@ extern "C" int atlasx_model_time_classes(atlasx_model* m, unsigned mask, int ite
     atlasx_ctx* c = m->ctx;
     cudaStream_t s = c->stream;
     AX_CUDA(cudaStreamSynchronize(s));
-    const int saved = m->class_mask, saved_launches = m->launches_per_step, saved_resid = m->final_resid;
+    const int saved = m->class_mask, saved_launches = m->launches_per_step;
     m->class_mask = (int)(mask & ((1u << CLS_COUNT) - 1u)) & ~(1 << CLS_SELECT);
     // bytes and launch count of the family from one eager, profiled pass
     {
@@ -1210,7 +1299,7 @@ extern "C" int atlasx_model_time_classes(atlasx_model* m, unsigned mask, int ite
         if (bytes_per_pass) *bytes_per_pass = b;
         if (launches) *launches = pr.n;
         for (auto& e : pr.ev) cudaEventDestroy(e);
-        if (rc0) { m->class_mask = saved; m->launches_per_step = saved_launches; m->final_resid = saved_resid; return rc0; }
+        if (rc0) { m->class_mask = saved; m->launches_per_step = saved_launches; return rc0; }
     }
     cudaGraph_t g = nullptr; cudaGraphExec_t ge = nullptr;
     int rc = ATLASX_OK;
@@ -1219,7 +1308,7 @@ extern "C" int atlasx_model_time_classes(atlasx_model* m, unsigned mask, int ite
         rc = run_step(m, nullptr, true);
         e = cudaStreamEndCapture(s, &g);
     }
-    m->class_mask = saved; m->launches_per_step = saved_launches; m->final_resid = saved_resid;
+    m->class_mask = saved; m->launches_per_step = saved_launches;
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "capture failed: %s", cudaGetErrorString(e));
     e = cudaGraphInstantiate(&ge, g, 0);

@@ -215,10 +215,45 @@ class OlmoModel:
 
     forward_one = forward_one_gpu
 
-    def hidden(self):
+    def hidden(self, layer=None):
+        """Residual stream after the last layer (or after `layer`) of the last forward."""
         out = np.empty(self.config.d_model, np.float32)
-        check(_ffi.lib().atlasx_model_hidden(self._h, out.ctypes.data))
+        if layer is None:
+            check(_ffi.lib().atlasx_model_hidden(self._h, out.ctypes.data))
+        else:
+            check(_ffi.lib().atlasx_model_layer_hidden(self._h, int(layer), out.ctypes.data))
         return out
+
+    def set_layer_hook(self, fn):
+        """fn(layer_idx, hidden: float32 array) -> Optional[float], called for every layer of every
+        forward (forward_one_gpu_hooked, :1524-1557; generate_with_sampling_hooked, :1745-1846).
+        None detaches.  Returns the native callback object (kept alive by the model as well)."""
+        if fn is None:
+            check(_ffi.lib().atlasx_model_set_layer_hook(self._h, None, None))
+            self._hook_cb = None
+            return None
+        d = self.config.d_model
+
+        def trampoline(_user, layer, hidden, d_model, delta_out):
+            r = fn(int(layer), np.ctypeslib.as_array(hidden, shape=(d_model,)))
+            if r is None:
+                return 0
+            delta_out[0] = float(r)
+            return 1
+        cb = _ffi.LAYER_HOOK(trampoline)
+        check(_ffi.lib().atlasx_model_set_layer_hook(self._h, C.cast(cb, C.c_void_p), None))
+        self._hook_cb = cb
+        return cb
+
+    def deposits(self):
+        """(token_id, total_delta, layers_fired) per token generated by the last generate call with a hook."""
+        n = C.c_int(0)
+        check(_ffi.lib().atlasx_model_deposits(self._h, None, None, None, 0, C.byref(n)))
+        k = n.value
+        tok, delta, fired = np.zeros(k, np.uint32), np.zeros(k, np.float32), np.zeros(k, np.uint32)
+        if k:
+            check(_ffi.lib().atlasx_model_deposits(self._h, tok.ctypes.data, delta.ctypes.data, fired.ctypes.data, k, C.byref(n)))
+        return [(int(t), float(x), int(f)) for t, x, f in zip(tok, delta, fired)]
 
     def generate(self, prompt, max_new, temperature=0.0):
         """:1584-1590"""

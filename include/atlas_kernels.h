@@ -304,6 +304,22 @@ int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
 int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective);
 /* residual stream after the last forward (d_model floats), for layer-level parity checks */
 int atlasx_model_hidden(atlasx_model* m, float* hidden_host);
+/* the same after layer `layer` of the last forward (every layer's output survives the step) */
+int atlasx_model_layer_hidden(atlasx_model* m, int layer, float* hidden_host);
+/* StigmergicHook on the GPU path (crates/atlas-infer/src/hook.rs:31-33: on_layer(layer_idx, hidden) -> Option<f32>).
+ * The reference runs hooked generation on its CPU model (crates/atlas-infer/src/engine.rs:144-162); here the
+ * layer outputs of a forward are copied to pinned host memory behind the step (n_layers × d_model floats) and
+ * the hook runs on the host while the next forward executes.  The hook returns nonzero for Some(delta) and
+ * stores the delta.  With a hook attached atlasx_model_forward_one calls it for every layer before returning
+ * (forward_one_gpu_hooked, crates/atlas-model/src/lib.rs:1524-1557); atlasx_model_generate_greedy / _sampling call
+ * it for every layer of every forward, prompt included, and collect one deposit per generated token
+ * (generate_with_sampling_hooked, :1745-1846: negative deltas count as zero), read with atlasx_model_deposits
+ * after the call.  Prompt tokens are then ingested one by one.  fn = NULL detaches the hook. */
+typedef int (*atlasx_layer_hook)(void* user, int layer, const float* hidden_host, int d_model, float* delta_out);
+int atlasx_model_set_layer_hook(atlasx_model* m, atlasx_layer_hook fn, void* user);
+/* deposits of the last generate call: per generated token its id, the sum of the deltas and the number of
+ * layers that returned one; *n receives the count (all of them, even if cap is smaller) */
+int atlasx_model_deposits(atlasx_model* m, uint32_t* token_ids, float* total_delta, uint32_t* layers_fired, int cap, int* n);
 
 /* ── safetensors (crates/atlas-model/src/lib.rs: SafetensorsFile :2046-2240, loaders :2283-2570) ──
  * A file is mapped, not read: opening costs the header only. */
