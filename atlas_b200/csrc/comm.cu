@@ -133,7 +133,7 @@ int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out) {
     if (!ctx->tune.peer_allreduce) { cm->mail_failed = true; return ATLASX_OK; }
     const int W = cm->world;
     const size_t mail_bytes = (((size_t)2 * W * d * sizeof(uint2)) + 255) / 256 * 256;
-    const size_t total = mail_bytes + 256;                  // + the use counter
+    const size_t total = mail_bytes + 512;                  // + the use counter, + the selection slots
     AX_CUDA(cudaMalloc(&cm->mail_local, total));
     AX_CUDA(cudaMemset(cm->mail_local, 0, total));
     AX_CUDA(cudaDeviceSynchronize());
@@ -167,6 +167,7 @@ int ax_comm_peer_setup(atlasx_ctx* ctx, int d, const AxPeerMail** out) {
             if (cudaIpcOpenMemHandle(&ptr, all[p].h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) { cudaGetLastError(); ok = false; }
             mail.base[p] = (uint2*)ptr;
         }
+        for (int p = 0; p < W && ok; p++) mail.sel_base[p] = reinterpret_cast<uint4*>((uint8_t*)mail.base[p] + mail_bytes + 256);
     }
     Wire mapped = {}; mapped.ok = ok ? 1 : 0;
     rc = gather(mapped);                                    // second exchange: did every rank map every peer?

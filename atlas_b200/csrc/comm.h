@@ -18,6 +18,10 @@ struct AxPeerMail {
     // *useq + layer + 1 and advances the word by its layer count per step, so sequence numbers
     // never repeat while the mailbox lives, whatever models come and go on the context.
     unsigned* useq = nullptr;
+    // Selection slots: rank r leaves its local best (value bits, vocabulary index, sequence, sequence) in
+    // entry r of every rank's `sel` array with one 16-byte store (vocabulary-parallel argmax).
+    uint4* sel_base[kMaxPeers] = {};
+    uint4* sel(int owner, int from) const { return sel_base[owner] + from; }
     uint2* base[kMaxPeers] = {};        // mailbox of rank p as mapped in this process (own allocation for p == rank)
     uint2* part(int owner, int buf, int from) const { return base[owner] + ((size_t)buf * world + from) * d; }
 };

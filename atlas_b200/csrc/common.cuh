@@ -62,7 +62,9 @@ struct atlasx_ctx {
         int attn_stages = 3;           // ATLASX_ATTN_STAGES: landing stages of the one-launch attention inside a step (2..4)
         int attn_wave = 2;             // ATLASX_ATTN_WAVE: attention CTAs per SM that one wave of splits may fill
         int peer_allreduce = 1;        // ATLASX_PEER_ALLREDUCE=0: ncclAllReduce instead of the peer mailboxes
-        int mail_reduce = -1;          // ATLASX_MAIL_REDUCE: 1 = mailbox parts summed by a kernel of their own, 0 = by the consumer, −1 = automatic
+        int mail_reduce = -1;          // ATLASX_MAIL_REDUCE: mailbox parts summed 0 = by every consumer CTA, 1 = by a kernel of their own,
+                                       // 2 = by the first CTAs of the consumer (default, −1)
+        int tp_select = 1;             // ATLASX_TP_SELECT=0: greedy selection always over all-gathered logits
         int step_trace = 0;            // ATLASX_STEP_TRACE=1: timeline stamps in the captured step
         int comm_timeout_ms = 30000;   // ATLASX_COMM_TIMEOUT_MS: host deadline for a tensor-parallel step to complete
     } tune;

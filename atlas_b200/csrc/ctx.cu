@@ -60,6 +60,7 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_ATTN_WAVE", &c->tune.attn_wave);
         env_int("ATLASX_PEER_ALLREDUCE", &c->tune.peer_allreduce);
         env_int("ATLASX_MAIL_REDUCE", &c->tune.mail_reduce);
+        env_int("ATLASX_TP_SELECT", &c->tune.tp_select);
         env_int("ATLASX_STEP_TRACE", &c->tune.step_trace);
         env_int("ATLASX_COMM_TIMEOUT_MS", &c->tune.comm_timeout_ms);
         if (c->tune.attn_stages < 2 || c->tune.attn_stages > 4) c->tune.attn_stages = 3;

@@ -39,6 +39,12 @@ struct AxPrologue {
     // element it needs (bounded) — no fence and no separate flag on either side.
     int ll_n = 0; size_t ll_stride = 0;              // parts, and elements between parts
     const unsigned* ll_epoch = nullptr; unsigned ll_mul = 0, ll_add = 0;
+    // With ll_red set the parts are summed once per GPU instead of by every CTA: the first
+    // ll_red_ctas CTAs of the grid each poll a slice of all parts, add them in rank order and leave
+    // the sums in ll_red as (value, sequence) pairs again; every CTA then polls that one local
+    // vector.  Same result as summing the parts itself, one L2 round trip later, without the
+    // n × 8·K bytes of polling per CTA and without a reduction kernel of its own in the stream.
+    uint2* ll_red = nullptr; int ll_red_ctas = 0;
     int base_early = 0;                 // `base` was written at least two kernels back in the stream: may be read before the dependency wait
 };
 

@@ -217,8 +217,8 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
         float ss = 0.f;
         const unsigned seq = p.ll_n ? __ldcg(p.ll_epoch) * p.ll_mul + p.ll_add : 0u;
         // four (value, sequence) pairs of one part, polled until all four carry this use's number
-        auto load_ll = [&](int r, int k4) -> float4 {
-            const uint4* q = reinterpret_cast<const uint4*>(reinterpret_cast<const uint2*>(p.y) + (size_t)r * p.ll_stride + ((size_t)k4 << 2));
+        auto load_pairs = [&](const uint2* part, int k4) -> float4 {
+            const uint4* q = reinterpret_cast<const uint4*>(part + ((size_t)k4 << 2));
             uint4 a0, a1;
             const unsigned long long t0 = ax_globaltimer();
             for (;;) {
@@ -231,10 +231,27 @@ __device__ __forceinline__ void stage_input(const GemvArgs& a, float4* xs, float
             }
             return make_float4(__uint_as_float(a0.x), __uint_as_float(a0.z), __uint_as_float(a1.x), __uint_as_float(a1.z));
         };
+        auto load_ll = [&](int r, int k4) -> float4 { return load_pairs(reinterpret_cast<const uint2*>(p.y) + (size_t)r * p.ll_stride, k4); };
+        if (p.ll_n && p.ll_red && (int)blockIdx.x < p.ll_red_ctas) {
+            // this CTA's slice of the vector: all parts, in rank order, then the sums with the same sequence number
+            const int per = (n4 + p.ll_red_ctas - 1) / p.ll_red_ctas;
+            const int k_end = min(n4, ((int)blockIdx.x + 1) * per);
+            for (int k4 = (int)blockIdx.x * per + tid; k4 < k_end; k4 += NTHR) {
+                float4 t = load_ll(0, k4);
+                for (int r = 1; r < p.ll_n; r++) { const float4 u = load_ll(r, k4); t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
+                uint4* dst = reinterpret_cast<uint4*>(p.ll_red + ((size_t)k4 << 2));
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(dst), "r"(__float_as_uint(t.x)), "r"(seq),
+                             "r"(__float_as_uint(t.y)), "r"(seq) : "memory");
+                asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(dst + 1), "r"(__float_as_uint(t.z)), "r"(seq),
+                             "r"(__float_as_uint(t.w)), "r"(seq) : "memory");
+            }
+        }
 #pragma unroll 4
         for (int k4 = tid; k4 < n4; k4 += NTHR) {
             float4 t;
-            if (p.ll_n) {
+            if (p.ll_n && p.ll_red) {
+                t = load_pairs(p.ll_red, k4);
+            } else if (p.ll_n) {
                 t = load_ll(0, k4);
                 for (int r = 1; r < p.ll_n; r++) { const float4 u = load_ll(r, k4); t.x += u.x; t.y += u.y; t.z += u.z; t.w += u.w; }
             } else {

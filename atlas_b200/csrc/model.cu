@@ -91,7 +91,10 @@ struct atlasx_model {
     float* attn_partials = nullptr; unsigned* attn_tickets = nullptr;   // split-attention scratch of this model's step graph
     const AxPeerMail* mail = nullptr;            // tensor parallel: all-reduce fused into o_proj/down over peer memory
     int class_mask = (1 << CLS_COUNT) - 1;       // launch classes issued by run_step (all, except while one family is timed)
-    bool mail_reduce = false;                    // parts are summed by one small kernel per use instead of by every consumer CTA
+    int mail_mode = 0;                           // who sums the mailbox parts: 0 every consumer CTA, 1 a kernel of its own, 2 the consumer's first CTAs
+    uint2* mail_red[2] = { nullptr, nullptr };   // mode 2: the summed vector as (value, sequence) pairs, per mailbox buffer
+    bool tp_select = false;                      // greedy selection over the ranks' local maxima instead of all-gathered logits
+    cudaGraphExec_t graph_tok = nullptr;         // the step without the logits all-gather (tensor parallel, token-only callers)
     std::vector<void*> owned;                    // device allocations to free
     int* pin = nullptr;                          // pinned host ints
     float* pin_logits = nullptr;                 // pinned staging for logits handed to the host (allocated on first use)
@@ -201,9 +204,20 @@ int place_slice(atlasx_model* m, const void* src, int src_dtype, int rows, int c
 // ── argmax of the logits + advance of the device-resident state ─────────────────
 // Last CTA: last_token = argmax; if the next position is not a caller-given one, the token is
 // stored as the next input; pos += 1.
+// Vocabulary-parallel selection: every rank holds the logits of its own rows only.  The last CTA
+// leaves the local best in entry `rank` of every rank's selection slots (one 16-byte store: value,
+// vocabulary index, sequence number twice) and then picks the best of all ranks' entries — the same
+// (value, last index) rule, so every rank arrives at the same token without the logits leaving their GPU.
+struct SelPeers {
+    int n = 0, rank = 0, index_base = 0, vocab = 0;
+    uint4* dst[AX_MAX_PEERS] = {};        // this rank's entry in rank p's slots
+    const uint4* mine = nullptr;          // this rank's slots [n]
+    int* err = nullptr;
+};
+
 // useq (may be null): the mailbox use counter of the tensor-parallel group, advanced by `bump` per step.
 __global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, AxArgmaxScratch sc, StepState* st, int* seq, int seq_cap, int advance,
-                                                        unsigned* useq, unsigned bump) {
+                                                        unsigned* useq, unsigned bump, SelPeers peers) {
     __shared__ float sv[8];
     __shared__ int si[8];
     __shared__ int s_last;
@@ -237,6 +251,28 @@ __global__ void __launch_bounds__(256) select_advance_k(const float* x, int n, A
         if (ax_better(bv, bi, v, idx, 1)) { v = bv; idx = bi; }
     }
     ax_warp_best(v, idx, 1);
+    if (peers.n > 0) {
+        const unsigned stamp = *useq + bump;                      // the counter's value after this step: unique per step, never 0
+        if (idx >= 0) idx += peers.index_base;
+        if (lane < peers.n)
+            asm volatile("st.volatile.global.v4.u32 [%0], {%1,%2,%3,%4};" :: "l"(peers.dst[lane]), "r"(__float_as_uint(v)), "r"((unsigned)idx),
+                         "r"(stamp), "r"(stamp) : "memory");
+        float pv = 0.f; int pi = -1;
+        if (lane < peers.n) {
+            uint4 e;
+            const unsigned long long t0 = ax_globaltimer();
+            for (;;) {
+                asm volatile("ld.volatile.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(e.x), "=r"(e.y), "=r"(e.z), "=r"(e.w) : "l"(peers.mine + lane) : "memory");
+                if (e.z == stamp && e.w == stamp) break;
+                if (*reinterpret_cast<volatile int*>(peers.err) != 0) break;
+                if (ax_globaltimer() - t0 > 2000000000ull) { atomicExch(peers.err, 4); break; }
+            }
+            pv = __uint_as_float(e.x); pi = (int)e.y;
+        }
+        v = pv; idx = pi;
+        ax_warp_best(v, idx, 1);
+        n = peers.vocab;                                          // idx is a vocabulary index now
+    }
     if (lane == 0) {
         if (idx < 0) idx = n - 1;
         *sc.ticket = 0u;
@@ -286,7 +322,9 @@ double gemv_bytes(const AxWeight& w) { return (double)ax_weight_bytes(w) + 4.0 *
     } while (0)
 
 // One token: every launch of the step, in order, on the context stream.
-int run_step(atlasx_model* m, Profile* prof, bool advance) {
+// gather: under tensor parallelism, all-gather the logits and select over the full vector (callers
+// that read logits); otherwise the ranks exchange only their local maxima.
+int run_step(atlasx_model* m, Profile* prof, bool advance, bool gather = true) {
     atlasx_ctx* c = m->ctx;
     cudaStream_t s = c->stream;
     const atlasx_model_config& cf = m->cfg;
@@ -307,11 +345,12 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         return po;
     };
     auto peer_in = [&](AxPrologue& p, int buf, int l) {
-        if (m->mail_reduce) return;                        // p.y already names the reduced vector
+        if (m->mail_mode == 1) return;                     // p.y already names the reduced vector
         p.y = reinterpret_cast<const float*>(mail->part(mail->rank, buf, 0));
         p.nparts = mail->world; p.part_stride = (size_t)mail->d;
         p.ll_n = mail->world; p.ll_stride = (size_t)mail->d;
         p.ll_epoch = mail->useq; p.ll_mul = 1u; p.ll_add = (unsigned)l + 1u;
+        if (m->mail_mode == 2) { p.ll_red = m->mail_red[buf]; p.ll_red_ctas = 8; }
     };
 
     for (int l = 0; l < L; l++) {
@@ -375,7 +414,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         if (mail) {
             const AxPeerOut px = peer_out(0, l);
             STEP_LAUNCH(CLS_OPROJ, gemv_bytes(ly.wo), ax_gemv_launch(c, ly.wo, po, AX_EPI_PLAIN, 1, m->o, P(CLS_OPROJ), &px));
-            if (m->mail_reduce)
+            if (m->mail_mode == 1)
                 STEP_LAUNCH(CLS_COMM, 8.0 * d * mail->world, ax_mail_reduce_launch(c, mail->part(mail->rank, 0, 0), mail->world, (size_t)mail->d, d,
                                                                                    mail->useq, 1u, (unsigned)l + 1u, m->o, P(CLS_COMM)));
         } else {
@@ -398,7 +437,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
         if (mail) {
             const AxPeerOut px = peer_out(1, l);
             STEP_LAUNCH(CLS_DOWN, gemv_bytes(ly.down), ax_gemv_launch(c, ly.down, pd, AX_EPI_PLAIN, 1, m->dn, P(CLS_DOWN), &px));
-            if (m->mail_reduce)
+            if (m->mail_mode == 1)
                 STEP_LAUNCH(CLS_COMM, 8.0 * d * mail->world, ax_mail_reduce_launch(c, mail->part(mail->rank, 1, 0), mail->world, (size_t)mail->d, d,
                                                                                    mail->useq, 1u, (unsigned)l + 1u, m->dn, P(CLS_COMM)));
         } else {
@@ -416,20 +455,30 @@ int run_step(atlasx_model* m, Profile* prof, bool advance) {
     pl.wx = m->final_norm;
     pl.resid_out = m->taps + (size_t)(L - 1) * d;
     STEP_LAUNCH(CLS_LMHEAD, gemv_bytes(m->lm_head), ax_gemv_launch(c, m->lm_head, pl, AX_EPI_PLAIN, 1, m->logits_loc, P(CLS_LMHEAD)));
-    if (m->world > 1)
+    const bool local_select = m->world > 1 && m->tp_select && mail && !gather;
+    if (m->world > 1 && !local_select)
         STEP_LAUNCH(CLS_COMM, 4.0 * m->vocab_loc * m->world, ax_comm_allgather(c, m->logits_loc, m->logits, (size_t)m->vocab_loc));
 
     // ── greedy selection + state advance ────────────────────────────────────────
     if ((m->class_mask >> CLS_SELECT) & 1) {
         AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
-        const int n = cf.vocab_size;
+        int n = cf.vocab_size;
+        const float* sel_from = m->logits;
+        SelPeers sp;
+        if (local_select) {
+            sp.n = mail->world; sp.rank = mail->rank; sp.index_base = m->rank * m->vocab_loc; sp.vocab = cf.vocab_size; sp.err = c->dev_error;
+            for (int q = 0; q < mail->world; q++) sp.dst[q] = mail->sel(q, mail->rank);
+            sp.mine = mail->sel(mail->rank, 0);
+            sel_from = m->logits_loc;
+            n = cf.vocab_size - sp.index_base; n = n > m->vocab_loc ? m->vocab_loc : (n < 0 ? 0 : n);   // this rank's rows (none past the vocabulary)
+        }
         if (prof) cudaEventRecord(prof->ev[2 * prof->n], s);
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)((n + 1023) / 1024)); cfg.blockDim = dim3(256); cfg.stream = s;
+        cfg.gridDim = dim3((unsigned)((n + 1023) / 1024 > 0 ? (n + 1023) / 1024 : 1)); cfg.blockDim = dim3(256); cfg.stream = s;
         cudaLaunchAttribute attr[1];
         if (pdl) { attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization; attr[0].val.programmaticStreamSerializationAllowed = 1; cfg.attrs = attr; cfg.numAttrs = 1; }
-        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, (const float*)m->logits, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0,
-                                   mail ? mail->useq : (unsigned*)nullptr, (unsigned)L));
+        AX_CUDA(cudaLaunchKernelEx(&cfg, select_advance_k, sel_from, n, sc, m->st, m->seq, cf.max_seq_len + 1, advance ? 1 : 0,
+                                   mail ? mail->useq : (unsigned*)nullptr, (unsigned)L, sp));
         if (prof) { cudaEventRecord(prof->ev[2 * prof->n + 1], s); prof->cls[prof->n] = CLS_SELECT; prof->bytes[prof->n] = 4.0 * n; prof->n++; }
         n_launch++;
     }
@@ -575,15 +624,22 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     pf_advance_k<<<1, 1, 0, s>>>(m->st, n - 1);
     AxArgmaxScratch sc = { c->amax_vals, c->amax_idx, c->amax_ticket };
     // the chunk used NCCL, not the mailboxes: the use counter stays where it is
-    select_advance_k<<<(cf.vocab_size + 1023) / 1024, 256, 0, s>>>(m->logits, cf.vocab_size, sc, m->st, m->seq, cf.max_seq_len + 1, 1, nullptr, 0u);
+    select_advance_k<<<(cf.vocab_size + 1023) / 1024, 256, 0, s>>>(m->logits, cf.vocab_size, sc, m->st, m->seq, cf.max_seq_len + 1, 1, nullptr, 0u, SelPeers());
     AX_CHECK_LAUNCH("prefill selection");
     m->host_pos += n;
     return ATLASX_OK;
 }
 
+int capture_one(atlasx_model* m, bool gather, cudaGraphExec_t* out);
 int capture_graph(atlasx_model* m) {
-    atlasx_ctx* c = m->ctx;
     if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+    if (m->graph_tok) { cudaGraphExecDestroy(m->graph_tok); m->graph_tok = nullptr; }
+    int rc = capture_one(m, true, &m->graph);
+    if (!rc && m->world > 1 && m->tp_select && m->mail) rc = capture_one(m, false, &m->graph_tok);
+    return rc;
+}
+int capture_one(atlasx_model* m, bool gather, cudaGraphExec_t* out) {
+    atlasx_ctx* c = m->ctx;
     cudaGraph_t g = nullptr;
     if (c->tune.step_trace && !m->step_trace) {
         int r0 = dmalloc(m, (void**)&m->step_trace, 1024 * sizeof(AxTraceSlot));
@@ -591,23 +647,25 @@ int capture_graph(atlasx_model* m) {
     }
     AX_CUDA(cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal));
     c->trace_next = m->step_trace;
-    int rc = run_step(m, nullptr, true);
+    int rc = run_step(m, nullptr, true, gather);
     if (m->step_trace) { m->step_trace_slots = (int)((c->trace_next - m->step_trace) / 6); c->trace_next = nullptr; }
     cudaError_t e = cudaStreamEndCapture(c->stream, &g);
     if (rc) { if (g) cudaGraphDestroy(g); return rc; }
     if (e != cudaSuccess) return atlasx_fail(ATLASX_ERR_CUDA, "stream capture failed: %s", cudaGetErrorString(e));
-    e = cudaGraphInstantiate(&m->graph, g, 0);
+    e = cudaGraphInstantiate(out, g, 0);
     cudaGraphDestroy(g);
-    if (e != cudaSuccess) { m->graph = nullptr; return atlasx_fail(ATLASX_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e)); }
+    if (e != cudaSuccess) { *out = nullptr; return atlasx_fail(ATLASX_ERR_CUDA, "graph instantiation failed: %s", cudaGetErrorString(e)); }
     return ATLASX_OK;
 }
 
-int step(atlasx_model* m) {
+// need_logits = false: the caller only wants the token (tensor parallel: no logits all-gather)
+int step(atlasx_model* m, bool need_logits = true) {
     if (m->host_pos >= m->cfg.max_seq_len)
         return atlasx_fail(ATLASX_ERR_STATE, "position %d is past max_seq_len %d", m->host_pos, m->cfg.max_seq_len);
     int rc;
-    if (m->use_graph && m->graph) { AX_CUDA(cudaGraphLaunch(m->graph, m->ctx->stream)); rc = ATLASX_OK; }
-    else rc = run_step(m, nullptr, true);
+    const bool tok_only = !need_logits && m->world > 1 && m->tp_select && m->mail;
+    if (m->use_graph && m->graph) { AX_CUDA(cudaGraphLaunch(tok_only && m->graph_tok ? m->graph_tok : m->graph, m->ctx->stream)); rc = ATLASX_OK; }
+    else rc = run_step(m, nullptr, true, !tok_only);
     if (!rc) m->host_pos++;
     return rc;
 }
@@ -629,8 +687,8 @@ int run_hooks(atlasx_model* m, int k) {
 // One forward inside generate: the step, then — with a hook attached — the copy of its layer outputs
 // to the host, and the hook calls of the PREVIOUS forward while this one runs on the GPU.
 // tok: the generated token this forward processes (−1 for a prompt token: hook results are dropped).
-int gen_step(atlasx_model* m, long long tok) {
-    int rc = step(m);
+int gen_step(atlasx_model* m, long long tok, bool need_logits = true) {
+    int rc = step(m, need_logits);
     if (rc || !m->hook_fn) return rc;
     const int k = m->tap_k;
     AX_CUDA(cudaMemcpyAsync(m->tap_host[k], m->taps, (size_t)m->cfg.n_layers * m->cfg.d_model * 4, cudaMemcpyDeviceToHost, m->ctx->stream));
@@ -735,6 +793,7 @@ extern "C" int atlasx_model_free(atlasx_model* m) {
     if (!m) return ATLASX_OK;
     cudaStreamSynchronize(m->ctx->stream);
     if (m->graph) cudaGraphExecDestroy(m->graph);
+    if (m->graph_tok) cudaGraphExecDestroy(m->graph_tok);
     for (Layer& ly : m->layers) if (ly.kv) atlasx_kvcache_free(ly.kv);
     for (void* p : m->owned) cudaFree(p);
     for (int k = 0; k < 2; k++) { if (m->tap_host[k]) cudaFreeHost(m->tap_host[k]); if (m->tap_ev[k]) cudaEventDestroy(m->tap_ev[k]); }
@@ -954,8 +1013,14 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
         rc = ax_comm_peer_setup(c, d, &m->mail); if (rc) return rc;
         // every consumer CTA polling every part costs world × 8·d bytes of L2 reads per CTA; one more
         // small launch per use is cheaper already with two ranks (466 against 462 tok/s)
-        m->mail_reduce = m->mail != nullptr;
-        if (c->tune.mail_reduce >= 0) m->mail_reduce = m->mail && c->tune.mail_reduce != 0;
+        if (m->mail) {
+            m->mail_mode = (c->tune.mail_reduce >= 0 && c->tune.mail_reduce <= 2) ? c->tune.mail_reduce : 2;
+            for (int b = 0; b < 2; b++) {
+                if ((rc = dmalloc(m, (void**)&m->mail_red[b], (size_t)d * sizeof(uint2)))) return rc;
+                AX_CUDA(cudaMemsetAsync(m->mail_red[b], 0, (size_t)d * sizeof(uint2), s));
+            }
+            m->tp_select = c->tune.tp_select != 0;
+        }
         AX_CUDA(cudaMemsetAsync(m->o, 0, (size_t)d * 4, s));
         rc = ax_comm_allreduce_sum(c, m->o, (size_t)d); if (rc) return rc;
         AX_CUDA(cudaStreamSynchronize(s));
@@ -1031,6 +1096,7 @@ extern "C" int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_
     if (m->finalized && changed) {
         AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
         if (m->graph) { cudaGraphExecDestroy(m->graph); m->graph = nullptr; }
+        if (m->graph_tok) { cudaGraphExecDestroy(m->graph_tok); m->graph_tok = nullptr; }
         if (m->use_graph) return capture_graph(m);
     }
     return ATLASX_OK;
@@ -1069,7 +1135,7 @@ extern "C" int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* 
     m->pin[0] = (int)token;
     AX_CUDA(cudaMemcpyAsync(m->seq + m->host_pos, m->pin, 4, cudaMemcpyHostToDevice, s));
     set_state_k<<<1, 1, 0, s>>>(m->st, m->host_pos, INT_MAX);
-    int rc = step(m); if (rc) return rc;
+    int rc = step(m, logits_host != nullptr); if (rc) return rc;
     if (m->hook_fn) {                     // forward_one_gpu_hooked (:1524-1557): the hook sees every layer's output of this token
         m->tap_pending = false;
         AX_CUDA(cudaMemcpyAsync(m->tap_host[0], m->taps, (size_t)m->cfg.n_layers * m->cfg.d_model * 4, cudaMemcpyDeviceToHost, s));
@@ -1120,6 +1186,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
     } sup_guard;
     sup_guard.s = s;
     const bool fix = n_suppress > 0 || rep_penalty != 1.0f;
+    const bool need_logits = fix || n_prompt == 0;     // logit edits work on the full vector: every step all-gathers it under tensor parallelism
     if (n_suppress > 0) {
         AX_CUDA(cudaMalloc((void**)&sup_guard.p, (size_t)n_suppress * 4));
         AX_CUDA(cudaMemcpyAsync(sup_guard.p, suppress, (size_t)n_suppress * 4, cudaMemcpyHostToDevice, s));
@@ -1134,7 +1201,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         const int left = n_prompt - i;
         // with a hook every prompt token is a forward of its own: the hook sees each token's layers
         const int n = (m->prefill_chunk > 1 && left >= 2 && !m->hook_fn) ? (left < m->prefill_chunk ? left : m->prefill_chunk) : 1;
-        rc = n > 1 ? run_prefill_chunk(m, n) : gen_step(m, -1);
+        rc = n > 1 ? run_prefill_chunk(m, n) : gen_step(m, -1, need_logits);
         if (rc) return done(rc);
         i += n;
     }
@@ -1147,7 +1214,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
             if (need_fix)
                 logit_fixups_k<<<1, 32, 0, s>>>(m->logits, V, sup_dev, stepi == 0 ? n_suppress : 0,
                                                 m->seq + n_prompt + start, rep_penalty != 1.0f ? stepi - start : 0, rep_penalty);
-            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0, nullptr, 0u);
+            select_advance_k<<<(V + 1023) / 1024, 256, 0, s>>>(m->logits, V, sc, m->st, m->seq, m->cfg.max_seq_len + 1, 0, nullptr, 0u, SelPeers());
             cudaError_t e = cudaGetLastError();
             if (e != cudaSuccess) return done(atlasx_fail(ATLASX_ERR_CUDA, "selection launch failed: %s", cudaGetErrorString(e)));
         }
@@ -1161,7 +1228,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
         if (stop) break;
         out_tokens[(*n_out)++] = tok;
-        rc = gen_step(m, (long long)tok); if (rc) return done(rc);
+        rc = gen_step(m, (long long)tok, need_logits); if (rc) return done(rc);
     }
     return done(ATLASX_OK);
 }
@@ -1254,9 +1321,9 @@ extern "C" int atlasx_model_decode_timed(atlasx_model* m, int steps, int lead, f
     // untimed lead-in steps, queued without a host synchronisation before the first event: the ranks
     // of a tensor-parallel group leave them coupled through their mailboxes, so the timed region
     // starts at the same moment on every GPU however far apart the hosts got here
-    for (int i = 0; i < lead && !rc; i++) rc = step(m);
+    for (int i = 0; i < lead && !rc; i++) rc = step(m, false);
     if (!rc) AX_CUDA(cudaEventRecord(e0, s));
-    for (int i = 0; i < steps && !rc; i++) rc = step(m);
+    for (int i = 0; i < steps && !rc; i++) rc = step(m, false);
     cudaEventRecord(e1, s);
     const int rq = queue_wait_status(m);
     const int rs = ax_comm_stream_sync(m->ctx);

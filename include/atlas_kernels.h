@@ -260,7 +260,9 @@ int atlasx_model_set_tensor_slice(atlasx_model* m, int layer, int which, const v
 int atlasx_model_finalize(atlasx_model* m);
 int atlasx_model_reset(atlasx_model* m);                                            /* reset :1389 */
 int atlasx_model_pos(const atlasx_model* m);
-/* forward_one_gpu (:1463-1505): logits_host may be NULL (no download) */
+/* forward_one_gpu (:1463-1505): logits_host may be NULL (no download).  Tensor parallel: every rank of the
+ * group must make the same choice — with NULL the ranks exchange only their local maxima, otherwise they
+ * all-gather the logits. */
 int atlasx_model_forward_one(atlasx_model* m, uint32_t token, float* logits_host);
 /* generate_with_sampling, greedy branch (:1599-1646,1713-1730): EOS/stop tokens end the
  * run before being emitted; suppress applies to the first generated token only;

@@ -29,14 +29,17 @@ def _free_port():
 
 
 @pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("peer", ["mailbox", "mailbox_reduce", "nccl"])
+@pytest.mark.parametrize("peer", ["mailbox", "mailbox_reduce", "mailbox_fused", "mailbox_fused_gather", "nccl"])
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
 def test_two_gpu_tensor_parallel_matches_single_gpu_and_oracle(tmp_path, kv, peer):
     import atlas_b200 as ab
     n_tok = 20
     out = str(tmp_path / "tp.npz")
+    # who sums the mailbox parts: every consumer CTA (0), a kernel of its own (1), the consumer's first CTAs (2, the
+    # default); and greedy selection over the ranks' local maxima (default) or over all-gathered logits
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", ATLASX_PEER_ALLREDUCE="0" if peer == "nccl" else "1",
-               ATLASX_MAIL_REDUCE="1" if peer == "mailbox_reduce" else "0")
+               ATLASX_MAIL_REDUCE={"mailbox": "0", "mailbox_reduce": "1"}.get(peer, "2"),
+               ATLASX_TP_SELECT="0" if peer == "mailbox_fused_gather" else "1")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "tp_worker.py"), out, kv, str(n_tok)]
