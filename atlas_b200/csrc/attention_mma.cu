@@ -1,0 +1,591 @@
+// attention_mma.cu — GQA decode attention on the tensor cores (bf16 cache, head_dim 128, 3..8
+// query heads per KV head).
+//
+// With several query heads per KV head the scalar kernels of attention.cu are bound by
+// instruction issue, not by HBM: every cached row costs 128·G multiply-adds twice.  Here the G
+// query vectors of a KV head form the (zero-padded) 16-row A operand of mma.sync m16n8k16 and the
+// cached rows the B operand, so a 32-row tile of K and V costs a warp 128 tensor instructions
+// instead of ~8000 scalar ones.  Semantics are those of decode_attention_kernel of the reference
+// (kernels/matmul.cu:786-894): kv head = head / group, rows pos − t ≥ window masked, softmax over
+// the rest — computed flash-decoding style (online softmax, sequence split across CTAs and merged
+// by the last CTA of a head group).
+//   * Each of the four warps of a CTA streams its own 32-row tiles: cp.async into warp-private
+//     shared memory (three stages, rows padded to 272 bytes so that ldmatrix is conflict-free),
+//     no CTA barrier in the loop.
+//   * Accuracy: K and V are bf16 already, so products with them are exact in the f32 accumulator;
+//     the f32 queries and probabilities enter as hi + lo bf16 pairs (two MMAs each), which leaves
+//     an error of 2⁻¹⁷ relative — far inside the 1e-3 parity bound.
+#include <math_constants.h>
+
+#include "attention.cuh"
+#include "attention_mma.cuh"
+
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kTileRows = 32;                  // cached rows per warp tile
+constexpr int kPitch = 272;                    // bytes per staged row: 256 + 16, shifts rows across the banks
+constexpr int kStages = 3;
+constexpr int kTileBytes = kTileRows * kPitch; // one of K or V
+constexpr int kStageBytes = 2 * kTileBytes;
+constexpr int kWarpBytes = kStages * kStageBytes;
+constexpr int kST = 130;                       // partial state: m, l, 128 outputs
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;              // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" :: "r"(dst), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+// D += A·B, A 16×16 bf16 (rows 8..15 of A are zero here: a1 = a3 = 0), B 16×8 bf16, f32 accumulate
+__device__ __forceinline__ void mma_bf16(float (&c)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma_bf16_full(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// two floats → (hi pair, lo pair) of bf16, x = hi + lo to 2⁻¹⁷; first argument in the low half
+__device__ __forceinline__ void split2(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const uint16_t hx = ax_f32_to_bf16_rne(x), hy = ax_f32_to_bf16_rne(y);
+    const uint16_t lx = ax_f32_to_bf16_rne(x - ax_bf16_to_f32(hx)), ly = ax_f32_to_bf16_rne(y - ax_bf16_to_f32(hy));
+    hi = (uint32_t)hx | ((uint32_t)hy << 16);
+    lo = (uint32_t)lx | ((uint32_t)ly << 16);
+}
+__device__ __forceinline__ float fast_exp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+struct MmaDev {
+    const float* q; const uint16_t* kc; const uint16_t* vc; float* out;
+    size_t seq_stride;              // elements between sequences of the cache
+    const int* pos; int pos_shared; int pos_scalar;
+    int n_heads, n_kv, g, window, n_splits;
+    float scale;
+    float* partials; unsigned* tickets;
+};
+
+__device__ __forceinline__ float merge_exp(float m, float M) { return (m == -CUDART_INF_F) ? 0.f : expf(m - M); }
+
+__global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_last;
+    const int split = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = dv.g;
+    const int quad = lane >> 2, qi = lane & 3;               // row of the fragments, position inside the row's quad
+
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    const int pos = dv.pos ? dv.pos[dv.pos_shared ? 0 : b] : dv.pos_scalar;
+    const int tb = (dv.window > 0 && pos - dv.window + 1 > 0) ? pos - dv.window + 1 : 0;      // pos − t < window
+    const int te = pos + 1;
+    const int rows = te - tb;
+    int S = dv.n_splits;
+    {   // splits in whole tiles, never more than there are tiles
+        const int tiles = (rows + kTileRows - 1) / kTileRows;
+        if (S > tiles) S = tiles;
+        if (S < 1) S = 1;
+    }
+    if (split >= S) return;
+    const int tiles_all = (rows + kTileRows - 1) / kTileRows;
+    const int tile0 = (int)((long long)tiles_all * split / S), tile1 = (int)((long long)tiles_all * (split + 1) / S);
+    const int t0 = tb + tile0 * kTileRows, t1 = min(te, tb + tile1 * kTileRows);
+    const int n_tiles = tile1 - tile0;                        // of this CTA; warp w takes tiles w, w + 4, …
+    const int my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
+
+    // ── query fragments: rows = the G heads of this KV head (scaled by scale·log2 e), hi + lo ──
+    uint32_t qh[8][2], ql[8][2];
+    {
+        const float sc = dv.scale * 1.4426950408889634f;
+        const float* qp = dv.q + ((size_t)b * dv.n_heads + (size_t)kh * G + quad) * 128;
+#pragma unroll
+        for (int ks = 0; ks < 8; ks++) {
+            float2 v0 = make_float2(0.f, 0.f), v1 = make_float2(0.f, 0.f);
+            if (quad < G) {
+                v0 = *reinterpret_cast<const float2*>(qp + ks * 16 + qi * 2);
+                v1 = *reinterpret_cast<const float2*>(qp + ks * 16 + 8 + qi * 2);
+            }
+            split2(v0.x * sc, v0.y * sc, qh[ks][0], ql[ks][0]);
+            split2(v1.x * sc, v1.y * sc, qh[ks][1], ql[ks][1]);
+        }
+    }
+
+    uint8_t* wbase = smem + (size_t)warp * kWarpBytes;
+    const size_t row_elems = (size_t)dv.n_kv * 128;
+    const uint16_t* kg = dv.kc + (size_t)b * dv.seq_stride + (size_t)kh * 128;
+    const uint16_t* vg = dv.vc + (size_t)b * dv.seq_stride + (size_t)kh * 128;
+    // tile j of this warp → stage j % kStages; each lane copies 16 pieces of K and 16 of V (row = 2i + lane/16, piece = lane % 16)
+    auto issue = [&](int j) {
+        if (j < my_tiles) {
+            const int tt = t0 + (warp + j * kWarps) * kTileRows;
+            uint8_t* st = wbase + (size_t)(j % kStages) * kStageBytes;
+            const int piece = lane & 15;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int r = i * 2 + (lane >> 4);
+                const int t = tt + r;
+                const bool ok = t < t1;
+                const size_t go = (size_t)(ok ? t : t0) * row_elems + piece * 8;
+                cp_async16_zfill(smem_addr(st + r * kPitch + piece * 16), kg + go, ok);
+                cp_async16_zfill(smem_addr(st + kTileBytes + r * kPitch + piece * 16), vg + go, ok);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int j = 0; j < kStages - 1; j++) issue(j);
+
+    float o[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+    float m_run = -CUDART_INF_F, l_run = 0.f;                  // of row `quad` (log2 domain); l is this lane's share
+
+    for (int j = 0; j < my_tiles; j++) {
+        asm volatile("cp.async.wait_group %0;" :: "n"(kStages - 2) : "memory");
+        __syncwarp();                                         // tile j has landed for every lane; tile j − 1 is consumed
+        issue(j + kStages - 1);                               // into the stage tile j − 1 occupied
+        const int tt = t0 + (warp + j * kWarps) * kTileRows;
+        const uint8_t* st = wbase + (size_t)(j % kStages) * kStageBytes;
+        const uint32_t ks_addr = smem_addr(st), vs_addr = smem_addr(st + kTileBytes);
+
+        // ── S = Q·Kᵀ: 4 column tiles of 8 rows of K, 8 steps of 16 dims, hi and lo ──
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+            for (int k2 = 0; k2 < 4; k2++) {                 // two 16-dim steps per ldmatrix.x4
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(ks_addr + (nt * 8 + (lane & 7)) * kPitch + k2 * 64 + (lane >> 3) * 16, b0, b1, b2, b3);
+                mma_bf16(s[nt], qh[2 * k2][0], qh[2 * k2][1], b0, b1);
+                mma_bf16(s[nt], ql[2 * k2][0], ql[2 * k2][1], b0, b1);
+                mma_bf16(s[nt], qh[2 * k2 + 1][0], qh[2 * k2 + 1][1], b2, b3);
+                mma_bf16(s[nt], ql[2 * k2 + 1][0], ql[2 * k2 + 1][1], b2, b3);
+            }
+        }
+        // ── online softmax of row `quad` (columns nt·8 + 2·qi + {0,1}) ──
+        float mx = -CUDART_INF_F;
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const int c = tt + nt * 8 + qi * 2;
+            if (c >= t1) s[nt][0] = -CUDART_INF_F;
+            if (c + 1 >= t1) s[nt][1] = -CUDART_INF_F;
+            mx = fmaxf(mx, fmaxf(s[nt][0], s[nt][1]));
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+        const float corr = fast_exp2(m_run - m_use);          // 0 for the first tile (m_run = −inf)
+        m_run = m_new;
+        l_run *= corr;
+        uint32_t ph[2][2], pl[2][2];                          // [16-row step of the tile][a0, a2]
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const float p0 = fast_exp2(s[nt][0] - m_use), p1 = fast_exp2(s[nt][1] - m_use);
+            l_run += p0 + p1;
+            split2(p0, p1, ph[nt >> 1][nt & 1], pl[nt >> 1][nt & 1]);
+        }
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) { o[nt][0] *= corr; o[nt][1] *= corr; }
+        // ── O += P·V: 2 steps of 16 rows, 16 column tiles of 8 dims, hi and lo ──
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+#pragma unroll
+            for (int n2 = 0; n2 < 8; n2++) {                 // two 8-dim column tiles per ldmatrix.x4.trans
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(vs_addr + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kPitch + n2 * 32 + (lane >> 4) * 16, b0, b1, b2, b3);
+                mma_bf16(o[2 * n2], ph[kk][0], ph[kk][1], b0, b1);
+                mma_bf16(o[2 * n2], pl[kk][0], pl[kk][1], b0, b1);
+                mma_bf16(o[2 * n2 + 1], ph[kk][0], ph[kk][1], b2, b3);
+                mma_bf16(o[2 * n2 + 1], pl[kk][0], pl[kk][1], b2, b3);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+    // ── merge the warps, then (last CTA of the head group) the splits ──
+    l_run += __shfl_xor_sync(AX_FULL, l_run, 1);
+    l_run += __shfl_xor_sync(AX_FULL, l_run, 2);
+    __syncthreads();                                          // all warps are done with their staging memory
+    float* smm = reinterpret_cast<float*>(smem);              // [warp][G][kST]
+    if (quad < G) {
+        float* dst = smm + ((size_t)warp * G + quad) * kST;
+        if (qi == 0) { dst[0] = m_run * 0.6931471805599453f; dst[1] = l_run; }       // back to natural-log units
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) { dst[2 + nt * 8 + qi * 2] = o[nt][0]; dst[2 + nt * 8 + qi * 2 + 1] = o[nt][1]; }
+    }
+    __syncthreads();
+    const int SP = dv.n_splits;                               // partial slots per head
+    for (int idx = tid; idx < G * 128; idx += kThreads) {
+        const int g = idx >> 7, d = idx & 127;
+        float M = -CUDART_INF_F;
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, smm[((size_t)w * G + g) * kST]);
+        float L = 0.f, A = 0.f;
+        for (int w = 0; w < kWarps; w++) {
+            const float* sp = smm + ((size_t)w * G + g) * kST;
+            const float c = merge_exp(sp[0], M);
+            L = fmaf(c, sp[1], L); A = fmaf(c, sp[2 + d], A);
+        }
+        const size_t h = (size_t)b * dv.n_heads + (size_t)kh * G + g;
+        if (S == 1) dv.out[h * 128 + d] = A / L;
+        else {
+            float* P = dv.partials + (h * SP + split) * kST;
+            P[2 + d] = A;
+            if (d == 0) { P[0] = M; P[1] = L; }
+        }
+    }
+    if (S == 1) return;
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) s_last = atomicAdd(&dv.tickets[(size_t)b * gridDim.y + kh], 1u) == (unsigned)(S - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < G * 128; idx += kThreads) {
+        const int g = idx >> 7, d = idx & 127;
+        const size_t h = (size_t)b * dv.n_heads + (size_t)kh * G + g;
+        const float* P = dv.partials + h * SP * kST;
+        float M = -CUDART_INF_F;
+        for (int i = 0; i < S; i++) M = fmaxf(M, P[(size_t)i * kST]);
+        float L = 0.f, A = 0.f;
+        for (int i = 0; i < S; i++) {
+            const float c = merge_exp(P[(size_t)i * kST], M);
+            L = fmaf(c, P[(size_t)i * kST + 1], L); A = fmaf(c, P[(size_t)i * kST + 2 + d], A);
+        }
+        dv.out[h * 128 + d] = A / L;
+    }
+    if (tid == 0) dv.tickets[(size_t)b * gridDim.y + kh] = 0u;       // ready for the next launch
+}
+
+constexpr size_t kSmemBytes = (size_t)kWarps * kWarpBytes;
+
+// ── causal attention of a chunk of prompt tokens ──────────────────────────────────────
+// The n tokens of a chunk (positions pos0 .. pos0 + n − 1, their K/V rows already in the cache) in ONE
+// launch per layer instead of one decode-attention launch per token
+// (crates/atlas-model/src/lib.rs:1611-1618 feeds the prompt token by token).  The 16 rows of the A
+// operand are (token, head of the group) pairs — 16 tokens for one head per KV head, 4 tokens × 4
+// heads, … — and each row carries its own causal and window mask: row of token i sees keys
+// t ≤ pos0 + i with pos0 + i − t < window.  Otherwise the kernel is ax_attn_mma_kernel with both
+// halves of the fragments in use.
+struct ChunkDev {
+    const float* q; size_t q_stride;            // token i, head h: q + i·q_stride + h·128 (normed and rotated)
+    const uint16_t* kc; const uint16_t* vc;
+    float* out; size_t out_stride;
+    const int* pos0;                            // device: position of the chunk's first token
+    int n_tok, n_heads, n_kv, g, window, n_splits;
+    float scale;
+    float* partials; unsigned* tickets;         // [n_tok·n_heads][n_splits][130]; [n_kv · row groups]
+};
+
+__global__ void __launch_bounds__(kThreads) ax_attn_mma_chunk_kernel(const ChunkDev dv) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int s_last;
+    const int split = blockIdx.x, kh = blockIdx.y, rg = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = dv.g, TPG = 16 / G;                          // tokens per row group
+    const int quad = lane >> 2, qi = lane & 3;
+
+    const int pos0 = *dv.pos0;
+    const int tok_lo = rg * TPG, tok_hi = min(dv.n_tok, tok_lo + TPG);       // tokens of this row group
+    // rows `quad` and `quad + 8` of the fragments
+    int r_tok[2], r_head[2], r_pos[2], r_lo[2];
+    bool r_ok[2];
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+        const int r = quad + 8 * hf;
+        r_tok[hf] = tok_lo + r / G; r_head[hf] = kh * G + r % G;
+        r_ok[hf] = r < TPG * G && r_tok[hf] < dv.n_tok;
+        r_pos[hf] = pos0 + r_tok[hf];
+        r_lo[hf] = (dv.window > 0 && r_pos[hf] - dv.window + 1 > 0) ? r_pos[hf] - dv.window + 1 : 0;
+    }
+    const int p_first = pos0 + tok_lo, p_last = pos0 + tok_hi - 1;
+    const int tb = (dv.window > 0 && p_first - dv.window + 1 > 0) ? p_first - dv.window + 1 : 0;
+    const int te = p_last + 1;
+    const int rows = te - tb;
+    const int tiles_all = (rows + kTileRows - 1) / kTileRows;
+    int S = dv.n_splits; if (S > tiles_all) S = tiles_all; if (S < 1) S = 1;
+    if (split >= S) return;
+    const int tile0 = (int)((long long)tiles_all * split / S), tile1 = (int)((long long)tiles_all * (split + 1) / S);
+    const int t0 = tb + tile0 * kTileRows, t1 = min(te, tb + tile1 * kTileRows);
+    const int n_tiles = tile1 - tile0;
+    const int my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
+
+    uint32_t qh[8][4], ql[8][4];                               // a0..a3 per 16-dim step
+    {
+        const float sc = dv.scale * 1.4426950408889634f;
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            const float* qp = dv.q + (size_t)(r_ok[hf] ? r_tok[hf] : 0) * dv.q_stride + (size_t)r_head[hf] * 128;
+#pragma unroll
+            for (int ks = 0; ks < 8; ks++) {
+                float2 v0 = make_float2(0.f, 0.f), v1 = make_float2(0.f, 0.f);
+                if (r_ok[hf]) {
+                    v0 = *reinterpret_cast<const float2*>(qp + ks * 16 + qi * 2);
+                    v1 = *reinterpret_cast<const float2*>(qp + ks * 16 + 8 + qi * 2);
+                }
+                split2(v0.x * sc, v0.y * sc, qh[ks][hf], ql[ks][hf]);              // a0 (row quad) / a1 (row quad + 8)
+                split2(v1.x * sc, v1.y * sc, qh[ks][2 + hf], ql[ks][2 + hf]);      // a2 / a3
+            }
+        }
+    }
+
+    uint8_t* wbase = smem + (size_t)warp * kWarpBytes;
+    const size_t row_elems = (size_t)dv.n_kv * 128;
+    const uint16_t* kg = dv.kc + (size_t)kh * 128;
+    const uint16_t* vg = dv.vc + (size_t)kh * 128;
+    auto issue = [&](int j) {
+        if (j < my_tiles) {
+            const int tt = t0 + (warp + j * kWarps) * kTileRows;
+            uint8_t* st = wbase + (size_t)(j % kStages) * kStageBytes;
+            const int piece = lane & 15;
+#pragma unroll
+            for (int i = 0; i < 16; i++) {
+                const int r = i * 2 + (lane >> 4);
+                const int t = tt + r;
+                const bool ok = t < t1;
+                const size_t go = (size_t)(ok ? t : t0) * row_elems + piece * 8;
+                cp_async16_zfill(smem_addr(st + r * kPitch + piece * 16), kg + go, ok);
+                cp_async16_zfill(smem_addr(st + kTileBytes + r * kPitch + piece * 16), vg + go, ok);
+            }
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+#pragma unroll
+    for (int j = 0; j < kStages - 1; j++) issue(j);
+
+    float o[16][4];
+#pragma unroll
+    for (int nt = 0; nt < 16; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
+    float m_run[2] = { -CUDART_INF_F, -CUDART_INF_F }, l_run[2] = { 0.f, 0.f };
+
+    for (int j = 0; j < my_tiles; j++) {
+        asm volatile("cp.async.wait_group %0;" :: "n"(kStages - 2) : "memory");
+        __syncwarp();
+        issue(j + kStages - 1);
+        const int tt = t0 + (warp + j * kWarps) * kTileRows;
+        const uint8_t* st = wbase + (size_t)(j % kStages) * kStageBytes;
+        const uint32_t ks_addr = smem_addr(st), vs_addr = smem_addr(st + kTileBytes);
+        float s[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+            for (int k2 = 0; k2 < 4; k2++) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(ks_addr + (nt * 8 + (lane & 7)) * kPitch + k2 * 64 + (lane >> 3) * 16, b0, b1, b2, b3);
+                mma_bf16_full(s[nt], qh[2 * k2], b0, b1);
+                mma_bf16_full(s[nt], ql[2 * k2], b0, b1);
+                mma_bf16_full(s[nt], qh[2 * k2 + 1], b2, b3);
+                mma_bf16_full(s[nt], ql[2 * k2 + 1], b2, b3);
+            }
+        }
+        // per-row causal / window mask and online softmax, rows quad (c0, c1) and quad + 8 (c2, c3)
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int hf = 0; hf < 2; hf++) {
+            float mx = -CUDART_INF_F;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+                for (int e = 0; e < 2; e++) {
+                    const int c = tt + nt * 8 + qi * 2 + e;
+                    const bool ok = r_ok[hf] && c <= r_pos[hf] && c >= r_lo[hf] && c < t1;
+                    if (!ok) s[nt][2 * hf + e] = -CUDART_INF_F;
+                    mx = fmaxf(mx, s[nt][2 * hf + e]);
+                }
+            }
+            mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 2));
+            const float m_new = fmaxf(m_run[hf], mx);
+            m_use[hf] = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+            corr[hf] = fast_exp2(m_run[hf] - m_use[hf]);
+            m_run[hf] = m_new;
+            l_run[hf] *= corr[hf];
+        }
+        uint32_t ph[2][4], pl[2][4];                          // [16-row step][a0..a3]
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+            for (int hf = 0; hf < 2; hf++) {
+                const float p0 = fast_exp2(s[nt][2 * hf] - m_use[hf]), p1 = fast_exp2(s[nt][2 * hf + 1] - m_use[hf]);
+                l_run[hf] += p0 + p1;
+                split2(p0, p1, ph[nt >> 1][(nt & 1) * 2 + hf], pl[nt >> 1][(nt & 1) * 2 + hf]);
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) { o[nt][0] *= corr[0]; o[nt][1] *= corr[0]; o[nt][2] *= corr[1]; o[nt][3] *= corr[1]; }
+#pragma unroll
+        for (int kk = 0; kk < 2; kk++) {
+#pragma unroll
+            for (int n2 = 0; n2 < 8; n2++) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_trans(vs_addr + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kPitch + n2 * 32 + (lane >> 4) * 16, b0, b1, b2, b3);
+                mma_bf16_full(o[2 * n2], ph[kk], b0, b1);
+                mma_bf16_full(o[2 * n2], pl[kk], b0, b1);
+                mma_bf16_full(o[2 * n2 + 1], ph[kk], b2, b3);
+                mma_bf16_full(o[2 * n2 + 1], pl[kk], b2, b3);
+            }
+        }
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+        l_run[hf] += __shfl_xor_sync(AX_FULL, l_run[hf], 1);
+        l_run[hf] += __shfl_xor_sync(AX_FULL, l_run[hf], 2);
+    }
+    __syncthreads();
+    float* smm = reinterpret_cast<float*>(smem);              // [warp][16 rows][kST]
+#pragma unroll
+    for (int hf = 0; hf < 2; hf++) {
+        float* dst = smm + ((size_t)warp * 16 + quad + 8 * hf) * kST;
+        if (qi == 0) { dst[0] = m_run[hf] * 0.6931471805599453f; dst[1] = l_run[hf]; }
+#pragma unroll
+        for (int nt = 0; nt < 16; nt++) { dst[2 + nt * 8 + qi * 2] = o[nt][2 * hf]; dst[2 + nt * 8 + qi * 2 + 1] = o[nt][2 * hf + 1]; }
+    }
+    __syncthreads();
+    const int SP = dv.n_splits;
+    const int n_rows = (tok_hi - tok_lo) * G;                  // real rows of this group
+    for (int idx = tid; idx < n_rows * 128; idx += kThreads) {
+        const int r = idx >> 7, d = idx & 127;
+        float M = -CUDART_INF_F;
+        for (int w = 0; w < kWarps; w++) M = fmaxf(M, smm[((size_t)w * 16 + r) * kST]);
+        float L = 0.f, A = 0.f;
+        for (int w = 0; w < kWarps; w++) {
+            const float* sp = smm + ((size_t)w * 16 + r) * kST;
+            const float c = merge_exp(sp[0], M);
+            L = fmaf(c, sp[1], L); A = fmaf(c, sp[2 + d], A);
+        }
+        const int tok = tok_lo + r / G, head = kh * G + r % G;
+        if (S == 1) dv.out[(size_t)tok * dv.out_stride + (size_t)head * 128 + d] = A / L;
+        else {
+            float* P = dv.partials + (((size_t)tok * dv.n_heads + head) * SP + split) * kST;
+            P[2 + d] = A;
+            if (d == 0) { P[0] = M; P[1] = L; }
+        }
+    }
+    if (S == 1) return;
+    __threadfence();
+    __syncthreads();
+    unsigned* ticket = dv.tickets + (size_t)rg * gridDim.y + kh;
+    if (tid == 0) s_last = atomicAdd(ticket, 1u) == (unsigned)(S - 1);
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int idx = tid; idx < n_rows * 128; idx += kThreads) {
+        const int r = idx >> 7, d = idx & 127;
+        const int tok = tok_lo + r / G, head = kh * G + r % G;
+        const float* P = dv.partials + ((size_t)tok * dv.n_heads + head) * SP * kST;
+        float M = -CUDART_INF_F;
+        for (int i = 0; i < S; i++) M = fmaxf(M, P[(size_t)i * kST]);
+        float L = 0.f, A = 0.f;
+        for (int i = 0; i < S; i++) {
+            const float c = merge_exp(P[(size_t)i * kST], M);
+            L = fmaf(c, P[(size_t)i * kST + 1], L); A = fmaf(c, P[(size_t)i * kST + 2 + d], A);
+        }
+        dv.out[(size_t)tok * dv.out_stride + (size_t)head * 128 + d] = A / L;
+    }
+    if (tid == 0) *ticket = 0u;
+}
+
+}  // namespace
+
+bool ax_attn_mma_supported(const AxAttnArgs& a) {
+    if (a.hd != 128 || a.kv_dtype != ATLASX_BF16 || a.n_kv <= 0 || a.n_heads % a.n_kv) return false;
+    const int g = a.n_heads / a.n_kv;
+    if (g < 3 || g > 8) return false;
+    return ((((uintptr_t)a.q | (uintptr_t)a.kc | (uintptr_t)a.vc | (uintptr_t)a.out) & 15) == 0) && (a.seq_stride % 8 == 0);
+}
+
+// Splits so that the grid fills the GPU in whole waves (one CTA per SM) with at least 16 tiles per CTA.
+int ax_attn_mma_pick_splits(const atlasx_ctx* ctx, int n_kv, int batch, int max_rows) {
+    const int groups = n_kv * batch;
+    const int tiles = (max_rows + kTileRows - 1) / kTileRows;
+    int cap = tiles / 16; if (cap < 1) cap = 1; if (cap > 256) cap = 256;
+    int best = 1; double best_eff = -1.0;
+    for (int s = 1; s <= cap; s++) {
+        const double waves = (double)groups * s / ctx->sm_count;
+        const double eff = waves / (double)(long long)(waves + 0.999999);     // filled share of the last wave included
+        // prefer more CTAs at equal efficiency only while a single wave is not yet full
+        if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+    }
+    return best;
+}
+
+int ax_attn_mma_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
+    AX_ARG(ax_attn_mma_supported(a), "shape not covered by the tensor-core attention kernel");
+    static bool attr_done = false;
+    if (!attr_done) {
+        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        attr_done = true;
+    }
+    MmaDev dv;
+    dv.q = a.q; dv.kc = (const uint16_t*)a.kc; dv.vc = (const uint16_t*)a.vc; dv.out = a.out; dv.seq_stride = a.seq_stride;
+    dv.pos = a.pos; dv.pos_shared = a.pos_shared; dv.pos_scalar = a.pos_scalar;
+    dv.n_heads = a.n_heads; dv.n_kv = a.n_kv; dv.g = a.n_heads / a.n_kv; dv.window = a.window; dv.scale = a.scale;
+    dv.n_splits = a.n_splits < 1 ? 1 : a.n_splits;
+    if (a.scratch_partials && a.scratch_tickets) { dv.partials = a.scratch_partials; dv.tickets = a.scratch_tickets; }
+    else {
+        int rc = atlasx_ctx_ensure_attn_scratch(ctx, (size_t)a.batch * a.n_heads * dv.n_splits * kST, (size_t)a.batch * a.n_heads);
+        if (rc) return rc;
+        dv.partials = ctx->attn_partials; dv.tickets = ctx->attn_tickets;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)dv.n_splits, (unsigned)a.n_kv, (unsigned)a.batch);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel, dv));
+    return ATLASX_OK;
+}
+
+bool ax_attn_mma_chunk_supported(int hd, int n_heads, int n_kv, int kv_dtype) {
+    if (hd != 128 || kv_dtype != ATLASX_BF16 || n_kv <= 0 || n_heads % n_kv) return false;
+    const int g = n_heads / n_kv;
+    return g == 1 || g == 2 || g == 4 || g == 8 || g == 16;
+}
+int ax_attn_mma_chunk_splits(const atlasx_ctx* ctx, int n_heads, int n_kv, int n_tok, int max_rows) {
+    const int g = n_heads / n_kv, tpg = 16 / g;
+    const int groups = n_kv * ((n_tok + tpg - 1) / tpg);
+    const int tiles = (max_rows + kTileRows - 1) / kTileRows;
+    int s = (2 * ctx->sm_count + groups - 1) / groups;                     // about two waves of CTAs
+    const int cap = tiles / 8 > 1 ? tiles / 8 : 1;                          // at least eight tiles (two per warp) per CTA
+    if (s > cap) s = cap;
+    return s < 1 ? 1 : (s > 64 ? 64 : s);
+}
+size_t ax_attn_mma_chunk_partial_floats(int n_tok, int n_heads, int n_splits) { return (size_t)n_tok * n_heads * n_splits * kST; }
+
+int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a) {
+    AX_ARG(ax_attn_mma_chunk_supported(128, a.n_heads, a.n_kv, ATLASX_BF16), "shape not covered by the chunk attention kernel");
+    AX_ARG(a.q && a.kc && a.vc && a.out && a.pos0 && a.partials && a.tickets && a.n_tok >= 1 && a.n_tok <= 16, "bad argument");
+    static bool attr_done = false;
+    if (!attr_done) {
+        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        attr_done = true;
+    }
+    ChunkDev dv;
+    dv.q = a.q; dv.q_stride = a.q_stride; dv.kc = (const uint16_t*)a.kc; dv.vc = (const uint16_t*)a.vc;
+    dv.out = a.out; dv.out_stride = a.out_stride; dv.pos0 = a.pos0;
+    dv.n_tok = a.n_tok; dv.n_heads = a.n_heads; dv.n_kv = a.n_kv; dv.g = a.n_heads / a.n_kv; dv.window = a.window;
+    dv.n_splits = a.n_splits < 1 ? 1 : a.n_splits; dv.scale = a.scale;
+    dv.partials = a.partials; dv.tickets = a.tickets;
+    const int tpg = 16 / dv.g;
+    dim3 grid((unsigned)dv.n_splits, (unsigned)a.n_kv, (unsigned)((a.n_tok + tpg - 1) / tpg));
+    ax_attn_mma_chunk_kernel<<<grid, kThreads, kSmemBytes, ctx->stream>>>(dv);
+    AX_CHECK_LAUNCH("ax_attn_mma_chunk_kernel");
+    return ATLASX_OK;
+}

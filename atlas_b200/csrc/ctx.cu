@@ -6,6 +6,7 @@
 #include <vector>
 
 #include "attention.cuh"
+#include "attention_mma.cuh"
 #include "common.cuh"
 #include "elementwise.cuh"
 #include "gemv.cuh"
@@ -58,6 +59,7 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_ATTN_FUSED", &c->tune.attn_fused);
         env_int("ATLASX_ATTN_STAGES", &c->tune.attn_stages);
         env_int("ATLASX_ATTN_WAVE", &c->tune.attn_wave);
+        env_int("ATLASX_ATTN_MMA", &c->tune.attn_mma);
         env_int("ATLASX_PEER_ALLREDUCE", &c->tune.peer_allreduce);
         env_int("ATLASX_MAIL_REDUCE", &c->tune.mail_reduce);
         env_int("ATLASX_TP_SELECT", &c->tune.tp_select);
@@ -504,6 +506,10 @@ extern "C" int atlasx_decode_attention(atlasx_ctx* c, const atlasx_kvcache* kv, 
     a.seq_stride = (size_t)kv->max_seq * kv->n_kv * kv->hd;
     a.pos = c->pos_dev; a.batch = kv->batch; a.n_heads = n_heads; a.n_kv = kv->n_kv; a.hd = kv->hd;
     a.window = window; a.kv_dtype = kv->dtype; a.scale = scale;
+    if (c->tune.attn_mma && ax_attn_mma_supported(a)) {       // several query heads per KV head: tensor-core kernel
+        a.n_splits = ax_attn_mma_pick_splits(c, kv->n_kv, kv->batch, max_rows);
+        return ax_attn_mma_launch(c, a, false);
+    }
     a.n_splits = ax_attn_pick_splits(c, kv->n_kv, kv->batch, max_rows);
     return ax_attn_launch(c, a, false);
 }

@@ -31,21 +31,23 @@ namespace {
 // partial sum in shared memory (zero if it had no part in it); after a barrier one thread per
 // pair adds the eight values in warp order — deterministic — and applies the epilogue.
 // ── quantised formats on the integer dot-product unit ─────────────────────────────
-// The f32 input is split once per launch into three int8 digit planes in base 254, with one
+// The f32 input is split once per launch into kPlanes int8 digit planes in base 254, with one
 // scale per 32 elements:
-//   x ≈ s_c·(q1 + q2/254 + q3/254²),  s_c = max|x| over the 32 elements / 127,  digits in [−127, 127],
-// leaving |error| ≤ s_c / (2·254²) ≈ 6e-8·max|x| — the size of an f32 rounding, far inside the
-// 1e-3 parity bar.  The weights are then used as they lie in memory (int8 words; int4 nibbles
+//   x ≈ s_c·(q1 + q2/254 [+ q3/254²]),  s_c = max|x| over the 32 elements / 127,  digits in [−127, 127].
+// Two planes leave |error| ≤ s_c / (2·254) ≈ 1.6e-5·max|x| of the group per element — errors of
+// random sign that add up to ≈ 1e-5 of the result, a hundred times inside the 1e-3 parity bar —
+// for two thirds of the integer dot products of three planes (which would leave 6e-8·max|x|).  The weights are then used as they lie in memory (int8 words; int4 nibbles
 // spread to bytes with two logic operations) in dp4a instructions with integer-exact sums:
 // 0.75 (int8) or 1 (int4) instruction per element instead of 3 for convert-subtract-FMA.
 // Scales per 32 elements need no block-wide reduction: eight neighbouring threads own a group.
 constexpr float kDigitBase = 254.0f;
+constexpr int kPlanes = 2;
 __host__ __device__ constexpr int digit_plane_bytes(int K) { return (K + 127) / 128 * 128; }
 __host__ __device__ constexpr int digit_groups(int K) { return ((K + 31) / 32 + 31) / 32 * 32; }
-// three planes, the group scales, and for int4 three tables of digit sums per group (the +8 offset of the nibbles)
+// the planes, the group scales, and for int4 one table of digit sums per plane and group (the +8 offset of the nibbles)
 __host__ __device__ constexpr int digit_bytes(int fmt, int K) {
-    return fmt == ATLASX_INT8 ? 3 * digit_plane_bytes(K) + digit_groups(K) * 4
-         : fmt == ATLASX_INT4 ? 3 * digit_plane_bytes(K) + 4 * digit_groups(K) * 4 : 0;
+    return fmt == ATLASX_INT8 ? kPlanes * digit_plane_bytes(K) + digit_groups(K) * 4
+         : fmt == ATLASX_INT4 ? kPlanes * digit_plane_bytes(K) + (1 + kPlanes) * digit_groups(K) * 4 : 0;
 }
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
     int d; asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
@@ -100,7 +102,7 @@ __device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* 
             for (int o = 1; o < 8; o <<= 1) {
                 t1 += __shfl_xor_sync(AX_FULL, t1, o); t2 += __shfl_xor_sync(AX_FULL, t2, o); t3 += __shfl_xor_sync(AX_FULL, t3, o);
             }
-            if (in && (k4 & 7) == 0) { bs[k4 >> 3] = t1; bs[ng + (k4 >> 3)] = t2; bs[2 * ng + (k4 >> 3)] = t3; }
+            if (in && (k4 & 7) == 0) { bs[k4 >> 3] = t1; bs[ng + (k4 >> 3)] = t2; if (kPlanes > 2) bs[2 * ng + (k4 >> 3)] = t3; }
         }
         if (!in) continue;
         if ((k4 & 7) == 0) xsc[k4 >> 3] = mx / 127.0f + bad;
@@ -108,7 +110,7 @@ __device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* 
             auto word = [](const int (&d)[4]) { return (uint32_t)(d[0] & 255) | ((uint32_t)(d[1] & 255) << 8) | ((uint32_t)(d[2] & 255) << 16) | ((uint32_t)(d[3] & 255) << 24); };
             reinterpret_cast<uint32_t*>(xq)[k4] = word(d1);
             reinterpret_cast<uint32_t*>(xq + pb)[k4] = word(d2);
-            reinterpret_cast<uint32_t*>(xq + 2 * pb)[k4] = word(d3);
+            if (kPlanes > 2) reinterpret_cast<uint32_t*>(xq + 2 * pb)[k4] = word(d3);
         } else {
             // elements 4k4..4k4+3 sit at j0..j0+3 of their group of eight (j0 = 0 or 4): the even ones
             // go to bytes j0/2, j0/2+1 of the group, the odd ones to bytes 4+j0/2, 4+j0/2+1
@@ -116,7 +118,7 @@ __device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* 
             auto half = [](int lo, int hi) { return (uint16_t)((lo & 255) | ((hi & 255) << 8)); };
             *reinterpret_cast<uint16_t*>(xq + g8 + h) = half(d1[0], d1[2]);           *reinterpret_cast<uint16_t*>(xq + g8 + 4 + h) = half(d1[1], d1[3]);
             *reinterpret_cast<uint16_t*>(xq + pb + g8 + h) = half(d2[0], d2[2]);      *reinterpret_cast<uint16_t*>(xq + pb + g8 + 4 + h) = half(d2[1], d2[3]);
-            *reinterpret_cast<uint16_t*>(xq + 2 * pb + g8 + h) = half(d3[0], d3[2]);  *reinterpret_cast<uint16_t*>(xq + 2 * pb + g8 + 4 + h) = half(d3[1], d3[3]);
+            if (kPlanes > 2) { *reinterpret_cast<uint16_t*>(xq + 2 * pb + g8 + h) = half(d3[0], d3[2]);  *reinterpret_cast<uint16_t*>(xq + 2 * pb + g8 + 4 + h) = half(d3[1], d3[3]); }
         }
     }
     consumer_sync<NTHR>();
@@ -216,7 +218,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                     // 16 elements: four weight words against four digit words per plane, then the group's scale
                     float f0 = 0.f, f1 = 0.f;
 #pragma unroll
-                    for (int pl = 0; pl < 3; pl++) {
+                    for (int pl = 0; pl < kPlanes; pl++) {
                         const uint4 q = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 16);
                         int t0 = dp4a_ss(wa[u].x, q.x, 0); t0 = dp4a_ss(wa[u].y, q.y, t0); t0 = dp4a_ss(wa[u].z, q.z, t0); t0 = dp4a_ss(wa[u].w, q.w, t0);
                         int t1 = 0;
@@ -236,7 +238,7 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                     const uint32_t wy[4] = { wb[u].x ^ 0x88888888u, wb[u].y ^ 0x88888888u, wb[u].z ^ 0x88888888u, wb[u].w ^ 0x88888888u };
                     float f0 = 0.f, f1 = 0.f;
 #pragma unroll
-                    for (int pl = 0; pl < 3; pl++) {
+                    for (int pl = 0; pl < kPlanes; pl++) {
                         const uint4 qa = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 32);
                         const uint4 qb = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 32 + 16);
                         const uint32_t qe[4] = { qa.x, qa.z, qb.x, qb.z }, qo[4] = { qa.y, qa.w, qb.y, qb.w };
@@ -329,7 +331,7 @@ ax_gemv_stream_kernel(const GemvArgs a) {
         uint8_t* after_x = ring + (a.pro.base_early ? x_bytes : 0);
         uint32_t* sland = reinterpret_cast<uint32_t*>(after_x);                              // int4 only: [2][8][threads] scale slots
         uint8_t* xq = after_x + (FMT == ATLASX_INT4 ? scale_land_bytes(NTHR) : 0);
-        float* xsc = reinterpret_cast<float*>(xq + 3 * digit_plane_bytes(a.K));              // scale per 32 input elements
+        float* xsc = reinterpret_cast<float*>(xq + kPlanes * digit_plane_bytes(a.K));              // scale per 32 input elements
         int* bs = reinterpret_cast<int*>(xsc + digit_groups(a.K));                           // int4: digit sums per 32 elements
         float* part = reinterpret_cast<float*>(xq + digit_bytes(FMT, a.K));                  // [pairs][warps][2]
         consume_direct<FMT, NTHR>(a, xs, xb, red, part, sland, xq, xsc, bs, lo, hi);

@@ -91,6 +91,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
                    bool pdl = false, const AxPeerOut* peer = nullptr);
 // Tensor-core path for n = 2..16 columns (bf16 / int8 / int4 weights); X [cols×n], Y [rows×n] row-major f32.
 bool ax_gemv_mma_supported(const AxWeight& w, int n, const float* x, const float* y);
+size_t ax_gemv_mma_scratch_bytes(int rows, int cols);   // context scratch one such product needs
 // token_major: X is [n][cols] and Y is [n][rows] (one contiguous vector per column).
 int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false);
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "attention.cuh"
+#include "attention_mma.cuh"
 #include "comm.h"
 #include "common.cuh"
 #include "elementwise.cuh"
@@ -104,6 +105,7 @@ struct atlasx_model {
     float *pf_r = nullptr, *pf_a = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_o = nullptr,
           *pf_gu = nullptr, *pf_h = nullptr, *pf_dn = nullptr;
     int* pf_pos = nullptr;
+    float* pf_attn_partials = nullptr; unsigned* pf_attn_tickets = nullptr; int pf_attn_splits = 0;   // causal chunk attention (bf16 cache, head_dim 128)
     // timeline diagnostics of the captured step (ATLASX_STEP_TRACE)
     unsigned long long* step_trace = nullptr; int step_trace_slots = 0;
 };
@@ -573,6 +575,23 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
         if ((rc = ax_gemv_mma_launch(c, ly.qkv, a_in, n, m->pf_qkv, true))) return rc;
+        if (m->pf_attn_splits > 0) {
+            // QK-norm, RoPE and cache write of all n tokens at once, then ONE causal attention launch
+            AxQkPrepArgs qa;
+            qa.q = m->pf_qkv; qa.k = m->pf_qkv + m->q_rows; qa.v = m->pf_qkv + m->q_rows + m->kv_rows;
+            qa.q_norm = ly.q_norm; qa.k_norm = ly.k_norm; qa.cos_t = m->cos_t; qa.sin_t = m->sin_t;
+            qa.kc = ly.kv->k; qa.vc = ly.kv->v; qa.seq_stride = 0;
+            qa.pos = m->pf_pos; qa.pos_shared = 0; qa.batch = n;
+            qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype; qa.eps = 1e-6f;
+            qa.q_stride = (size_t)qkv_rows; qa.kv_in_stride = (size_t)qkv_rows;
+            if ((rc = ax_qk_prep_launch(c, qa, false))) return rc;
+            AxAttnChunkArgs ca;
+            ca.q = m->pf_qkv; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
+            ca.out = m->pf_att; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos;
+            ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
+            ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
+            if ((rc = ax_attn_mma_chunk_launch(c, ca))) return rc;
+        } else
         for (int i = 0; i < n; i++) {
             float* qkv = m->pf_qkv + (size_t)i * qkv_rows;
             float* out = m->pf_att + (size_t)i * m->q_rows;
@@ -1056,11 +1075,20 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
             (rc = dmalloc(m, (void**)&m->pf_o, P * d * 4)) || (rc = dmalloc(m, (void**)&m->pf_gu, P * 2 * (size_t)m->ffn_loc * 4)) ||
             (rc = dmalloc(m, (void**)&m->pf_h, P * (size_t)m->ffn_loc * 4)) || (rc = dmalloc(m, (void**)&m->pf_dn, P * d * 4)) ||
             (rc = dmalloc(m, (void**)&m->pf_pos, P * sizeof(int)))) return rc;
-        // scratch of the multi-column kernel for the widest input
-        int kmax = d > m->ffn_loc ? d : m->ffn_loc;
-        if (m->q_rows > kmax) kmax = m->q_rows;
-        rc = atlasx_ctx_ensure_split_scratch(m->ctx, (size_t)2 * (kPrefillMax + 1) * ((size_t)kmax + 8192) * sizeof(uint16_t));
+        // scratch of the multi-column kernel for the largest of the layer's products
+        size_t need = 0;
+        for (const Layer& ly : m->layers) {
+            const AxWeight* ws[4] = { &ly.qkv, &ly.wo, &ly.gateup, &ly.down };
+            for (const AxWeight* w : ws) { const size_t b = ax_gemv_mma_scratch_bytes(w->rows, w->cols); if (b > need) need = b; }
+        }
+        rc = atlasx_ctx_ensure_split_scratch(m->ctx, need);
         if (rc) return rc;
+        if (m->cfg.kv_dtype == ATLASX_BF16 && ax_attn_mma_chunk_supported(m->hd, m->nh_loc, m->nkv_loc, m->cfg.kv_dtype)) {
+            m->pf_attn_splits = ax_attn_mma_chunk_splits(m->ctx, m->nh_loc, m->nkv_loc, (int)P, m->cfg.max_seq_len);
+            if ((rc = dmalloc(m, (void**)&m->pf_attn_partials, ax_attn_mma_chunk_partial_floats((int)P, m->nh_loc, m->pf_attn_splits) * 4)) ||
+                (rc = dmalloc(m, (void**)&m->pf_attn_tickets, (size_t)m->nkv_loc * P * sizeof(unsigned)))) return rc;
+            AX_CUDA(cudaMemsetAsync(m->pf_attn_tickets, 0, (size_t)m->nkv_loc * P * sizeof(unsigned), m->ctx->stream));
+        }
     }
     m->prefill_chunk = eff;
     if (effective) *effective = eff;
