@@ -2,10 +2,10 @@
 // query heads per KV head).
 //
 // With several query heads per KV head the scalar kernels of attention.cu are bound by
-// instruction issue, not by HBM: every cached row costs 128·G multiply-adds twice.  Here the G
-// query vectors of a KV head form the (zero-padded) 16-row A operand of mma.sync m16n8k16 and the
-// cached rows the B operand, so a 32-row tile of K and V costs a warp 128 tensor instructions
-// instead of ~8000 scalar ones.  Semantics are those of decode_attention_kernel of the reference
+// instruction issue, not by HBM: every cached row costs 128·G multiply-adds twice.  Here the
+// cached rows are the 16-row A operand of mma.sync m16n8k16 and the query heads of a KV head the 8
+// columns of B, so a 32-row tile of K and V costs a warp 32 tensor instructions (up to four heads;
+// 64 for five to eight) instead of ~8000 scalar ones.  Semantics are those of decode_attention_kernel of the reference
 // (kernels/matmul.cu:786-894): kv head = head / group, rows pos − t ≥ window masked, softmax over
 // the rest — computed flash-decoding style (online softmax, sequence split across CTAs and merged
 // by the last CTA of a head group).
@@ -72,13 +72,38 @@ struct MmaDev {
 
 __device__ __forceinline__ float merge_exp(float m, float M) { return (m == -CUDART_INF_F) ? 0.f : expf(m - M); }
 
+// movmatrix: transposes an 8×8 matrix of 16-bit elements held one 32-bit register per lane
+__device__ __forceinline__ uint32_t movmatrix_trans(uint32_t a) {
+    uint32_t d;
+    asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(d) : "r"(a));
+    return d;
+}
+__device__ __forceinline__ void mma_bf16_4(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Operand roles.  The warp-level MMA of this GPU is slow next to its HBM (about one m16n8k16 per ten
+// clocks and SM), so the kernel is built to issue as few of them as possible: the cached rows are the
+// 16-row A operand and the query heads the 8 columns of B.
+//   Sᵀ[16 keys × 8 cols] = K[16 keys × 16 dims]·Qᵀ[16 dims × 8 cols]      (A by ldmatrix from the staged K rows)
+//   Oᵀ[16 dims × 8 cols] = Vᵀ[16 dims × 16 keys]·Pᵀ[16 keys × 8 cols]     (A by ldmatrix.trans from the staged V rows,
+//                                                                           B from the Sᵀ fragments by movmatrix)
+// PACK (≤ 4 heads per KV head): columns 0..3 carry the bf16 hi parts of the heads' queries (and
+// probabilities), columns 4..7 the lo parts, so ONE MMA yields both products — 32 MMAs per 32-row
+// tile where the heads-as-rows form needs 128.  Otherwise (5..8 heads) columns are heads and the hi
+// and lo products are two MMAs into the same accumulator.
+template <bool PACK>
 __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_last;
     const int split = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = dv.g;
-    const int quad = lane >> 2, qi = lane & 3;               // row of the fragments, position inside the row's quad
+    const int quad = lane >> 2, qi = lane & 3;
+    // this thread's two columns 2·qi, 2·qi + 1 belong to heads hA, hA + 1; with PACK lanes qi ≥ 2 hold the lo parts
+    const int hA = PACK ? 2 * (qi & 1) : 2 * qi;
+    const bool lo_part = PACK && qi >= 2;
 
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -87,33 +112,34 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
     const int tb = (dv.window > 0 && pos - dv.window + 1 > 0) ? pos - dv.window + 1 : 0;      // pos − t < window
     const int te = pos + 1;
     const int rows = te - tb;
-    int S = dv.n_splits;
-    {   // splits in whole tiles, never more than there are tiles
-        const int tiles = (rows + kTileRows - 1) / kTileRows;
-        if (S > tiles) S = tiles;
-        if (S < 1) S = 1;
-    }
-    if (split >= S) return;
     const int tiles_all = (rows + kTileRows - 1) / kTileRows;
+    int S = dv.n_splits; if (S > tiles_all) S = tiles_all; if (S < 1) S = 1;
+    if (split >= S) return;
     const int tile0 = (int)((long long)tiles_all * split / S), tile1 = (int)((long long)tiles_all * (split + 1) / S);
     const int t0 = tb + tile0 * kTileRows, t1 = min(te, tb + tile1 * kTileRows);
     const int n_tiles = tile1 - tile0;                        // of this CTA; warp w takes tiles w, w + 4, …
     const int my_tiles = n_tiles > warp ? (n_tiles - warp + kWarps - 1) / kWarps : 0;
 
-    // ── query fragments: rows = the G heads of this KV head (scaled by scale·log2 e), hi + lo ──
-    uint32_t qh[8][2], ql[8][2];
+    // ── B fragments of Qᵀ: column `quad`, dims 16·ks + 2·qi + {0,1} and + 8; scaled by scale·log2 e, hi / lo ──
+    uint32_t qb[8][2], qb2[PACK ? 1 : 8][2];                  // qb2: the lo parts when columns are heads
     {
         const float sc = dv.scale * 1.4426950408889634f;
-        const float* qp = dv.q + ((size_t)b * dv.n_heads + (size_t)kh * G + quad) * 128;
+        const int head = PACK ? (quad & 3) : quad;
+        const bool want_lo = PACK && quad >= 4;
+        const bool ok = head < G;
+        const float* qp = dv.q + ((size_t)b * dv.n_heads + (size_t)kh * G + (ok ? head : 0)) * 128;
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
             float2 v0 = make_float2(0.f, 0.f), v1 = make_float2(0.f, 0.f);
-            if (quad < G) {
+            if (ok) {
                 v0 = *reinterpret_cast<const float2*>(qp + ks * 16 + qi * 2);
                 v1 = *reinterpret_cast<const float2*>(qp + ks * 16 + 8 + qi * 2);
             }
-            split2(v0.x * sc, v0.y * sc, qh[ks][0], ql[ks][0]);
-            split2(v1.x * sc, v1.y * sc, qh[ks][1], ql[ks][1]);
+            uint32_t h0, l0, h1, l1;
+            split2(v0.x * sc, v0.y * sc, h0, l0);
+            split2(v1.x * sc, v1.y * sc, h1, l1);
+            if (PACK) { qb[ks][0] = want_lo ? l0 : h0; qb[ks][1] = want_lo ? l1 : h1; }
+            else { qb[ks][0] = h0; qb[ks][1] = h1; qb2[ks][0] = l0; qb2[ks][1] = l1; }
         }
     }
 
@@ -142,10 +168,10 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
 #pragma unroll
     for (int j = 0; j < kStages - 1; j++) issue(j);
 
-    float o[16][4];
+    float ot[8][4];                                           // Oᵀ: 8 blocks of 16 dims × this thread's two columns
 #pragma unroll
-    for (int nt = 0; nt < 16; nt++) { o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f; }
-    float m_run = -CUDART_INF_F, l_run = 0.f;                  // of row `quad` (log2 domain); l is this lane's share
+    for (int md = 0; md < 8; md++) { ot[md][0] = ot[md][1] = ot[md][2] = ot[md][3] = 0.f; }
+    float m_run[2] = { -CUDART_INF_F, -CUDART_INF_F }, l_run[2] = { 0.f, 0.f };     // heads hA, hA + 1 (log2 domain); l: this lane's keys
 
     for (int j = 0; j < my_tiles; j++) {
         asm volatile("cp.async.wait_group %0;" :: "n"(kStages - 2) : "memory");
@@ -155,72 +181,111 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
         const uint8_t* st = wbase + (size_t)(j % kStages) * kStageBytes;
         const uint32_t ks_addr = smem_addr(st), vs_addr = smem_addr(st + kTileBytes);
 
-        // ── S = Q·Kᵀ: 4 column tiles of 8 rows of K, 8 steps of 16 dims, hi and lo ──
-        float s[4][4];
+        // ── Sᵀ: two blocks of 16 keys, 8 steps of 16 dims ──
+        float sT[2][4];
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+        for (int mt = 0; mt < 2; mt++) { sT[mt][0] = sT[mt][1] = sT[mt][2] = sT[mt][3] = 0.f; }
 #pragma unroll
-            for (int k2 = 0; k2 < 4; k2++) {                 // two 16-dim steps per ldmatrix.x4
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4(ks_addr + (nt * 8 + (lane & 7)) * kPitch + k2 * 64 + (lane >> 3) * 16, b0, b1, b2, b3);
-                mma_bf16(s[nt], qh[2 * k2][0], qh[2 * k2][1], b0, b1);
-                mma_bf16(s[nt], ql[2 * k2][0], ql[2 * k2][1], b0, b1);
-                mma_bf16(s[nt], qh[2 * k2 + 1][0], qh[2 * k2 + 1][1], b2, b3);
-                mma_bf16(s[nt], ql[2 * k2 + 1][0], ql[2 * k2 + 1][1], b2, b3);
+        for (int ks = 0; ks < 8; ks++) {
+#pragma unroll
+            for (int mt = 0; mt < 2; mt++) {
+                // matrices: (keys 0-7, dims 0-7) (keys 8-15, dims 0-7) (keys 0-7, dims 8-15) (keys 8-15, dims 8-15) of the block
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4(ks_addr + (mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kPitch + ks * 32 + (lane >> 4) * 16, a0, a1, a2, a3);
+                mma_bf16_4(sT[mt], a0, a1, a2, a3, qb[ks][0], qb[ks][1]);
+                if (!PACK) mma_bf16_4(sT[mt], a0, a1, a2, a3, qb2[ks][0], qb2[ks][1]);
             }
         }
-        // ── online softmax of row `quad` (columns nt·8 + 2·qi + {0,1}) ──
-        float mx = -CUDART_INF_F;
+        if (PACK) {                                            // hi columns + lo columns: lanes qi and qi ^ 2
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            const int c = tt + nt * 8 + qi * 2;
-            if (c >= t1) s[nt][0] = -CUDART_INF_F;
-            if (c + 1 >= t1) s[nt][1] = -CUDART_INF_F;
-            mx = fmaxf(mx, fmaxf(s[nt][0], s[nt][1]));
+            for (int mt = 0; mt < 2; mt++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) sT[mt][e] += __shfl_xor_sync(AX_FULL, sT[mt][e], 2);
         }
-        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(AX_FULL, mx, 2));
-        const float m_new = fmaxf(m_run, mx);
-        const float m_use = (m_new == -CUDART_INF_F) ? 0.f : m_new;
-        const float corr = fast_exp2(m_run - m_use);          // 0 for the first tile (m_run = −inf)
-        m_run = m_new;
-        l_run *= corr;
-        uint32_t ph[2][2], pl[2][2];                          // [16-row step of the tile][a0, a2]
+        // ── online softmax of heads hA (elements 0, 2) and hA + 1 (elements 1, 3); keys tt + 16·mt + quad (+ 8) ──
+        float mx[2] = { -CUDART_INF_F, -CUDART_INF_F };
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++) {
-            const float p0 = fast_exp2(s[nt][0] - m_use), p1 = fast_exp2(s[nt][1] - m_use);
-            l_run += p0 + p1;
-            split2(p0, p1, ph[nt >> 1][nt & 1], pl[nt >> 1][nt & 1]);
+        for (int mt = 0; mt < 2; mt++) {
+            const int k0 = tt + mt * 16 + quad;
+            if (k0 >= t1) { sT[mt][0] = -CUDART_INF_F; sT[mt][1] = -CUDART_INF_F; }
+            if (k0 + 8 >= t1) { sT[mt][2] = -CUDART_INF_F; sT[mt][3] = -CUDART_INF_F; }
+            mx[0] = fmaxf(mx[0], fmaxf(sT[mt][0], sT[mt][2]));
+            mx[1] = fmaxf(mx[1], fmaxf(sT[mt][1], sT[mt][3]));
+        }
+        float corr[2], m_use[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(AX_FULL, mx[h], 4));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(AX_FULL, mx[h], 8));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(AX_FULL, mx[h], 16));
+            const float m_new = fmaxf(m_run[h], mx[h]);
+            m_use[h] = (m_new == -CUDART_INF_F) ? 0.f : m_new;
+            corr[h] = fast_exp2(m_run[h] - m_use[h]);         // 0 for the first tile (m_run = −inf)
+            m_run[h] = m_new;
+            l_run[h] *= corr[h];
+        }
+        // probabilities → B fragments of Pᵀ (k = keys, n = columns) through movmatrix
+        uint32_t pb[2][2], pb2[PACK ? 1 : 2][2];              // [16-key block][keys 0-7 | keys 8-15]; pb2: lo parts when columns are heads
+#pragma unroll
+        for (int mt = 0; mt < 2; mt++) {
+            const float p0 = fast_exp2(sT[mt][0] - m_use[0]), p1 = fast_exp2(sT[mt][1] - m_use[1]);
+            const float p2 = fast_exp2(sT[mt][2] - m_use[0]), p3 = fast_exp2(sT[mt][3] - m_use[1]);
+            l_run[0] += p0 + p2; l_run[1] += p1 + p3;
+            uint32_t h01, l01, h23, l23;
+            split2(p0, p1, h01, l01);
+            split2(p2, p3, h23, l23);
+            if (PACK) {
+                pb[mt][0] = movmatrix_trans(lo_part ? l01 : h01);
+                pb[mt][1] = movmatrix_trans(lo_part ? l23 : h23);
+            } else {
+                pb[mt][0] = movmatrix_trans(h01); pb[mt][1] = movmatrix_trans(h23);
+                pb2[mt][0] = movmatrix_trans(l01); pb2[mt][1] = movmatrix_trans(l23);
+            }
         }
 #pragma unroll
-        for (int nt = 0; nt < 16; nt++) { o[nt][0] *= corr; o[nt][1] *= corr; }
-        // ── O += P·V: 2 steps of 16 rows, 16 column tiles of 8 dims, hi and lo ──
+        for (int md = 0; md < 8; md++) { ot[md][0] *= corr[0]; ot[md][1] *= corr[1]; ot[md][2] *= corr[0]; ot[md][3] *= corr[1]; }
+        // ── Oᵀ += Vᵀ·Pᵀ: 8 blocks of 16 dims, 2 steps of 16 keys ──
 #pragma unroll
         for (int kk = 0; kk < 2; kk++) {
 #pragma unroll
-            for (int n2 = 0; n2 < 8; n2++) {                 // two 8-dim column tiles per ldmatrix.x4.trans
-                uint32_t b0, b1, b2, b3;
-                ldsm_x4_trans(vs_addr + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kPitch + n2 * 32 + (lane >> 4) * 16, b0, b1, b2, b3);
-                mma_bf16(o[2 * n2], ph[kk][0], ph[kk][1], b0, b1);
-                mma_bf16(o[2 * n2], pl[kk][0], pl[kk][1], b0, b1);
-                mma_bf16(o[2 * n2 + 1], ph[kk][0], ph[kk][1], b2, b3);
-                mma_bf16(o[2 * n2 + 1], pl[kk][0], pl[kk][1], b2, b3);
+            for (int md = 0; md < 8; md++) {
+                // stored matrices (rows = keys): (keys 0-7, dims 0-7) (keys 0-7, dims 8-15) (keys 8-15, dims 0-7) (keys 8-15, dims 8-15);
+                // transposed on load they are a0..a3 of Vᵀ
+                uint32_t a0, a1, a2, a3;
+                ldsm_x4_trans(vs_addr + (kk * 16 + (lane >> 4) * 8 + (lane & 7)) * kPitch + md * 32 + ((lane >> 3) & 1) * 16, a0, a1, a2, a3);
+                mma_bf16_4(ot[md], a0, a1, a2, a3, pb[kk][0], pb[kk][1]);
+                if (!PACK) mma_bf16_4(ot[md], a0, a1, a2, a3, pb2[kk][0], pb2[kk][1]);
             }
         }
     }
     asm volatile("cp.async.wait_group 0;" ::: "memory");
 
     // ── merge the warps, then (last CTA of the head group) the splits ──
-    l_run += __shfl_xor_sync(AX_FULL, l_run, 1);
-    l_run += __shfl_xor_sync(AX_FULL, l_run, 2);
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        l_run[h] += __shfl_xor_sync(AX_FULL, l_run[h], 4);
+        l_run[h] += __shfl_xor_sync(AX_FULL, l_run[h], 8);
+        l_run[h] += __shfl_xor_sync(AX_FULL, l_run[h], 16);
+    }
+    if (PACK) {                                                // hi columns + lo columns of the output
+#pragma unroll
+        for (int md = 0; md < 8; md++)
+#pragma unroll
+            for (int e = 0; e < 4; e++) ot[md][e] += __shfl_xor_sync(AX_FULL, ot[md][e], 2);
+    }
     __syncthreads();                                          // all warps are done with their staging memory
     float* smm = reinterpret_cast<float*>(smem);              // [warp][G][kST]
-    if (quad < G) {
-        float* dst = smm + ((size_t)warp * G + quad) * kST;
-        if (qi == 0) { dst[0] = m_run * 0.6931471805599453f; dst[1] = l_run; }       // back to natural-log units
+    if (!lo_part) {
 #pragma unroll
-        for (int nt = 0; nt < 16; nt++) { dst[2 + nt * 8 + qi * 2] = o[nt][0]; dst[2 + nt * 8 + qi * 2 + 1] = o[nt][1]; }
+        for (int h = 0; h < 2; h++) {
+            const int head = hA + h;
+            if (head < G) {
+                float* dst = smm + ((size_t)warp * G + head) * kST;
+                if (quad == 0) { dst[0] = m_run[h] * 0.6931471805599453f; dst[1] = l_run[h]; }     // back to natural-log units
+#pragma unroll
+                for (int md = 0; md < 8; md++) { dst[2 + md * 16 + quad] = ot[md][h]; dst[2 + md * 16 + quad + 8] = ot[md][2 + h]; }
+            }
+        }
     }
     __syncthreads();
     const int SP = dv.n_splits;                               // partial slots per head
@@ -505,11 +570,11 @@ bool ax_attn_mma_supported(const AxAttnArgs& a) {
     return ((((uintptr_t)a.q | (uintptr_t)a.kc | (uintptr_t)a.vc | (uintptr_t)a.out) & 15) == 0) && (a.seq_stride % 8 == 0);
 }
 
-// Splits so that the grid fills the GPU in whole waves (one CTA per SM) with at least 16 tiles per CTA.
+// Splits so that the grid fills the GPU in whole waves (one CTA per SM), with at least one tile per warp.
 int ax_attn_mma_pick_splits(const atlasx_ctx* ctx, int n_kv, int batch, int max_rows) {
     const int groups = n_kv * batch;
     const int tiles = (max_rows + kTileRows - 1) / kTileRows;
-    int cap = tiles / 16; if (cap < 1) cap = 1; if (cap > 256) cap = 256;
+    int cap = tiles / 4; if (cap < 1) cap = 1; if (cap > 256) cap = 256;     // at least one tile per warp
     int best = 1; double best_eff = -1.0;
     for (int s = 1; s <= cap; s++) {
         const double waves = (double)groups * s / ctx->sm_count;
@@ -524,7 +589,8 @@ int ax_attn_mma_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
     AX_ARG(ax_attn_mma_supported(a), "shape not covered by the tensor-core attention kernel");
     static bool attr_done = false;
     if (!attr_done) {
-        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
+        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
         attr_done = true;
     }
     MmaDev dv;
@@ -549,7 +615,8 @@ int ax_attn_mma_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr; cfg.numAttrs = 1;
     }
-    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel, dv));
+    if (dv.g <= 4) AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel<true>, dv));
+    else AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel<false>, dv));
     return ATLASX_OK;
 }
 

@@ -558,6 +558,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     if (impl == 2) {
         a.pro.base_early = 0;
         const int grid = units < ctx->sm_count ? units : ctx->sm_count;
+        if (a.pro.ll_red_ctas > grid) a.pro.ll_red_ctas = grid;
         const size_t smem = 256 + x_bytes + (size_t)stages * a.stage_stride;
         switch (w.dtype) {
             case ATLASX_F32:  rc = launch_stream<ATLASX_F32, true>(ctx, a, grid, smem, pdl); break;
@@ -612,6 +613,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
             if (s2 > smem) { AX_ARG(s2 <= smem_max, "input vector does not fit in shared memory"); }
             smem = s2 > smem ? s2 : smem;
         }
+        if (a.pro.ll_red_ctas > grid) a.pro.ll_red_ctas = grid;     // every slice of the parts needs a CTA that sums it
         if (ctx->trace_next) { a.trace = ctx->trace_next; ctx->trace_next += 6; }
         if (wide) {
             switch (w.dtype) {

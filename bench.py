@@ -188,6 +188,65 @@ def cpu_baseline_sample(context=2049):
                       % (context + 1, n, full)}
 
 
+def ref_gpu_sample(ab, ctx, context, n_tok=8):
+    """Informational: the reference's OWN CUDA kernels (kernels/matmul.cu compiled unchanged into
+    oracle/_ref) replaying forward_one_gpu's launch sequence for the same model on this GPU, at the
+    benchmark's context length.  Kernels only: the Rust host's per-op allocations are not included, so this
+    is an upper bound on what the reference reaches here.  None when the checker library is absent."""
+    import ctypes as C
+    from oracle import orc
+    from atlas_b200 import _ffi
+    if not os.path.exists(orc.REF_SO):
+        return None
+    R = C.CDLL(orc.REF_SO)
+    vp, ci, cf = C.c_void_p, C.c_int, C.c_float
+    R.refgpu_model_new.restype = vp
+    R.refgpu_model_new.argtypes = [ci, ci, ci, ci, ci, ci, ci, cf, cf, ci, vp]
+    R.refgpu_model_free.argtypes = [vp]; R.refgpu_set_tensor.argtypes = [vp, ci, ci, vp, ci]
+    R.refgpu_upload_rope.argtypes = [vp, vp, vp]; R.refgpu_set_pos.argtypes = [vp, ci]
+    R.refgpu_forward_one.restype = ci; R.refgpu_forward_one.argtypes = [vp, C.c_uint32, vp]
+    R.atlas_sync.argtypes = []
+    L = _ffi.lib()
+    mc = model_config(ab, context + n_tok + 8)
+    d, f, V, hd = mc.d_model, mc.ffn_hidden, mc.vocab_size, 128
+    shapes = {"wq": (d, d), "wk": (d, d), "wv": (d, d), "wo": (d, d), "gate": (f, d), "up": (f, d), "down": (d, f)}
+    windows = (C.c_int * mc.n_layers)(*[(mc.sliding_window if t == ab.LAYER_SLIDING else 0) for t in mc.layer_types])
+    scale = float(np.float32(1.0) / np.sqrt(np.float32(hd)) * np.float32(mc.rope_scaling.attn_factor))
+    h = R.refgpu_model_new(V, d, mc.n_layers, mc.n_heads, mc.n_kv_heads, f, mc.max_seq_len, mc.rms_norm_eps, scale, 1, windows)
+    bufs = []
+
+    def mat(layer, which, rows, cols, stream):
+        p = ctx.malloc(rows * cols * 2); bufs.append(p)
+        _ffi.check(L.atlasx_fill_normal_bf16(ctx.handle, p, rows * cols, 0, stream, 0, 0.02))
+        assert R.refgpu_set_tensor(h, layer, which, p, 1) == 0
+    mat(0, 0, V, d, 1); mat(0, 2, V, d, 2)
+    ones = ctx.to_device(np.ones(d, np.float32)); bufs.append(ones)
+    assert R.refgpu_set_tensor(h, 0, 1, ones, 0) == 0
+    for l in range(mc.n_layers):
+        for name, tid in PER_LAYER:
+            mat(l, tid, shapes[name][0], shapes[name][1], 1000 + l * 32 + tid)
+        for tid in (17, 18, 19, 20):
+            assert R.refgpu_set_tensor(h, l, tid, ones, 0) == 0
+    cos, sin = ab.rope_tables(hd, mc.max_seq_len, mc.rope_theta, dict(factor=8.0, orig_max_pos=8192, beta_fast=32.0, beta_slow=1.0))
+    R.refgpu_upload_rope(h, cos.ctypes.data, sin.ctypes.data)
+    ctx.sync()
+    R.refgpu_set_pos(h, context)
+    tok = 11
+    for _ in range(2):
+        assert R.refgpu_forward_one(h, tok, None) == 0
+    R.atlas_sync()
+    t0 = time.perf_counter()
+    for _ in range(n_tok):
+        assert R.refgpu_forward_one(h, tok, None) == 0
+    R.atlas_sync()
+    dt = time.perf_counter() - t0
+    R.refgpu_model_free(h)
+    for p in bufs:
+        ctx.free(p)
+    return {"value": n_tok / dt, "unit": UNIT, "what": "the reference's kernels (kernels/matmul.cu, unchanged) in forward_one_gpu's launch order "
+            "on this GPU, %d tokens from pos %d, host wall clock; no logits download, no per-op allocations" % (n_tok, context + 2)}
+
+
 def run_reference(args, rank):
     """CPU arm: the restatement of the reference's forward_one (oracle/) on the full model."""
     if rank != 0:
@@ -466,11 +525,18 @@ def main():
     if rank != 0:
         return
     cpu = None
+    gpu_launches = m.launches_per_step * steps
     if not args.no_cpu_baseline and world == 1:
         try:
             cpu = cpu_baseline_sample(args.prompt + 1)
         except Exception as e:       # the baseline is reported, never required
             cpu = {"value": None, "unit": UNIT, "cores": os.cpu_count(), "kind": "port", "sample": "failed: %s" % e}
+        if not PROFILE_LAYERS:
+            try:
+                del m                                           # the reference's kernels get the device to themselves
+                cpu["ref_gpu"] = ref_gpu_sample(ab, ctx, args.prompt + 1)
+            except Exception as e:
+                cpu["ref_gpu"] = {"value": None, "what": "failed: %s" % e}
     line = {"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": steps, "warmup": warm,
             "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic",
@@ -479,7 +545,7 @@ def main():
                        "timing": "median of %d regions of %d steps, CUDA events, max over ranks; regions (ms): %s"
                                  % (reps, steps, ", ".join("%.2f" % x for x in all_ms)),
                        "l2": "inputs larger than L2: 13.77 GB of weights stream per step"},
-            "clocks": clocks, "e2e": e2e, "gpu_launches": m.launches_per_step * steps,
+            "clocks": clocks, "e2e": e2e, "gpu_launches": gpu_launches,
             "first_tokens": [int(t) for t in toks[:8]], "tp_parity": tp_parity, "prompt_ingest": prompt_ingest,
             "roofline": roofline, "cpu_baseline": cpu}
     if PROFILE_LAYERS:

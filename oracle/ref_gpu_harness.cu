@@ -120,6 +120,9 @@ void refgpu_upload_rope(ref_model* m, const float* cos_h, const float* sin_h) {
 }
 
 void refgpu_reset(ref_model* m) { m->pos = 0; }
+/* measurement aid: continue at position `pos` as if a prompt of that length had been processed (the cache
+ * rows below keep whatever they hold — zeros after creation —, which costs the kernels the same traffic) */
+void refgpu_set_pos(ref_model* m, int pos) { m->pos = pos < 0 ? 0 : (pos >= m->max_seq ? m->max_seq - 1 : pos); }
 
 static void gemv(ref_w w, const float* x, float* y, int out_dim, int in_dim) {
     if (w.dtype) atlas_sgemm_bf16_f32((const uint16_t*)w.p, x, y, out_dim, 1, in_dim);

@@ -85,9 +85,11 @@ def test_config5_largest(ab):
     run_case(ab, 32, 8, 128, 32768, 8, 0, ab.BF16)
 
 
-@pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 128), (8, 8, 64), (8, 2, 64), (4, 2, 16), (15, 5, 64), (6, 2, 128), (9, 3, 64)])
+@pytest.mark.parametrize("nh,nkv,hd", [(32, 32, 128), (8, 8, 64), (8, 2, 64), (4, 2, 16), (15, 5, 64), (6, 2, 128), (9, 3, 64),
+                                       (16, 2, 128), (10, 2, 128), (14, 2, 128)])
 def test_head_layouts(ab, nh, nkv, hd):
-    """MHA (config 4), GQA groups of 1/2/3/4, small and odd head_dim (generic kernel)."""
+    """MHA (config 4), GQA groups of 1/2/3/4 and 5/7/8 (the two forms of the tensor-core kernel at head_dim 128),
+    small and odd head_dim (generic kernel)."""
     for dtype in (ab.BF16, ab.F32):
         run_case(ab, nh, nkv, hd, 300, 2, 0, dtype, positions=[299, 57])
 

@@ -83,7 +83,9 @@ def test_gemv_sweep_shapes(ab, impl, fmt, shape):
     z = orc.normal_f32(K, 42, 6, 1.0)
     yz = gm.sgemm_vec(ab.GpuVec.from_slice(z), 1).download()
     y2 = gm.sgemm_vec(ab.GpuVec.from_slice(2 * x + z), 1).download()
-    assert rel_err(y2, 2 * y + yz) <= 1e-5
+    # the quantised formats see the input through two base-254 digits per 32-element group (1.6e-5 of the group's
+    # maximum per element), so they are linear only to that resolution
+    assert rel_err(y2, 2 * y + yz) <= (1e-5 if fmt == "bf16" else 1e-4)
 
 
 def test_gemv_lm_head_shape(ab, impl):
