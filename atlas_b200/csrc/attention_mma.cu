@@ -93,8 +93,11 @@ __device__ __forceinline__ void mma_bf16_4(float (&c)[4], uint32_t a0, uint32_t 
 // probabilities), columns 4..7 the lo parts, so ONE MMA yields both products — 32 MMAs per 32-row
 // tile where the heads-as-rows form needs 128.  Otherwise (5..8 heads) columns are heads and the hi
 // and lo products are two MMAs into the same accumulator.
-template <bool PACK>
-__global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) {
+template <bool PACK, int WARPS, int STAGES, int TR>
+__global__ void __launch_bounds__(WARPS * 32) ax_attn_mma_kernel(const MmaDev dv) {
+    constexpr int kWarps = WARPS, kThreads = WARPS * 32, kStages = STAGES, kTileRows = TR;      // TR: 16 or 32 cached rows per warp tile
+    constexpr int kTileBytes = TR * kPitch, kStageBytes = 2 * kTileBytes, kWarpBytes = STAGES * kStageBytes;
+    constexpr int kMT = TR / 16;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_last;
     const int split = blockIdx.x, kh = blockIdx.y, b = blockIdx.z;
@@ -147,14 +150,14 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
     const size_t row_elems = (size_t)dv.n_kv * 128;
     const uint16_t* kg = dv.kc + (size_t)b * dv.seq_stride + (size_t)kh * 128;
     const uint16_t* vg = dv.vc + (size_t)b * dv.seq_stride + (size_t)kh * 128;
-    // tile j of this warp → stage j % kStages; each lane copies 16 pieces of K and 16 of V (row = 2i + lane/16, piece = lane % 16)
+    // tile j of this warp → stage j % kStages; each lane copies TR/2 pieces of K and as many of V (row = 2i + lane/16, piece = lane % 16)
     auto issue = [&](int j) {
         if (j < my_tiles) {
             const int tt = t0 + (warp + j * kWarps) * kTileRows;
             uint8_t* st = wbase + (size_t)(j % kStages) * kStageBytes;
             const int piece = lane & 15;
 #pragma unroll
-            for (int i = 0; i < 16; i++) {
+            for (int i = 0; i < TR / 2; i++) {
                 const int r = i * 2 + (lane >> 4);
                 const int t = tt + r;
                 const bool ok = t < t1;
@@ -182,13 +185,13 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
         const uint32_t ks_addr = smem_addr(st), vs_addr = smem_addr(st + kTileBytes);
 
         // ── Sᵀ: two blocks of 16 keys, 8 steps of 16 dims ──
-        float sT[2][4];
+        float sT[kMT][4];
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) { sT[mt][0] = sT[mt][1] = sT[mt][2] = sT[mt][3] = 0.f; }
+        for (int mt = 0; mt < kMT; mt++) { sT[mt][0] = sT[mt][1] = sT[mt][2] = sT[mt][3] = 0.f; }
 #pragma unroll
         for (int ks = 0; ks < 8; ks++) {
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++) {
+            for (int mt = 0; mt < kMT; mt++) {
                 // matrices: (keys 0-7, dims 0-7) (keys 8-15, dims 0-7) (keys 0-7, dims 8-15) (keys 8-15, dims 8-15) of the block
                 uint32_t a0, a1, a2, a3;
                 ldsm_x4(ks_addr + (mt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * kPitch + ks * 32 + (lane >> 4) * 16, a0, a1, a2, a3);
@@ -198,14 +201,14 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
         }
         if (PACK) {                                            // hi columns + lo columns: lanes qi and qi ^ 2
 #pragma unroll
-            for (int mt = 0; mt < 2; mt++)
+            for (int mt = 0; mt < kMT; mt++)
 #pragma unroll
                 for (int e = 0; e < 4; e++) sT[mt][e] += __shfl_xor_sync(AX_FULL, sT[mt][e], 2);
         }
         // ── online softmax of heads hA (elements 0, 2) and hA + 1 (elements 1, 3); keys tt + 16·mt + quad (+ 8) ──
         float mx[2] = { -CUDART_INF_F, -CUDART_INF_F };
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
+        for (int mt = 0; mt < kMT; mt++) {
             const int k0 = tt + mt * 16 + quad;
             if (k0 >= t1) { sT[mt][0] = -CUDART_INF_F; sT[mt][1] = -CUDART_INF_F; }
             if (k0 + 8 >= t1) { sT[mt][2] = -CUDART_INF_F; sT[mt][3] = -CUDART_INF_F; }
@@ -225,9 +228,9 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
             l_run[h] *= corr[h];
         }
         // probabilities → B fragments of Pᵀ (k = keys, n = columns) through movmatrix
-        uint32_t pb[2][2], pb2[PACK ? 1 : 2][2];              // [16-key block][keys 0-7 | keys 8-15]; pb2: lo parts when columns are heads
+        uint32_t pb[kMT][2], pb2[PACK ? 1 : kMT][2];              // [16-key block][keys 0-7 | keys 8-15]; pb2: lo parts when columns are heads
 #pragma unroll
-        for (int mt = 0; mt < 2; mt++) {
+        for (int mt = 0; mt < kMT; mt++) {
             const float p0 = fast_exp2(sT[mt][0] - m_use[0]), p1 = fast_exp2(sT[mt][1] - m_use[1]);
             const float p2 = fast_exp2(sT[mt][2] - m_use[0]), p3 = fast_exp2(sT[mt][3] - m_use[1]);
             l_run[0] += p0 + p2; l_run[1] += p1 + p3;
@@ -246,7 +249,7 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_kernel(const MmaDev dv) 
         for (int md = 0; md < 8; md++) { ot[md][0] *= corr[0]; ot[md][1] *= corr[1]; ot[md][2] *= corr[0]; ot[md][3] *= corr[1]; }
         // ── Oᵀ += Vᵀ·Pᵀ: 8 blocks of 16 dims, 2 steps of 16 keys ──
 #pragma unroll
-        for (int kk = 0; kk < 2; kk++) {
+        for (int kk = 0; kk < kMT; kk++) {
 #pragma unroll
             for (int md = 0; md < 8; md++) {
                 // stored matrices (rows = keys): (keys 0-7, dims 0-7) (keys 0-7, dims 8-15) (keys 8-15, dims 0-7) (keys 8-15, dims 8-15);
@@ -570,29 +573,73 @@ bool ax_attn_mma_supported(const AxAttnArgs& a) {
     return ((((uintptr_t)a.q | (uintptr_t)a.kc | (uintptr_t)a.vc | (uintptr_t)a.out) & 15) == 0) && (a.seq_stride % 8 == 0);
 }
 
-// Splits so that the grid fills the GPU in whole waves (one CTA per SM), with at least one tile per warp.
+// Split count by a small cost model: the launch takes ⌈CTAs / SMs⌉ waves (one CTA per SM), and a CTA costs
+// its share of a head group's tiles spread over its four warps plus a fixed part (query split, merges,
+// partial results) worth about two tiles per warp.
+namespace {
+// shapes of the operator kernel: warps, stages, cached rows per warp tile, CTAs that fit one SM's shared memory
+struct MmaShape { int warps, stages, rows, per_sm; };
+constexpr MmaShape kShapes[] = { {6, 2, 32, 1}, {4, 3, 32, 1}, {8, 3, 16, 1}, {12, 2, 16, 1}, {6, 4, 16, 1}, {8, 2, 16, 1},
+                                 {6, 2, 16, 2}, {4, 2, 16, 3}, {4, 3, 16, 2} };
+constexpr int kNumShapes = (int)(sizeof(kShapes) / sizeof(kShapes[0]));
+// Many (sequence, KV head) groups: two smaller CTAs per SM, so that one CTA's pipeline fill and merge run
+// under the other's steady state.  Few groups: one CTA per SM with eight warps, fewer and longer splits.
+inline int shape_index(const atlasx_ctx* ctx, int groups) {
+    const int i = ctx->tune.attn_cfg;
+    if (i >= 0 && i < kNumShapes) return i;
+    return groups >= 2 * ctx->sm_count ? 6 : 5;
+}
+}  // namespace
+
+// Splits per (sequence, KV head): the cost of a launch is modelled as waves of CTAs × (tiles one warp
+// walks + a fixed two tiles for the pipeline fill and the merge); the cheapest split count wins.
 int ax_attn_mma_pick_splits(const atlasx_ctx* ctx, int n_kv, int batch, int max_rows) {
     const int groups = n_kv * batch;
-    const int tiles = (max_rows + kTileRows - 1) / kTileRows;
-    int cap = tiles / 4; if (cap < 1) cap = 1; if (cap > 256) cap = 256;     // at least one tile per warp
-    int best = 1; double best_eff = -1.0;
+    const MmaShape& sh = kShapes[shape_index(ctx, groups)];
+    const int tiles = (max_rows + sh.rows - 1) / sh.rows;
+    int cap = tiles / sh.warps; if (cap < 1) cap = 1; if (cap > 128) cap = 128;     // at least one tile per warp
+    const long long slots = (long long)ctx->sm_count * sh.per_sm;
+    const double fixed = 2.0 * 32 / sh.rows / sh.per_sm;        // co-resident CTAs hide each other's fill
+    int best = 1; double best_cost = 1e300;
     for (int s = 1; s <= cap; s++) {
-        const double waves = (double)groups * s / ctx->sm_count;
-        const double eff = waves / (double)(long long)(waves + 0.999999);     // filled share of the last wave included
-        // prefer more CTAs at equal efficiency only while a single wave is not yet full
-        if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+        const long long ctas = (long long)groups * s;
+        const double waves = (double)((ctas + slots - 1) / slots);
+        const double per_warp = (double)((tiles + s - 1) / s + sh.warps - 1) / sh.warps;
+        const double cost = waves * (per_warp + fixed);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
     return best;
 }
 
+namespace {
+template <bool PACK, int WARPS, int STAGES, int TR>
+int launch_mma_cfg(atlasx_ctx* ctx, const MmaDev& dv, int batch, bool pdl) {
+    constexpr size_t smem = (size_t)WARPS * STAGES * 2 * TR * kPitch;
+    static_assert(smem >= (size_t)WARPS * 8 * kST * sizeof(float), "the warps' merge area reuses the staging memory");
+    static bool attr_done[64] = {};                          // per device: the attribute belongs to the device's copy of the function
+    const int dev = ctx->device & 63;
+    if (!attr_done[dev]) {
+        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel<PACK, WARPS, STAGES, TR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        attr_done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)dv.n_splits, (unsigned)dv.n_kv, (unsigned)batch);
+    cfg.blockDim = dim3(WARPS * 32);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel<PACK, WARPS, STAGES, TR>, dv));
+    return ATLASX_OK;
+}
+}  // namespace
+
 int ax_attn_mma_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
     AX_ARG(ax_attn_mma_supported(a), "shape not covered by the tensor-core attention kernel");
-    static bool attr_done = false;
-    if (!attr_done) {
-        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        attr_done = true;
-    }
     MmaDev dv;
     dv.q = a.q; dv.kc = (const uint16_t*)a.kc; dv.vc = (const uint16_t*)a.vc; dv.out = a.out; dv.seq_stride = a.seq_stride;
     dv.pos = a.pos; dv.pos_shared = a.pos_shared; dv.pos_scalar = a.pos_scalar;
@@ -604,20 +651,20 @@ int ax_attn_mma_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
         if (rc) return rc;
         dv.partials = ctx->attn_partials; dv.tickets = ctx->attn_tickets;
     }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)dv.n_splits, (unsigned)a.n_kv, (unsigned)a.batch);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = kSmemBytes;
-    cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
-    if (pdl) {
-        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[0].val.programmaticStreamSerializationAllowed = 1;
-        cfg.attrs = attr; cfg.numAttrs = 1;
+    const bool pack = dv.g <= 4 && ctx->tune.attn_pack != 0;
+    switch (shape_index(ctx, a.n_kv * a.batch)) {           // rows of kShapes
+#define AX_CFG(n, W, S, T) case n: return pack ? launch_mma_cfg<true, W, S, T>(ctx, dv, a.batch, pdl) : launch_mma_cfg<false, W, S, T>(ctx, dv, a.batch, pdl)
+        AX_CFG(1, 4, 3, 32);
+        AX_CFG(2, 8, 3, 16);
+        AX_CFG(3, 12, 2, 16);
+        AX_CFG(4, 6, 4, 16);
+        AX_CFG(5, 8, 2, 16);
+        AX_CFG(6, 6, 2, 16);
+        AX_CFG(7, 4, 2, 16);
+        AX_CFG(8, 4, 3, 16);
+        default: AX_CFG(0, 6, 2, 32);
+#undef AX_CFG
     }
-    if (dv.g <= 4) AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel<true>, dv));
-    else AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_kernel<false>, dv));
-    return ATLASX_OK;
 }
 
 bool ax_attn_mma_chunk_supported(int hd, int n_heads, int n_kv, int kv_dtype) {

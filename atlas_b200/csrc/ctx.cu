@@ -60,6 +60,8 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_ATTN_STAGES", &c->tune.attn_stages);
         env_int("ATLASX_ATTN_WAVE", &c->tune.attn_wave);
         env_int("ATLASX_ATTN_MMA", &c->tune.attn_mma);
+        env_int("ATLASX_ATTN_PACK", &c->tune.attn_pack);
+        env_int("ATLASX_ATTN_CFG", &c->tune.attn_cfg);
         env_int("ATLASX_PEER_ALLREDUCE", &c->tune.peer_allreduce);
         env_int("ATLASX_MAIL_REDUCE", &c->tune.mail_reduce);
         env_int("ATLASX_TP_SELECT", &c->tune.tp_select);
@@ -494,17 +496,19 @@ extern "C" int atlasx_decode_attention(atlasx_ctx* c, const atlasx_kvcache* kv, 
     AX_ARG(c && kv && q && out && pos_host, "null argument");
     AX_ARG(window >= 0, "window must be non-negative");
     int rc = check_pos(kv, pos_host); if (rc) return rc;
-    rc = ensure_pos(c, pos_host, kv->batch); if (rc) return rc;
     int max_rows = 1;
-    for (int b = 0; b < kv->batch; b++) {
+    bool uniform = true;                  // every sequence at the same position (always so at batch 1): the position
+    for (int b = 0; b < kv->batch; b++) { // travels as a kernel argument and no copy is queued
         int r = pos_host[b] + 1;
         if (window > 0 && r > window) r = window;
         if (r > max_rows) max_rows = r;
+        uniform = uniform && pos_host[b] == pos_host[0];
     }
+    if (!uniform) { rc = ensure_pos(c, pos_host, kv->batch); if (rc) return rc; }
     AxAttnArgs a;
     a.q = q; a.kc = kv->k; a.vc = kv->v; a.out = out;
     a.seq_stride = (size_t)kv->max_seq * kv->n_kv * kv->hd;
-    a.pos = c->pos_dev; a.batch = kv->batch; a.n_heads = n_heads; a.n_kv = kv->n_kv; a.hd = kv->hd;
+    a.pos = uniform ? nullptr : c->pos_dev; a.pos_scalar = pos_host[0]; a.batch = kv->batch; a.n_heads = n_heads; a.n_kv = kv->n_kv; a.hd = kv->hd;
     a.window = window; a.kv_dtype = kv->dtype; a.scale = scale;
     if (c->tune.attn_mma && ax_attn_mma_supported(a)) {       // several query heads per KV head: tensor-core kernel
         a.n_splits = ax_attn_mma_pick_splits(c, kv->n_kv, kv->batch, max_rows);

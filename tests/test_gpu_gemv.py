@@ -128,7 +128,8 @@ def test_gemv_multi_column(ab, fmt, n, shape):
     Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
     assert rel_err(Y, orc.gemm(wo, X)) <= TOL
     y0 = gm.sgemm_vec(ab.GpuVec.from_slice(np.ascontiguousarray(X[:, 0])), 1).download()
-    assert rel_err(Y[:, 0], y0) <= 1e-5
+    # the single-column kernel sees a quantised matrix's input through two base-254 digits (≈1e-5 of the result)
+    assert rel_err(Y[:, 0], y0) <= (1e-5 if fmt == "bf16" else 1e-4)
 
 
 @pytest.mark.parametrize("fmt", ["int8", "int4"])

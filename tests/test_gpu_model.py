@@ -247,7 +247,8 @@ def test_head_dim_128_one_launch_attention_against_oracle(ab, kv, fmt):
     for t in toks:
         lo, hid = o.forward_one(int(t), want_hidden=True)
         assert np.max(np.abs(m.forward_one_gpu(int(t)) - lo)) <= tol
-        assert np.max(np.abs(m.hidden() - hid[-1])) <= tol
+        # the residual stream is not normalised (values of several units here): bound relative to its size
+        assert np.max(np.abs(m.hidden() - hid[-1])) <= tol * max(1.0, float(np.max(np.abs(hid[-1]))))
     if kv == "f32" and fmt == "f32":
         prompt = toks[:12]
         assert m.generate(prompt, 24, 0.0) == o.generate_greedy(prompt, 24).tolist()
