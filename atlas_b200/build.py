@@ -12,7 +12,7 @@ from concurrent.futures import ThreadPoolExecutor
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "lib")
-SOURCES = ["ctx.cu", "gemv.cu", "attention.cu", "elementwise.cu", "legacy_abi.cu", "model.cu", "comm.cu", "gemv_mma.cu", "loader.cu", "sampling.cu", "attention_mma.cu"]
+SOURCES = ["ctx.cu", "gemv.cu", "attention.cu", "elementwise.cu", "legacy_abi.cu", "model.cu", "comm.cu", "gemv_mma.cu", "loader.cu", "sampling.cu", "attention_mma.cu", "gemv_umma.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "-Xptxas", "-v"]
 LIB_SO = os.path.join(OUT, "libatlas_kernels.so")

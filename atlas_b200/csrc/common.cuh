@@ -62,6 +62,7 @@ struct atlasx_ctx {
         int attn_stages = 3;           // ATLASX_ATTN_STAGES: landing stages of the one-launch attention inside a step (2..4)
         int attn_wave = 2;             // ATLASX_ATTN_WAVE: attention CTAs per SM that one wave of splits may fill
         int attn_mma = 1;              // ATLASX_ATTN_MMA=0: operator-form GQA attention on the scalar kernels instead of the tensor cores
+        int umma = 1;                  // ATLASX_UMMA=0: token batches on the warp-level MMA kernel instead of tcgen05
         int attn_pack = 1;             // ATLASX_ATTN_PACK=0: ≤ 4 heads per KV head as columns with separate hi / lo MMAs
         int attn_cfg = -1;             // ATLASX_ATTN_CFG: shape (warps × stages × rows) of the tensor-core attention; -1 = by problem size
         int peer_allreduce = 1;        // ATLASX_PEER_ALLREDUCE=0: ncclAllReduce instead of the peer mailboxes

@@ -1,0 +1,410 @@
+// gemv_umma.cu — many-column weight-streaming product Y[n][M] = X[n][K]·W[M][K]ᵀ, n = 2..64 tokens, on the
+// fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory, operands brought into
+// shared memory by tiled bulk copies (cp.async.bulk.tensor) and handed over through mbarriers.
+//
+// It serves the same callers as the warp-level kernel of gemv_mma.cu — the token batches of prompt ingestion
+// and speculative verification, which the reference runs as one sgemm_bf16_kernel thread per output element
+// (kernels/matmul.cu:384-420) or token by token (crates/atlas-model/src/lib.rs:1611-1618) — and exists because
+// the warp-level MMA of this GPU is too slow to keep up with HBM beyond a few columns.
+//
+//   * Work item = (128-row tile of W, range of 64-element K blocks); one item per CTA, two CTAs per SM.  K is
+//     split so that short matrices still give every SM work; the partial tiles of a row tile meet in global
+//     scratch and the CTA that arrives last (ticket) adds them in split order, so the result does not depend
+//     on timing.
+//   * A operand: the W tile, 128 rows × 64 bf16 per stage (16 KB), 128-byte swizzle.  Rows beyond M are filled
+//     with zeros by the copy engine.
+//   * B operand: the tokens.  The f32 activations are split into bf16 hi + lo parts (x = hi + lo to 2⁻¹⁷
+//     relative) stored as 2·n8 rows of one plane (n8 = n rounded up to 8): rows 0..n8−1 hi, n8..2·n8−1 lo.
+//     One MMA of width N = 2·n8 yields both partial products; the epilogue adds column j and column n8 + j.
+//     Products with bf16 W are exact in the f32 accumulator, so the result matches an f32 dot product to the
+//     accumulation order.
+//   * Roles: warp 0 issues the copies, warp 1 owns tensor memory and issues the MMAs (one lane), warps 2..5
+//     read the accumulator (tcgen05.ld, one lane quarter each) and write Y or the partial tile.
+//   * Every wait on an mbarrier is bounded (two seconds of %globaltimer): on expiry the CTA raises the
+//     context's device error word, all roles leave their loops, copies in flight are waited for (bounded again)
+//     and tensor memory is released before the CTA returns.
+//   * The tensor maps cover this GPU's own memory only and no copy is multicast.
+#include <cuda.h>
+
+#include "gemv.cuh"
+
+namespace {
+
+constexpr int kTileM = 128;
+constexpr int kBlockK = 64;                       // bf16 elements per K block: 128 bytes, one swizzle row
+constexpr int kABytes = kTileM * kBlockK * 2;     // 16 KB
+constexpr int kThreads = 192;
+constexpr int kMaxStages = 8;
+constexpr int kMaxTokens = 64;
+constexpr int kMaxSplits = 8;
+constexpr unsigned long long kWaitNs = 2000000000ull;
+
+struct UmmaArgs {
+    float* Y;
+    int M, n, n8;                 // rows of W, tokens, tokens rounded up to 8
+    int KB, KS, T;                // K blocks, K splits, row tiles
+    int stages, b_bytes;          // pipeline depth, bytes of one B stage (2·n8 rows × 128)
+    int tmem_cols;                // power of two ≥ 32 holding 2·n8 accumulator columns
+    int token_major;              // Y[j·M + row] (one contiguous vector per token) or Y[row·n + j]
+    float* parts;                 // [T·KS][n][128] partial tiles (KS > 1)
+    unsigned* tickets;            // [T], zero between launches
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long global_ns() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait.  false: gave up (this thread's deadline passed, or another role raised the abort flag).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* err, int code) {
+    unsigned spins = 0;
+    unsigned long long t0 = 0;
+    while (!mbar_try(bar, parity)) {
+        if (*abort_flag) return false;
+        if ((++spins & 255u) == 0) {
+            const unsigned long long t = global_ns();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > kWaitNs) { *abort_flag = 1; atomicExch(err, code); return false; }
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory matrix descriptor of a K-major tile with 128-byte swizzle: rows of 128 bytes, groups of eight
+// rows 1024 bytes apart (stride offset), descriptor version 1, layout code 2.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {       // the barrier gets one arrival when every MMA issued so far is done
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
+    uint32_t r[8];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// f32 tokens → one bf16 plane [2·n8][K]: rows 0..n8−1 hi parts, rows n8..2·n8−1 lo parts, rows of absent tokens zero.
+// Also clears the tickets of the product that follows.
+__global__ void ax_umma_split_kernel(const float* __restrict__ X, int K, int n, int n8, int token_major,
+                                     uint16_t* __restrict__ plane, unsigned* tickets, int n_tickets) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx < (size_t)n_tickets) tickets[idx] = 0u;
+    const int k8 = K / 8;
+    if (idx >= (size_t)2 * n8 * k8) return;
+    const int row = (int)(idx / k8), kg = (int)(idx % k8);
+    const int j = row < n8 ? row : row - n8;
+    const bool lo = row >= n8;
+    uint32_t out[4] = { 0u, 0u, 0u, 0u };
+    if (j < n) {
+        float x[8];
+        if (token_major) {
+            const float4 a = *reinterpret_cast<const float4*>(X + (size_t)j * K + kg * 8);
+            const float4 b = *reinterpret_cast<const float4*>(X + (size_t)j * K + kg * 8 + 4);
+            x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+        } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) x[i] = X[(size_t)(kg * 8 + i) * n + j];
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const uint16_t h = ax_f32_to_bf16_rne(x[i]);
+            const uint16_t v = lo ? ax_f32_to_bf16_rne(x[i] - ax_bf16_to_f32(h)) : h;
+            out[i >> 1] |= (uint32_t)v << ((i & 1) * 16);
+        }
+    }
+    *reinterpret_cast<uint4*>(plane + (size_t)row * K + kg * 8) = make_uint4(out[0], out[1], out[2], out[3]);
+}
+
+__global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w,
+                                                                const __grid_constant__ CUtensorMap map_x, const UmmaArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], done_bar;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort, s_issued, s_last, s_go;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int tile = blockIdx.x / a.KS, ks = blockIdx.x % a.KS;
+    const int kb0 = (int)((long long)a.KB * ks / a.KS), kb1 = (int)((long long)a.KB * (ks + 1) / a.KS);
+    const int nkb = kb1 - kb0;
+    const int ST = a.stages;
+    const int NP = 2 * a.n8;
+    const uint32_t stage_bytes = (uint32_t)kABytes + (uint32_t)a.b_bytes;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;           // swizzled tiles want 1024-byte alignment
+    volatile int* abort_flag = &s_abort;
+
+    if (tid == 0) {
+        for (int s = 0; s < ST; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        mbar_init(smem_u32(&done_bar), 1);
+        s_abort = 0; s_issued = 0; s_last = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {                                                         // tensor memory: allocated and released by this warp
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"((uint32_t)a.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("griddepcontrol.wait;" ::: "memory");              // the token plane is written by the launch before
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % ST;
+                if (i >= ST && !mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((i / ST) - 1) & 1u, abort_flag, a.err, 701)) break;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                const uint32_t dst = smem0 + (uint32_t)s * stage_bytes;
+                mbar_expect_tx(bar, stage_bytes);
+                tma_load_2d(dst, &map_w, (kb0 + i) * kBlockK, tile * kTileM, bar);
+                tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * kBlockK, 0, bar);
+                s_issued = i + 1;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N = 2·n8, M = 128
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            bool ok = true;
+            for (int i = 0; i < nkb && ok; i++) {
+                const int s = i % ST;
+                ok = mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(i / ST) & 1u, abort_flag, a.err, 702);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sa = smem0 + (uint32_t)s * stage_bytes, sb = sa + kABytes;
+#pragma unroll
+                for (int k = 0; k < kBlockK / 16; k++)                       // 16 bf16 = 32 bytes along the swizzled row per MMA
+                    umma_bf16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                umma_commit(smem_u32(&empty_bar[s]));                        // the stage is free once these MMAs have read it
+            }
+            umma_commit(smem_u32(&done_bar));                                // also on the way out of a failed wait: see the tail
+        }
+    } else {
+        const int q = warp & 3;                                              // lane quarter of tensor memory this warp may read
+        const int r_in = q * 32 + lane, row = tile * kTileM + r_in;
+        // one thread waits and tells the other 127: a deadline that only some of them saw pass must not split the group
+        if (tid == 64) s_go = mbar_wait(smem_u32(&done_bar), 0u, abort_flag, a.err, 703) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_go) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t t_row = tmem + ((uint32_t)(q * 32) << 16);
+            float* part = a.parts + (size_t)blockIdx.x * a.n * kTileM;
+            for (int c = 0; c < a.n8; c += 8) {
+                float hi[8], lo[8];
+                tmem_ld8(t_row + (uint32_t)c, hi);
+                tmem_ld8(t_row + (uint32_t)(a.n8 + c), lo);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const int j = c + e;
+                    if (j < a.n) {
+                        const float v = hi[e] + lo[e];
+                        if (a.KS > 1) part[(size_t)j * kTileM + r_in] = v;
+                        else if (row < a.M) a.Y[a.token_major ? (size_t)j * a.M + row : (size_t)row * a.n + j] = v;
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (a.KS > 1) {
+                __threadfence();
+                asm volatile("bar.sync 1, 128;" ::: "memory");               // the four epilogue warps
+                if (tid == 64) s_last = atomicAdd(&a.tickets[tile], 1u) == (unsigned)(a.KS - 1);
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (s_last) {
+                    __threadfence();
+                    // [split][token][128 rows]: a thread adds four rows of every fourth token, splits in order;
+                    // the loads of two tokens × all splits are issued before the first addition
+                    const float* p0 = a.parts + (size_t)tile * a.KS * a.n * kTileM;
+                    const int et = tid - 64;                                 // 0..127
+                    const int r4 = (et & 31) * 4, jq = et >> 5;
+                    const size_t split_stride = (size_t)a.n * kTileM;
+                    for (int j0 = jq; j0 < a.n; j0 += 8) {
+                        float4 v[2][kMaxSplits];
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int j = j0 + 4 * u;
+#pragma unroll
+                            for (int s = 0; s < kMaxSplits; s++)
+                                if (j < a.n && s < a.KS) v[u][s] = __ldcg(reinterpret_cast<const float4*>(p0 + s * split_stride + (size_t)j * kTileM + r4));
+                        }
+#pragma unroll
+                        for (int u = 0; u < 2; u++) {
+                            const int j = j0 + 4 * u;
+                            if (j >= a.n) continue;
+                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                            for (int s = 0; s < kMaxSplits; s++)
+                                if (s < a.KS) { acc.x += v[u][s].x; acc.y += v[u][s].y; acc.z += v[u][s].z; acc.w += v[u][s].w; }
+                            const float o[4] = { acc.x, acc.y, acc.z, acc.w };
+#pragma unroll
+                            for (int e = 0; e < 4; e++) {
+                                const int rr = tile * kTileM + r4 + e;
+                                if (rr < a.M) a.Y[a.token_major ? (size_t)j * a.M + rr : (size_t)rr * a.n + j] = o[e];
+                            }
+                        }
+                    }
+                    if (tid == 64) a.tickets[tile] = 0u;
+                }
+            }
+        }
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+
+    // ── tail: nothing of this CTA may still be in flight when its shared and tensor memory go away ──
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort) {
+        if (tid == 0) {                                                      // copies issued into stages nobody consumed any more
+            const int issued = s_issued;
+            for (int i = issued > ST ? issued - ST : 0; i < issued; i++) {
+                unsigned long long t0 = global_ns();
+                while (!mbar_try(smem_u32(&full_bar[i % ST]), (uint32_t)(i / ST) & 1u) && global_ns() - t0 < kWaitNs) { }
+            }
+        }
+        if (tid == 32) {                                                     // MMAs issued before the failure: done_bar was committed behind them
+            unsigned long long t0 = global_ns();
+            while (!mbar_try(smem_u32(&done_bar), 0u) && global_ns() - t0 < kWaitNs) { }
+        }
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"((uint32_t)a.tmem_cols) : "memory");
+    }
+}
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// bf16 matrix [rows][cols] (cols contiguous), boxes of 64 columns × box_rows rows, 128-byte swizzle, zeros outside
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return atlasx_fail(ATLASX_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t dims[2] = { cols, rows };
+    const cuuint64_t strides[1] = { cols * 2 };
+    const cuuint32_t box[2] = { (cuuint32_t)kBlockK, box_rows };
+    const cuuint32_t elem[2] = { 1, 1 };
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return atlasx_fail(ATLASX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
+    return ATLASX_OK;
+}
+
+struct UmmaPlan { int n8, T, KB, KS, stages, b_bytes, tmem_cols; size_t plane_bytes, parts_bytes, ticket_bytes, smem; };
+
+UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n) {
+    UmmaPlan p;
+    p.n8 = (n + 7) / 8 * 8;
+    p.T = (rows + kTileM - 1) / kTileM;
+    p.KB = cols / kBlockK;
+    // K splits: enough items for two CTAs on every SM, at least eight K blocks (128 KB of W) per item
+    int ks = (2 * ctx->sm_count + p.T - 1) / p.T;
+    if (ks > p.KB / 8) ks = p.KB / 8;
+    if (ks > kMaxSplits) ks = kMaxSplits;
+    if (ks < 1) ks = 1;
+    p.KS = ks;
+    p.b_bytes = 2 * p.n8 * 128;
+    int st = (100 * 1024) / (kABytes + p.b_bytes);
+    if (st > kMaxStages) st = kMaxStages;
+    if (st < 2) st = 2;
+    p.stages = st;
+    int c = 32; while (c < 2 * p.n8) c <<= 1;
+    p.tmem_cols = c;
+    p.plane_bytes = ((size_t)2 * p.n8 * cols * 2 + 1023) / 1024 * 1024;
+    p.parts_bytes = p.KS > 1 ? (size_t)p.T * p.KS * n * kTileM * sizeof(float) : 0;
+    p.ticket_bytes = ((size_t)p.T * sizeof(unsigned) + 255) / 256 * 256;
+    p.smem = (size_t)st * (kABytes + p.b_bytes) + 1024;
+    return p;
+}
+
+}  // namespace
+
+bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y) {
+    if (n < 2 || n > kMaxTokens || !x || !y) return false;
+    if (w.dtype != ATLASX_BF16 || w.cols % kBlockK != 0 || w.cols < kBlockK) return false;
+    return (((uintptr_t)w.data | (uintptr_t)x) & 15) == 0;
+}
+
+size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, int rows, int cols, int n) {
+    const UmmaPlan p = make_plan(ctx, rows, cols, n);
+    return p.plane_bytes + p.parts_bytes + p.ticket_bytes;
+}
+
+int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
+    AX_ARG(ax_gemv_umma_supported(w, n, x, y), "shape or format not covered by the tcgen05 multi-column kernel");
+    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n);
+    int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.parts_bytes + p.ticket_bytes);
+    if (rc) return rc;
+    uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch);
+    uint16_t* plane = reinterpret_cast<uint16_t*>(base);
+    float* parts = reinterpret_cast<float*>(base + p.plane_bytes);
+    unsigned* tickets = reinterpret_cast<unsigned*>(base + p.plane_bytes + p.parts_bytes);
+
+    CUtensorMap map_w, map_x;
+    if ((rc = make_map(&map_w, w.data, (uint64_t)w.rows, (uint64_t)w.cols, kTileM))) return rc;
+    if ((rc = make_map(&map_x, plane, (uint64_t)2 * p.n8, (uint64_t)w.cols, (uint32_t)(2 * p.n8)))) return rc;
+
+    static bool attr_done[64] = {};
+    const int dev = ctx->device & 63;
+    if (!attr_done[dev]) {
+        AX_CUDA(cudaFuncSetAttribute(ax_gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+        attr_done[dev] = true;
+    }
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        const size_t work = (size_t)2 * p.n8 * (w.cols / 8);
+        const size_t threads = work > (size_t)p.T ? work : (size_t)p.T;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)((threads + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = ctx->stream;
+        if (pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }
+        AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, w.cols, n, p.n8, token_major ? 1 : 0, plane, tickets, p.T));
+    }
+    UmmaArgs a;
+    a.Y = y; a.M = w.rows; a.n = n; a.n8 = p.n8; a.KB = p.KB; a.KS = p.KS; a.T = p.T;
+    a.stages = p.stages; a.b_bytes = p.b_bytes; a.tmem_cols = p.tmem_cols; a.token_major = token_major ? 1 : 0;
+    a.parts = parts; a.tickets = tickets; a.err = ctx->dev_error;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(p.T * p.KS)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = p.smem; cfg.stream = ctx->stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;                                      // its producer warp waits for the split kernel itself
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_umma_kernel, map_w, map_x, a));
+    return ATLASX_OK;
+}

@@ -488,7 +488,8 @@ int run_step(atlasx_model* m, Profile* prof, bool advance, bool gather = true) {
     return ATLASX_OK;
 }
 
-constexpr int kPrefillMax = 16;
+constexpr int kPrefillMax = 64;                // tokens per chunk with the tcgen05 kernel; 16 with the warp-level one
+constexpr int kPrefillMaxMma = 16;
 
 // ── prompt ingestion: row-wise helpers, one CTA per token ───────────────────────────
 __global__ void pf_positions_k(const StepState* st, int* pos_arr, int n) {
@@ -547,14 +548,26 @@ __global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out) {
 }
 __global__ void pf_advance_k(StepState* st, int by) { st->pos += by; }
 
-bool prefill_supported(const atlasx_model* m) {
-    if (m->cfg.weight_format == ATLASX_F32) return false;
-    float dummy;
+// Largest chunk the layer products of this model can take: kPrefillMax when every matrix goes through the
+// tcgen05 kernel, kPrefillMaxMma when some need the warp-level one, 1 when neither covers a matrix.
+int prefill_limit(const atlasx_model* m) {
+    if (m->cfg.weight_format == ATLASX_F32) return 1;
+    alignas(16) static float dummy[4];
+    int limit = kPrefillMax;
     for (const Layer& ly : m->layers) {
         const AxWeight* ws[4] = { &ly.qkv, &ly.wo, &ly.gateup, &ly.down };
-        for (const AxWeight* w : ws) if (!ax_gemv_mma_supported(*w, 2, &dummy, &dummy)) return false;
+        for (const AxWeight* w : ws) {
+            if (m->ctx->tune.umma && ax_gemv_umma_supported(*w, 2, dummy, dummy)) continue;
+            if (!ax_gemv_mma_supported(*w, 2, dummy, dummy)) return 1;
+            limit = kPrefillMaxMma;
+        }
     }
-    return true;
+    return limit;
+}
+// One layer product of a chunk: X [n][cols] → Y [n][rows]
+int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y) {
+    if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, false);
+    return ax_gemv_mma_launch(c, w, x, n, y, true);
 }
 
 // n prompt tokens (2..kPrefillMax) at once: seq[pos .. pos+n) → caches, logits of the last one,
@@ -568,13 +581,13 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     const bool post = cf.post_norm != 0;
     const int qkv_rows = m->q_rows + 2 * m->kv_rows;
     int rc;
-    pf_positions_k<<<1, 32, 0, s>>>(m->st, m->pf_pos, n);
+    pf_positions_k<<<1, kPrefillMax, 0, s>>>(m->st, m->pf_pos, n);
     pf_embed_rows_k<<<n, 256, 0, s>>>(m->embed, m->embed_bf16, cf.vocab_size, m->seq, m->pf_pos, d, m->pf_r);
     const float* a_in = m->pf_r;
     if (!post) { pf_rows_norm_add_k<<<n, 256, 0, s>>>(nullptr, m->pf_r, nullptr, m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a); a_in = m->pf_a; }
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
-        if ((rc = ax_gemv_mma_launch(c, ly.qkv, a_in, n, m->pf_qkv, true))) return rc;
+        if ((rc = pf_product(c, ly.qkv, a_in, n, m->pf_qkv))) return rc;
         if (m->pf_attn_splits > 0) {
             // QK-norm, RoPE and cache write of all n tokens at once, then ONE causal attention launch
             AxQkPrepArgs qa;
@@ -585,12 +598,16 @@ int run_prefill_chunk(atlasx_model* m, int n) {
             qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype; qa.eps = 1e-6f;
             qa.q_stride = (size_t)qkv_rows; qa.kv_in_stride = (size_t)qkv_rows;
             if ((rc = ax_qk_prep_launch(c, qa, false))) return rc;
-            AxAttnChunkArgs ca;
-            ca.q = m->pf_qkv; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
-            ca.out = m->pf_att; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos;
-            ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
-            ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
-            if ((rc = ax_attn_mma_chunk_launch(c, ca))) return rc;
+            // the attention kernel takes 16 tokens a launch; a later group sees the rows of the earlier ones in the cache
+            for (int g0 = 0; g0 < n; g0 += kPrefillMaxMma) {
+                AxAttnChunkArgs ca;
+                ca.q = m->pf_qkv + (size_t)g0 * qkv_rows; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
+                ca.out = m->pf_att + (size_t)g0 * m->q_rows; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos + g0;
+                ca.n_tok = n - g0 < kPrefillMaxMma ? n - g0 : kPrefillMaxMma;
+                ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
+                ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
+                if ((rc = ax_attn_mma_chunk_launch(c, ca))) return rc;
+            }
         } else
         for (int i = 0; i < n; i++) {
             float* qkv = m->pf_qkv + (size_t)i * qkv_rows;
@@ -619,13 +636,13 @@ int run_prefill_chunk(atlasx_model* m, int n) {
                 if ((rc = ax_attn_launch(c, aa, false))) return rc;
             }
         }
-        if ((rc = ax_gemv_mma_launch(c, ly.wo, m->pf_att, n, m->pf_o, true))) return rc;
+        if ((rc = pf_product(c, ly.wo, m->pf_att, n, m->pf_o))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
         pf_rows_norm_add_k<<<n, 256, 0, s>>>(m->pf_o, m->pf_r, post ? ly.attn_norm : nullptr, post ? nullptr : ly.ffn_norm,
                                              cf.rms_norm_eps, d, m->pf_r, m->pf_a);
-        if ((rc = ax_gemv_mma_launch(c, ly.gateup, m->pf_a, n, m->pf_gu, true))) return rc;
+        if ((rc = pf_product(c, ly.gateup, m->pf_a, n, m->pf_gu))) return rc;
         pf_silu_pair_rows_k<<<dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)n), 256, 0, s>>>(m->pf_gu, m->ffn_loc, m->pf_h);
-        if ((rc = ax_gemv_mma_launch(c, ly.down, m->pf_h, n, m->pf_dn, true))) return rc;
+        if ((rc = pf_product(c, ly.down, m->pf_h, n, m->pf_dn))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_dn, (size_t)n * d))) return rc;
         const float* next_wx = (post || l == L - 1) ? nullptr : m->layers[l + 1].attn_norm;
         pf_rows_norm_add_k<<<n, 256, 0, s>>>(m->pf_dn, m->pf_r, post ? ly.ffn_norm : nullptr, next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a);
@@ -1058,14 +1075,15 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     return ATLASX_OK;
 }
 
-// Prompt tokens are ingested `chunk` at a time (2..16) through the multi-column kernels; 0 or 1
-// restores the token-by-token path.  Returns the chunk size in effect through *effective: 1 when
-// the weight format or a matrix shape is outside what the multi-column kernel covers.
+// Prompt tokens are ingested `chunk` at a time (2..64) through the multi-column kernels; 0 or 1
+// restores the token-by-token path.  Returns the chunk size in effect through *effective: at most 16
+// when a matrix needs the warp-level kernel (int8 / int4 weights), 1 when the weight format or a
+// matrix shape is outside what the multi-column kernels cover.
 extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective) {
     AX_ARG(m && m->finalized, "model is not finalised");
-    AX_ARG(chunk >= 0 && chunk <= kPrefillMax, "chunk must be in 0..16");
+    AX_ARG(chunk >= 0 && chunk <= kPrefillMax, "chunk must be in 0..64");
     int eff = chunk < 2 ? 1 : chunk;
-    if (eff > 1 && !prefill_supported(m)) eff = 1;
+    if (eff > 1) { const int lim = prefill_limit(m); if (eff > lim) eff = lim; }
     if (eff > 1 && !m->pf_r) {
         const size_t P = kPrefillMax;
         const int d = m->cfg.d_model, qkv_rows = m->q_rows + 2 * m->kv_rows;
@@ -1079,15 +1097,19 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
         size_t need = 0;
         for (const Layer& ly : m->layers) {
             const AxWeight* ws[4] = { &ly.qkv, &ly.wo, &ly.gateup, &ly.down };
-            for (const AxWeight* w : ws) { const size_t b = ax_gemv_mma_scratch_bytes(w->rows, w->cols); if (b > need) need = b; }
+            for (const AxWeight* w : ws) {
+                size_t b = ax_gemv_mma_scratch_bytes(w->rows, w->cols); if (b > need) need = b;
+                for (int n = 2; n <= kPrefillMax; n++) { b = ax_gemv_umma_scratch_bytes(m->ctx, w->rows, w->cols, n); if (b > need) need = b; }
+            }
         }
         rc = atlasx_ctx_ensure_split_scratch(m->ctx, need);
         if (rc) return rc;
         if (m->cfg.kv_dtype == ATLASX_BF16 && ax_attn_mma_chunk_supported(m->hd, m->nh_loc, m->nkv_loc, m->cfg.kv_dtype)) {
-            m->pf_attn_splits = ax_attn_mma_chunk_splits(m->ctx, m->nh_loc, m->nkv_loc, (int)P, m->cfg.max_seq_len);
-            if ((rc = dmalloc(m, (void**)&m->pf_attn_partials, ax_attn_mma_chunk_partial_floats((int)P, m->nh_loc, m->pf_attn_splits) * 4)) ||
-                (rc = dmalloc(m, (void**)&m->pf_attn_tickets, (size_t)m->nkv_loc * P * sizeof(unsigned)))) return rc;
-            AX_CUDA(cudaMemsetAsync(m->pf_attn_tickets, 0, (size_t)m->nkv_loc * P * sizeof(unsigned), m->ctx->stream));
+            const int A = kPrefillMaxMma;                     // tokens per attention launch
+            m->pf_attn_splits = ax_attn_mma_chunk_splits(m->ctx, m->nh_loc, m->nkv_loc, A, m->cfg.max_seq_len);
+            if ((rc = dmalloc(m, (void**)&m->pf_attn_partials, ax_attn_mma_chunk_partial_floats(A, m->nh_loc, m->pf_attn_splits) * 4)) ||
+                (rc = dmalloc(m, (void**)&m->pf_attn_tickets, (size_t)m->nkv_loc * A * sizeof(unsigned)))) return rc;
+            AX_CUDA(cudaMemsetAsync(m->pf_attn_tickets, 0, (size_t)m->nkv_loc * A * sizeof(unsigned), m->ctx->stream));
         }
     }
     m->prefill_chunk = eff;

@@ -159,6 +159,30 @@ def test_config3_lm_head_shape_bf16_multi_column(ab, n):
     assert rel_err(Y, orc.gemm(w16, X)) <= TOL
 
 
+@pytest.mark.parametrize("n", [2, 5, 16, 24, 33, 64])
+@pytest.mark.parametrize("shape", [(256, 512), (4096, 4096), (1000, 4096), (200, 11008), (129, 64), (12288, 4096)],
+                         ids=lambda s: "%dx%d" % s)
+def test_gemv_many_columns_tensor_memory_kernel(ab, n, shape):
+    """Token batches of up to 64 columns (bf16 weights, K a multiple of 64) run on the tcgen05 kernel: one
+    K block only, K split over several CTAs with the ticketed merge, rows that do not fill the last 128-row
+    tile, and column counts that are not multiples of 8.  Every output element against the oracle's f32
+    product; afterwards the bounded waits of the kernel must not have raised the device error word."""
+    M, K = shape
+    w16 = orc.normal_bf16(M * K, 50, M + K, 0.02).reshape(M, K)
+    X = orc.normal_f32(K * n, 50, n, 1.0).reshape(K, n)
+    Y = ab.GpuMatrix.upload_bf16(w16, M, K).sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+    # the hi + lo split of the tokens keeps f32 accuracy: far inside the 1e-3 parity bound
+    assert rel_err(Y, orc.gemm(w16, X)) <= 2e-5
+    assert ab.Context.default().poll_device_error() == 0
+
+
+def test_gemv_more_than_16_columns_needs_the_tensor_memory_kernel(ab):
+    w = orc.normal_f32(64 * 96, 51, 1, 0.02).reshape(64, 96)      # K = 96 is no multiple of 64
+    gm, _ = make(ab, "bf16", w)
+    with pytest.raises(ab.AtlasError):
+        gm.sgemm_vec(ab.GpuVec.from_slice(orc.normal_f32(96 * 17, 51, 2, 1.0)), 17)
+
+
 @pytest.mark.parametrize("fmt", ["int8", "int4"])
 def test_quantised_gemv_propagates_nan_and_inf_in_the_input(ab, fmt):
     """A NaN (or inf) in the input vector must not be masked by the integer dot-product path: every
