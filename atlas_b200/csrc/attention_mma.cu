@@ -22,11 +22,11 @@
 
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 6;                      // chunk kernel; the operator kernel takes its shape as template arguments
 constexpr int kThreads = kWarps * 32;
 constexpr int kTileRows = 32;                  // cached rows per warp tile
 constexpr int kPitch = 272;                    // bytes per staged row: 256 + 16, shifts rows across the banks
-constexpr int kStages = 3;
+constexpr int kStages = 2;
 constexpr int kTileBytes = kTileRows * kPitch; // one of K or V
 constexpr int kStageBytes = 2 * kTileBytes;
 constexpr int kWarpBytes = kStages * kStageBytes;
@@ -685,11 +685,11 @@ size_t ax_attn_mma_chunk_partial_floats(int n_tok, int n_heads, int n_splits) { 
 
 int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a) {
     AX_ARG(ax_attn_mma_chunk_supported(128, a.n_heads, a.n_kv, ATLASX_BF16), "shape not covered by the chunk attention kernel");
-    AX_ARG(a.q && a.kc && a.vc && a.out && a.pos0 && a.partials && a.tickets && a.n_tok >= 1 && a.n_tok <= 16, "bad argument");
-    static bool attr_done = false;
-    if (!attr_done) {
+    AX_ARG(a.q && a.kc && a.vc && a.out && a.pos0 && a.partials && a.tickets && a.n_tok >= 1 && a.n_tok <= 64, "bad argument");
+    static bool attr_done[64] = {};
+    if (!attr_done[ctx->device & 63]) {
         AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));
-        attr_done = true;
+        attr_done[ctx->device & 63] = true;
     }
     ChunkDev dv;
     dv.q = a.q; dv.q_stride = a.q_stride; dv.kc = (const uint16_t*)a.kc; dv.vc = (const uint16_t*)a.vc;

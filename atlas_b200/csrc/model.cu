@@ -514,18 +514,19 @@ __device__ __forceinline__ float pf_block_sum(float v, float* red) {
 }
 // The fused prologue of the GEMVs, row by row:  v = base + (wy ? rmsnorm(y, wy) : y);  resid = v;
 // x = wx ? rmsnorm(v, wx) : v.   y may be null (v = base).  resid may alias base, x may alias resid.
-__global__ void __launch_bounds__(256) pf_rows_norm_add_k(const float* y, const float* base, const float* wy, const float* wx, float eps,
-                                                          int d, float* resid, float* x) {
-    __shared__ float red[8];
+__global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const float* base, const float* wy, const float* wx, float eps,
+                                                           int d, float* resid, float* x) {
+    __shared__ float red[32];
     const size_t o = (size_t)blockIdx.x * d;
+    const int nt = blockDim.x;
     float inv_y = 1.f;
     if (y && wy) {
         float ss = 0.f;
-        for (int k = threadIdx.x; k < d; k += 256) ss = fmaf(y[o + k], y[o + k], ss);
+        for (int k = threadIdx.x; k < d; k += nt) ss = fmaf(y[o + k], y[o + k], ss);
         inv_y = 1.0f / sqrtf(pf_block_sum(ss, red) / (float)d + eps);
     }
     float ss2 = 0.f;
-    for (int k = threadIdx.x; k < d; k += 256) {
+    for (int k = threadIdx.x; k < d; k += nt) {
         float v = base[o + k];
         if (y) { float t = y[o + k]; if (wy) t = t * inv_y * wy[k]; v += t; }
         resid[o + k] = v;
@@ -533,9 +534,9 @@ __global__ void __launch_bounds__(256) pf_rows_norm_add_k(const float* y, const 
     }
     if (wx) {
         const float inv_x = 1.0f / sqrtf(pf_block_sum(ss2, red) / (float)d + eps);
-        for (int k = threadIdx.x; k < d; k += 256) x[o + k] = resid[o + k] * inv_x * wx[k];
+        for (int k = threadIdx.x; k < d; k += nt) x[o + k] = resid[o + k] * inv_x * wx[k];
     } else if (x != resid) {
-        for (int k = threadIdx.x; k < d; k += 256) x[o + k] = resid[o + k];
+        for (int k = threadIdx.x; k < d; k += nt) x[o + k] = resid[o + k];
     }
 }
 // gate/up rows are interleaved (even: gate, odd: up): out[i][j] = silu(gu[i][2j]) · gu[i][2j+1]
@@ -584,7 +585,7 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     pf_positions_k<<<1, kPrefillMax, 0, s>>>(m->st, m->pf_pos, n);
     pf_embed_rows_k<<<n, 256, 0, s>>>(m->embed, m->embed_bf16, cf.vocab_size, m->seq, m->pf_pos, d, m->pf_r);
     const float* a_in = m->pf_r;
-    if (!post) { pf_rows_norm_add_k<<<n, 256, 0, s>>>(nullptr, m->pf_r, nullptr, m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a); a_in = m->pf_a; }
+    if (!post) { pf_rows_norm_add_k<<<n, 1024, 0, s>>>(nullptr, m->pf_r, nullptr, m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a); a_in = m->pf_a; }
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
         if ((rc = pf_product(c, ly.qkv, a_in, n, m->pf_qkv))) return rc;
@@ -598,16 +599,12 @@ int run_prefill_chunk(atlasx_model* m, int n) {
             qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype; qa.eps = 1e-6f;
             qa.q_stride = (size_t)qkv_rows; qa.kv_in_stride = (size_t)qkv_rows;
             if ((rc = ax_qk_prep_launch(c, qa, false))) return rc;
-            // the attention kernel takes 16 tokens a launch; a later group sees the rows of the earlier ones in the cache
-            for (int g0 = 0; g0 < n; g0 += kPrefillMaxMma) {
-                AxAttnChunkArgs ca;
-                ca.q = m->pf_qkv + (size_t)g0 * qkv_rows; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
-                ca.out = m->pf_att + (size_t)g0 * m->q_rows; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos + g0;
-                ca.n_tok = n - g0 < kPrefillMaxMma ? n - g0 : kPrefillMaxMma;
-                ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
-                ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
-                if ((rc = ax_attn_mma_chunk_launch(c, ca))) return rc;
-            }
+            AxAttnChunkArgs ca;                                // ONE causal attention launch for the chunk
+            ca.q = m->pf_qkv; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
+            ca.out = m->pf_att; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos;
+            ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
+            ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
+            if ((rc = ax_attn_mma_chunk_launch(c, ca))) return rc;
         } else
         for (int i = 0; i < n; i++) {
             float* qkv = m->pf_qkv + (size_t)i * qkv_rows;
@@ -638,14 +635,14 @@ int run_prefill_chunk(atlasx_model* m, int n) {
         }
         if ((rc = pf_product(c, ly.wo, m->pf_att, n, m->pf_o))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
-        pf_rows_norm_add_k<<<n, 256, 0, s>>>(m->pf_o, m->pf_r, post ? ly.attn_norm : nullptr, post ? nullptr : ly.ffn_norm,
+        pf_rows_norm_add_k<<<n, 1024, 0, s>>>(m->pf_o, m->pf_r, post ? ly.attn_norm : nullptr, post ? nullptr : ly.ffn_norm,
                                              cf.rms_norm_eps, d, m->pf_r, m->pf_a);
         if ((rc = pf_product(c, ly.gateup, m->pf_a, n, m->pf_gu))) return rc;
         pf_silu_pair_rows_k<<<dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)n), 256, 0, s>>>(m->pf_gu, m->ffn_loc, m->pf_h);
         if ((rc = pf_product(c, ly.down, m->pf_h, n, m->pf_dn))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_dn, (size_t)n * d))) return rc;
         const float* next_wx = (post || l == L - 1) ? nullptr : m->layers[l + 1].attn_norm;
-        pf_rows_norm_add_k<<<n, 256, 0, s>>>(m->pf_dn, m->pf_r, post ? ly.ffn_norm : nullptr, next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a);
+        pf_rows_norm_add_k<<<n, 1024, 0, s>>>(m->pf_dn, m->pf_r, post ? ly.ffn_norm : nullptr, next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a);
         a_in = m->pf_a;
     }
     AX_CHECK_LAUNCH("prefill chunk");
@@ -1105,7 +1102,7 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
         rc = atlasx_ctx_ensure_split_scratch(m->ctx, need);
         if (rc) return rc;
         if (m->cfg.kv_dtype == ATLASX_BF16 && ax_attn_mma_chunk_supported(m->hd, m->nh_loc, m->nkv_loc, m->cfg.kv_dtype)) {
-            const int A = kPrefillMaxMma;                     // tokens per attention launch
+            const int A = kPrefillMax;
             m->pf_attn_splits = ax_attn_mma_chunk_splits(m->ctx, m->nh_loc, m->nkv_loc, A, m->cfg.max_seq_len);
             if ((rc = dmalloc(m, (void**)&m->pf_attn_partials, ax_attn_mma_chunk_partial_floats(A, m->nh_loc, m->pf_attn_splits) * 4)) ||
                 (rc = dmalloc(m, (void**)&m->pf_attn_tickets, (size_t)m->nkv_loc * A * sizeof(unsigned)))) return rc;

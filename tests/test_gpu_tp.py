@@ -86,4 +86,7 @@ def test_two_gpu_model_loaded_from_a_safetensors_file(tmp_path, fmt):
     one = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=ab.F32, weight_format=code)
     toks = orc.uniform_u32(n_tok, 33, 1, cfg["vocab_size"])
     ref = np.stack([one.forward_one_gpu(int(t)) for t in toks])
-    assert np.max(np.abs(got["logits"] - ref)) <= 1e-4
+    # quantised matrices see their input through two base-254 digits scaled by the largest element of the
+    # vector THEY get: a rank's slice of a row-parallel input has its own scale, so the two models round the
+    # activations differently (about 1e-5 of a product, a few 1e-4 on the logits after three layers)
+    assert np.max(np.abs(got["logits"] - ref)) <= (1e-4 if fmt == "auto" else 5e-4)
