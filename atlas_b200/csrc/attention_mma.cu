@@ -83,9 +83,9 @@ __device__ __forceinline__ void mma_bf16_4(float (&c)[4], uint32_t a0, uint32_t 
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// Operand roles.  The warp-level MMA of this GPU is slow next to its HBM (about one m16n8k16 per ten
-// clocks and SM), so the kernel is built to issue as few of them as possible: the cached rows are the
-// 16-row A operand and the query heads the 8 columns of B.
+// Operand roles.  The MMAs of a tile depend on one another (scores, softmax, output) and a warp gets each
+// back after tens of clocks, so the kernel is built to issue as few of them per byte as possible: the
+// cached rows are the 16-row A operand and the query heads the 8 columns of B.
 //   Sᵀ[16 keys × 8 cols] = K[16 keys × 16 dims]·Qᵀ[16 dims × 8 cols]      (A by ldmatrix from the staged K rows)
 //   Oᵀ[16 dims × 8 cols] = Vᵀ[16 dims × 16 keys]·Pᵀ[16 keys × 8 cols]     (A by ldmatrix.trans from the staged V rows,
 //                                                                           B from the Sᵀ fragments by movmatrix)

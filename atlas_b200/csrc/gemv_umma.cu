@@ -5,7 +5,7 @@
 // It serves the same callers as the warp-level kernel of gemv_mma.cu — the token batches of prompt ingestion
 // and speculative verification, which the reference runs as one sgemm_bf16_kernel thread per output element
 // (kernels/matmul.cu:384-420) or token by token (crates/atlas-model/src/lib.rs:1611-1618) — and exists because
-// the warp-level MMA of this GPU is too slow to keep up with HBM beyond a few columns.
+// the warp-level kernel falls to half the HBM rate at 16 columns and cannot take more.
 //
 //   * Work item = (128-row tile of W, range of 64-element K blocks); one item per CTA, two CTAs per SM.  K is
 //     split so that short matrices still give every SM work; the partial tiles of a row tile meet in global

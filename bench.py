@@ -90,8 +90,8 @@ class ClockSampler:
         return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": float(max(mx)), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# (32 x (100.73 + 33.63 + 180.46 + 90.28) + 821.60) / 129 MB read + 2.27 MB written, from the ncu capture
-NCU_GEMV_TRAFFIC_PER_LAUNCH = 109.13e6
+# (32 x (100.74 + 33.63 + 180.47 + 90.29) + 821.61) / 129 MB read + 2.64 MB written, from the ncu capture
+NCU_GEMV_TRAFFIC_PER_LAUNCH = 109.51e6
 PROFILE_LAYERS = 0          # > 0: a truncated model for profiler captures only (--profile-layers)
 
 
