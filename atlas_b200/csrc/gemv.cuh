@@ -94,9 +94,10 @@ bool ax_gemv_mma_supported(const AxWeight& w, int n, const float* x, const float
 size_t ax_gemv_mma_scratch_bytes(int rows, int cols);   // context scratch one such product needs
 // token_major: X is [n][cols] and Y is [n][rows] (one contiguous vector per column).
 int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false);
-// tcgen05 path for n = 2..64 tokens (bf16 weights, cols a multiple of 64); same operand layouts as above.
+// tcgen05 path for n = 2..64 tokens (bf16 weights with cols a multiple of 8, int8 weights with cols a multiple of 16);
+// same operand layouts as above.
 bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y);
-size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, int rows, int cols, int n);
+size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n);
 int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false, bool pdl = false);
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes
 size_t ax_weight_bytes(const AxWeight& w);

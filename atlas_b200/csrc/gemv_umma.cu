@@ -23,6 +23,10 @@
 //   * Every wait on an mbarrier is bounded (two seconds of %globaltimer): on expiry the CTA raises the
 //     context's device error word, all roles leave their loops, copies in flight are waited for (bounded again)
 //     and tensor memory is released before the CTA returns.
+//   * int8 weights (crates/atlas-quant/src/lib.rs:41-75: one f32 scale per row) run as kind::i8 with the raw
+//     weight bytes as A (128 int8 per K block) and the tokens as three int8 digit planes in base 254 with one
+//     scale per token (x ≈ s·(q1 + q2/254 + q3/254²), |error| ≤ 6e-8·max|x| of the token): the s32 sums in
+//     tensor memory are exact, the epilogue combines the planes and applies token and row scale.
 //   * The tensor maps cover this GPU's own memory only and no copy is multicast.
 #include <cuda.h>
 
@@ -31,8 +35,9 @@
 namespace {
 
 constexpr int kTileM = 128;
-constexpr int kBlockK = 64;                       // bf16 elements per K block: 128 bytes, one swizzle row
-constexpr int kABytes = kTileM * kBlockK * 2;     // 16 KB
+constexpr int kBlockBytes = 128;                  // bytes of a row per K block: one swizzle row (64 bf16 or 128 int8)
+constexpr int kABytes = kTileM * kBlockBytes;     // 16 KB
+constexpr float kDigitBase = 254.0f;
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr int kMaxTokens = 64;
@@ -41,10 +46,14 @@ constexpr unsigned long long kWaitNs = 2000000000ull;
 
 struct UmmaArgs {
     float* Y;
-    int M, n, n8;                 // rows of W, tokens, tokens rounded up to 8
+    int M, n, nc;                 // rows of W, tokens, columns per plane (tokens rounded up to 8; to 16 for int8)
+    int i8, planes;               // int8 weights with three digit planes, or bf16 with hi and lo planes
+    int kblk;                     // elements per K block (64 bf16, 128 int8)
+    const float* wscale;          // int8: scale per row of W
+    const float* xscale;          // int8: scale per token
     int KB, KS, T;                // K blocks, K splits, row tiles
-    int stages, b_bytes;          // pipeline depth, bytes of one B stage (2·n8 rows × 128)
-    int tmem_cols;                // power of two ≥ 32 holding 2·n8 accumulator columns
+    int stages, b_bytes;          // pipeline depth, bytes of one B stage (planes·nc rows × 128)
+    int tmem_cols;                // power of two ≥ 32 holding planes·nc accumulator columns
     int token_major;              // Y[j·M + row] (one contiguous vector per token) or Y[row·n + j]
     float* parts;                 // [T·KS][n][128] partial tiles (KS > 1)
     unsigned* tickets;            // [T], zero between launches
@@ -94,6 +103,11 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t adesc, uint6
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+                 :: "r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {       // the barrier gets one arrival when every MMA issued so far is done
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" :: "r"(bar) : "memory");
 }
@@ -139,6 +153,64 @@ __global__ void ax_umma_split_kernel(const float* __restrict__ X, int K, int n, 
     *reinterpret_cast<uint4*>(plane + (size_t)row * K + kg * 8) = make_uint4(out[0], out[1], out[2], out[3]);
 }
 
+// f32 tokens → three int8 digit planes [3·n16][K] in base 254 with one scale per token: rows p·n16 + j hold
+// digit p of token j, rows of absent tokens are zero.  One CTA per row index j < n16.  A NaN or inf in a token
+// makes its scale NaN, and with it every output of that token.  Also clears the tickets.
+__global__ void __launch_bounds__(256) ax_umma_digits_kernel(const float* __restrict__ X, int K, int n, int n16, int token_major,
+                                                             int8_t* __restrict__ plane, float* __restrict__ xscale,
+                                                             unsigned* tickets, int n_tickets) {
+    __shared__ float red[8];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int j = blockIdx.x, tid = threadIdx.x;
+    if (j == 0) for (int i = tid; i < n_tickets; i += 256) tickets[i] = 0u;
+    const size_t plane_stride = (size_t)n16 * K;
+    int8_t* r0 = plane + (size_t)j * K;
+    if (j >= n) {
+        for (int k = tid * 16; k < K; k += 256 * 16)
+            for (int pl = 0; pl < 3; pl++) *reinterpret_cast<uint4*>(r0 + pl * plane_stride + k) = make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    auto xat = [&](int k) { return token_major ? X[(size_t)j * K + k] : X[(size_t)k * n + j]; };
+    float mx = 0.f, bad = 0.f;
+    for (int k = tid; k < K; k += 256) { const float v = xat(k); mx = fmaxf(mx, fabsf(v)); bad += v * 0.f; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) { mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o)); bad += __shfl_xor_sync(0xFFFFFFFFu, bad, o); }
+    if ((tid & 31) == 0) red[tid >> 5] = mx;
+    __syncthreads();
+    mx = red[0];
+#pragma unroll
+    for (int w = 1; w < 8; w++) mx = fmaxf(mx, red[w]);
+    __syncthreads();
+    if ((tid & 31) == 0) red[tid >> 5] = bad;
+    __syncthreads();
+    bad = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; w++) bad += red[w];
+    if (!(mx < 3.0e38f)) mx = 3.0e38f;
+    const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+    if (tid == 0) xscale[j] = mx / 127.0f + bad;                 // bad is 0, or NaN when the token holds a NaN or an inf
+    for (int k4 = tid; k4 * 4 < K; k4 += 256) {
+        uint32_t w1 = 0, w2 = 0, w3 = 0;
+#pragma unroll
+        for (int e = 0; e < 4; e++) {
+            // round to nearest by adding 1.5·2^23: the integer then sits in the low mantissa bits
+            constexpr float Mg = 12582912.0f;
+            float t = xat(k4 * 4 + e) * inv;
+            t = fminf(fmaxf(t, -127.f), 127.f);
+            const float a1 = t + Mg, q1 = a1 - Mg;
+            const float rr = (t - q1) * kDigitBase;
+            const float a2 = rr + Mg, q2 = a2 - Mg;
+            const float a3 = (rr - q2) * kDigitBase + Mg;
+            w1 |= (uint32_t)((__float_as_int(a1) - 0x4B400000) & 255) << (8 * e);
+            w2 |= (uint32_t)((__float_as_int(a2) - 0x4B400000) & 255) << (8 * e);
+            w3 |= (uint32_t)((__float_as_int(a3) - 0x4B400000) & 255) << (8 * e);
+        }
+        *reinterpret_cast<uint32_t*>(r0 + k4 * 4) = w1;
+        *reinterpret_cast<uint32_t*>(r0 + plane_stride + k4 * 4) = w2;
+        *reinterpret_cast<uint32_t*>(r0 + 2 * plane_stride + k4 * 4) = w3;
+    }
+}
+
 __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, const UmmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
@@ -151,7 +223,7 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     const int kb0 = (int)((long long)a.KB * ks / a.KS), kb1 = (int)((long long)a.KB * (ks + 1) / a.KS);
     const int nkb = kb1 - kb0;
     const int ST = a.stages;
-    const int NP = 2 * a.n8;
+    const int NP = a.planes * a.nc;
     const uint32_t stage_bytes = (uint32_t)kABytes + (uint32_t)a.b_bytes;
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;           // swizzled tiles want 1024-byte alignment
     volatile int* abort_flag = &s_abort;
@@ -181,15 +253,16 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                 const uint32_t bar = smem_u32(&full_bar[s]);
                 const uint32_t dst = smem0 + (uint32_t)s * stage_bytes;
                 mbar_expect_tx(bar, stage_bytes);
-                tma_load_2d(dst, &map_w, (kb0 + i) * kBlockK, tile * kTileM, bar);
-                tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * kBlockK, 0, bar);
+                tma_load_2d(dst, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
+                tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * a.kblk, 0, bar);
                 s_issued = i + 1;
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            // instruction descriptor: f32 accumulator, bf16 A and B, both K-major, N = 2·n8, M = 128
-            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            // instruction descriptor: accumulator f32 (1) or s32 (2), A and B bf16 (1) or signed int8 (1), both K-major,
+            // N = planes·nc, M = 128
+            const uint32_t idesc = ((a.i8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
                 const int s = i % ST;
@@ -198,8 +271,10 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = smem0 + (uint32_t)s * stage_bytes, sb = sa + kABytes;
 #pragma unroll
-                for (int k = 0; k < kBlockK / 16; k++)                       // 16 bf16 = 32 bytes along the swizzled row per MMA
-                    umma_bf16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                for (int k = 0; k < kBlockBytes / 32; k++) {                 // 16 bf16 or 32 int8 = 32 bytes along the swizzled row per MMA
+                    if (a.i8) umma_i8(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                    else umma_bf16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                }
                 umma_commit(smem_u32(&empty_bar[s]));                        // the stage is free once these MMAs have read it
             }
             umma_commit(smem_u32(&done_bar));                                // also on the way out of a failed wait: see the tail
@@ -214,15 +289,22 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t t_row = tmem + ((uint32_t)(q * 32) << 16);
             float* part = a.parts + (size_t)blockIdx.x * a.n * kTileM;
-            for (int c = 0; c < a.n8; c += 8) {
-                float hi[8], lo[8];
+            const float ws = (a.i8 && row < a.M) ? a.wscale[row] : 1.f;
+            for (int c = 0; c < a.nc && c < a.n; c += 8) {
+                float hi[8], lo[8], d3[8];
                 tmem_ld8(t_row + (uint32_t)c, hi);
-                tmem_ld8(t_row + (uint32_t)(a.n8 + c), lo);
+                tmem_ld8(t_row + (uint32_t)(a.nc + c), lo);
+                if (a.i8) tmem_ld8(t_row + (uint32_t)(2 * a.nc + c), d3);
 #pragma unroll
                 for (int e = 0; e < 8; e++) {
                     const int j = c + e;
                     if (j < a.n) {
-                        const float v = hi[e] + lo[e];
+                        float v;
+                        if (a.i8) {                                          // exact s32 sums of the three digit planes
+                            constexpr float k2 = 1.0f / kDigitBase, k3 = 1.0f / (kDigitBase * kDigitBase);
+                            v = (float)__float_as_int(hi[e]) + (float)__float_as_int(lo[e]) * k2 + (float)__float_as_int(d3[e]) * k3;
+                            v *= a.xscale[j] * ws;
+                        } else v = hi[e] + lo[e];
                         if (a.KS > 1) part[(size_t)j * kTileM + r_in] = v;
                         else if (row < a.M) a.Y[a.token_major ? (size_t)j * a.M + row : (size_t)row * a.n + j] = v;
                     }
@@ -312,42 +394,46 @@ EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// bf16 matrix [rows][cols] (cols contiguous), boxes of 64 columns × box_rows rows, 128-byte swizzle, zeros outside
-int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows) {
+// bf16 or int8 matrix [rows][cols] (cols contiguous), boxes of 128 bytes × box_rows rows, 128-byte swizzle, zeros outside
+int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows, bool i8) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return atlasx_fail(ATLASX_ERR_CUDA, "the driver does not export cuTensorMapEncodeTiled");
+    const cuuint64_t esz = i8 ? 1 : 2;
     const cuuint64_t dims[2] = { cols, rows };
-    const cuuint64_t strides[1] = { cols * 2 };
-    const cuuint32_t box[2] = { (cuuint32_t)kBlockK, box_rows };
+    const cuuint64_t strides[1] = { cols * esz };
+    const cuuint32_t box[2] = { (cuuint32_t)(kBlockBytes / esz), box_rows };
     const cuuint32_t elem[2] = { 1, 1 };
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+    const CUresult r = fn(map, i8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return atlasx_fail(ATLASX_ERR_CUDA, "cuTensorMapEncodeTiled failed with code %d", (int)r);
     return ATLASX_OK;
 }
 
-struct UmmaPlan { int n8, T, KB, KS, stages, b_bytes, tmem_cols; size_t plane_bytes, parts_bytes, ticket_bytes, smem; };
+struct UmmaPlan { int nc, planes, kblk, T, KB, KS, stages, b_bytes, tmem_cols; size_t plane_bytes, xscale_bytes, parts_bytes, ticket_bytes, smem; };
 
-UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n) {
+UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     UmmaPlan p;
-    p.n8 = (n + 7) / 8 * 8;
+    p.planes = i8 ? 3 : 2;
+    p.nc = i8 ? (n + 15) / 16 * 16 : (n + 7) / 8 * 8;         // planes·nc must be a multiple of 16
+    p.kblk = i8 ? 128 : 64;
     p.T = (rows + kTileM - 1) / kTileM;
-    p.KB = cols / kBlockK;
+    p.KB = (cols + p.kblk - 1) / p.kblk;                       // the copy engine zero-fills a last, partial block
     // K splits: enough items for two CTAs on every SM, at least eight K blocks (128 KB of W) per item
     int ks = (2 * ctx->sm_count + p.T - 1) / p.T;
     if (ks > p.KB / 8) ks = p.KB / 8;
     if (ks > kMaxSplits) ks = kMaxSplits;
     if (ks < 1) ks = 1;
     p.KS = ks;
-    p.b_bytes = 2 * p.n8 * 128;
+    p.b_bytes = p.planes * p.nc * kBlockBytes;
     int st = (100 * 1024) / (kABytes + p.b_bytes);
     if (st > kMaxStages) st = kMaxStages;
     if (st < 2) st = 2;
     p.stages = st;
-    int c = 32; while (c < 2 * p.n8) c <<= 1;
+    int c = 32; while (c < p.planes * p.nc) c <<= 1;
     p.tmem_cols = c;
-    p.plane_bytes = ((size_t)2 * p.n8 * cols * 2 + 1023) / 1024 * 1024;
+    p.plane_bytes = ((size_t)p.planes * p.nc * cols * (i8 ? 1 : 2) + 1023) / 1024 * 1024;
+    p.xscale_bytes = i8 ? 256 : 0;
     p.parts_bytes = p.KS > 1 ? (size_t)p.T * p.KS * n * kTileM * sizeof(float) : 0;
     p.ticket_bytes = ((size_t)p.T * sizeof(unsigned) + 255) / 256 * 256;
     p.smem = (size_t)st * (kABytes + p.b_bytes) + 1024;
@@ -358,28 +444,32 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n) {
 
 bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y) {
     if (n < 2 || n > kMaxTokens || !x || !y) return false;
-    if (w.dtype != ATLASX_BF16 || w.cols % kBlockK != 0 || w.cols < kBlockK) return false;
-    return (((uintptr_t)w.data | (uintptr_t)x) & 15) == 0;
+    if ((((uintptr_t)w.data | (uintptr_t)x) & 15) != 0) return false;
+    if (w.dtype == ATLASX_BF16) return w.cols % 8 == 0 && w.cols >= 64;          // row pitch a multiple of 16 bytes
+    if (w.dtype == ATLASX_INT8) return w.cols % 16 == 0 && w.cols >= 128 && w.scales != nullptr;
+    return false;
 }
 
-size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, int rows, int cols, int n) {
-    const UmmaPlan p = make_plan(ctx, rows, cols, n);
-    return p.plane_bytes + p.parts_bytes + p.ticket_bytes;
+size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n) {
+    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, w.dtype == ATLASX_INT8);
+    return p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.ticket_bytes;
 }
 
 int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
     AX_ARG(ax_gemv_umma_supported(w, n, x, y), "shape or format not covered by the tcgen05 multi-column kernel");
-    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n);
-    int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.parts_bytes + p.ticket_bytes);
+    const bool i8 = w.dtype == ATLASX_INT8;
+    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, i8);
+    int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.ticket_bytes);
     if (rc) return rc;
     uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch);
-    uint16_t* plane = reinterpret_cast<uint16_t*>(base);
-    float* parts = reinterpret_cast<float*>(base + p.plane_bytes);
-    unsigned* tickets = reinterpret_cast<unsigned*>(base + p.plane_bytes + p.parts_bytes);
+    float* xscale = reinterpret_cast<float*>(base + p.plane_bytes);
+    float* parts = reinterpret_cast<float*>(base + p.plane_bytes + p.xscale_bytes);
+    unsigned* tickets = reinterpret_cast<unsigned*>(base + p.plane_bytes + p.xscale_bytes + p.parts_bytes);
 
     CUtensorMap map_w, map_x;
-    if ((rc = make_map(&map_w, w.data, (uint64_t)w.rows, (uint64_t)w.cols, kTileM))) return rc;
-    if ((rc = make_map(&map_x, plane, (uint64_t)2 * p.n8, (uint64_t)w.cols, (uint32_t)(2 * p.n8)))) return rc;
+    const uint32_t np = (uint32_t)(p.planes * p.nc);
+    if ((rc = make_map(&map_w, w.data, (uint64_t)w.rows, (uint64_t)w.cols, kTileM, i8))) return rc;
+    if ((rc = make_map(&map_x, base, (uint64_t)np, (uint64_t)w.cols, np, i8))) return rc;
 
     static bool attr_done[64] = {};
     const int dev = ctx->device & 63;
@@ -391,15 +481,25 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     {
-        const size_t work = (size_t)2 * p.n8 * (w.cols / 8);
-        const size_t threads = work > (size_t)p.T ? work : (size_t)p.T;
         cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3((unsigned)((threads + 255) / 256)); cfg.blockDim = dim3(256); cfg.stream = ctx->stream;
+        cfg.blockDim = dim3(256); cfg.stream = ctx->stream;
         if (pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }
-        AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, w.cols, n, p.n8, token_major ? 1 : 0, plane, tickets, p.T));
+        if (i8) {
+            cfg.gridDim = dim3((unsigned)p.nc);
+            AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_digits_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
+                                       reinterpret_cast<int8_t*>(base), xscale, tickets, p.T));
+        } else {
+            const size_t work = (size_t)2 * p.nc * (w.cols / 8);
+            const size_t threads = work > (size_t)p.T ? work : (size_t)p.T;
+            cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+            AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
+                                       reinterpret_cast<uint16_t*>(base), tickets, p.T));
+        }
     }
     UmmaArgs a;
-    a.Y = y; a.M = w.rows; a.n = n; a.n8 = p.n8; a.KB = p.KB; a.KS = p.KS; a.T = p.T;
+    a.Y = y; a.M = w.rows; a.n = n; a.nc = p.nc; a.i8 = i8 ? 1 : 0; a.planes = p.planes; a.kblk = p.kblk;
+    a.wscale = reinterpret_cast<const float*>(w.scales); a.xscale = xscale;
+    a.KB = p.KB; a.KS = p.KS; a.T = p.T;
     a.stages = p.stages; a.b_bytes = p.b_bytes; a.tmem_cols = p.tmem_cols; a.token_major = token_major ? 1 : 0;
     a.parts = parts; a.tickets = tickets; a.err = ctx->dev_error;
     cudaLaunchConfig_t cfg = {};

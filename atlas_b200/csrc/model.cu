@@ -1096,7 +1096,8 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
             const AxWeight* ws[4] = { &ly.qkv, &ly.wo, &ly.gateup, &ly.down };
             for (const AxWeight* w : ws) {
                 size_t b = ax_gemv_mma_scratch_bytes(w->rows, w->cols); if (b > need) need = b;
-                for (int n = 2; n <= kPrefillMax; n++) { b = ax_gemv_umma_scratch_bytes(m->ctx, w->rows, w->cols, n); if (b > need) need = b; }
+                if (w->dtype == ATLASX_BF16 || w->dtype == ATLASX_INT8)
+                    for (int n = 2; n <= kPrefillMax; n++) { b = ax_gemv_umma_scratch_bytes(m->ctx, *w, n); if (b > need) need = b; }
             }
         }
         rc = atlasx_ctx_ensure_split_scratch(m->ctx, need);

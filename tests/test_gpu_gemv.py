@@ -159,26 +159,45 @@ def test_config3_lm_head_shape_bf16_multi_column(ab, n):
     assert rel_err(Y, orc.gemm(w16, X)) <= TOL
 
 
+@pytest.mark.parametrize("fmt", ["bf16", "int8"])
 @pytest.mark.parametrize("n", [2, 5, 16, 24, 33, 64])
-@pytest.mark.parametrize("shape", [(256, 512), (4096, 4096), (1000, 4096), (200, 11008), (129, 64), (12288, 4096)],
+@pytest.mark.parametrize("shape", [(256, 512), (4096, 4096), (1000, 4096), (200, 11008), (129, 128), (12288, 4096), (300, 1376)],
                          ids=lambda s: "%dx%d" % s)
-def test_gemv_many_columns_tensor_memory_kernel(ab, n, shape):
-    """Token batches of up to 64 columns (bf16 weights, K a multiple of 64) run on the tcgen05 kernel: one
-    K block only, K split over several CTAs with the ticketed merge, rows that do not fill the last 128-row
-    tile, and column counts that are not multiples of 8.  Every output element against the oracle's f32
-    product; afterwards the bounded waits of the kernel must not have raised the device error word."""
+def test_gemv_many_columns_tensor_memory_kernel(ab, fmt, n, shape):
+    """Token batches of up to 64 columns run on the tcgen05 kernel (bf16 weights: tokens as hi|lo bf16 planes;
+    int8 weights: raw weight bytes against three int8 digit planes of the tokens): one K block only, K split
+    over several CTAs with the ticketed merge, rows that do not fill the last 128-row tile, a K that ends inside
+    a block (zero-filled by the copy engine), column counts that are not multiples of 8.  Every output element
+    against the oracle's f32 product of the stored weights; afterwards the bounded waits of the kernel must not
+    have raised the device error word."""
     M, K = shape
-    w16 = orc.normal_bf16(M * K, 50, M + K, 0.02).reshape(M, K)
+    w = orc.normal_f32(M * K, 50, M + K, 0.02).reshape(M, K)
     X = orc.normal_f32(K * n, 50, n, 1.0).reshape(K, n)
-    Y = ab.GpuMatrix.upload_bf16(w16, M, K).sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
-    # the hi + lo split of the tokens keeps f32 accuracy: far inside the 1e-3 parity bound
-    assert rel_err(Y, orc.gemm(w16, X)) <= 2e-5
+    X[K // 3, 0] = 37.5                                       # an outlier: the int8 digit planes scale with the token's largest element
+    gm, wo = make(ab, fmt, w)
+    Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+    # hi + lo planes (bf16) and three base-254 digits (int8) keep f32 accuracy: far inside the 1e-3 parity bound
+    assert rel_err(Y, orc.gemm(wo, X)) <= 2e-5
     assert ab.Context.default().poll_device_error() == 0
 
 
+def test_gemv_many_columns_propagates_nan_per_token(ab):
+    """A NaN or inf in one token reaches every output of that token, and of that token only, on both
+    tcgen05 paths."""
+    M, K, n = 256, 512, 24
+    w = orc.normal_f32(M * K, 52, 1, 0.02).reshape(M, K)
+    for fmt in ("bf16", "int8"):
+        gm, _ = make(ab, fmt, w)
+        for bad in (np.nan, np.inf):
+            X = orc.normal_f32(K * n, 52, 2, 1.0).reshape(K, n)
+            X[100, 7] = bad
+            Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+            assert np.all(~np.isfinite(Y[:, 7])) and np.all(np.isfinite(np.delete(Y, 7, axis=1)))
+
+
 def test_gemv_more_than_16_columns_needs_the_tensor_memory_kernel(ab):
-    w = orc.normal_f32(64 * 96, 51, 1, 0.02).reshape(64, 96)      # K = 96 is no multiple of 64
-    gm, _ = make(ab, "bf16", w)
+    w = orc.normal_f32(64 * 96, 51, 1, 0.02).reshape(64, 96)
+    gm, _ = make(ab, "int4", w)                               # int4 weights stay on the warp-level kernel: 16 columns at most
     with pytest.raises(ab.AtlasError):
         gm.sgemm_vec(ab.GpuVec.from_slice(orc.normal_f32(96 * 17, 51, 2, 1.0)), 17)
 
