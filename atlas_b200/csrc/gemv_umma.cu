@@ -263,6 +263,7 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
             // instruction descriptor: accumulator f32 (1) or s32 (2), A and B bf16 (1) or signed int8 (1), both K-major,
             // N = planes·nc, M = 128
             const uint32_t idesc = ((a.i8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            const bool i8 = a.i8 != 0;
             bool ok = true;
             for (int i = 0; i < nkb && ok; i++) {
                 const int s = i % ST;
@@ -270,10 +271,14 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t sa = smem0 + (uint32_t)s * stage_bytes, sb = sa + kABytes;
+                if (i8) {                                                    // 16 bf16 or 32 int8 = 32 bytes along the swizzled row per MMA
 #pragma unroll
-                for (int k = 0; k < kBlockBytes / 32; k++) {                 // 16 bf16 or 32 int8 = 32 bytes along the swizzled row per MMA
-                    if (a.i8) umma_i8(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
-                    else umma_bf16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                    for (int k = 0; k < kBlockBytes / 32; k++)
+                        umma_i8(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                } else {
+#pragma unroll
+                    for (int k = 0; k < kBlockBytes / 32; k++)
+                        umma_bf16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
                 }
                 umma_commit(smem_u32(&empty_bar[s]));                        // the stage is free once these MMAs have read it
             }
@@ -419,12 +424,19 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     p.kblk = i8 ? 128 : 64;
     p.T = (rows + kTileM - 1) / kTileM;
     p.KB = (cols + p.kblk - 1) / p.kblk;                       // the copy engine zero-fills a last, partial block
-    // K splits: enough items for two CTAs on every SM, at least eight K blocks (128 KB of W) per item
-    int ks = (2 * ctx->sm_count + p.T - 1) / p.T;
-    if (ks > p.KB / 8) ks = p.KB / 8;
-    if (ks > kMaxSplits) ks = kMaxSplits;
-    if (ks < 1) ks = 1;
-    p.KS = ks;
+    // K splits: the count that fills the waves of CTAs best (two CTAs per SM; a last wave that is half empty costs
+    // as much as a full one), at least four K blocks per item, charged with the bytes of the partial tiles it adds
+    // (written once, read once) relative to the weight bytes of a row tile
+    const int slots = 2 * ctx->sm_count;
+    int best = 1; double best_cost = 1e300;
+    for (int ks = 1; ks <= kMaxSplits && ks * 4 <= (p.KB > 4 ? p.KB : 4); ks++) {
+        const long long items = (long long)p.T * ks;
+        const long long waves = (items + slots - 1) / slots;
+        const double extra = ks > 1 ? 2.0 * n * kTileM * sizeof(float) * ks / ((double)p.KB * kABytes) : 0.0;
+        const double cost = (double)(waves * slots) / (double)items * (1.0 + extra);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
+    }
+    p.KS = best;
     p.b_bytes = p.planes * p.nc * kBlockBytes;
     int st = (100 * 1024) / (kABytes + p.b_bytes);
     if (st > kMaxStages) st = kMaxStages;

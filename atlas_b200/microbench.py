@@ -65,9 +65,8 @@ def run_gemv(args):
     L = _ffi.lib()
     pk, kind = peak()
     for fmt in args.formats.split(","):
-        for (M, K) in SHAPES:
-            if args.shapes and "%dx%d" % (M, K) not in args.shapes.split(","):
-                continue
+        shapes = [tuple(int(v) for v in t.split("x")) for t in args.shapes.split(",")] if args.shapes else SHAPES
+        for (M, K) in shapes:
             m0, bufs = make_matrix(ctx, fmt, M, K, 1)
             wb = m0.weight_bytes
             copies = args.copies if args.copies > 0 else max(2, min(16, int(math.ceil(600e6 / wb))))
