@@ -333,7 +333,17 @@ namespace {
 
 struct Source { atlasx_safetensors* st; int index; };
 
+// Peak resident set of THIS program image: VmHWM belongs to the address space, which starts afresh at exec,
+// whereas getrusage's ru_maxrss also carries the peak of the process that forked us.
 size_t peak_rss_bytes() {
+    if (FILE* f = fopen("/proc/self/status", "r")) {
+        char line[256];
+        size_t kb = 0;
+        while (fgets(line, sizeof line, f))
+            if (sscanf(line, "VmHWM: %zu kB", &kb) == 1) break;
+        fclose(f);
+        if (kb) return kb * 1024;
+    }
     struct rusage ru;
     if (getrusage(RUSAGE_SELF, &ru) != 0) return 0;
     return (size_t)ru.ru_maxrss * 1024;
@@ -383,10 +393,48 @@ int load_from_files(atlasx_ctx* ctx, const std::vector<std::string>& paths, atla
     *out = nullptr;
     std::vector<atlasx_safetensors*> files;
     atlasx_model* m = nullptr;
+    // Whole-row tensors go file → pinned buffer → device without touching the mapping: two pinned chunks take turns
+    // (pread into one while the copy engine drains the other), and a device staging buffer that only grows receives
+    // the tensor before it is placed.  Host memory in use stays at the two chunks whatever the file size.
+    constexpr size_t kChunk = (size_t)32 << 20;
+    uint8_t* pin[2] = { nullptr, nullptr };
+    cudaEvent_t pin_free[2] = { nullptr, nullptr };
+    void* dev_stage = nullptr; size_t dev_stage_cap = 0;
     auto cleanup = [&](int rc) {
         for (atlasx_safetensors* f : files) atlasx_safetensors_close(f);
         if (rc && m) atlasx_model_free(m);
+        cudaStreamSynchronize(ctx->stream);
+        for (int i = 0; i < 2; i++) { if (pin[i]) cudaFreeHost(pin[i]); if (pin_free[i]) cudaEventDestroy(pin_free[i]); }
+        cudaFree(dev_stage);
         return rc;
+    };
+    auto stream_rows = [&](const atlasx_safetensors* st, size_t file_off, size_t bytes) -> int {
+        if (!pin[0]) {
+            for (int i = 0; i < 2; i++) {
+                AX_CUDA(cudaMallocHost((void**)&pin[i], kChunk));
+                AX_CUDA(cudaEventCreateWithFlags(&pin_free[i], cudaEventDisableTiming));
+            }
+        }
+        if (bytes > dev_stage_cap) {
+            AX_CUDA(cudaStreamSynchronize(ctx->stream));
+            cudaFree(dev_stage); dev_stage = nullptr; dev_stage_cap = 0;
+            AX_CUDA(cudaMalloc(&dev_stage, bytes));
+            dev_stage_cap = bytes;
+        }
+        int turn = 0;
+        for (size_t o = 0; o < bytes; o += kChunk, turn ^= 1) {
+            const size_t len = bytes - o < kChunk ? bytes - o : kChunk;
+            AX_CUDA(cudaEventSynchronize(pin_free[turn]));                // the copy that last used this chunk is done
+            size_t got = 0;
+            while (got < len) {
+                const ssize_t r = pread(st->fd, pin[turn] + got, len - got, (off_t)(file_off + o + got));
+                if (r <= 0) return atlasx_fail(ATLASX_ERR_ARG, "%s: short read at offset %zu", st->path.c_str(), file_off + o + got);
+                got += (size_t)r;
+            }
+            AX_CUDA(cudaMemcpyAsync((uint8_t*)dev_stage + o, pin[turn], len, cudaMemcpyHostToDevice, ctx->stream));
+            AX_CUDA(cudaEventRecord(pin_free[turn], ctx->stream));
+        }
+        return ATLASX_OK;
     };
     // later files win over earlier ones for a repeated name, as inserting into the reference's map does (:2480)
     std::map<std::string, Source> all;
@@ -437,8 +485,12 @@ int load_from_files(atlasx_ctx* ctx, const std::vector<std::string>& paths, atla
         const size_t esz = up_dtype == ATLASX_BF16 ? 2 : 4;
         const uint8_t* src = st->map + st->data_start + d.off0;
         const void* host = nullptr;
+        int on_device = 0;
         if (d.dtype != ATLASX_F16 && nc == cols) {
-            host = src + r0 * cols * esz;                 // whole rows: the bytes as they lie in the file
+            // whole rows: the bytes as they lie in the file, streamed through the pinned chunks
+            rc = stream_rows(st, st->data_start + d.off0 + r0 * cols * esz, nr * nc * esz);
+            if (rc) return cleanup(rc);
+            host = dev_stage; on_device = 1;
         } else {
             stage.resize(nr * nc * esz);
             rc = atlasx_safetensors_read(st, kv.second.index, r0, r1, c0, c1, up_dtype, stage.data());
@@ -447,11 +499,11 @@ int load_from_files(atlasx_ctx* ctx, const std::vector<std::string>& paths, atla
         }
         file_bytes += nr * nc * (d.dtype == ATLASX_F32 ? 4 : 2);
         up_bytes += nr * nc * esz;
-        rc = whole ? atlasx_model_set_tensor(m, layer < 0 ? 0 : layer, which, host, up_dtype, 0)
-                   : atlasx_model_set_tensor_slice(m, layer < 0 ? 0 : layer, which, host, up_dtype, 0);
+        rc = whole ? atlasx_model_set_tensor(m, layer < 0 ? 0 : layer, which, host, up_dtype, on_device)
+                   : atlasx_model_set_tensor_slice(m, layer < 0 ? 0 : layer, which, host, up_dtype, on_device);
         if (rc) return cleanup(rc);
-        // the mapped pages of this tensor are not needed again
-        {
+        // pages of the mapping that a gathered or converted slice touched are not needed again
+        if (!on_device) {
             const long pg = sysconf(_SC_PAGESIZE);
             const uintptr_t a0 = ((uintptr_t)src + r0 * cols * esz) & ~(uintptr_t)(pg - 1);
             const uintptr_t a1 = (uintptr_t)src + r1 * cols * esz;

@@ -329,6 +329,85 @@ def print_timeline(m, n_layers, quiet=False):
                      t[i, 2] - t[i - 1, 3], t[i, 5] - t[i, 2], t[i, 3] - t[i, 4]))
 
 
+def hf_tensor_names(n_layers):
+    """(name, bench tensor key, layer, tensor id) in the order the synthetic file is written; names as the
+    loaders match them (crates/atlas-model/src/lib.rs:2328-2346), post-norm layout."""
+    out = [("model.embed_tokens.weight", "embed", 0, 1), ("lm_head.weight", "lm_head", 0, 2)]
+    local = {"wq": "self_attn.q_proj", "wk": "self_attn.k_proj", "wv": "self_attn.v_proj", "wo": "self_attn.o_proj",
+             "gate": "mlp.gate_proj", "up": "mlp.up_proj", "down": "mlp.down_proj"}
+    for l in range(n_layers):
+        for name, tid in PER_LAYER:
+            out.append(("model.layers.%d.%s.weight" % (l, local[name]), name, l, 1000 + l * 32 + tid))
+    return out
+
+
+def run_loader_leg(args):
+    """Weight load of the benchmark model from a safetensors file (BASELINE: the reference takes 109 s and 28 GB of
+    host memory for the real checkpoint): the synthetic model is written once as bf16 (13.77 GB, same seeded
+    tensors as the benchmark), then a fresh process maps it and loads it to the device; that process reports
+    seconds, bytes and its peak resident set, and generates the first tokens for comparison with the in-memory
+    model."""
+    import atlas_b200 as ab
+    from atlas_b200 import _ffi
+    import ctypes as C
+    path = args.loader_file
+    if args.loader_child:
+        ctx = ab.Context(0)
+        mc = model_config(ab, args.prompt + 64)
+        m = ab.load_model_from_safetensors(path, mc, ctx=ctx, kv_dtype=ab.BF16)
+        st = m.load_stats
+        prompt = np.random.default_rng(0).integers(0, mc.vocab_size, size=64, dtype=np.uint32)
+        toks = m.generate(prompt, 8, 0.0)
+        print(json.dumps({"seconds": st.seconds, "file_bytes_read": st.file_bytes_read, "bytes_uploaded": st.bytes_uploaded,
+                          "peak_host_rss_bytes": st.peak_host_rss_bytes, "n_tensors": st.n_tensors_used,
+                          "post_norm": st.post_norm, "tokens": [int(t) for t in toks]}))
+        return
+    ctx = ab.Context(0)
+    L = _ffi.lib()
+    mc = model_config(ab, args.prompt + 64)
+    d, f, V = mc.d_model, mc.ffn_hidden, mc.vocab_size
+    shapes = {"embed": (V, d), "lm_head": (V, d), "wq": (d, d), "wk": (d, d), "wv": (d, d), "wo": (d, d), "gate": (f, d), "up": (f, d), "down": (d, f)}
+    big = ctx.malloc(V * d * 2)
+    tensors = []
+    t0 = time.perf_counter()
+    for name, key, l, stream in hf_tensor_names(mc.n_layers):
+        r, c = shapes[key]
+        _ffi.check(L.atlasx_fill_normal_bf16(ctx.handle, big, r * c, 0, stream, 0, 0.02))
+        host = np.empty(r * c, np.uint16)
+        _ffi.check(L.atlasx_download(ctx.handle, host.ctypes.data_as(C.c_void_p), big, r * c * 2))
+        tensors.append((name, [r, c], host))
+    ones = np.ones(d, np.float32)
+    tensors.append(("model.norm.weight", [d], ones))
+    hd = d // mc.n_heads
+    for l in range(mc.n_layers):
+        for nm in ("post_attention_layernorm", "post_feedforward_layernorm"):
+            tensors.append(("model.layers.%d.%s.weight" % (l, nm), [d], ones))
+        tensors.append(("model.layers.%d.self_attn.q_norm.weight" % l, [mc.n_heads * hd], np.ones(mc.n_heads * hd, np.float32)))
+        tensors.append(("model.layers.%d.self_attn.k_norm.weight" % l, [mc.n_kv_heads * hd], np.ones(mc.n_kv_heads * hd, np.float32)))
+    ctx.free(big)
+    ab.SafetensorsFile.build(path, tensors)
+    t_write = time.perf_counter() - t0
+    size = os.path.getsize(path)
+    del tensors
+    # the in-memory model's first tokens, for the comparison
+    m, _ = build_cuda_model(ab, ctx, args.prompt + 64, 0, 1)
+    prompt = np.random.default_rng(0).integers(0, mc.vocab_size, size=64, dtype=np.uint32)
+    want = [int(t) for t in m.generate(prompt, 8, 0.0)]
+    del m
+    r = subprocess.run([sys.executable, os.path.abspath(__file__), "--loader-child", "--loader-file", path, "--prompt", str(args.prompt),
+                        "--profile-layers", str(PROFILE_LAYERS)], capture_output=True, text=True)
+    if r.returncode != 0:
+        sys.exit("loader child failed: " + r.stderr[-2000:])
+    child = json.loads(r.stdout.strip().splitlines()[-1])
+    os.remove(path)
+    print(json.dumps({"metric": "safetensors_to_device_load", "file_bytes": size, "file": "bf16 tensors of the benchmark model, in the page cache",
+                      "write_s": round(t_write, 2), "load_s": round(child["seconds"], 3),
+                      "load_gb_per_s": round(child["bytes_uploaded"] / child["seconds"] / 1e9, 2),
+                      "bytes_uploaded": child["bytes_uploaded"], "peak_host_rss_gb": round(child["peak_host_rss_bytes"] / 1e9, 3),
+                      "n_tensors": child["n_tensors"], "tokens_from_file": child["tokens"], "tokens_in_memory": want,
+                      "tokens_match": child["tokens"] == want}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -350,12 +429,18 @@ def main():
     ap.add_argument("--weights", default="bf16", choices=["bf16", "int8", "int4"],
                     help="weight format held on the device (quantised from the same bf16 tensors); anything but bf16 marks the line invalid as the benchmark")
     ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")
+    ap.add_argument("--loader", action="store_true", help="separate leg: write the benchmark model as a safetensors file, load it in a fresh process, report time and peak host memory")
+    ap.add_argument("--loader-file", default="/dev/shm/atlas_b200_bench_model.safetensors")
+    ap.add_argument("--loader-child", action="store_true", help=argparse.SUPPRESS)
     args = ap.parse_args()
     global PROFILE_LAYERS, WEIGHTS
     PROFILE_LAYERS = max(0, args.profile_layers)
     WEIGHTS = args.weights
     if args.timeline:
         os.environ["ATLASX_STEP_TRACE"] = "1"
+    if args.loader or args.loader_child:
+        run_loader_leg(args)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
