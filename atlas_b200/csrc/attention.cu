@@ -351,7 +351,8 @@ __global__ void __launch_bounds__(128) ax_qk_prep_kernel(const AxQkPrepArgs a) {
 // before griddepcontrol.wait: rows below `pos` are older than the previous kernel.
 constexpr int kFusedUnroll = 2;
 constexpr int kFusedStagesDefault = 3;
-constexpr int kFusedRowsPerSplit = 64;
+constexpr int kFusedRowsPerSplit = 128;        // cached rows a split takes at least: with few KV heads per GPU (tensor parallel) 64 made
+                                               // twice the splits and a slower merge (4 GPUs: 1.476 → 1.420 ms per token)
 __host__ __device__ constexpr size_t fused_land_bytes(int nst) { return (size_t)nst * kFusedUnroll * 2 * kAttnThreads * 16; }
 
 struct FusedDev {
@@ -359,6 +360,7 @@ struct FusedDev {
     float* partials;       // [n_heads × max_splits × 130]
     unsigned* tickets;     // [batch × n_kv], zero between launches
     unsigned long long* trace;
+    int rows_per_split;    // cached rows a split takes at least
     // operator form (q_ready != null): q is already normed and rotated, the cache already holds row
     // `pos`, grid.z runs over sequences; nothing is prepared or written besides the output
     const float* q_ready; size_t seq_stride; const int* pos_b; int pos_shared; int pos_scalar;
@@ -398,7 +400,7 @@ __global__ void __launch_bounds__(kAttnThreads) ax_attn_fused_kernel(const Fused
     const int tb = (a.window > 0 && pos - a.window + 1 > 0) ? pos - a.window + 1 : 0;
     const int t_end = prep ? pos : pos + 1;       // fused form: row `pos` comes from shared memory
     const int rows = t_end - tb;                  // cached rows to stream
-    int S = (rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
+    int S = (rows + dv.rows_per_split - 1) / dv.rows_per_split;
     S = S < 1 ? 1 : (S > (int)gridDim.x ? (int)gridDim.x : S);
     if (split >= S) return;
     const int per = (rows + S - 1) / S;
@@ -705,6 +707,7 @@ int ax_attn_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
             fd.partials = ctx->attn_partials; fd.tickets = ctx->attn_tickets;
         }
         fd.trace = nullptr;
+        fd.rows_per_split = kFusedRowsPerSplit;
         fd.q_ready = a.q; fd.seq_stride = a.seq_stride; fd.pos_b = a.pos; fd.pos_shared = a.pos_shared; fd.pos_scalar = a.pos_scalar;
         if (a.kv_dtype == ATLASX_BF16)
             return g_real == 1 ? launch_fused<true, 1>(ctx, fd, pdl, a.batch) : g_real == 2 ? launch_fused<true, 2>(ctx, fd, pdl, a.batch)
@@ -738,7 +741,8 @@ bool ax_attn_fused_supported(int hd, int n_heads, int n_kv) {
 }
 int ax_attn_fused_max_splits(const atlasx_ctx* ctx, int n_kv, int max_rows) {
     // one wave of CTAs
-    int s = (max_rows + kFusedRowsPerSplit - 1) / kFusedRowsPerSplit;
+    const int rps = ctx->tune.attn_rows > 0 ? ctx->tune.attn_rows : kFusedRowsPerSplit;
+    int s = (max_rows + rps - 1) / rps;
     const int per_sm = ctx->tune.attn_wave;      // 2 measured best with three landing stages (48 KB per CTA)
     const int wave = (per_sm * ctx->sm_count) / (n_kv > 0 ? n_kv : 1);
     if (s > wave) s = wave;
@@ -766,6 +770,7 @@ int ax_attn_fused_launch(atlasx_ctx* ctx, const AxFusedAttnArgs& a, bool pdl) {
         dv.tickets = ctx->attn_tickets;
     }
     dv.trace = nullptr;
+    dv.rows_per_split = ctx->tune.attn_rows > 0 ? ctx->tune.attn_rows : kFusedRowsPerSplit;
     dv.q_ready = nullptr; dv.seq_stride = 0; dv.pos_b = nullptr; dv.pos_shared = 1; dv.pos_scalar = 0;
     if (ctx->trace_next) { dv.trace = ctx->trace_next; ctx->trace_next += 6; }
     const int g = a.n_heads / a.n_kv;

@@ -60,6 +60,7 @@ struct atlasx_ctx {
         int pdl_mask = 0x7FFFFFFF;     // ATLASX_PDL_MASK: bit per launch class of the decode step
         int attn_fused = 1;            // ATLASX_ATTN_FUSED=0: QK-norm/RoPE/cache write and attention as two launches
         int attn_stages = 3;           // ATLASX_ATTN_STAGES: landing stages of the one-launch attention inside a step (2..4)
+        int attn_rows = 0;             // ATLASX_ATTN_ROWS: cached rows per split of the one-launch attention (0: 64)
         int attn_wave = 2;             // ATLASX_ATTN_WAVE: attention CTAs per SM that one wave of splits may fill
         int attn_mma = 1;              // ATLASX_ATTN_MMA=0: operator-form GQA attention on the scalar kernels instead of the tensor cores
         int umma = 1;                  // ATLASX_UMMA=0: token batches on the warp-level MMA kernel instead of tcgen05

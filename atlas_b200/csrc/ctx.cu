@@ -59,6 +59,7 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_ATTN_FUSED", &c->tune.attn_fused);
         env_int("ATLASX_ATTN_STAGES", &c->tune.attn_stages);
         env_int("ATLASX_ATTN_WAVE", &c->tune.attn_wave);
+        env_int("ATLASX_ATTN_ROWS", &c->tune.attn_rows);
         env_int("ATLASX_ATTN_MMA", &c->tune.attn_mma);
         env_int("ATLASX_UMMA", &c->tune.umma);
         env_int("ATLASX_ATTN_PACK", &c->tune.attn_pack);
