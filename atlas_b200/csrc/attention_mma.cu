@@ -356,6 +356,8 @@ struct ChunkDev {
 __global__ void __launch_bounds__(kThreads) ax_attn_mma_chunk_kernel(const ChunkDev dv) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ int s_last;
+    asm volatile("griddepcontrol.wait;" ::: "memory");        // queries and the chunk's K/V rows come from the kernels before
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int split = blockIdx.x, kh = blockIdx.y, rg = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = dv.g, TPG = 16 / G;                          // tokens per row group
@@ -683,7 +685,7 @@ int ax_attn_mma_chunk_splits(const atlasx_ctx* ctx, int n_heads, int n_kv, int n
 }
 size_t ax_attn_mma_chunk_partial_floats(int n_tok, int n_heads, int n_splits) { return (size_t)n_tok * n_heads * n_splits * kST; }
 
-int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a) {
+int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a, bool pdl) {
     AX_ARG(ax_attn_mma_chunk_supported(128, a.n_heads, a.n_kv, ATLASX_BF16), "shape not covered by the chunk attention kernel");
     AX_ARG(a.q && a.kc && a.vc && a.out && a.pos0 && a.partials && a.tickets && a.n_tok >= 1 && a.n_tok <= 64, "bad argument");
     static bool attr_done[64] = {};
@@ -699,7 +701,14 @@ int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a) {
     dv.partials = a.partials; dv.tickets = a.tickets;
     const int tpg = 16 / dv.g;
     dim3 grid((unsigned)dv.n_splits, (unsigned)a.n_kv, (unsigned)((a.n_tok + tpg - 1) / tpg));
-    ax_attn_mma_chunk_kernel<<<grid, kThreads, kSmemBytes, ctx->stream>>>(dv);
-    AX_CHECK_LAUNCH("ax_attn_mma_chunk_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = kSmemBytes; cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_attn_mma_chunk_kernel, dv));
     return ATLASX_OK;
 }

@@ -492,10 +492,14 @@ constexpr int kPrefillMax = 64;                // tokens per chunk with the tcge
 constexpr int kPrefillMaxMma = 16;
 
 // ── prompt ingestion: row-wise helpers, one CTA per token ───────────────────────────
+// Every kernel of a chunk starts with griddepcontrol.wait, so each may be launched with programmatic stream
+// serialization: it becomes resident while its predecessor drains and touches memory only after that one is complete.
 __global__ void pf_positions_k(const StepState* st, int* pos_arr, int n) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     if ((int)threadIdx.x < n) pos_arr[threadIdx.x] = st->pos + threadIdx.x;
 }
 __global__ void pf_embed_rows_k(const void* embed, int bf16, int vocab, const int* seq, const int* pos_arr, int d, float* out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int i = blockIdx.x;
     long long tok = seq[pos_arr[i]];
     if (tok < 0) tok = 0;
@@ -517,6 +521,7 @@ __device__ __forceinline__ float pf_block_sum(float v, float* red) {
 __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const float* base, const float* wy, const float* wx, float eps,
                                                            int d, float* resid, float* x) {
     __shared__ float red[32];
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t o = (size_t)blockIdx.x * d;
     const int nt = blockDim.x;
     float inv_y = 1.f;
@@ -541,6 +546,7 @@ __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const
 }
 // gate/up rows are interleaved (even: gate, odd: up): out[i][j] = silu(gu[i][2j]) · gu[i][2j+1]
 __global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t i = blockIdx.y;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= f) return;
@@ -566,9 +572,24 @@ int prefill_limit(const atlasx_model* m) {
     return limit;
 }
 // One layer product of a chunk: X [n][cols] → Y [n][rows]
-int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y) {
-    if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, false);
+int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y, bool pdl) {
+    if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, pdl);
     return ax_gemv_mma_launch(c, w, x, n, y, true);
+}
+
+// Launch with programmatic stream serialization (the kernel waits for its predecessor itself).
+template <typename... KArgs, typename... Args>
+int pf_launch(cudaStream_t s, bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+    }
+    AX_CUDA(cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...));
+    return ATLASX_OK;
 }
 
 // n prompt tokens (2..kPrefillMax) at once: seq[pos .. pos+n) → caches, logits of the last one,
@@ -582,13 +603,19 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     const bool post = cf.post_norm != 0;
     const int qkv_rows = m->q_rows + 2 * m->kv_rows;
     int rc;
-    pf_positions_k<<<1, kPrefillMax, 0, s>>>(m->st, m->pf_pos, n);
-    pf_embed_rows_k<<<n, 256, 0, s>>>(m->embed, m->embed_bf16, cf.vocab_size, m->seq, m->pf_pos, d, m->pf_r);
+    const bool pdl = m->use_pdl != 0;
+    if ((rc = pf_launch(s, false, pf_positions_k, dim3(1), dim3(kPrefillMax), (const StepState*)m->st, m->pf_pos, n))) return rc;
+    if ((rc = pf_launch(s, pdl, pf_embed_rows_k, dim3((unsigned)n), dim3(256), (const void*)m->embed, (int)m->embed_bf16, cf.vocab_size,
+                        (const int*)m->seq, (const int*)m->pf_pos, d, m->pf_r))) return rc;
     const float* a_in = m->pf_r;
-    if (!post) { pf_rows_norm_add_k<<<n, 1024, 0, s>>>(nullptr, m->pf_r, nullptr, m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a); a_in = m->pf_a; }
+    if (!post) {
+        if ((rc = pf_launch(s, pdl, pf_rows_norm_add_k, dim3((unsigned)n), dim3(1024), (const float*)nullptr, (const float*)m->pf_r, (const float*)nullptr,
+                            (const float*)m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a))) return rc;
+        a_in = m->pf_a;
+    }
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
-        if ((rc = pf_product(c, ly.qkv, a_in, n, m->pf_qkv))) return rc;
+        if ((rc = pf_product(c, ly.qkv, a_in, n, m->pf_qkv, pdl))) return rc;
         if (m->pf_attn_splits > 0) {
             // QK-norm, RoPE and cache write of all n tokens at once, then ONE causal attention launch
             AxQkPrepArgs qa;
@@ -598,13 +625,13 @@ int run_prefill_chunk(atlasx_model* m, int n) {
             qa.pos = m->pf_pos; qa.pos_shared = 0; qa.batch = n;
             qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype; qa.eps = 1e-6f;
             qa.q_stride = (size_t)qkv_rows; qa.kv_in_stride = (size_t)qkv_rows;
-            if ((rc = ax_qk_prep_launch(c, qa, false))) return rc;
+            if ((rc = ax_qk_prep_launch(c, qa, pdl))) return rc;
             AxAttnChunkArgs ca;                                // ONE causal attention launch for the chunk
             ca.q = m->pf_qkv; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
             ca.out = m->pf_att; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos;
             ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
             ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
-            if ((rc = ax_attn_mma_chunk_launch(c, ca))) return rc;
+            if ((rc = ax_attn_mma_chunk_launch(c, ca, pdl))) return rc;
         } else
         for (int i = 0; i < n; i++) {
             float* qkv = m->pf_qkv + (size_t)i * qkv_rows;
@@ -633,16 +660,20 @@ int run_prefill_chunk(atlasx_model* m, int n) {
                 if ((rc = ax_attn_launch(c, aa, false))) return rc;
             }
         }
-        if ((rc = pf_product(c, ly.wo, m->pf_att, n, m->pf_o))) return rc;
+        if ((rc = pf_product(c, ly.wo, m->pf_att, n, m->pf_o, pdl))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
-        pf_rows_norm_add_k<<<n, 1024, 0, s>>>(m->pf_o, m->pf_r, post ? ly.attn_norm : nullptr, post ? nullptr : ly.ffn_norm,
-                                             cf.rms_norm_eps, d, m->pf_r, m->pf_a);
-        if ((rc = pf_product(c, ly.gateup, m->pf_a, n, m->pf_gu))) return rc;
-        pf_silu_pair_rows_k<<<dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)n), 256, 0, s>>>(m->pf_gu, m->ffn_loc, m->pf_h);
-        if ((rc = pf_product(c, ly.down, m->pf_h, n, m->pf_dn))) return rc;
+        const bool after_nccl = m->world > 1;             // an NCCL kernel in front: plain stream order
+        if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)n), dim3(1024), (const float*)m->pf_o, (const float*)m->pf_r,
+                            (const float*)(post ? ly.attn_norm : nullptr), (const float*)(post ? nullptr : ly.ffn_norm),
+                            cf.rms_norm_eps, d, m->pf_r, m->pf_a))) return rc;
+        if ((rc = pf_product(c, ly.gateup, m->pf_a, n, m->pf_gu, pdl))) return rc;
+        if ((rc = pf_launch(s, pdl, pf_silu_pair_rows_k, dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)n), dim3(256),
+                            (const float*)m->pf_gu, m->ffn_loc, m->pf_h))) return rc;
+        if ((rc = pf_product(c, ly.down, m->pf_h, n, m->pf_dn, pdl))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_dn, (size_t)n * d))) return rc;
         const float* next_wx = (post || l == L - 1) ? nullptr : m->layers[l + 1].attn_norm;
-        pf_rows_norm_add_k<<<n, 1024, 0, s>>>(m->pf_dn, m->pf_r, post ? ly.ffn_norm : nullptr, next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a);
+        if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)n), dim3(1024), (const float*)m->pf_dn, (const float*)m->pf_r,
+                            (const float*)(post ? ly.ffn_norm : nullptr), next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a))) return rc;
         a_in = m->pf_a;
     }
     AX_CHECK_LAUNCH("prefill chunk");
