@@ -36,34 +36,33 @@ namespace {
 //   x ≈ s_c·(q1 + q2/254 [+ q3/254²]),  s_c = max|x| over the 32 elements / 127,  digits in [−127, 127].
 // Two planes leave |error| ≤ s_c / (2·254) ≈ 1.6e-5·max|x| of the group per element — errors of
 // random sign that add up to ≈ 1e-5 of the result, a hundred times inside the 1e-3 parity bar —
-// for two thirds of the integer dot products of three planes (which would leave 6e-8·max|x|).  The weights are then used as they lie in memory (int8 words; int4 nibbles
-// spread to bytes with two logic operations) in dp4a instructions with integer-exact sums:
-// 0.75 (int8) or 1 (int4) instruction per element instead of 3 for convert-subtract-FMA.
+// for two thirds of the integer dot products of three planes (which would leave 6e-8·max|x|).
+// The weights are then used as they lie in memory in dp4a instructions with integer-exact sums:
+// int8 words directly; int4 nibbles as the HIGH halves of signed bytes — (w & 0xF0F0F0F0) is sixteen
+// times the even elements in two's complement, ((w << 4) & 0xF0F0F0F0) sixteen times the odd ones,
+// so there is no offset to undo and the factor 16 is divided out of the group scale.  That is 0.5
+// (int8) or 0.75 (int4) instruction per element instead of 3 for convert-subtract-FMA.
 // Scales per 32 elements need no block-wide reduction: eight neighbouring threads own a group.
 constexpr float kDigitBase = 254.0f;
 constexpr int kPlanes = 2;
 __host__ __device__ constexpr int digit_plane_bytes(int K) { return (K + 127) / 128 * 128; }
 __host__ __device__ constexpr int digit_groups(int K) { return ((K + 31) / 32 + 31) / 32 * 32; }
-// the planes, the group scales, and for int4 one table of digit sums per plane and group (the +8 offset of the nibbles)
+// the planes and the group scales
 __host__ __device__ constexpr int digit_bytes(int fmt, int K) {
-    return fmt == ATLASX_INT8 ? kPlanes * digit_plane_bytes(K) + digit_groups(K) * 4
-         : fmt == ATLASX_INT4 ? kPlanes * digit_plane_bytes(K) + (1 + kPlanes) * digit_groups(K) * 4 : 0;
+    return (fmt == ATLASX_INT8 || fmt == ATLASX_INT4) ? kPlanes * digit_plane_bytes(K) + digit_groups(K) * 4 : 0;
 }
 __device__ __forceinline__ int dp4a_ss(uint32_t a, uint32_t b, int c) {
     int d; asm("dp4a.s32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
 }
-__device__ __forceinline__ int dp4a_us(uint32_t a, uint32_t b, int c) {      // a: four unsigned bytes, b: four signed bytes
-    int d; asm("dp4a.u32.s32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c)); return d;
-}
 
 // After stage_input: xs holds the f32 input in natural order.  Writes the digit planes
 // (int8: natural element order; int4: inside every group of eight elements the even ones first,
-// then the odd ones, matching the nibble spread), the scale of every 32 elements and, for int4,
-// the sum of each plane over the same 32 elements.  Ends with a barrier.
+// then the odd ones, matching the nibble masks) and the scale of every 32 elements (for int4 divided by the 16
+// the nibbles carry as high halves of their bytes).  Ends with a barrier.
 template <int FMT, int NTHR>
-__device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* xs, uint8_t* xq, float* xsc, int* bs) {
+__device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* xs, uint8_t* xq, float* xsc) {
     const int K = a.K, n4 = K >> 2, tid = threadIdx.x;
-    const int pb = digit_plane_bytes(K), ng = digit_groups(K);
+    const int pb = digit_plane_bytes(K);
     for (int base = 0; base < n4; base += NTHR) {            // every lane of a warp runs the same trips (shuffles below)
         const int k4 = base + tid;
         const bool in = k4 < n4;
@@ -96,16 +95,8 @@ __device__ __forceinline__ void digitize_input(const GemvArgs& a, const float4* 
             const float a3 = (r1 - q2) * kDigitBase + M;
             d1[j] = __float_as_int(a1) - 0x4B400000; d2[j] = __float_as_int(a2) - 0x4B400000; d3[j] = __float_as_int(a3) - 0x4B400000;
         }
-        if (FMT == ATLASX_INT4) {
-            int t1 = d1[0] + d1[1] + d1[2] + d1[3], t2 = d2[0] + d2[1] + d2[2] + d2[3], t3 = d3[0] + d3[1] + d3[2] + d3[3];
-#pragma unroll
-            for (int o = 1; o < 8; o <<= 1) {
-                t1 += __shfl_xor_sync(AX_FULL, t1, o); t2 += __shfl_xor_sync(AX_FULL, t2, o); t3 += __shfl_xor_sync(AX_FULL, t3, o);
-            }
-            if (in && (k4 & 7) == 0) { bs[k4 >> 3] = t1; bs[ng + (k4 >> 3)] = t2; if (kPlanes > 2) bs[2 * ng + (k4 >> 3)] = t3; }
-        }
         if (!in) continue;
-        if ((k4 & 7) == 0) xsc[k4 >> 3] = mx / 127.0f + bad;
+        if ((k4 & 7) == 0) xsc[k4 >> 3] = (mx / 127.0f + bad) * (FMT == ATLASX_INT4 ? 0.0625f : 1.0f);
         if (FMT == ATLASX_INT8) {
             auto word = [](const int (&d)[4]) { return (uint32_t)(d[0] & 255) | ((uint32_t)(d[1] & 255) << 8) | ((uint32_t)(d[2] & 255) << 16) | ((uint32_t)(d[3] & 255) << 24); };
             reinterpret_cast<uint32_t*>(xq)[k4] = word(d1);
@@ -128,7 +119,7 @@ __host__ __device__ constexpr int scale_land_bytes(int nthr) { return 2 * 8 * nt
 
 template <int FMT, int NTHR>
 __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, float4* xb, float* red, float* part, uint32_t* sland,
-                                               uint8_t* xq, float* xsc, int* bs, int lo, int hi) {
+                                               uint8_t* xq, float* xsc, int lo, int hi) {
     constexpr int EPC = Fmt<FMT>::EPC;
     constexpr int P = EPC / 4;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -193,10 +184,9 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
     ax_trace_release(a.trace);
     constexpr bool QUANT = FMT == ATLASX_INT8 || FMT == ATLASX_INT4;
     stage_input<FMT, NTHR, QUANT>(a, xs, red, xb);     // ends with a barrier: the zeroed partials are visible too
-    if (QUANT) digitize_input<FMT, NTHR>(a, xs, xq, xsc, bs);
+    if (QUANT) digitize_input<FMT, NTHR>(a, xs, xq, xsc);
     ax_trace_staged(a.trace);
     const int pb = digit_plane_bytes(a.K);
-    const int nbp = digit_groups(a.K);
     constexpr float k2 = 1.0f / kDigitBase, k3 = 1.0f / (kDigitBase * kDigitBase);
 
     Acc4 acc0 = acc4_zero(), acc1 = acc4_zero();
@@ -233,21 +223,22 @@ __device__ __forceinline__ void consume_direct(const GemvArgs& a, float4* xs, fl
                     // of 32 and divides the row length): scale index = row · scales_per_row + chunk / (block/32)
                     int idx0, idx1; bool ok;
                     scale_index(p, b, u, idx0, idx1, ok);
-                    // nibbles (q + 8) spread to bytes: high nibbles = even elements, low nibbles = odd ones
-                    const uint32_t wx[4] = { wa[u].x ^ 0x88888888u, wa[u].y ^ 0x88888888u, wa[u].z ^ 0x88888888u, wa[u].w ^ 0x88888888u };
-                    const uint32_t wy[4] = { wb[u].x ^ 0x88888888u, wb[u].y ^ 0x88888888u, wb[u].z ^ 0x88888888u, wb[u].w ^ 0x88888888u };
+                    // a nibble in the high half of a byte IS sixteen times its two's-complement value as a signed byte:
+                    // high nibbles = even elements as they lie, low nibbles = odd elements after a shift by four
+                    const uint32_t wx[4] = { wa[u].x, wa[u].y, wa[u].z, wa[u].w };
+                    const uint32_t wy[4] = { wb[u].x, wb[u].y, wb[u].z, wb[u].w };
+                    constexpr uint32_t HI = 0xF0F0F0F0u;
                     float f0 = 0.f, f1 = 0.f;
 #pragma unroll
                     for (int pl = 0; pl < kPlanes; pl++) {
                         const uint4 qa = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 32);
                         const uint4 qb = *reinterpret_cast<const uint4*>(xq + pl * pb + c * 32 + 16);
                         const uint32_t qe[4] = { qa.x, qa.z, qb.x, qb.z }, qo[4] = { qa.y, qa.w, qb.y, qb.w };
-                        const int off = 8 * bs[pl * nbp + c];
-                        int t0 = -off, t1 = -off;
+                        int t0 = 0, t1 = 0;
 #pragma unroll
                         for (int g = 0; g < 4; g++) {
-                            t0 = dp4a_us((wx[g] >> 4) & 0x0F0F0F0Fu, qe[g], t0); t0 = dp4a_us(wx[g] & 0x0F0F0F0Fu, qo[g], t0);
-                            if (v1) { t1 = dp4a_us((wy[g] >> 4) & 0x0F0F0F0Fu, qe[g], t1); t1 = dp4a_us(wy[g] & 0x0F0F0F0Fu, qo[g], t1); }
+                            t0 = dp4a_ss(wx[g] & HI, qe[g], t0); t0 = dp4a_ss((wx[g] << 4) & HI, qo[g], t0);
+                            if (v1) { t1 = dp4a_ss(wy[g] & HI, qe[g], t1); t1 = dp4a_ss((wy[g] << 4) & HI, qo[g], t1); }
                         }
                         const float wgt = pl == 0 ? 1.f : pl == 1 ? k2 : k3;
                         f0 = fmaf((float)t0, wgt, f0); f1 = fmaf((float)t1, wgt, f1);
@@ -332,9 +323,8 @@ ax_gemv_stream_kernel(const GemvArgs a) {
         uint32_t* sland = reinterpret_cast<uint32_t*>(after_x);                              // int4 only: [2][8][threads] scale slots
         uint8_t* xq = after_x + (FMT == ATLASX_INT4 ? scale_land_bytes(NTHR) : 0);
         float* xsc = reinterpret_cast<float*>(xq + kPlanes * digit_plane_bytes(a.K));              // scale per 32 input elements
-        int* bs = reinterpret_cast<int*>(xsc + digit_groups(a.K));                           // int4: digit sums per 32 elements
         float* part = reinterpret_cast<float*>(xq + digit_bytes(FMT, a.K));                  // [pairs][warps][2]
-        consume_direct<FMT, NTHR>(a, xs, xb, red, part, sland, xq, xsc, bs, lo, hi);
+        consume_direct<FMT, NTHR>(a, xs, xb, red, part, sland, xq, xsc, lo, hi);
         return;
     }
 
