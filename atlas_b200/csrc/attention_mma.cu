@@ -31,6 +31,7 @@ constexpr int kTileBytes = kTileRows * kPitch; // one of K or V
 constexpr int kStageBytes = 2 * kTileBytes;
 constexpr int kWarpBytes = kStages * kStageBytes;
 constexpr int kST = 130;                       // partial state: m, l, 128 outputs
+constexpr int kChunkMaxSplits = 16;
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, bool valid) {
@@ -674,15 +675,25 @@ bool ax_attn_mma_chunk_supported(int hd, int n_heads, int n_kv, int kv_dtype) {
     const int g = n_heads / n_kv;
     return g == 1 || g == 2 || g == 4 || g == 8 || g == 16;
 }
-int ax_attn_mma_chunk_splits(const atlasx_ctx* ctx, int n_heads, int n_kv, int n_tok, int max_rows) {
+// Splits over the context for a chunk launch that sees `rows` cached rows: waves of CTAs (one CTA per SM) ×
+// (tiles a warp walks + four tile times for building the query fragments, the merge of the warps and the partial
+// states), the cheapest count up to kChunkMaxSplits.  Short contexts run unsplit: a split that leaves a warp two
+// tiles spends most of its time on the fixed part.
+int ax_attn_mma_chunk_splits(const atlasx_ctx* ctx, int n_heads, int n_kv, int n_tok, int rows) {
     const int g = n_heads / n_kv, tpg = 16 / g;
     const int groups = n_kv * ((n_tok + tpg - 1) / tpg);
-    const int tiles = (max_rows + kTileRows - 1) / kTileRows;
-    int s = (2 * ctx->sm_count + groups - 1) / groups;                     // about two waves of CTAs
-    const int cap = tiles / 8 > 1 ? tiles / 8 : 1;                          // at least eight tiles (two per warp) per CTA
-    if (s > cap) s = cap;
-    return s < 1 ? 1 : (s > 64 ? 64 : s);
+    const int tiles = (rows + kTileRows - 1) / kTileRows;
+    int best = 1; double best_cost = 1e300;
+    for (int s = 1; s <= kChunkMaxSplits && s <= (tiles > 1 ? tiles : 1); s++) {
+        const long long ctas = (long long)groups * s;
+        const double waves = (double)((ctas + ctx->sm_count - 1) / ctx->sm_count);
+        const double per_warp = (double)((tiles + s - 1) / s + kWarps - 1) / kWarps;
+        const double cost = waves * (per_warp + 4.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
+    }
+    return best;
 }
+int ax_attn_mma_chunk_max_splits() { return kChunkMaxSplits; }
 size_t ax_attn_mma_chunk_partial_floats(int n_tok, int n_heads, int n_splits) { return (size_t)n_tok * n_heads * n_splits * kST; }
 
 int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a, bool pdl) {

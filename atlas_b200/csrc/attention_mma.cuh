@@ -23,4 +23,5 @@ struct AxAttnChunkArgs {
 bool ax_attn_mma_chunk_supported(int hd, int n_heads, int n_kv, int kv_dtype);
 int ax_attn_mma_chunk_splits(const atlasx_ctx* ctx, int n_heads, int n_kv, int n_tok, int max_rows);
 size_t ax_attn_mma_chunk_partial_floats(int n_tok, int n_heads, int n_splits);
+int ax_attn_mma_chunk_max_splits();                  // scratch is sized for this many
 int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a, bool pdl = false);

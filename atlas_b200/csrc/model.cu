@@ -629,7 +629,13 @@ int run_prefill_chunk(atlasx_model* m, int n) {
             AxAttnChunkArgs ca;                                // ONE causal attention launch for the chunk
             ca.q = m->pf_qkv; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
             ca.out = m->pf_att; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos;
-            ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window; ca.n_splits = m->pf_attn_splits;
+            ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window;
+            {   // splits for the rows this chunk really sees in this layer (the position is known on the host)
+                int rows_seen = m->host_pos + n;
+                if (ly.window > 0 && rows_seen > ly.window + n) rows_seen = ly.window + n;
+                ca.n_splits = ax_attn_mma_chunk_splits(c, m->nh_loc, m->nkv_loc, n, rows_seen);
+                if (ca.n_splits > m->pf_attn_splits) ca.n_splits = m->pf_attn_splits;
+            }
             ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
             if ((rc = ax_attn_mma_chunk_launch(c, ca, pdl))) return rc;
         } else
@@ -1135,7 +1141,7 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
         if (rc) return rc;
         if (m->cfg.kv_dtype == ATLASX_BF16 && ax_attn_mma_chunk_supported(m->hd, m->nh_loc, m->nkv_loc, m->cfg.kv_dtype)) {
             const int A = kPrefillMax;
-            m->pf_attn_splits = ax_attn_mma_chunk_splits(m->ctx, m->nh_loc, m->nkv_loc, A, m->cfg.max_seq_len);
+            m->pf_attn_splits = ax_attn_mma_chunk_max_splits();      // scratch for the largest split count; each chunk picks its own
             if ((rc = dmalloc(m, (void**)&m->pf_attn_partials, ax_attn_mma_chunk_partial_floats(A, m->nh_loc, m->pf_attn_splits) * 4)) ||
                 (rc = dmalloc(m, (void**)&m->pf_attn_tickets, (size_t)m->nkv_loc * A * sizeof(unsigned)))) return rc;
             AX_CUDA(cudaMemsetAsync(m->pf_attn_tickets, 0, (size_t)m->nkv_loc * A * sizeof(unsigned), m->ctx->stream));
