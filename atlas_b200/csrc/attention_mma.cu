@@ -582,15 +582,14 @@ bool ax_attn_mma_supported(const AxAttnArgs& a) {
 namespace {
 // shapes of the operator kernel: warps, stages, cached rows per warp tile, CTAs that fit one SM's shared memory
 struct MmaShape { int warps, stages, rows, per_sm; };
-constexpr MmaShape kShapes[] = { {6, 2, 32, 1}, {4, 3, 32, 1}, {8, 3, 16, 1}, {12, 2, 16, 1}, {6, 4, 16, 1}, {8, 2, 16, 1},
-                                 {6, 2, 16, 2}, {4, 2, 16, 3}, {4, 3, 16, 2} };
+constexpr MmaShape kShapes[] = { {6, 2, 32, 1}, {4, 3, 32, 1}, {8, 2, 16, 1}, {6, 2, 16, 2}, {4, 2, 16, 3} };
 constexpr int kNumShapes = (int)(sizeof(kShapes) / sizeof(kShapes[0]));
 // Many (sequence, KV head) groups: two smaller CTAs per SM, so that one CTA's pipeline fill and merge run
 // under the other's steady state.  Few groups: one CTA per SM with eight warps, fewer and longer splits.
 inline int shape_index(const atlasx_ctx* ctx, int groups) {
     const int i = ctx->tune.attn_cfg;
     if (i >= 0 && i < kNumShapes) return i;
-    return groups >= 2 * ctx->sm_count ? 6 : 5;
+    return groups >= 2 * ctx->sm_count ? 3 : 2;
 }
 }  // namespace
 
@@ -658,13 +657,9 @@ int ax_attn_mma_launch(atlasx_ctx* ctx, const AxAttnArgs& a, bool pdl) {
     switch (shape_index(ctx, a.n_kv * a.batch)) {           // rows of kShapes
 #define AX_CFG(n, W, S, T) case n: return pack ? launch_mma_cfg<true, W, S, T>(ctx, dv, a.batch, pdl) : launch_mma_cfg<false, W, S, T>(ctx, dv, a.batch, pdl)
         AX_CFG(1, 4, 3, 32);
-        AX_CFG(2, 8, 3, 16);
-        AX_CFG(3, 12, 2, 16);
-        AX_CFG(4, 6, 4, 16);
-        AX_CFG(5, 8, 2, 16);
-        AX_CFG(6, 6, 2, 16);
-        AX_CFG(7, 4, 2, 16);
-        AX_CFG(8, 4, 3, 16);
+        AX_CFG(2, 8, 2, 16);
+        AX_CFG(3, 6, 2, 16);
+        AX_CFG(4, 4, 2, 16);
         default: AX_CFG(0, 6, 2, 32);
 #undef AX_CFG
     }

@@ -65,7 +65,7 @@ struct atlasx_ctx {
         int attn_mma = 1;              // ATLASX_ATTN_MMA=0: operator-form GQA attention on the scalar kernels instead of the tensor cores
         int umma = 1;                  // ATLASX_UMMA=0: token batches on the warp-level MMA kernel instead of tcgen05
         int attn_pack = 1;             // ATLASX_ATTN_PACK=0: ≤ 4 heads per KV head as columns with separate hi / lo MMAs
-        int attn_cfg = -1;             // ATLASX_ATTN_CFG: shape (warps × stages × rows) of the tensor-core attention; -1 = by problem size
+        int attn_cfg = -1;             // ATLASX_ATTN_CFG: shape 0..4 (warps × stages × rows per tile) of the tensor-core attention; -1 = by problem size
         int peer_allreduce = 1;        // ATLASX_PEER_ALLREDUCE=0: ncclAllReduce instead of the peer mailboxes
         int mail_reduce = -1;          // ATLASX_MAIL_REDUCE: mailbox parts summed 0 = by every consumer CTA, 1 = by a kernel of their own,
                                        // 2 = by the first CTAs of the consumer (default, −1)
