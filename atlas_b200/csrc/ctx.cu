@@ -62,6 +62,7 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_ATTN_ROWS", &c->tune.attn_rows);
         env_int("ATLASX_ATTN_MMA", &c->tune.attn_mma);
         env_int("ATLASX_UMMA", &c->tune.umma);
+        env_int("ATLASX_UMMA_PERSIST", &c->tune.umma_persist);
         env_int("ATLASX_ATTN_PACK", &c->tune.attn_pack);
         env_int("ATLASX_ATTN_CFG", &c->tune.attn_cfg);
         env_int("ATLASX_PEER_ALLREDUCE", &c->tune.peer_allreduce);

@@ -7,10 +7,12 @@
 // (kernels/matmul.cu:384-420) or token by token (crates/atlas-model/src/lib.rs:1611-1618) — and exists because
 // the warp-level kernel falls to half the HBM rate at 16 columns and cannot take more.
 //
-//   * Work item = (128-row tile of W, range of 64-element K blocks); one item per CTA, two CTAs per SM.  K is
-//     split so that short matrices still give every SM work; the partial tiles of a row tile meet in global
-//     scratch and the CTA that arrives last (ticket) adds them in split order, so the result does not depend
-//     on timing.
+//   * Work item = (128-row tile of W, range of K blocks of 128 bytes per row), two CTAs per SM.  K is split so that
+//     short matrices still give every SM work; the partial tiles of a row tile meet in global scratch and the
+//     CTA that arrives last (ticket) adds them in split order, so the result does not depend on timing.  Items
+//     are handed out dynamically — SMs do not stream at equal rates: one item per CTA by the hardware's CTA
+//     scheduler, or, for matrices with many long items, resident CTAs that take item numbers from a global counter and
+//     keep two accumulators in tensor memory, so that the epilogue of an item runs under the MMAs of the next.
 //   * A operand: the W tile, 128 rows × 64 bf16 per stage (16 KB), 128-byte swizzle.  Rows beyond M are filled
 //     with zeros by the copy engine.
 //   * B operand: the tokens.  The f32 activations are split into bf16 hi + lo parts (x = hi + lo to 2⁻¹⁷
@@ -42,6 +44,7 @@ constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr int kMaxTokens = 64;
 constexpr int kMaxSplits = 8;
+constexpr int kItemRing = 8;                      // item numbers in flight between the roles of a CTA
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
 struct UmmaArgs {
@@ -53,7 +56,9 @@ struct UmmaArgs {
     const float* xscale;          // int8: scale per token
     int KB, KS, T;                // K blocks, K splits, row tiles
     int stages, b_bytes;          // pipeline depth, bytes of one B stage (planes·nc rows × 128)
-    int tmem_cols;                // power of two ≥ 32 holding planes·nc accumulator columns
+    int acc_cols, tmem_cols;      // columns of one accumulator (power of two ≥ 32 holding planes·nc) and of the allocation
+    int persist;                  // 1: CTAs stay and take items from the counter; 0: one item per CTA
+    unsigned* counter;            // next item (persistent form), zeroed by the kernel that prepares the tokens
     int token_major;              // Y[j·M + row] (one contiguous vector per token) or Y[row·n + j]
     float* parts;                 // [T·KS][n][128] partial tiles (KS > 1)
     unsigned* tickets;            // [T], zero between launches
@@ -126,7 +131,7 @@ __global__ void ax_umma_split_kernel(const float* __restrict__ X, int K, int n, 
                                      uint16_t* __restrict__ plane, unsigned* tickets, int n_tickets) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx < (size_t)n_tickets) tickets[idx] = 0u;
+    if (idx <= (size_t)n_tickets) tickets[idx] = 0u;          // the word behind the tickets is the item counter
     const int k8 = K / 8;
     if (idx >= (size_t)2 * n8 * k8) return;
     const int row = (int)(idx / k8), kg = (int)(idx % k8);
@@ -162,7 +167,7 @@ __global__ void __launch_bounds__(256) ax_umma_digits_kernel(const float* __rest
     __shared__ float red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int j = blockIdx.x, tid = threadIdx.x;
-    if (j == 0) for (int i = tid; i < n_tickets; i += 256) tickets[i] = 0u;
+    if (j == 0) for (int i = tid; i <= n_tickets; i += 256) tickets[i] = 0u;     // the word behind the tickets is the item counter
     const size_t plane_stride = (size_t)n16 * K;
     int8_t* r0 = plane + (size_t)j * K;
     if (j >= n) {
@@ -214,23 +219,28 @@ __global__ void __launch_bounds__(256) ax_umma_digits_kernel(const float* __rest
 __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_constant__ CUtensorMap map_w,
                                                                 const __grid_constant__ CUtensorMap map_x, const UmmaArgs a) {
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], done_bar;
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2], item_bar[kItemRing];
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort, s_issued, s_last, s_go;
+    __shared__ int s_abort, s_issued, s_last, s_go, s_item[kItemRing];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int tile = blockIdx.x / a.KS, ks = blockIdx.x % a.KS;
-    const int kb0 = (int)((long long)a.KB * ks / a.KS), kb1 = (int)((long long)a.KB * (ks + 1) / a.KS);
-    const int nkb = kb1 - kb0;
     const int ST = a.stages;
     const int NP = a.planes * a.nc;
+    const int n_items = a.T * a.KS;
     const uint32_t stage_bytes = (uint32_t)kABytes + (uint32_t)a.b_bytes;
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;           // swizzled tiles want 1024-byte alignment
     volatile int* abort_flag = &s_abort;
+    auto item_range = [&](int item, int& tile, int& kb0, int& nkb) {
+        tile = item / a.KS;
+        const int ks = item - tile * a.KS;
+        kb0 = (int)((long long)a.KB * ks / a.KS);
+        nkb = (int)((long long)a.KB * (ks + 1) / a.KS) - kb0;
+    };
 
     if (tid == 0) {
         for (int s = 0; s < ST; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        mbar_init(smem_u32(&done_bar), 1);
+        for (int u = 0; u < 2; u++) { mbar_init(smem_u32(&acc_full[u]), 1); mbar_init(smem_u32(&acc_empty[u]), 1); }
+        for (int u = 0; u < kItemRing; u++) mbar_init(smem_u32(&item_bar[u]), 1);
         s_abort = 0; s_issued = 0; s_last = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -244,18 +254,31 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
 
+    // Items reach the three roles through a small ring: the copy warp takes the next item (its own block index, or —
+    // persistent form — the next number of a global counter, so faster SMs take more items), writes it into the ring
+    // and arrives on the slot's mbarrier; the MMA warp and the epilogue read it from there.  −1 ends the walk.
     if (warp == 0) {
         if (lane == 0) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");              // the token plane is written by the launch before
-            for (int i = 0; i < nkb; i++) {
-                const int s = i % ST;
-                if (i >= ST && !mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((i / ST) - 1) & 1u, abort_flag, a.err, 701)) break;
-                const uint32_t bar = smem_u32(&full_bar[s]);
-                const uint32_t dst = smem0 + (uint32_t)s * stage_bytes;
-                mbar_expect_tx(bar, stage_bytes);
-                tma_load_2d(dst, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
-                tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * a.kblk, 0, bar);
-                s_issued = i + 1;
+            asm volatile("griddepcontrol.wait;" ::: "memory");              // the token plane and the counter are written by the launch before
+            int f = 0;                                                       // stages filled so far, over all items
+            bool ok = true;
+            for (int li = 0; ok; li++) {
+                int item = a.persist ? (int)atomicAdd(a.counter, 1u) : (li == 0 ? (int)blockIdx.x : n_items);
+                if (item >= n_items) item = -1;
+                s_item[li % kItemRing] = item;
+                asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&item_bar[li % kItemRing])) : "memory");
+                if (item < 0) break;
+                int tile, kb0, nkb; item_range(item, tile, kb0, nkb);
+                for (int i = 0; i < nkb; i++, f++) {
+                    const int s = f % ST;
+                    if (f >= ST && !mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((f / ST) - 1) & 1u, abort_flag, a.err, 701)) { ok = false; break; }
+                    const uint32_t bar = smem_u32(&full_bar[s]);
+                    const uint32_t dst = smem0 + (uint32_t)s * stage_bytes;
+                    mbar_expect_tx(bar, stage_bytes);
+                    tma_load_2d(dst, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
+                    tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * a.kblk, 0, bar);
+                    s_issued = f + 1;
+                }
             }
         }
     } else if (warp == 1) {
@@ -265,35 +288,60 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
             const uint32_t idesc = ((a.i8 ? 2u : 1u) << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
             const bool i8 = a.i8 != 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; i++) {
-                const int s = i % ST;
-                ok = mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(i / ST) & 1u, abort_flag, a.err, 702);
-                if (!ok) break;
+            int f = 0;
+            for (int li = 0; ok; li++) {
+                if (!mbar_wait(smem_u32(&item_bar[li % kItemRing]), (uint32_t)(li / kItemRing) & 1u, abort_flag, a.err, 705)) break;
+                const int item = *reinterpret_cast<volatile int*>(&s_item[li % kItemRing]);
+                if (item < 0) break;
+                int tile, kb0, nkb; item_range(item, tile, kb0, nkb);
+                const int buf = li & 1;                                      // two accumulators: the epilogue of one item runs under the next
+                if (li >= 2 && !mbar_wait(smem_u32(&acc_empty[buf]), (uint32_t)((li >> 1) - 1) & 1u, abort_flag, a.err, 704)) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t sa = smem0 + (uint32_t)s * stage_bytes, sb = sa + kABytes;
-                if (i8) {                                                    // 16 bf16 or 32 int8 = 32 bytes along the swizzled row per MMA
+                const uint32_t acc = tmem + (uint32_t)(buf * a.acc_cols);
+                for (int i = 0; i < nkb; i++, f++) {
+                    const int s = f % ST;
+                    if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(f / ST) & 1u, abort_flag, a.err, 702)) { ok = false; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem0 + (uint32_t)s * stage_bytes, sb = sa + kABytes;
+                    if (i8) {                                                // 16 bf16 or 32 int8 = 32 bytes along the swizzled row per MMA
 #pragma unroll
-                    for (int k = 0; k < kBlockBytes / 32; k++)
-                        umma_i8(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
-                } else {
+                        for (int k = 0; k < kBlockBytes / 32; k++)
+                            umma_i8(acc, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                    } else {
 #pragma unroll
-                    for (int k = 0; k < kBlockBytes / 32; k++)
-                        umma_bf16(tmem, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                        for (int k = 0; k < kBlockBytes / 32; k++)
+                            umma_bf16(acc, smem_desc_sw128(sa + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+                    }
+                    umma_commit(smem_u32(&empty_bar[s]));                    // the stage is free once these MMAs have read it
                 }
-                umma_commit(smem_u32(&empty_bar[s]));                        // the stage is free once these MMAs have read it
+                umma_commit(smem_u32(&acc_full[buf]));                       // also on the way out of a failed wait
             }
-            umma_commit(smem_u32(&done_bar));                                // also on the way out of a failed wait: see the tail
         }
     } else {
         const int q = warp & 3;                                              // lane quarter of tensor memory this warp may read
-        const int r_in = q * 32 + lane, row = tile * kTileM + r_in;
-        // one thread waits and tells the other 127: a deadline that only some of them saw pass must not split the group
-        if (tid == 64) s_go = mbar_wait(smem_u32(&done_bar), 0u, abort_flag, a.err, 703) ? 1 : 0;
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (s_go) {
+        const int r_in = q * 32 + lane;
+        const int et = tid - 64;                                             // 0..127
+        for (int li = 0;; li++) {
+            // one thread waits (for the item, then for its accumulator) and tells the other 127: a deadline that only
+            // some of them saw pass must not split the group
+            if (tid == 64) {
+                int item = -1;
+                if (mbar_wait(smem_u32(&item_bar[li % kItemRing]), (uint32_t)(li / kItemRing) & 1u, abort_flag, a.err, 706)) {
+                    item = *reinterpret_cast<volatile int*>(&s_item[li % kItemRing]);
+                    if (item >= 0 && !mbar_wait(smem_u32(&acc_full[li & 1]), (uint32_t)(li >> 1) & 1u, abort_flag, a.err, 703)) item = -1;
+                }
+                s_go = item;
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int item = s_go;
+            asm volatile("bar.sync 1, 128;" ::: "memory");                   // s_go is rewritten for the next item
+            if (item < 0) break;
+            int tile, kb0, nkb; item_range(item, tile, kb0, nkb);
+            const int buf = li & 1;
+            const int row = tile * kTileM + r_in;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t t_row = tmem + ((uint32_t)(q * 32) << 16);
-            float* part = a.parts + (size_t)blockIdx.x * a.n * kTileM;
+            const uint32_t t_row = tmem + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * a.acc_cols);
+            float* part = a.parts + (size_t)item * a.n * kTileM;
             const float ws = (a.i8 && row < a.M) ? a.wscale[row] : 1.f;
             for (int c = 0; c < a.nc && c < a.n; c += 8) {
                 float hi[8], lo[8], d3[8];
@@ -315,18 +363,23 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                     }
                 }
             }
+            // the accumulator is read (every tcgen05.ld above has been waited for): hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            if (a.KS > 1) __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");                   // the four epilogue warps
+            if (tid == 64) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&acc_empty[buf])) : "memory");
+                if (a.KS > 1) s_last = atomicAdd(&a.tickets[tile], 1u) == (unsigned)(a.KS - 1);
+            }
             if (a.KS > 1) {
-                __threadfence();
-                asm volatile("bar.sync 1, 128;" ::: "memory");               // the four epilogue warps
-                if (tid == 64) s_last = atomicAdd(&a.tickets[tile], 1u) == (unsigned)(a.KS - 1);
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (s_last) {
+                const int last = s_last;
+                asm volatile("bar.sync 1, 128;" ::: "memory");               // s_last is rewritten for the next item
+                if (last) {
                     __threadfence();
                     // [split][token][128 rows]: a thread adds four rows of every fourth token, splits in order;
                     // the loads of two tokens × all splits are issued before the first addition
                     const float* p0 = a.parts + (size_t)tile * a.KS * a.n * kTileM;
-                    const int et = tid - 64;                                 // 0..127
                     const int r4 = (et & 31) * 4, jq = et >> 5;
                     const size_t split_stride = (size_t)a.n * kTileM;
                     for (int j0 = jq; j0 < a.n; j0 += 8) {
@@ -372,9 +425,9 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                 while (!mbar_try(smem_u32(&full_bar[i % ST]), (uint32_t)(i / ST) & 1u) && global_ns() - t0 < kWaitNs) { }
             }
         }
-        if (tid == 32) {                                                     // MMAs issued before the failure: done_bar was committed behind them
+        if (tid == 32) {                                                     // MMAs issued before the failure: time to drain
             unsigned long long t0 = global_ns();
-            while (!mbar_try(smem_u32(&done_bar), 0u) && global_ns() - t0 < kWaitNs) { }
+            while (global_ns() - t0 < 2000000ull) { }
         }
         __syncthreads();
     }
@@ -415,7 +468,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
     return ATLASX_OK;
 }
 
-struct UmmaPlan { int nc, planes, kblk, T, KB, KS, stages, b_bytes, tmem_cols; size_t plane_bytes, xscale_bytes, parts_bytes, ticket_bytes, smem; };
+struct UmmaPlan { int nc, planes, kblk, T, KB, KS, stages, b_bytes, acc_cols, tmem_cols, persist, grid; size_t plane_bytes, xscale_bytes, parts_bytes, ticket_bytes, smem; };
 
 UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     UmmaPlan p;
@@ -443,11 +496,29 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     if (st < 2) st = 2;
     p.stages = st;
     int c = 32; while (c < p.planes * p.nc) c <<= 1;
-    p.tmem_cols = c;
+    p.acc_cols = c;
+    // Persistent form: CTAs stay resident and take items from a counter, with two accumulators so that the epilogue of
+    // an item runs under the MMAs of the next.  Used when there are more items than CTA slots and either the items are
+    // long (at least 16 K blocks) or there are many per CTA (at least four): the lm_head-like matrices, where it
+    // measured 10–25 % faster; with a few short items per CTA the handshakes per item cost more than a fresh CTA
+    // (22016 × 4096 at 64 tokens, three items of 13 blocks per CTA: 83 → 96 µs).  Two CTAs per SM need their two
+    // allocations inside the 512 columns of tensor memory; the item ring needs items of at least four blocks.
+    const long long n_items = (long long)p.T * p.KS;
+    const int per_sm = 2 * c <= 256 ? 2 : 1;
+    const long long slots_p = (long long)per_sm * ctx->sm_count;
+    p.persist = ctx->tune.umma_persist && p.KB / p.KS >= 4 && n_items > slots_p &&
+                (p.KB / p.KS >= 16 || n_items >= 4 * slots_p) ? 1 : 0;
+    p.tmem_cols = p.persist ? 2 * c : c;
+    p.grid = p.persist ? per_sm * ctx->sm_count : (int)n_items;
+    if (p.persist && per_sm == 1) {                                          // one CTA per SM: it may use twice the stages
+        st = (200 * 1024) / (kABytes + p.b_bytes);
+        if (st > kMaxStages) st = kMaxStages;
+        p.stages = st;
+    }
     p.plane_bytes = ((size_t)p.planes * p.nc * cols * (i8 ? 1 : 2) + 1023) / 1024 * 1024;
     p.xscale_bytes = i8 ? 256 : 0;
     p.parts_bytes = p.KS > 1 ? (size_t)p.T * p.KS * n * kTileM * sizeof(float) : 0;
-    p.ticket_bytes = ((size_t)p.T * sizeof(unsigned) + 255) / 256 * 256;
+    p.ticket_bytes = ((size_t)(p.T + 1) * sizeof(unsigned) + 255) / 256 * 256;      // + the item counter
     p.smem = (size_t)st * (kABytes + p.b_bytes) + 1024;
     return p;
 }
@@ -486,7 +557,7 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     static bool attr_done[64] = {};
     const int dev = ctx->device & 63;
     if (!attr_done[dev]) {
-        AX_CUDA(cudaFuncSetAttribute(ax_gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024));
+        AX_CUDA(cudaFuncSetAttribute(ax_gemv_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
         attr_done[dev] = true;
     }
     cudaLaunchAttribute attr[1];
@@ -502,7 +573,7 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
                                        reinterpret_cast<int8_t*>(base), xscale, tickets, p.T));
         } else {
             const size_t work = (size_t)2 * p.nc * (w.cols / 8);
-            const size_t threads = work > (size_t)p.T ? work : (size_t)p.T;
+            const size_t threads = work > (size_t)p.T + 1 ? work : (size_t)p.T + 1;      // tickets and the item counter
             cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
             AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
                                        reinterpret_cast<uint16_t*>(base), tickets, p.T));
@@ -512,10 +583,10 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     a.Y = y; a.M = w.rows; a.n = n; a.nc = p.nc; a.i8 = i8 ? 1 : 0; a.planes = p.planes; a.kblk = p.kblk;
     a.wscale = reinterpret_cast<const float*>(w.scales); a.xscale = xscale;
     a.KB = p.KB; a.KS = p.KS; a.T = p.T;
-    a.stages = p.stages; a.b_bytes = p.b_bytes; a.tmem_cols = p.tmem_cols; a.token_major = token_major ? 1 : 0;
+    a.stages = p.stages; a.b_bytes = p.b_bytes; a.acc_cols = p.acc_cols; a.tmem_cols = p.tmem_cols; a.persist = p.persist; a.counter = tickets + p.T; a.token_major = token_major ? 1 : 0;
     a.parts = parts; a.tickets = tickets; a.err = ctx->dev_error;
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(p.T * p.KS)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = p.smem; cfg.stream = ctx->stream;
+    cfg.gridDim = dim3((unsigned)p.grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = p.smem; cfg.stream = ctx->stream;
     cfg.attrs = attr; cfg.numAttrs = 1;                                      // its producer warp waits for the split kernel itself
     AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_umma_kernel, map_w, map_x, a));
     return ATLASX_OK;
