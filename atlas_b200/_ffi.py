@@ -46,6 +46,7 @@ class LoadStatsC(C.Structure):
                 ("tied_lm_head", C.c_int), ("weight_format", C.c_int)]
 
 
+TOKEN_CALLBACK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_uint32)
 LAYER_HOOK = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_int, C.POINTER(C.c_float), C.c_int, C.POINTER(C.c_float))
 
 _lib = None
@@ -159,6 +160,7 @@ SIGNATURES = {
     "atlasx_model_hidden": (ci, [vp, vp]),
     "atlasx_model_layer_hidden": (ci, [vp, ci, vp]),
     "atlasx_model_set_layer_hook": (ci, [vp, vp, vp]),
+    "atlasx_model_set_token_callback": (ci, [vp, vp, vp]),
     "atlasx_model_deposits": (ci, [vp, vp, vp, vp, ci, pi]),
     "atlasx_time_gemv": (ci, [vp, vp, ci, vp, ci, vp, ci, C.POINTER(cf)]),
     "atlasx_time_attention": (ci, [vp, vp, vp, vp, ci, vp, cf, ci, ci, C.POINTER(cf)]),

@@ -80,6 +80,7 @@ struct atlasx_model {
     // per-layer hook (StigmergicHook, crates/atlas-infer/src/hook.rs): the taps of a forward are copied to
     // pinned host memory behind it and the hook runs on the host while the next forward executes
     atlasx_layer_hook hook_fn = nullptr; void* hook_user = nullptr;
+    atlasx_token_callback tok_fn = nullptr; void* tok_user = nullptr;     // generate_streaming: called per emitted token, 0 stops
     float* tap_host[2] = { nullptr, nullptr }; cudaEvent_t tap_ev[2] = { nullptr, nullptr };
     int tap_k = 0; bool tap_pending = false; long long tap_tok[2] = { -1, -1 };
     std::vector<uint32_t> dep_tok, dep_fired; std::vector<float> dep_delta;
@@ -778,6 +779,13 @@ int flush_hooks(atlasx_model* m) {
 
 // StigmergicHook on the GPU path (crates/atlas-infer/src/hook.rs:31-33; the reference runs hooked
 // generation on its CPU model, engine.rs:144-162).  fn = NULL detaches.
+// generate_streaming (crates/atlas-model/src/lib.rs:1855-1965): fn is called with every token right after it is
+// emitted (EOS and stop tokens end the run before, unseen); a zero return ends the generation there.
+extern "C" int atlasx_model_set_token_callback(atlasx_model* m, atlasx_token_callback fn, void* user) {
+    AX_ARG(m, "model is null");
+    m->tok_fn = fn; m->tok_user = user;
+    return ATLASX_OK;
+}
 extern "C" int atlasx_model_set_layer_hook(atlasx_model* m, atlasx_layer_hook fn, void* user) {
     AX_ARG(m && m->finalized, "model is not finalised");
     AX_CUDA(cudaStreamSynchronize(m->ctx->stream));
@@ -1313,6 +1321,7 @@ extern "C" int atlasx_model_generate_greedy(atlasx_model* m, const uint32_t* pro
         for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
         if (stop) break;
         out_tokens[(*n_out)++] = tok;
+        if (m->tok_fn && !m->tok_fn(m->tok_user, tok)) break;            // the caller has enough (:1958-1960): no forward for this token
         rc = gen_step(m, (long long)tok, need_logits); if (rc) return done(rc);
     }
     return done(ATLASX_OK);
@@ -1386,6 +1395,7 @@ extern "C" int atlasx_model_generate_sampling(atlasx_model* m, const uint32_t* p
         for (int i = 0; i < n_stops; i++) if (stops[i] == tok) stop = true;
         if (stop) break;
         out_tokens[(*n_out)++] = tok;
+        if (m->tok_fn && !m->tok_fn(m->tok_user, tok)) break;
         if ((rc = gen_step(m, (long long)tok))) break;
     }
     cudaStreamSynchronize(s);

@@ -54,11 +54,21 @@ class InferEngine:
         return toks, [PheromoneDeposit(t, d, f) for t, d, f in self.model.deposits()]
 
     def generate_streaming(self, prompt, max_new, cfg: SamplingConfig, on_token, seed=None):
-        toks, deps = self.generate(prompt, max_new, cfg, seed=seed)
+        """engine.rs:171-217 — on_token(token, deposit or None) -> keep going?; returns the number of tokens seen.
+        Without a hook the tokens are handed over while the generation runs and a false return ends it;
+        with a hook the reference generates first and then walks the tokens, and so does this."""
         count = 0
-        for i, tok in enumerate(toks):
+        if self.hook is None:
+            def each(tok):
+                nonlocal count
+                count += 1
+                return on_token(tok, None)
+            self.model.generate_streaming(prompt, max_new, cfg, each, seed=seed)
+            return count
+        toks, deps = self.generate(prompt, max_new, cfg, seed=seed)
+        for tok, dep in zip(toks, deps):
             count += 1
-            if not on_token(tok, deps[i] if deps else None):
+            if not on_token(tok, dep):
                 break
         return count
 

@@ -255,6 +255,18 @@ class OlmoModel:
             check(_ffi.lib().atlasx_model_deposits(self._h, tok.ctypes.data, delta.ctypes.data, fired.ctypes.data, k, C.byref(n)))
         return [(int(t), float(x), int(f)) for t, x, f in zip(tok, delta, fired)]
 
+    def generate_streaming(self, prompt, max_new, config: "SamplingConfig", on_token, seed=None):
+        """:1855-1965 — as generate_with_sampling, with on_token(token) called for every token right after
+        it is emitted; a false return ends the generation there (no forward runs for that token)."""
+        def trampoline(_user, tok):
+            return 1 if on_token(int(tok)) else 0
+        cb = _ffi.TOKEN_CALLBACK(trampoline)
+        check(_ffi.lib().atlasx_model_set_token_callback(self._h, C.cast(cb, C.c_void_p), None))
+        try:
+            return self.generate_with_sampling(prompt, max_new, config, seed=seed)
+        finally:
+            check(_ffi.lib().atlasx_model_set_token_callback(self._h, None, None))
+
     def generate(self, prompt, max_new, temperature=0.0):
         """:1584-1590"""
         return self.generate_with_sampling(prompt, max_new, SamplingConfig(temperature=temperature))

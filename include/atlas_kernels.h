@@ -319,6 +319,12 @@ int atlasx_model_layer_hidden(atlasx_model* m, int layer, float* hidden_host);
  * (generate_with_sampling_hooked, :1745-1846: negative deltas count as zero), read with atlasx_model_deposits
  * after the call.  Prompt tokens are then ingested one by one.  fn = NULL detaches the hook. */
 typedef int (*atlasx_layer_hook)(void* user, int layer, const float* hidden_host, int d_model, float* delta_out);
+/* generate_streaming (crates/atlas-model/src/lib.rs:1855-1965, crates/atlas-infer/src/engine.rs:171-190): with a callback set,
+ * atlasx_model_generate_greedy / _sampling call it with every token right after it is emitted (EOS and stop tokens end
+ * the run before and are not seen); a zero return ends the generation there, without a forward for that token.
+ * fn = NULL detaches it. */
+typedef int (*atlasx_token_callback)(void* user, uint32_t token);
+int atlasx_model_set_token_callback(atlasx_model* m, atlasx_token_callback fn, void* user);
 int atlasx_model_set_layer_hook(atlasx_model* m, atlasx_layer_hook fn, void* user);
 /* deposits of the last generate call: per generated token its id, the sum of the deltas and the number of
  * layers that returned one; *n receives the count (all of them, even if cap is smaller) */

@@ -97,3 +97,25 @@ def test_hook_with_sampling_and_streaming(ab):
     toks, deposits = eng.generate(prompt, 12, sc, seed=4)
     cut = plain.index(plain[6])
     assert toks == plain[:cut] and [dp.token_id for dp in deposits] == toks
+
+
+def test_streaming_without_a_hook_stops_the_generation_itself(ab):
+    """engine.rs:181-190 / atlas-model :1855-1965: without a hook the tokens arrive while the run is going on, the
+    deposit is None, and a false return ends the generation at once — the model has then processed the prompt and
+    the tokens before the last one, nothing more."""
+    cfg = dict(helpers.SMALL_SWA)
+    w = helpers.synth_weights(cfg, seed=93, norm_jitter=0.1, std=0.08)
+    prompt = orc.uniform_u32(6, 93, 1, cfg["vocab_size"])
+    m = helpers.cuda_model(cfg, w, helpers.SMALL_SWA_LAYERS, kv_dtype=ab.F32)
+    for sc, seed in ((ab.SamplingConfig(temperature=0.0), None), (ab.SamplingConfig(temperature=0.8, top_k=50), 7)):
+        plain = m.generate_with_sampling(prompt, 10, sc, seed=seed)
+        eng = ab.InferEngine(m)
+        seen = []
+        n = eng.generate_streaming(prompt, 10, sc, lambda tok, dep: (seen.append((tok, dep)) or len(seen) < 4), seed=seed)
+        assert n == 4 and seen == [(t, None) for t in plain[:4]]
+        assert m.pos == len(prompt) + 3                       # no forward ran for the token that ended the run
+        # a callback that never says stop sees the whole run, and the callback is gone afterwards
+        seen.clear()
+        assert eng.generate_streaming(prompt, 10, sc, lambda tok, dep: seen.append(tok) or True, seed=seed) == len(plain)
+        assert seen == plain
+        assert m.generate_with_sampling(prompt, 10, sc, seed=seed) == plain
