@@ -63,6 +63,7 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_ATTN_MMA", &c->tune.attn_mma);
         env_int("ATLASX_UMMA", &c->tune.umma);
         env_int("ATLASX_UMMA_PERSIST", &c->tune.umma_persist);
+        env_int("ATLASX_UMMA_FUSED", &c->tune.umma_fused);
         env_int("ATLASX_ATTN_PACK", &c->tune.attn_pack);
         env_int("ATLASX_ATTN_CFG", &c->tune.attn_cfg);
         env_int("ATLASX_PEER_ALLREDUCE", &c->tune.peer_allreduce);
@@ -128,6 +129,7 @@ int atlasx_ctx_ensure_split_scratch(atlasx_ctx* c, size_t bytes) {
     c->split_scratch = nullptr; c->split_scratch_cap = 0;
     if (bytes < (1u << 21)) bytes = 1u << 21;
     AX_CUDA(cudaMalloc(&c->split_scratch, bytes));
+    AX_CUDA(cudaMemsetAsync(c->split_scratch, 0, 16384, c->stream));      // the ticket area of the tcgen05 product starts out zero
     c->split_scratch_cap = bytes;
     return ATLASX_OK;
 }

@@ -99,5 +99,7 @@ int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n
 bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y);
 size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n);
 int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false, bool pdl = false);
+// bf16 weights: address at which producer kernels may leave the hi|lo token plane themselves (then x = nullptr above)
+int ax_gemv_umma_plane(atlasx_ctx* ctx, const AxWeight& w, int n, uint16_t** plane, int* n8);
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes
 size_t ax_weight_bytes(const AxWeight& w);

@@ -28,6 +28,7 @@ constexpr int kMmaThreads = 256;
 constexpr int kMmaWarps = 8;
 constexpr int kMaxTiles = 4;          // 16-row tiles per row group
 constexpr int kMmaUnroll = 4;         // k-steps whose loads are issued together
+constexpr size_t kScratchHead = 16384; // the first bytes of the context scratch belong to the tcgen05 product (its tickets)
 
 struct MmaArgs {
     const uint8_t* W; const uint8_t* scales;
@@ -280,7 +281,7 @@ bool ax_gemv_mma_supported(const AxWeight& w, int n, const float* x, const float
 // Context scratch one such product needs: the two split planes [n + 1][K rounded up to whole chunks] bf16.
 size_t ax_gemv_mma_scratch_bytes(int rows, int cols) {
     (void)rows;
-    return (size_t)2 * 17 * ((size_t)cols + 8192) * sizeof(uint16_t);
+    return kScratchHead + (size_t)2 * 17 * ((size_t)cols + 8192) * sizeof(uint16_t);
 }
 
 int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major) {
@@ -305,9 +306,9 @@ int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n
     const size_t smem = (size_t)4 * (n + 1) * a.pitch + red_bytes;
     // split planes in context scratch (grown on demand, never inside a stream capture)
     const size_t plane = (size_t)(n + 1) * a.kpad;
-    int rc = atlasx_ctx_ensure_split_scratch(ctx, 2 * plane * sizeof(uint16_t));
+    int rc = atlasx_ctx_ensure_split_scratch(ctx, kScratchHead + 2 * plane * sizeof(uint16_t));
     if (rc) return rc;
-    uint16_t* xh = reinterpret_cast<uint16_t*>(ctx->split_scratch);
+    uint16_t* xh = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(ctx->split_scratch) + kScratchHead);
     a.xh = xh; a.xl = xh + plane;
     ax_gemv_mma_split_x<<<(a.kpad + 255) / 256, 256, 0, ctx->stream>>>(x, w.cols, n, a.kpad, a.token_major, xh, xh + plane);
     AX_CHECK_LAUNCH("ax_gemv_mma_split_x");

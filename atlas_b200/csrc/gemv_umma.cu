@@ -44,7 +44,8 @@ constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
 constexpr int kMaxTokens = 64;
 constexpr int kMaxSplits = 8;
-constexpr int kItemRing = 8;                      // item numbers in flight between the roles of a CTA
+constexpr int kItemRing = 8;
+constexpr size_t kTicketBytes = 16384;              // ticket area at the start of the scratch: row tiles ≤ 4095                      // item numbers in flight between the roles of a CTA
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
 struct UmmaArgs {
@@ -518,7 +519,7 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     p.plane_bytes = ((size_t)p.planes * p.nc * cols * (i8 ? 1 : 2) + 1023) / 1024 * 1024;
     p.xscale_bytes = i8 ? 256 : 0;
     p.parts_bytes = p.KS > 1 ? (size_t)p.T * p.KS * n * kTileM * sizeof(float) : 0;
-    p.ticket_bytes = ((size_t)(p.T + 1) * sizeof(unsigned) + 255) / 256 * 256;      // + the item counter
+    p.ticket_bytes = kTicketBytes;                                           // tickets + the item counter
     p.smem = (size_t)st * (kABytes + p.b_bytes) + 1024;
     return p;
 }
@@ -527,6 +528,7 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
 
 bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y) {
     if (n < 2 || n > kMaxTokens || !x || !y) return false;
+    if ((w.rows + kTileM - 1) / kTileM + 1 > (int)(kTicketBytes / sizeof(unsigned))) return false;
     if ((((uintptr_t)w.data | (uintptr_t)x) & 15) != 0) return false;
     if (w.dtype == ATLASX_BF16) return w.cols % 8 == 0 && w.cols >= 64;          // row pitch a multiple of 16 bytes
     if (w.dtype == ATLASX_INT8) return w.cols % 16 == 0 && w.cols >= 128 && w.scales != nullptr;
@@ -538,16 +540,36 @@ size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int 
     return p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.ticket_bytes;
 }
 
+// Where a producer kernel may leave the bf16 hi|lo plane of n tokens for a product with w (bf16 weights): rows 0..n8−1
+// hi parts, n8..2·n8−1 lo parts, row pitch w.cols, rows of absent tokens zero.  *plane stays null where the product
+// takes its tokens as f32 only (int8 weights, the persistent form, a scratch that was not sized for it).
+int ax_gemv_umma_plane(atlasx_ctx* ctx, const AxWeight& w, int n, uint16_t** plane, int* n8) {
+    AX_ARG(plane && n8, "null argument");
+    *plane = nullptr; *n8 = 0;                                               // no plane: the caller hands x over as usual
+    alignas(16) static float dummy[4];
+    if (w.dtype != ATLASX_BF16 || !ax_gemv_umma_supported(w, n, dummy, dummy)) return ATLASX_OK;
+    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, false);
+    if (p.persist || p.ticket_bytes + p.plane_bytes + p.parts_bytes > ctx->split_scratch_cap) return ATLASX_OK;
+    *plane = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.ticket_bytes);
+    *n8 = p.nc;
+    return ATLASX_OK;
+}
+
+// x == nullptr: the token plane was left at ax_gemv_umma_plane's address by the kernels before (bf16 weights, an
+// item-per-CTA product whose tickets reset themselves).
 int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
+    const bool prepared = x == nullptr;
+    if (prepared) x = y;                                                     // for the argument checks only
     AX_ARG(ax_gemv_umma_supported(w, n, x, y), "shape or format not covered by the tcgen05 multi-column kernel");
     const bool i8 = w.dtype == ATLASX_INT8;
     const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, i8);
     int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.ticket_bytes);
     if (rc) return rc;
-    uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch);
+    // scratch: [tickets + item counter, always at the start and always zero between launches][token planes][token scales][partial tiles]
+    unsigned* tickets = reinterpret_cast<unsigned*>(ctx->split_scratch);
+    uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.ticket_bytes;
     float* xscale = reinterpret_cast<float*>(base + p.plane_bytes);
     float* parts = reinterpret_cast<float*>(base + p.plane_bytes + p.xscale_bytes);
-    unsigned* tickets = reinterpret_cast<unsigned*>(base + p.plane_bytes + p.xscale_bytes + p.parts_bytes);
 
     CUtensorMap map_w, map_x;
     const uint32_t np = (uint32_t)(p.planes * p.nc);
@@ -563,7 +585,8 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    {
+    AX_ARG(!prepared || (!i8 && !p.persist), "a prepared token plane needs bf16 weights and an item-per-CTA product");
+    if (!prepared) {
         cudaLaunchConfig_t cfg = {};
         cfg.blockDim = dim3(256); cfg.stream = ctx->stream;
         if (pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }
@@ -587,7 +610,7 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     a.parts = parts; a.tickets = tickets; a.err = ctx->dev_error;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = p.smem; cfg.stream = ctx->stream;
-    cfg.attrs = attr; cfg.numAttrs = 1;                                      // its producer warp waits for the split kernel itself
+    if (!prepared || pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }            // its producer warp waits for the kernel before itself
     AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_umma_kernel, map_w, map_x, a));
     return ATLASX_OK;
 }

@@ -519,12 +519,23 @@ __device__ __forceinline__ float pf_block_sum(float v, float* red) {
 }
 // The fused prologue of the GEMVs, row by row:  v = base + (wy ? rmsnorm(y, wy) : y);  resid = v;
 // x = wx ? rmsnorm(v, wx) : v.   y may be null (v = base).  resid may alias base, x may alias resid.
+// plane (may be null): the bf16 hi|lo plane the tcgen05 product of the NEXT projection reads — row i the hi parts of
+// token i's x, row n8 + i the lo parts; CTAs n..n8−1 only clear their two rows.  With a plane x is not written.
+__device__ __forceinline__ void pf_plane_store(uint16_t* plane, int n8, int d, int row, int k, float v) {
+    const uint16_t h = ax_f32_to_bf16_rne(v);
+    plane[(size_t)row * d + k] = h;
+    plane[(size_t)(n8 + row) * d + k] = ax_f32_to_bf16_rne(v - ax_bf16_to_f32(h));
+}
 __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const float* base, const float* wy, const float* wx, float eps,
-                                                           int d, float* resid, float* x) {
+                                                           int d, float* resid, float* x, uint16_t* plane, int n8, int n) {
     __shared__ float red[32];
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    const size_t o = (size_t)blockIdx.x * d;
     const int nt = blockDim.x;
+    if ((int)blockIdx.x >= n) {                                  // padding rows of the plane
+        for (int k = threadIdx.x; k < d; k += nt) { plane[(size_t)blockIdx.x * d + k] = 0; plane[(size_t)(n8 + blockIdx.x) * d + k] = 0; }
+        return;
+    }
+    const size_t o = (size_t)blockIdx.x * d;
     float inv_y = 1.f;
     if (y && wy) {
         float ss = 0.f;
@@ -540,19 +551,26 @@ __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const
     }
     if (wx) {
         const float inv_x = 1.0f / sqrtf(pf_block_sum(ss2, red) / (float)d + eps);
-        for (int k = threadIdx.x; k < d; k += nt) x[o + k] = resid[o + k] * inv_x * wx[k];
+        for (int k = threadIdx.x; k < d; k += nt) {
+            const float v = resid[o + k] * inv_x * wx[k];
+            if (plane) pf_plane_store(plane, n8, d, (int)blockIdx.x, k, v); else x[o + k] = v;
+        }
+    } else if (plane) {
+        for (int k = threadIdx.x; k < d; k += nt) pf_plane_store(plane, n8, d, (int)blockIdx.x, k, resid[o + k]);
     } else if (x != resid) {
         for (int k = threadIdx.x; k < d; k += nt) x[o + k] = resid[o + k];
     }
 }
 // gate/up rows are interleaved (even: gate, odd: up): out[i][j] = silu(gu[i][2j]) · gu[i][2j+1]
-__global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out) {
+__global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out, uint16_t* plane, int n8, int n) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t i = blockIdx.y;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= f) return;
+    if ((int)i >= n) { plane[i * (size_t)f + j] = 0; plane[(n8 + i) * (size_t)f + j] = 0; return; }       // padding rows of the plane
     const float2 v = reinterpret_cast<const float2*>(gu + i * 2 * (size_t)f)[j];
-    out[i * (size_t)f + j] = (v.x / (1.0f + expf(-v.x))) * v.y;
+    const float r = (v.x / (1.0f + expf(-v.x))) * v.y;
+    if (plane) pf_plane_store(plane, n8, f, (int)i, j, r); else out[i * (size_t)f + j] = r;
 }
 __global__ void pf_advance_k(StepState* st, int by) { st->pos += by; }
 
@@ -573,7 +591,9 @@ int prefill_limit(const atlasx_model* m) {
     return limit;
 }
 // One layer product of a chunk: X [n][cols] → Y [n][rows]
+// x == nullptr: the kernel before left the token plane of this product in place (pf_plane_for)
 int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y, bool pdl) {
+    if (!x) return ax_gemv_umma_launch(c, w, nullptr, n, y, true, pdl);
     if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, pdl);
     return ax_gemv_mma_launch(c, w, x, n, y, true);
 }
@@ -608,11 +628,19 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     if ((rc = pf_launch(s, false, pf_positions_k, dim3(1), dim3(kPrefillMax), (const StepState*)m->st, m->pf_pos, n))) return rc;
     if ((rc = pf_launch(s, pdl, pf_embed_rows_k, dim3((unsigned)n), dim3(256), (const void*)m->embed, (int)m->embed_bf16, cf.vocab_size,
                         (const int*)m->seq, (const int*)m->pf_pos, d, m->pf_r))) return rc;
+    // Where the next product runs on the tcgen05 kernel with bf16 weights, the kernel that makes its input writes the
+    // bf16 hi|lo token plane itself (no split launch): the plane's address and row count, or null.
+    auto plane_for = [&](const AxWeight& w, uint16_t** pl, int* n8) {
+        *pl = nullptr; *n8 = 0;
+        return (c->tune.umma && c->tune.umma_fused) ? ax_gemv_umma_plane(c, w, n, pl, n8) : ATLASX_OK;
+    };
+    uint16_t* tpl = nullptr; int n8 = 0;
     const float* a_in = m->pf_r;
     if (!post) {
-        if ((rc = pf_launch(s, pdl, pf_rows_norm_add_k, dim3((unsigned)n), dim3(1024), (const float*)nullptr, (const float*)m->pf_r, (const float*)nullptr,
-                            (const float*)m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a))) return rc;
-        a_in = m->pf_a;
+        if ((rc = plane_for(m->layers[0].qkv, &tpl, &n8))) return rc;
+        if ((rc = pf_launch(s, pdl, pf_rows_norm_add_k, dim3((unsigned)(tpl ? n8 : n)), dim3(1024), (const float*)nullptr, (const float*)m->pf_r, (const float*)nullptr,
+                            (const float*)m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n))) return rc;
+        a_in = tpl ? nullptr : m->pf_a;
     }
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
@@ -670,18 +698,22 @@ int run_prefill_chunk(atlasx_model* m, int n) {
         if ((rc = pf_product(c, ly.wo, m->pf_att, n, m->pf_o, pdl))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
         const bool after_nccl = m->world > 1;             // an NCCL kernel in front: plain stream order
-        if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)n), dim3(1024), (const float*)m->pf_o, (const float*)m->pf_r,
+        if ((rc = plane_for(ly.gateup, &tpl, &n8))) return rc;
+        if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)(tpl ? n8 : n)), dim3(1024), (const float*)m->pf_o, (const float*)m->pf_r,
                             (const float*)(post ? ly.attn_norm : nullptr), (const float*)(post ? nullptr : ly.ffn_norm),
-                            cf.rms_norm_eps, d, m->pf_r, m->pf_a))) return rc;
-        if ((rc = pf_product(c, ly.gateup, m->pf_a, n, m->pf_gu, pdl))) return rc;
-        if ((rc = pf_launch(s, pdl, pf_silu_pair_rows_k, dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)n), dim3(256),
-                            (const float*)m->pf_gu, m->ffn_loc, m->pf_h))) return rc;
-        if ((rc = pf_product(c, ly.down, m->pf_h, n, m->pf_dn, pdl))) return rc;
+                            cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n))) return rc;
+        if ((rc = pf_product(c, ly.gateup, tpl ? nullptr : m->pf_a, n, m->pf_gu, pdl))) return rc;
+        if ((rc = plane_for(ly.down, &tpl, &n8))) return rc;
+        if ((rc = pf_launch(s, pdl, pf_silu_pair_rows_k, dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)(tpl ? n8 : n)), dim3(256),
+                            (const float*)m->pf_gu, m->ffn_loc, m->pf_h, tpl, n8, n))) return rc;
+        if ((rc = pf_product(c, ly.down, tpl ? nullptr : m->pf_h, n, m->pf_dn, pdl))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_dn, (size_t)n * d))) return rc;
         const float* next_wx = (post || l == L - 1) ? nullptr : m->layers[l + 1].attn_norm;
-        if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)n), dim3(1024), (const float*)m->pf_dn, (const float*)m->pf_r,
-                            (const float*)(post ? ly.ffn_norm : nullptr), next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a))) return rc;
-        a_in = m->pf_a;
+        tpl = nullptr; n8 = 0;
+        if (l + 1 < L && (rc = plane_for(m->layers[l + 1].qkv, &tpl, &n8))) return rc;
+        if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)(tpl ? n8 : n)), dim3(1024), (const float*)m->pf_dn, (const float*)m->pf_r,
+                            (const float*)(post ? ly.ffn_norm : nullptr), next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n))) return rc;
+        a_in = tpl ? nullptr : m->pf_a;
     }
     AX_CHECK_LAUNCH("prefill chunk");
     // logits of the chunk's last token through the single-column path, then selection
