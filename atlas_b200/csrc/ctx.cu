@@ -113,7 +113,12 @@ extern "C" int atlasx_ctx_poll_device_error(atlasx_ctx* c, int* code_out) {
     AX_CUDA(cudaMemcpyAsync(c->host_pin, c->dev_error, sizeof(int), cudaMemcpyDeviceToHost, c->stream));
     AX_CUDA(cudaStreamSynchronize(c->stream));
     const int code = c->host_pin[0];
-    if (code) AX_CUDA(cudaMemsetAsync(c->dev_error, 0, sizeof(int), c->stream));
+    if (code) {
+        AX_CUDA(cudaMemsetAsync(c->dev_error, 0, sizeof(int), c->stream));
+        // kernels that gave up may have left their arrival counters half counted; they are zero between launches otherwise
+        if (c->split_scratch) AX_CUDA(cudaMemsetAsync(c->split_scratch, 0, 16384, c->stream));
+        if (c->attn_tickets) AX_CUDA(cudaMemsetAsync(c->attn_tickets, 0, c->attn_tickets_cap * sizeof(unsigned), c->stream));
+    }
     if (code_out) *code_out = code;
     return code ? atlasx_fail(ATLASX_ERR_TIMEOUT, "a bounded device-side wait expired (code %d)", code) : ATLASX_OK;
 }

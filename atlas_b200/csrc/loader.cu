@@ -215,7 +215,8 @@ extern "C" int atlasx_safetensors_open(const char* path, atlasx_safetensors** ou
             const JVal* off = kv.second.get("data_offsets");
             if (!off || off->kind != JVal::Arr || off->arr.size() < 2)
                 return atlasx_fail(ATLASX_ERR_ARG, "safetensors: missing data_offsets for %s", d.name.c_str());
-            off->arr[0].as_usize(&d.off0); off->arr[1].as_usize(&d.off1);
+            if (!off->arr[0].as_usize(&d.off0) || !off->arr[1].as_usize(&d.off1))
+                return atlasx_fail(ATLASX_ERR_ARG, "safetensors: data_offsets of %s are not non-negative integers", d.name.c_str());
             if (d.off1 < d.off0 || d.off1 > n - st->data_start)
                 return atlasx_fail(ATLASX_ERR_ARG, "safetensors: data_offsets of %s lie outside the file", d.name.c_str());
             st->tensors.push_back(std::move(d));
@@ -252,8 +253,11 @@ bool tensor_2d(const TensorDesc& d, size_t* rows, size_t* cols) {
     const size_t n = (d.off1 - d.off0) / esz;
     if (d.shape.empty()) { *rows = 1; *cols = n; return true; }
     size_t c = d.shape.back(), r = 1;
-    for (size_t i = 0; i + 1 < d.shape.size(); i++) r *= d.shape[i];
-    if (r * c != n) return false;
+    for (size_t i = 0; i + 1 < d.shape.size(); i++) {
+        if (d.shape[i] != 0 && r > n / d.shape[i] + 1) return false;      // a product that left the byte count behind (and could wrap)
+        r *= d.shape[i];
+    }
+    if ((c != 0 && r > n / c + 1) || r * c != n) return false;
     *rows = r; *cols = c;
     return true;
 }

@@ -1233,6 +1233,10 @@ extern "C" int atlasx_model_reset(atlasx_model* m) {
     m->host_pos = 0;
     set_state_k<<<1, 1, 0, m->ctx->stream>>>(m->st, 0, INT_MAX);
     AX_CHECK_LAUNCH("set_state");
+    // arrival counters are zero between launches; a launch that gave up on a bounded wait may have left some counted
+    if (m->attn_tickets) AX_CUDA(cudaMemsetAsync(m->attn_tickets, 0, (size_t)m->nh_loc * sizeof(unsigned), m->ctx->stream));
+    if (m->pf_attn_tickets)
+        AX_CUDA(cudaMemsetAsync(m->pf_attn_tickets, 0, (size_t)m->nkv_loc * kPrefillMax * sizeof(unsigned), m->ctx->stream));
     return ATLASX_OK;
 }
 extern "C" int atlasx_model_pos(const atlasx_model* m) { return m ? m->host_pos : -1; }
