@@ -8,8 +8,9 @@
 // the warp-level kernel falls to half the HBM rate at 16 columns and cannot take more.
 //
 //   * Work item = (128-row tile of W, range of K blocks of 128 bytes per row), two CTAs per SM.  K is split so that
-//     short matrices still give every SM work; the partial tiles of a row tile meet in global scratch and the
-//     CTA that arrives last (ticket) adds them in split order, so the result does not depend on timing.  Items
+//     short matrices still give every SM work; the partial tiles of a row tile meet in global scratch and a small
+//     kernel behind the product (ax_umma_merge_kernel, the whole GPU) adds them in split order, so the result does
+//     not depend on timing.  (Merged by the CTA of a tile that arrived last it was a tail of 16 µs at 64 tokens.)  Items
 //     are handed out dynamically — SMs do not stream at equal rates: one item per CTA by the hardware's CTA
 //     scheduler, or, for matrices with many long items, resident CTAs that take item numbers from a global counter and
 //     keep two accumulators in tensor memory, so that the epilogue of an item runs under the MMAs of the next.
@@ -45,7 +46,7 @@ constexpr int kMaxStages = 8;
 constexpr int kMaxTokens = 64;
 constexpr int kMaxSplits = 8;
 constexpr int kItemRing = 8;
-constexpr size_t kTicketBytes = 16384;              // ticket area at the start of the scratch: row tiles ≤ 4095                      // item numbers in flight between the roles of a CTA
+constexpr size_t kHeadBytes = 16384;            // area at the start of the context scratch that holds the item counter
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
 struct UmmaArgs {
@@ -61,8 +62,7 @@ struct UmmaArgs {
     int persist;                  // 1: CTAs stay and take items from the counter; 0: one item per CTA
     unsigned* counter;            // next item (persistent form), zeroed by the kernel that prepares the tokens
     int token_major;              // Y[j·M + row] (one contiguous vector per token) or Y[row·n + j]
-    float* parts;                 // [T·KS][n][128] partial tiles (KS > 1)
-    unsigned* tickets;            // [T], zero between launches
+    float* parts;                 // [T·KS][n][128] partial tiles (KS > 1), added up by ax_umma_merge_kernel
     int* err;
 };
 
@@ -127,12 +127,12 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
 }
 
 // f32 tokens → one bf16 plane [2·n8][K]: rows 0..n8−1 hi parts, rows n8..2·n8−1 lo parts, rows of absent tokens zero.
-// Also clears the tickets of the product that follows.
+// Also resets the item counter of the product that follows.
 __global__ void ax_umma_split_kernel(const float* __restrict__ X, int K, int n, int n8, int token_major,
-                                     uint16_t* __restrict__ plane, unsigned* tickets, int n_tickets) {
+                                     uint16_t* __restrict__ plane, unsigned* counter) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx <= (size_t)n_tickets) tickets[idx] = 0u;          // the word behind the tickets is the item counter
+    if (idx == 0) *counter = 0u;
     const int k8 = K / 8;
     if (idx >= (size_t)2 * n8 * k8) return;
     const int row = (int)(idx / k8), kg = (int)(idx % k8);
@@ -161,14 +161,14 @@ __global__ void ax_umma_split_kernel(const float* __restrict__ X, int K, int n, 
 
 // f32 tokens → three int8 digit planes [3·n16][K] in base 254 with one scale per token: rows p·n16 + j hold
 // digit p of token j, rows of absent tokens are zero.  One CTA per row index j < n16.  A NaN or inf in a token
-// makes its scale NaN, and with it every output of that token.  Also clears the tickets.
+// makes its scale NaN, and with it every output of that token.  Also resets the item counter.
 __global__ void __launch_bounds__(256) ax_umma_digits_kernel(const float* __restrict__ X, int K, int n, int n16, int token_major,
                                                              int8_t* __restrict__ plane, float* __restrict__ xscale,
-                                                             unsigned* tickets, int n_tickets) {
+                                                             unsigned* counter) {
     __shared__ float red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int j = blockIdx.x, tid = threadIdx.x;
-    if (j == 0) for (int i = tid; i <= n_tickets; i += 256) tickets[i] = 0u;     // the word behind the tickets is the item counter
+    if (j == 0 && tid == 0) *counter = 0u;
     const size_t plane_stride = (size_t)n16 * K;
     int8_t* r0 = plane + (size_t)j * K;
     if (j >= n) {
@@ -222,7 +222,7 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full[2], acc_empty[2], item_bar[kItemRing];
     __shared__ uint32_t s_tmem;
-    __shared__ int s_abort, s_issued, s_last, s_go, s_item[kItemRing];
+    __shared__ int s_abort, s_issued, s_go, s_item[kItemRing];
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int ST = a.stages;
@@ -242,7 +242,7 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
         for (int s = 0; s < ST; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         for (int u = 0; u < 2; u++) { mbar_init(smem_u32(&acc_full[u]), 1); mbar_init(smem_u32(&acc_empty[u]), 1); }
         for (int u = 0; u < kItemRing; u++) mbar_init(smem_u32(&item_bar[u]), 1);
-        s_abort = 0; s_issued = 0; s_last = 0;
+        s_abort = 0; s_issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -260,23 +260,42 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     // and arrives on the slot's mbarrier; the MMA warp and the epilogue read it from there.  −1 ends the walk.
     if (warp == 0) {
         if (lane == 0) {
-            asm volatile("griddepcontrol.wait;" ::: "memory");              // the token plane and the counter are written by the launch before
             int f = 0;                                                       // stages filled so far, over all items
             bool ok = true;
+            // One item per CTA: the item is known from the block index and W does not depend on the launch before, so the
+            // W tiles of the first stages are requested before the dependency wait; their token tiles follow after it
+            // (same barrier: a stage is full when both have landed).
+            int pre = 0, next = (int)blockIdx.x;
+            if (!a.persist) {
+                int tile, kb0, nkb; item_range(next, tile, kb0, nkb);
+                pre = nkb < ST ? nkb : ST;
+                for (int i = 0; i < pre; i++) {
+                    const uint32_t bar = smem_u32(&full_bar[i]);
+                    mbar_expect_tx(bar, stage_bytes);
+                    tma_load_2d(smem0 + (uint32_t)i * stage_bytes, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
+                }
+                s_issued = pre;
+            }
+            asm volatile("griddepcontrol.wait;" ::: "memory");              // the token plane and the counter are written by the launch before
+            if (a.persist) next = (int)atomicAdd(a.counter, 1u);
             for (int li = 0; ok; li++) {
-                int item = a.persist ? (int)atomicAdd(a.counter, 1u) : (li == 0 ? (int)blockIdx.x : n_items);
-                if (item >= n_items) item = -1;
+                const int item = next < n_items ? next : -1;
                 s_item[li % kItemRing] = item;
                 asm volatile("mbarrier.arrive.release.cta.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&item_bar[li % kItemRing])) : "memory");
                 if (item < 0) break;
+                // the number of the item after this one is asked for before this item's copies are issued: the atomic's
+                // round trip runs under them instead of leaving the stages idle between two items
+                next = a.persist ? (int)atomicAdd(a.counter, 1u) : n_items;
                 int tile, kb0, nkb; item_range(item, tile, kb0, nkb);
                 for (int i = 0; i < nkb; i++, f++) {
                     const int s = f % ST;
-                    if (f >= ST && !mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((f / ST) - 1) & 1u, abort_flag, a.err, 701)) { ok = false; break; }
                     const uint32_t bar = smem_u32(&full_bar[s]);
                     const uint32_t dst = smem0 + (uint32_t)s * stage_bytes;
-                    mbar_expect_tx(bar, stage_bytes);
-                    tma_load_2d(dst, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
+                    if (f >= pre) {                                          // the first stages already expect their bytes and have their W tile on the way
+                        if (f >= ST && !mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((f / ST) - 1) & 1u, abort_flag, a.err, 701)) { ok = false; break; }
+                        mbar_expect_tx(bar, stage_bytes);
+                        tma_load_2d(dst, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
+                    }
                     tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * a.kblk, 0, bar);
                     s_issued = f + 1;
                 }
@@ -321,7 +340,6 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     } else {
         const int q = warp & 3;                                              // lane quarter of tensor memory this warp may read
         const int r_in = q * 32 + lane;
-        const int et = tid - 64;                                             // 0..127
         for (int li = 0;; li++) {
             // one thread waits (for the item, then for its accumulator) and tells the other 127: a deadline that only
             // some of them saw pass must not split the group
@@ -366,51 +384,8 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
             }
             // the accumulator is read (every tcgen05.ld above has been waited for): hand it back to the MMA warp
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            if (a.KS > 1) __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");                   // the four epilogue warps
-            if (tid == 64) {
-                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&acc_empty[buf])) : "memory");
-                if (a.KS > 1) s_last = atomicAdd(&a.tickets[tile], 1u) == (unsigned)(a.KS - 1);
-            }
-            if (a.KS > 1) {
-                asm volatile("bar.sync 1, 128;" ::: "memory");
-                const int last = s_last;
-                asm volatile("bar.sync 1, 128;" ::: "memory");               // s_last is rewritten for the next item
-                if (last) {
-                    __threadfence();
-                    // [split][token][128 rows]: a thread adds four rows of every fourth token, splits in order;
-                    // the loads of two tokens × all splits are issued before the first addition
-                    const float* p0 = a.parts + (size_t)tile * a.KS * a.n * kTileM;
-                    const int r4 = (et & 31) * 4, jq = et >> 5;
-                    const size_t split_stride = (size_t)a.n * kTileM;
-                    for (int j0 = jq; j0 < a.n; j0 += 8) {
-                        float4 v[2][kMaxSplits];
-#pragma unroll
-                        for (int u = 0; u < 2; u++) {
-                            const int j = j0 + 4 * u;
-#pragma unroll
-                            for (int s = 0; s < kMaxSplits; s++)
-                                if (j < a.n && s < a.KS) v[u][s] = __ldcg(reinterpret_cast<const float4*>(p0 + s * split_stride + (size_t)j * kTileM + r4));
-                        }
-#pragma unroll
-                        for (int u = 0; u < 2; u++) {
-                            const int j = j0 + 4 * u;
-                            if (j >= a.n) continue;
-                            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-                            for (int s = 0; s < kMaxSplits; s++)
-                                if (s < a.KS) { acc.x += v[u][s].x; acc.y += v[u][s].y; acc.z += v[u][s].z; acc.w += v[u][s].w; }
-                            const float o[4] = { acc.x, acc.y, acc.z, acc.w };
-#pragma unroll
-                            for (int e = 0; e < 4; e++) {
-                                const int rr = tile * kTileM + r4 + e;
-                                if (rr < a.M) a.Y[a.token_major ? (size_t)j * a.M + rr : (size_t)rr * a.n + j] = o[e];
-                            }
-                        }
-                    }
-                    if (tid == 64) a.tickets[tile] = 0u;
-                }
-            }
+            if (tid == 64) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&acc_empty[buf])) : "memory");
         }
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -435,6 +410,38 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"((uint32_t)a.tmem_cols) : "memory");
+    }
+}
+
+// Partial tiles of a K-split product → Y: thread = four rows of one token of one row tile, splits added in order (the
+// result does not depend on timing).  The whole GPU takes part: the sums are a few MB that lie in L2.
+__global__ void __launch_bounds__(256) ax_umma_merge_kernel(const float* __restrict__ parts, float* __restrict__ Y, int M, int n, int KS, int T,
+                                                            int token_major) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");                      // every partial tile of the product is written
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    if (idx >= (size_t)T * n * (kTileM / 4)) return;
+    const int r4 = (int)(idx & (kTileM / 4 - 1)) * 4;
+    const size_t tj = idx / (kTileM / 4);
+    const int j = (int)(tj % (size_t)n), tile = (int)(tj / (size_t)n);
+    const size_t split_stride = (size_t)n * kTileM;
+    const float* p = parts + (size_t)tile * KS * split_stride + (size_t)j * kTileM + r4;
+    float4 v[kMaxSplits];
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; s++)
+        if (s < KS) v[s] = __ldcg(reinterpret_cast<const float4*>(p + s * split_stride));
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s = 0; s < kMaxSplits; s++)
+        if (s < KS) { acc.x += v[s].x; acc.y += v[s].y; acc.z += v[s].z; acc.w += v[s].w; }
+    const int row = tile * kTileM + r4;
+    if (token_major) {
+        // one 16-byte store where the four rows exist and the address allows it (row is a multiple of 4, so M must be one too)
+        if (row + 3 < M && (M & 3) == 0) *reinterpret_cast<float4*>(Y + (size_t)j * M + row) = acc;
+        else { const float o[4] = { acc.x, acc.y, acc.z, acc.w }; for (int e = 0; e < 4; e++) if (row + e < M) Y[(size_t)j * M + row + e] = o[e]; }
+    } else {
+        const float o[4] = { acc.x, acc.y, acc.z, acc.w };
+        for (int e = 0; e < 4; e++) if (row + e < M) Y[(size_t)(row + e) * n + j] = o[e];
     }
 }
 
@@ -469,7 +476,7 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
     return ATLASX_OK;
 }
 
-struct UmmaPlan { int nc, planes, kblk, T, KB, KS, stages, b_bytes, acc_cols, tmem_cols, persist, grid; size_t plane_bytes, xscale_bytes, parts_bytes, ticket_bytes, smem; };
+struct UmmaPlan { int nc, planes, kblk, T, KB, KS, stages, b_bytes, acc_cols, tmem_cols, persist, grid; size_t plane_bytes, xscale_bytes, parts_bytes, head_bytes, smem; };
 
 UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     UmmaPlan p;
@@ -478,25 +485,37 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     p.kblk = i8 ? 128 : 64;
     p.T = (rows + kTileM - 1) / kTileM;
     p.KB = (cols + p.kblk - 1) / p.kblk;                       // the copy engine zero-fills a last, partial block
-    // K splits: the count that fills the waves of CTAs best (two CTAs per SM; a last wave that is half empty costs
-    // as much as a full one), at least four K blocks per item, charged with the bytes of the partial tiles it adds
-    // (written once, read once) relative to the weight bytes of a row tile
+    // K splits: the launch is modelled as waves of CTAs (two per SM), each wave lasting as long as one item — its K blocks,
+    // stretched by the partial tile it writes and the merge reads (relative to the weight bytes of the item), plus a
+    // fixed cost per item (start-up, latency of the first copies, epilogue) of six blocks' streaming time.  Fitted on
+    // 4096², 12288×4096, 22016×4096 and 4096×11008 at 16 and 64 tokens: within 2 % of the best count on average
+    // (plain wave filling chose five splits for 22016×4096, 15 % slower than three).  At least four K blocks per item.
+    // Resident CTAs (see below) pay less per item — no start-up, the epilogue runs under the next item: two blocks.
+    constexpr double kItemBlocks = 6.0, kItemBlocksResident = 2.0;
+    int c = 32; while (c < p.planes * p.nc) c <<= 1;           // columns of one accumulator
+    const int per_sm = 2 * c <= 256 ? 2 : 1;                   // resident form: two accumulators per CTA inside 512 columns
+    const long long slots_p = (long long)per_sm * ctx->sm_count;
+    auto resident = [&](int ks) {
+        const long long items = (long long)p.T * ks;
+        return ctx->tune.umma_persist && p.KB / ks >= 4 && items > slots_p &&
+               (ctx->tune.umma_persist == 2 || p.KB / ks >= 16 || items >= 4 * slots_p);
+    };
     const int slots = 2 * ctx->sm_count;
     int best = 1; double best_cost = 1e300;
     for (int ks = 1; ks <= kMaxSplits && ks * 4 <= (p.KB > 4 ? p.KB : 4); ks++) {
         const long long items = (long long)p.T * ks;
         const long long waves = (items + slots - 1) / slots;
         const double extra = ks > 1 ? 2.0 * n * kTileM * sizeof(float) * ks / ((double)p.KB * kABytes) : 0.0;
-        const double cost = (double)(waves * slots) / (double)items * (1.0 + extra);
+        const double cost = (double)waves * ((double)p.KB / ks * (1.0 + extra) + (resident(ks) ? kItemBlocksResident : kItemBlocks));
         if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
     }
+    if (ctx->tune.umma_ks > 0 && ctx->tune.umma_ks <= kMaxSplits && ctx->tune.umma_ks * 4 <= (p.KB > 4 ? p.KB : 4)) best = ctx->tune.umma_ks;
     p.KS = best;
     p.b_bytes = p.planes * p.nc * kBlockBytes;
     int st = (100 * 1024) / (kABytes + p.b_bytes);
     if (st > kMaxStages) st = kMaxStages;
     if (st < 2) st = 2;
     p.stages = st;
-    int c = 32; while (c < p.planes * p.nc) c <<= 1;
     p.acc_cols = c;
     // Persistent form: CTAs stay resident and take items from a counter, with two accumulators so that the epilogue of
     // an item runs under the MMAs of the next.  Used when there are more items than CTA slots and either the items are
@@ -504,13 +523,9 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     // measured 10–25 % faster; with a few short items per CTA the handshakes per item cost more than a fresh CTA
     // (22016 × 4096 at 64 tokens, three items of 13 blocks per CTA: 83 → 96 µs).  Two CTAs per SM need their two
     // allocations inside the 512 columns of tensor memory; the item ring needs items of at least four blocks.
-    const long long n_items = (long long)p.T * p.KS;
-    const int per_sm = 2 * c <= 256 ? 2 : 1;
-    const long long slots_p = (long long)per_sm * ctx->sm_count;
-    p.persist = ctx->tune.umma_persist && p.KB / p.KS >= 4 && n_items > slots_p &&
-                (p.KB / p.KS >= 16 || n_items >= 4 * slots_p) ? 1 : 0;
+    p.persist = resident(p.KS) ? 1 : 0;
     p.tmem_cols = p.persist ? 2 * c : c;
-    p.grid = p.persist ? per_sm * ctx->sm_count : (int)n_items;
+    p.grid = p.persist ? per_sm * ctx->sm_count : p.T * p.KS;
     if (p.persist && per_sm == 1) {                                          // one CTA per SM: it may use twice the stages
         st = (200 * 1024) / (kABytes + p.b_bytes);
         if (st > kMaxStages) st = kMaxStages;
@@ -519,7 +534,7 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
     p.plane_bytes = ((size_t)p.planes * p.nc * cols * (i8 ? 1 : 2) + 1023) / 1024 * 1024;
     p.xscale_bytes = i8 ? 256 : 0;
     p.parts_bytes = p.KS > 1 ? (size_t)p.T * p.KS * n * kTileM * sizeof(float) : 0;
-    p.ticket_bytes = kTicketBytes;                                           // tickets + the item counter
+    p.head_bytes = kHeadBytes;                                           // the item counter
     p.smem = (size_t)st * (kABytes + p.b_bytes) + 1024;
     return p;
 }
@@ -528,7 +543,6 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
 
 bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y) {
     if (n < 2 || n > kMaxTokens || !x || !y) return false;
-    if ((w.rows + kTileM - 1) / kTileM + 1 > (int)(kTicketBytes / sizeof(unsigned))) return false;
     if ((((uintptr_t)w.data | (uintptr_t)x) & 15) != 0) return false;
     if (w.dtype == ATLASX_BF16) return w.cols % 8 == 0 && w.cols >= 64;          // row pitch a multiple of 16 bytes
     if (w.dtype == ATLASX_INT8) return w.cols % 16 == 0 && w.cols >= 128 && w.scales != nullptr;
@@ -537,7 +551,7 @@ bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const floa
 
 size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n) {
     const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, w.dtype == ATLASX_INT8);
-    return p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.ticket_bytes;
+    return p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.head_bytes;
 }
 
 // Where a producer kernel may leave the bf16 hi|lo plane of n tokens for a product with w (bf16 weights): rows 0..n8−1
@@ -549,25 +563,25 @@ int ax_gemv_umma_plane(atlasx_ctx* ctx, const AxWeight& w, int n, uint16_t** pla
     alignas(16) static float dummy[4];
     if (w.dtype != ATLASX_BF16 || !ax_gemv_umma_supported(w, n, dummy, dummy)) return ATLASX_OK;
     const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, false);
-    if (p.persist || p.ticket_bytes + p.plane_bytes + p.parts_bytes > ctx->split_scratch_cap) return ATLASX_OK;
-    *plane = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.ticket_bytes);
+    if (p.persist || p.head_bytes + p.plane_bytes + p.parts_bytes > ctx->split_scratch_cap) return ATLASX_OK;
+    *plane = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.head_bytes);
     *n8 = p.nc;
     return ATLASX_OK;
 }
 
 // x == nullptr: the token plane was left at ax_gemv_umma_plane's address by the kernels before (bf16 weights, an
-// item-per-CTA product whose tickets reset themselves).
+// item-per-CTA product, which needs no counter).
 int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
     const bool prepared = x == nullptr;
     if (prepared) x = y;                                                     // for the argument checks only
     AX_ARG(ax_gemv_umma_supported(w, n, x, y), "shape or format not covered by the tcgen05 multi-column kernel");
     const bool i8 = w.dtype == ATLASX_INT8;
     const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, i8);
-    int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.ticket_bytes);
+    int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.head_bytes);
     if (rc) return rc;
-    // scratch: [tickets + item counter, always at the start and always zero between launches][token planes][token scales][partial tiles]
-    unsigned* tickets = reinterpret_cast<unsigned*>(ctx->split_scratch);
-    uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.ticket_bytes;
+    // scratch: [item counter, in an area of its own at the start][token planes][token scales][partial tiles]
+    unsigned* counter = reinterpret_cast<unsigned*>(ctx->split_scratch);
+    uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.head_bytes;
     float* xscale = reinterpret_cast<float*>(base + p.plane_bytes);
     float* parts = reinterpret_cast<float*>(base + p.plane_bytes + p.xscale_bytes);
 
@@ -593,24 +607,29 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
         if (i8) {
             cfg.gridDim = dim3((unsigned)p.nc);
             AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_digits_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
-                                       reinterpret_cast<int8_t*>(base), xscale, tickets, p.T));
+                                       reinterpret_cast<int8_t*>(base), xscale, counter));
         } else {
             const size_t work = (size_t)2 * p.nc * (w.cols / 8);
-            const size_t threads = work > (size_t)p.T + 1 ? work : (size_t)p.T + 1;      // tickets and the item counter
-            cfg.gridDim = dim3((unsigned)((threads + 255) / 256));
+            cfg.gridDim = dim3((unsigned)((work + 255) / 256));
             AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
-                                       reinterpret_cast<uint16_t*>(base), tickets, p.T));
+                                       reinterpret_cast<uint16_t*>(base), counter));
         }
     }
     UmmaArgs a;
     a.Y = y; a.M = w.rows; a.n = n; a.nc = p.nc; a.i8 = i8 ? 1 : 0; a.planes = p.planes; a.kblk = p.kblk;
     a.wscale = reinterpret_cast<const float*>(w.scales); a.xscale = xscale;
     a.KB = p.KB; a.KS = p.KS; a.T = p.T;
-    a.stages = p.stages; a.b_bytes = p.b_bytes; a.acc_cols = p.acc_cols; a.tmem_cols = p.tmem_cols; a.persist = p.persist; a.counter = tickets + p.T; a.token_major = token_major ? 1 : 0;
-    a.parts = parts; a.tickets = tickets; a.err = ctx->dev_error;
+    a.stages = p.stages; a.b_bytes = p.b_bytes; a.acc_cols = p.acc_cols; a.tmem_cols = p.tmem_cols; a.persist = p.persist; a.counter = counter; a.token_major = token_major ? 1 : 0;
+    a.parts = parts; a.err = ctx->dev_error;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = p.smem; cfg.stream = ctx->stream;
     if (!prepared || pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }            // its producer warp waits for the kernel before itself
     AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_umma_kernel, map_w, map_x, a));
+    if (p.KS > 1) {
+        cudaLaunchConfig_t mc = {};
+        mc.gridDim = dim3((unsigned)(((size_t)p.T * n * (kTileM / 4) + 255) / 256)); mc.blockDim = dim3(256); mc.stream = ctx->stream;
+        mc.attrs = attr; mc.numAttrs = 1;                                    // it waits for the product itself
+        AX_CUDA(cudaLaunchKernelEx(&mc, ax_umma_merge_kernel, (const float*)parts, y, w.rows, n, p.KS, p.T, token_major ? 1 : 0));
+    }
     return ATLASX_OK;
 }
