@@ -348,11 +348,21 @@ struct ChunkDev {
     const float* q; size_t q_stride;            // token i, head h: q + i·q_stride + h·128 (normed and rotated)
     const uint16_t* kc; const uint16_t* vc;
     float* out; size_t out_stride;
+    uint16_t* out_plane; int plane_rows;               // set: the result goes to a bf16 hi|lo token plane instead of out
     const int* pos0;                            // device: position of the chunk's first token
     int n_tok, n_heads, n_kv, g, window, n_splits;
     float scale;
     float* partials; unsigned* tickets;         // [n_tok·n_heads][n_splits][130]; [n_kv · row groups]
 };
+
+__device__ __forceinline__ void chunk_store(const ChunkDev& dv, int tok, int head, int d, float v) {
+    if (dv.out_plane) {
+        const size_t cols = (size_t)dv.n_heads * 128, k = (size_t)head * 128 + d;
+        const uint16_t h = ax_f32_to_bf16_rne(v);
+        dv.out_plane[(size_t)tok * cols + k] = h;
+        dv.out_plane[(size_t)(dv.plane_rows + tok) * cols + k] = ax_f32_to_bf16_rne(v - ax_bf16_to_f32(h));
+    } else dv.out[(size_t)tok * dv.out_stride + (size_t)head * 128 + d] = v;
+}
 
 __global__ void __launch_bounds__(kThreads) ax_attn_mma_chunk_kernel(const ChunkDev dv) {
     extern __shared__ __align__(128) uint8_t smem[];
@@ -536,7 +546,7 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_chunk_kernel(const Chunk
             L = fmaf(c, sp[1], L); A = fmaf(c, sp[2 + d], A);
         }
         const int tok = tok_lo + r / G, head = kh * G + r % G;
-        if (S == 1) dv.out[(size_t)tok * dv.out_stride + (size_t)head * 128 + d] = A / L;
+        if (S == 1) chunk_store(dv, tok, head, d, A / L);
         else {
             float* P = dv.partials + (((size_t)tok * dv.n_heads + head) * SP + split) * kST;
             P[2 + d] = A;
@@ -562,7 +572,7 @@ __global__ void __launch_bounds__(kThreads) ax_attn_mma_chunk_kernel(const Chunk
             const float c = merge_exp(P[(size_t)i * kST], M);
             L = fmaf(c, P[(size_t)i * kST + 1], L); A = fmaf(c, P[(size_t)i * kST + 2 + d], A);
         }
-        dv.out[(size_t)tok * dv.out_stride + (size_t)head * 128 + d] = A / L;
+        chunk_store(dv, tok, head, d, A / L);
     }
     if (tid == 0) *ticket = 0u;
 }
@@ -702,6 +712,8 @@ int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a, bool pdl
     ChunkDev dv;
     dv.q = a.q; dv.q_stride = a.q_stride; dv.kc = (const uint16_t*)a.kc; dv.vc = (const uint16_t*)a.vc;
     dv.out = a.out; dv.out_stride = a.out_stride; dv.pos0 = a.pos0;
+    dv.out_plane = a.out_plane; dv.plane_rows = a.plane_rows;
+    AX_ARG(!a.out_plane || a.plane_rows >= a.n_tok, "token plane with fewer rows than tokens");
     dv.n_tok = a.n_tok; dv.n_heads = a.n_heads; dv.n_kv = a.n_kv; dv.g = a.n_heads / a.n_kv; dv.window = a.window;
     dv.n_splits = a.n_splits < 1 ? 1 : a.n_splits; dv.scale = a.scale;
     dv.partials = a.partials; dv.tickets = a.tickets;

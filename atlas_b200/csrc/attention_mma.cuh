@@ -15,6 +15,8 @@ struct AxAttnChunkArgs {
     const float* q = nullptr; size_t q_stride = 0;     // token i, head h: q + i·q_stride + h·128, normed and rotated
     const void* kc = nullptr; const void* vc = nullptr;
     float* out = nullptr; size_t out_stride = 0;       // token i, head h: out + i·out_stride + h·128
+    uint16_t* out_plane = nullptr; int plane_rows = 0; // instead of out: bf16 hi|lo plane [2·plane_rows][n_heads·128] (row i hi parts of
+                                                       // token i, row plane_rows + i lo parts), as the tcgen05 product reads its tokens
     const int* pos0 = nullptr;                         // device
     int n_tok = 0, n_heads = 0, n_kv = 0, window = 0, n_splits = 1;
     float scale = 1.f;

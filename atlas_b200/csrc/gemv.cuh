@@ -98,7 +98,28 @@ int ax_gemv_mma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n
 // same operand layouts as above.
 bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const float* y);
 size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n);
-int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false, bool pdl = false);
+// Partial tiles of a K-split product that its caller adds up itself: element (token j, row r) is the sum over
+// s = 0..KS−1, in this order and starting from 0.0f, of parts[((r / 128 · KS + s) · n + j) · 128 + r % 128].
+// KS ≤ 1: nothing is pending, Y holds the result.
+struct AxUmmaParts {
+    const float* parts = nullptr; int KS = 0, n = 0;
+    __host__ __device__ bool pending() const { return KS > 1; }
+    __device__ __forceinline__ float at(int j, int r) const {
+        const float* p = parts + ((size_t)(r >> 7) * KS * n + j) * 128 + (r & 127);
+        float v[8];                                       // every split's load is issued before the first addition
+#pragma unroll
+        for (int s = 0; s < 8; s++) if (s < KS) v[s] = __ldcg(p + (size_t)s * n * 128);
+        float acc = 0.f;
+#pragma unroll
+        for (int s = 0; s < 8; s++) if (s < KS) acc += v[s];
+        return acc;
+    }
+};
+// ext_parts + pend: the partial tiles of a K-split product go to the caller's buffer (ax_gemv_umma_parts_bytes) and
+// are NOT added up — Y is then not written; *pend tells the consumer how to read them.
+int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false, bool pdl = false,
+                        float* ext_parts = nullptr, AxUmmaParts* pend = nullptr);
+size_t ax_gemv_umma_parts_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n);
 // bf16 weights: address at which producer kernels may leave the hi|lo token plane themselves (then x = nullptr above)
 int ax_gemv_umma_plane(atlasx_ctx* ctx, const AxWeight& w, int n, uint16_t** plane, int* n8);
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes

@@ -60,7 +60,7 @@ struct UmmaArgs {
     int stages, b_bytes;          // pipeline depth, bytes of one B stage (planes·nc rows × 128)
     int acc_cols, tmem_cols;      // columns of one accumulator (power of two ≥ 32 holding planes·nc) and of the allocation
     int persist;                  // 1: CTAs stay and take items from the counter; 0: one item per CTA
-    unsigned* counter;            // next item (persistent form), zeroed by the kernel that prepares the tokens
+    unsigned* counter;            // [0] next item (resident form), [1] CTAs that are through; both zero between launches
     int token_major;              // Y[j·M + row] (one contiguous vector per token) or Y[row·n + j]
     float* parts;                 // [T·KS][n][128] partial tiles (KS > 1), added up by ax_umma_merge_kernel
     int* err;
@@ -132,7 +132,7 @@ __global__ void ax_umma_split_kernel(const float* __restrict__ X, int K, int n, 
                                      uint16_t* __restrict__ plane, unsigned* counter) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (idx == 0) *counter = 0u;
+    if (idx < 2) counter[idx] = 0u;
     const int k8 = K / 8;
     if (idx >= (size_t)2 * n8 * k8) return;
     const int row = (int)(idx / k8), kg = (int)(idx % k8);
@@ -168,7 +168,7 @@ __global__ void __launch_bounds__(256) ax_umma_digits_kernel(const float* __rest
     __shared__ float red[8];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int j = blockIdx.x, tid = threadIdx.x;
-    if (j == 0 && tid == 0) *counter = 0u;
+    if (j == 0 && tid < 2) counter[tid] = 0u;
     const size_t plane_stride = (size_t)n16 * K;
     int8_t* r0 = plane + (size_t)j * K;
     if (j >= n) {
@@ -300,6 +300,9 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                     s_issued = f + 1;
                 }
             }
+            // Resident form: a CTA that has taken its last number (one beyond the items) says so; the CTA that says it
+            // last knows that nobody will ask again and sets both counters back to zero for the next launch.
+            if (a.persist && ok && atomicAdd(a.counter + 1, 1u) == gridDim.x - 1) { a.counter[1] = 0u; a.counter[0] = 0u; }
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -556,22 +559,27 @@ size_t ax_gemv_umma_scratch_bytes(const atlasx_ctx* ctx, const AxWeight& w, int 
 
 // Where a producer kernel may leave the bf16 hi|lo plane of n tokens for a product with w (bf16 weights): rows 0..n8−1
 // hi parts, n8..2·n8−1 lo parts, row pitch w.cols, rows of absent tokens zero.  *plane stays null where the product
-// takes its tokens as f32 only (int8 weights, the persistent form, a scratch that was not sized for it).
+// takes its tokens as f32 only (int8 weights, a scratch that was not sized for it).
 int ax_gemv_umma_plane(atlasx_ctx* ctx, const AxWeight& w, int n, uint16_t** plane, int* n8) {
     AX_ARG(plane && n8, "null argument");
     *plane = nullptr; *n8 = 0;                                               // no plane: the caller hands x over as usual
     alignas(16) static float dummy[4];
     if (w.dtype != ATLASX_BF16 || !ax_gemv_umma_supported(w, n, dummy, dummy)) return ATLASX_OK;
     const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, false);
-    if (p.persist || p.head_bytes + p.plane_bytes + p.parts_bytes > ctx->split_scratch_cap) return ATLASX_OK;
+    if (p.head_bytes + p.plane_bytes + p.parts_bytes > ctx->split_scratch_cap) return ATLASX_OK;
     *plane = reinterpret_cast<uint16_t*>(reinterpret_cast<uint8_t*>(ctx->split_scratch) + p.head_bytes);
     *n8 = p.nc;
     return ATLASX_OK;
 }
 
-// x == nullptr: the token plane was left at ax_gemv_umma_plane's address by the kernels before (bf16 weights, an
-// item-per-CTA product, which needs no counter).
-int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
+// x == nullptr: the token plane was left at ax_gemv_umma_plane's address by the kernels before (bf16 weights; the
+// item counter of the resident form sets itself back).
+size_t ax_gemv_umma_parts_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n) {
+    return make_plan(ctx, w.rows, w.cols, n, w.dtype == ATLASX_INT8).parts_bytes;
+}
+
+int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl,
+                        float* ext_parts, AxUmmaParts* pend) {
     const bool prepared = x == nullptr;
     if (prepared) x = y;                                                     // for the argument checks only
     AX_ARG(ax_gemv_umma_supported(w, n, x, y), "shape or format not covered by the tcgen05 multi-column kernel");
@@ -599,7 +607,10 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    AX_ARG(!prepared || (!i8 && !p.persist), "a prepared token plane needs bf16 weights and an item-per-CTA product");
+    AX_ARG(!prepared || !i8, "a prepared token plane needs bf16 weights");
+    AX_ARG((ext_parts == nullptr) == (pend == nullptr), "a buffer for the partial tiles and their description go together");
+    const bool defer = ext_parts != nullptr;
+    if (defer) { pend->parts = p.KS > 1 ? ext_parts : nullptr; pend->KS = p.KS; pend->n = n; }
     if (!prepared) {
         cudaLaunchConfig_t cfg = {};
         cfg.blockDim = dim3(256); cfg.stream = ctx->stream;
@@ -620,12 +631,12 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     a.wscale = reinterpret_cast<const float*>(w.scales); a.xscale = xscale;
     a.KB = p.KB; a.KS = p.KS; a.T = p.T;
     a.stages = p.stages; a.b_bytes = p.b_bytes; a.acc_cols = p.acc_cols; a.tmem_cols = p.tmem_cols; a.persist = p.persist; a.counter = counter; a.token_major = token_major ? 1 : 0;
-    a.parts = parts; a.err = ctx->dev_error;
+    a.parts = defer ? ext_parts : parts; a.err = ctx->dev_error;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)p.grid); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = p.smem; cfg.stream = ctx->stream;
     if (!prepared || pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }            // its producer warp waits for the kernel before itself
     AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_umma_kernel, map_w, map_x, a));
-    if (p.KS > 1) {
+    if (p.KS > 1 && !defer) {
         cudaLaunchConfig_t mc = {};
         mc.gridDim = dim3((unsigned)(((size_t)p.T * n * (kTileM / 4) + 255) / 256)); mc.blockDim = dim3(256); mc.stream = ctx->stream;
         mc.attrs = attr; mc.numAttrs = 1;                                    // it waits for the product itself

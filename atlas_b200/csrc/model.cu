@@ -106,6 +106,7 @@ struct atlasx_model {
     float *pf_r = nullptr, *pf_a = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_o = nullptr,
           *pf_gu = nullptr, *pf_h = nullptr, *pf_dn = nullptr;
     int* pf_pos = nullptr;
+    float* pf_parts = nullptr;                          // partial tiles of K-split layer products that the next kernel adds up
     float* pf_attn_partials = nullptr; unsigned* pf_attn_tickets = nullptr; int pf_attn_splits = 0;   // causal chunk attention (bf16 cache, head_dim 128)
     // timeline diagnostics of the captured step (ATLASX_STEP_TRACE)
     unsigned long long* step_trace = nullptr; int step_trace_slots = 0;
@@ -526,8 +527,9 @@ __device__ __forceinline__ void pf_plane_store(uint16_t* plane, int n8, int d, i
     plane[(size_t)row * d + k] = h;
     plane[(size_t)(n8 + row) * d + k] = ax_f32_to_bf16_rne(v - ax_bf16_to_f32(h));
 }
+// yp pending: y is not read; its elements are the sums of the partial tiles of the product before (same order as its merge kernel).
 __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const float* base, const float* wy, const float* wx, float eps,
-                                                           int d, float* resid, float* x, uint16_t* plane, int n8, int n) {
+                                                           int d, float* resid, float* x, uint16_t* plane, int n8, int n, AxUmmaParts yp) {
     __shared__ float red[32];
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const int nt = blockDim.x;
@@ -536,16 +538,36 @@ __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const
         return;
     }
     const size_t o = (size_t)blockIdx.x * d;
+    const bool parts = yp.pending();
+    auto y_at = [&](int k) { return parts ? yp.at((int)blockIdx.x, k) : y[o + k]; };
+    // the first kKeep elements a thread reads of y stay in registers between the two passes (all of them up to d = 8192)
+    constexpr int kKeep = 8;
+    float yk[kKeep];
     float inv_y = 1.f;
     if (y && wy) {
         float ss = 0.f;
-        for (int k = threadIdx.x; k < d; k += nt) ss = fmaf(y[o + k], y[o + k], ss);
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) { const int k = threadIdx.x + i * nt; if (k < d) { yk[i] = y_at(k); ss = fmaf(yk[i], yk[i], ss); } }
+        for (int k = threadIdx.x + kKeep * nt; k < d; k += nt) { const float t = y_at(k); ss = fmaf(t, t, ss); }
         inv_y = 1.0f / sqrtf(pf_block_sum(ss, red) / (float)d + eps);
+    } else if (y) {
+#pragma unroll
+        for (int i = 0; i < kKeep; i++) { const int k = threadIdx.x + i * nt; if (k < d) yk[i] = y_at(k); }
     }
     float ss2 = 0.f;
-    for (int k = threadIdx.x; k < d; k += nt) {
+#pragma unroll
+    for (int i = 0; i < kKeep; i++) {
+        const int k = threadIdx.x + i * nt;
+        if (k < d) {
+            float v = base[o + k];
+            if (y) { float t = yk[i]; if (wy) t = t * inv_y * wy[k]; v += t; }
+            resid[o + k] = v;
+            ss2 = fmaf(v, v, ss2);
+        }
+    }
+    for (int k = threadIdx.x + kKeep * nt; k < d; k += nt) {
         float v = base[o + k];
-        if (y) { float t = y[o + k]; if (wy) t = t * inv_y * wy[k]; v += t; }
+        if (y) { float t = y_at(k); if (wy) t = t * inv_y * wy[k]; v += t; }
         resid[o + k] = v;
         ss2 = fmaf(v, v, ss2);
     }
@@ -562,13 +584,14 @@ __global__ void __launch_bounds__(1024) pf_rows_norm_add_k(const float* y, const
     }
 }
 // gate/up rows are interleaved (even: gate, odd: up): out[i][j] = silu(gu[i][2j]) · gu[i][2j+1]
-__global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out, uint16_t* plane, int n8, int n) {
+__global__ void pf_silu_pair_rows_k(const float* gu, int f, float* out, uint16_t* plane, int n8, int n, AxUmmaParts gp) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     const size_t i = blockIdx.y;
     const int j = blockIdx.x * blockDim.x + threadIdx.x;
     if (j >= f) return;
     if ((int)i >= n) { plane[i * (size_t)f + j] = 0; plane[(n8 + i) * (size_t)f + j] = 0; return; }       // padding rows of the plane
-    const float2 v = reinterpret_cast<const float2*>(gu + i * 2 * (size_t)f)[j];
+    const float2 v = gp.pending() ? make_float2(gp.at((int)i, 2 * j), gp.at((int)i, 2 * j + 1))
+                                  : reinterpret_cast<const float2*>(gu + i * 2 * (size_t)f)[j];
     const float r = (v.x / (1.0f + expf(-v.x))) * v.y;
     if (plane) pf_plane_store(plane, n8, f, (int)i, j, r); else out[i * (size_t)f + j] = r;
 }
@@ -592,9 +615,12 @@ int prefill_limit(const atlasx_model* m) {
 }
 // One layer product of a chunk: X [n][cols] → Y [n][rows]
 // x == nullptr: the kernel before left the token plane of this product in place (pf_plane_for)
-int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y, bool pdl) {
-    if (!x) return ax_gemv_umma_launch(c, w, nullptr, n, y, true, pdl);
-    if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, pdl);
+// ext_parts + pend: where the product splits K, its partial tiles stay in ext_parts for the next kernel to add up
+int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y, bool pdl, float* ext_parts = nullptr, AxUmmaParts* pend = nullptr) {
+    if (pend) *pend = AxUmmaParts();
+    if (!ext_parts) pend = nullptr;
+    if (!x) return ax_gemv_umma_launch(c, w, nullptr, n, y, true, pdl, ext_parts, pend);
+    if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, pdl, ext_parts, pend);
     return ax_gemv_mma_launch(c, w, x, n, y, true);
 }
 
@@ -639,11 +665,12 @@ int run_prefill_chunk(atlasx_model* m, int n) {
     if (!post) {
         if ((rc = plane_for(m->layers[0].qkv, &tpl, &n8))) return rc;
         if ((rc = pf_launch(s, pdl, pf_rows_norm_add_k, dim3((unsigned)(tpl ? n8 : n)), dim3(1024), (const float*)nullptr, (const float*)m->pf_r, (const float*)nullptr,
-                            (const float*)m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n))) return rc;
+                            (const float*)m->layers[0].attn_norm, cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n, AxUmmaParts()))) return rc;
         a_in = tpl ? nullptr : m->pf_a;
     }
     for (int l = 0; l < L; l++) {
         Layer& ly = m->layers[l];
+        uint16_t* att_pl = nullptr;
         if ((rc = pf_product(c, ly.qkv, a_in, n, m->pf_qkv, pdl))) return rc;
         if (m->pf_attn_splits > 0) {
             // QK-norm, RoPE and cache write of all n tokens at once, then ONE causal attention launch
@@ -666,6 +693,9 @@ int run_prefill_chunk(atlasx_model* m, int n) {
                 if (ca.n_splits > m->pf_attn_splits) ca.n_splits = m->pf_attn_splits;
             }
             ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
+            // the attention writes o_proj's token plane itself where the chunk fills the plane's rows (no padding rows to clear)
+            if (n % 8 == 0 && (rc = plane_for(ly.wo, &att_pl, &n8))) return rc;
+            ca.out_plane = att_pl; ca.plane_rows = n8;
             if ((rc = ax_attn_mma_chunk_launch(c, ca, pdl))) return rc;
         } else
         for (int i = 0; i < n; i++) {
@@ -695,24 +725,27 @@ int run_prefill_chunk(atlasx_model* m, int n) {
                 if ((rc = ax_attn_launch(c, aa, false))) return rc;
             }
         }
-        if ((rc = pf_product(c, ly.wo, m->pf_att, n, m->pf_o, pdl))) return rc;
-        if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
         const bool after_nccl = m->world > 1;             // an NCCL kernel in front: plain stream order
+        float* own_parts = after_nccl ? nullptr : m->pf_parts;         // the all-reduce wants the finished vector
+        AxUmmaParts yp;
+        if ((rc = pf_product(c, ly.wo, att_pl ? nullptr : m->pf_att, n, m->pf_o, pdl, own_parts, &yp))) return rc;
+        if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_o, (size_t)n * d))) return rc;
         if ((rc = plane_for(ly.gateup, &tpl, &n8))) return rc;
         if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)(tpl ? n8 : n)), dim3(1024), (const float*)m->pf_o, (const float*)m->pf_r,
                             (const float*)(post ? ly.attn_norm : nullptr), (const float*)(post ? nullptr : ly.ffn_norm),
-                            cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n))) return rc;
-        if ((rc = pf_product(c, ly.gateup, tpl ? nullptr : m->pf_a, n, m->pf_gu, pdl))) return rc;
+                            cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n, yp))) return rc;
+        AxUmmaParts gp;
+        if ((rc = pf_product(c, ly.gateup, tpl ? nullptr : m->pf_a, n, m->pf_gu, pdl, m->pf_parts, &gp))) return rc;
         if ((rc = plane_for(ly.down, &tpl, &n8))) return rc;
         if ((rc = pf_launch(s, pdl, pf_silu_pair_rows_k, dim3((unsigned)((m->ffn_loc + 255) / 256), (unsigned)(tpl ? n8 : n)), dim3(256),
-                            (const float*)m->pf_gu, m->ffn_loc, m->pf_h, tpl, n8, n))) return rc;
-        if ((rc = pf_product(c, ly.down, tpl ? nullptr : m->pf_h, n, m->pf_dn, pdl))) return rc;
+                            (const float*)m->pf_gu, m->ffn_loc, m->pf_h, tpl, n8, n, gp))) return rc;
+        if ((rc = pf_product(c, ly.down, tpl ? nullptr : m->pf_h, n, m->pf_dn, pdl, own_parts, &yp))) return rc;
         if (m->world > 1 && (rc = ax_comm_allreduce_sum(c, m->pf_dn, (size_t)n * d))) return rc;
         const float* next_wx = (post || l == L - 1) ? nullptr : m->layers[l + 1].attn_norm;
         tpl = nullptr; n8 = 0;
         if (l + 1 < L && (rc = plane_for(m->layers[l + 1].qkv, &tpl, &n8))) return rc;
         if ((rc = pf_launch(s, pdl && !after_nccl, pf_rows_norm_add_k, dim3((unsigned)(tpl ? n8 : n)), dim3(1024), (const float*)m->pf_dn, (const float*)m->pf_r,
-                            (const float*)(post ? ly.ffn_norm : nullptr), next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n))) return rc;
+                            (const float*)(post ? ly.ffn_norm : nullptr), next_wx, cf.rms_norm_eps, d, m->pf_r, m->pf_a, tpl, n8, n, yp))) return rc;
         a_in = tpl ? nullptr : m->pf_a;
     }
     AX_CHECK_LAUNCH("prefill chunk");
@@ -1179,6 +1212,18 @@ extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effecti
         }
         rc = atlasx_ctx_ensure_split_scratch(m->ctx, need);
         if (rc) return rc;
+        // o_proj, gate/up and down leave the partial tiles of a K split to the row-wise kernel behind them
+        if (m->ctx->tune.umma && m->ctx->tune.umma_fused == 1) {
+            alignas(16) static float dummy[4];
+            size_t pb = 0;
+            for (const Layer& ly : m->layers) {
+                const AxWeight* ws[3] = { &ly.wo, &ly.gateup, &ly.down };
+                for (const AxWeight* w : ws)
+                    for (int n = 2; n <= kPrefillMax; n++)
+                        if (ax_gemv_umma_supported(*w, n, dummy, dummy)) { const size_t b = ax_gemv_umma_parts_bytes(m->ctx, *w, n); if (b > pb) pb = b; }
+            }
+            if (pb && (rc = dmalloc(m, (void**)&m->pf_parts, pb))) return rc;
+        }
         if (m->cfg.kv_dtype == ATLASX_BF16 && ax_attn_mma_chunk_supported(m->hd, m->nh_loc, m->nkv_loc, m->cfg.kv_dtype)) {
             const int A = kPrefillMax;
             m->pf_attn_splits = ax_attn_mma_chunk_max_splits();      // scratch for the largest split count; each chunk picks its own
