@@ -135,7 +135,7 @@ int atlasx_ctx_ensure_split_scratch(atlasx_ctx* c, size_t bytes) {
     c->split_scratch = nullptr; c->split_scratch_cap = 0;
     if (bytes < (1u << 21)) bytes = 1u << 21;
     AX_CUDA(cudaMalloc(&c->split_scratch, bytes));
-    AX_CUDA(cudaMemsetAsync(c->split_scratch, 0, 16384, c->stream));      // the ticket area of the tcgen05 product starts out zero
+    AX_CUDA(cudaMemsetAsync(c->split_scratch, 0, 16384, c->stream));      // the item counter of the tcgen05 product starts out zero
     c->split_scratch_cap = bytes;
     return ATLASX_OK;
 }

@@ -28,7 +28,7 @@ constexpr int kMmaThreads = 256;
 constexpr int kMmaWarps = 8;
 constexpr int kMaxTiles = 4;          // 16-row tiles per row group
 constexpr int kMmaUnroll = 4;         // k-steps whose loads are issued together
-constexpr size_t kScratchHead = 16384; // the first bytes of the context scratch belong to the tcgen05 product (its tickets)
+constexpr size_t kScratchHead = 16384; // the first bytes of the context scratch belong to the tcgen05 product (its item counter)
 
 struct MmaArgs {
     const uint8_t* W; const uint8_t* scales;

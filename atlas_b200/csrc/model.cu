@@ -614,7 +614,7 @@ int prefill_limit(const atlasx_model* m) {
     return limit;
 }
 // One layer product of a chunk: X [n][cols] → Y [n][rows]
-// x == nullptr: the kernel before left the token plane of this product in place (pf_plane_for)
+// x == nullptr: the kernel before left the token plane of this product in place (ax_gemv_umma_plane)
 // ext_parts + pend: where the product splits K, its partial tiles stay in ext_parts for the next kernel to add up
 int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y, bool pdl, float* ext_parts = nullptr, AxUmmaParts* pend = nullptr) {
     if (pend) *pend = AxUmmaParts();
