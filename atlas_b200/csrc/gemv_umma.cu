@@ -1,4 +1,4 @@
-// gemv_umma.cu — many-column weight-streaming product Y[n][M] = X[n][K]·W[M][K]ᵀ, n = 2..64 tokens, on the
+// gemv_umma.cu — many-column weight-streaming product Y[n][M] = X[n][K]·W[M][K]ᵀ, n = 2..128 tokens (64 with int8 weights), on the
 // fifth-generation tensor cores: tcgen05.mma with the accumulator in tensor memory, operands brought into
 // shared memory by tiled bulk copies (cp.async.bulk.tensor) and handed over through mbarriers.
 //
@@ -43,7 +43,8 @@ constexpr int kABytes = kTileM * kBlockBytes;     // 16 KB
 constexpr float kDigitBase = 254.0f;
 constexpr int kThreads = 192;
 constexpr int kMaxStages = 8;
-constexpr int kMaxTokens = 64;
+constexpr int kMaxTokens = 128;                  // bf16 weights: hi and lo plane fill the 256 columns one MMA can have
+constexpr int kMaxTokensI8 = 64;                 // int8 weights: three digit planes
 constexpr int kMaxSplits = 8;
 constexpr int kItemRing = 8;
 constexpr size_t kHeadBytes = 16384;            // area at the start of the context scratch that holds the item counter
@@ -548,7 +549,7 @@ bool ax_gemv_umma_supported(const AxWeight& w, int n, const float* x, const floa
     if (n < 2 || n > kMaxTokens || !x || !y) return false;
     if ((((uintptr_t)w.data | (uintptr_t)x) & 15) != 0) return false;
     if (w.dtype == ATLASX_BF16) return w.cols % 8 == 0 && w.cols >= 64;          // row pitch a multiple of 16 bytes
-    if (w.dtype == ATLASX_INT8) return w.cols % 16 == 0 && w.cols >= 128 && w.scales != nullptr;
+    if (w.dtype == ATLASX_INT8) return n <= kMaxTokensI8 && w.cols % 16 == 0 && w.cols >= 128 && w.scales != nullptr;
     return false;
 }
 

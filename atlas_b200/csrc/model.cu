@@ -490,8 +490,9 @@ int run_step(atlasx_model* m, Profile* prof, bool advance, bool gather = true) {
     return ATLASX_OK;
 }
 
-constexpr int kPrefillMax = 64;                // tokens per chunk with the tcgen05 kernel; 16 with the warp-level one
-constexpr int kPrefillMaxMma = 16;
+constexpr int kPrefillMax = 128;               // tokens per chunk with the tcgen05 kernel and bf16 weights; 64 with int8 weights;
+constexpr int kPrefillMaxMma = 16;             // 16 with the warp-level kernel
+constexpr int kAttnChunk = 64;                 // tokens per launch of the chunk attention
 
 // ── prompt ingestion: row-wise helpers, one CTA per token ───────────────────────────
 // Every kernel of a chunk starts with griddepcontrol.wait, so each may be launched with programmatic stream
@@ -606,9 +607,12 @@ int prefill_limit(const atlasx_model* m) {
     for (const Layer& ly : m->layers) {
         const AxWeight* ws[4] = { &ly.qkv, &ly.wo, &ly.gateup, &ly.down };
         for (const AxWeight* w : ws) {
-            if (m->ctx->tune.umma && ax_gemv_umma_supported(*w, 2, dummy, dummy)) continue;
+            if (m->ctx->tune.umma && ax_gemv_umma_supported(*w, 2, dummy, dummy)) {
+                while (limit > 2 && !ax_gemv_umma_supported(*w, limit, dummy, dummy)) limit /= 2;      // 128 → 64 with int8 weights
+                continue;
+            }
             if (!ax_gemv_mma_supported(*w, 2, dummy, dummy)) return 1;
-            limit = kPrefillMaxMma;
+            if (limit > kPrefillMaxMma) limit = kPrefillMaxMma;
         }
     }
     return limit;
@@ -682,21 +686,26 @@ int run_prefill_chunk(atlasx_model* m, int n) {
             qa.n_heads = m->nh_loc; qa.n_kv = m->nkv_loc; qa.hd = m->hd; qa.kv_dtype = cf.kv_dtype; qa.eps = 1e-6f;
             qa.q_stride = (size_t)qkv_rows; qa.kv_in_stride = (size_t)qkv_rows;
             if ((rc = ax_qk_prep_launch(c, qa, pdl))) return rc;
-            AxAttnChunkArgs ca;                                // ONE causal attention launch for the chunk
-            ca.q = m->pf_qkv; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
-            ca.out = m->pf_att; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos;
-            ca.n_tok = n; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window;
-            {   // splits for the rows this chunk really sees in this layer (the position is known on the host)
-                int rows_seen = m->host_pos + n;
-                if (ly.window > 0 && rows_seen > ly.window + n) rows_seen = ly.window + n;
-                ca.n_splits = ax_attn_mma_chunk_splits(c, m->nh_loc, m->nkv_loc, n, rows_seen);
-                if (ca.n_splits > m->pf_attn_splits) ca.n_splits = m->pf_attn_splits;
-            }
-            ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
-            // the attention writes o_proj's token plane itself where the chunk fills the plane's rows (no padding rows to clear)
+            // causal attention of the chunk: one launch per kAttnChunk tokens (all K/V rows of the chunk are in the cache;
+            // a token sees the rows up to its own position).  It writes o_proj's token plane itself where the chunk
+            // fills the plane's rows (no padding rows to clear).
             if (n % 8 == 0 && (rc = plane_for(ly.wo, &att_pl, &n8))) return rc;
-            ca.out_plane = att_pl; ca.plane_rows = n8;
-            if ((rc = ax_attn_mma_chunk_launch(c, ca, pdl))) return rc;
+            for (int t0 = 0; t0 < n; t0 += kAttnChunk) {
+                const int nt = n - t0 < kAttnChunk ? n - t0 : kAttnChunk;
+                AxAttnChunkArgs ca;
+                ca.q = m->pf_qkv + (size_t)t0 * qkv_rows; ca.q_stride = (size_t)qkv_rows; ca.kc = ly.kv->k; ca.vc = ly.kv->v;
+                ca.out = m->pf_att + (size_t)t0 * m->q_rows; ca.out_stride = (size_t)m->q_rows; ca.pos0 = m->pf_pos + t0;
+                ca.n_tok = nt; ca.n_heads = m->nh_loc; ca.n_kv = m->nkv_loc; ca.window = ly.window;
+                {   // splits for the rows these tokens really see in this layer (the position is known on the host)
+                    int rows_seen = m->host_pos + t0 + nt;
+                    if (ly.window > 0 && rows_seen > ly.window + nt) rows_seen = ly.window + nt;
+                    ca.n_splits = ax_attn_mma_chunk_splits(c, m->nh_loc, m->nkv_loc, nt, rows_seen);
+                    if (ca.n_splits > m->pf_attn_splits) ca.n_splits = m->pf_attn_splits;
+                }
+                ca.scale = m->scale; ca.partials = m->pf_attn_partials; ca.tickets = m->pf_attn_tickets;
+                ca.out_plane = att_pl ? att_pl + (size_t)t0 * m->q_rows : nullptr; ca.plane_rows = n8;
+                if ((rc = ax_attn_mma_chunk_launch(c, ca, pdl))) return rc;
+            }
         } else
         for (int i = 0; i < n; i++) {
             float* qkv = m->pf_qkv + (size_t)i * qkv_rows;
@@ -1182,13 +1191,13 @@ extern "C" int atlasx_model_finalize(atlasx_model* m) {
     return ATLASX_OK;
 }
 
-// Prompt tokens are ingested `chunk` at a time (2..64) through the multi-column kernels; 0 or 1
+// Prompt tokens are ingested `chunk` at a time (2..128) through the multi-column kernels; 0 or 1
 // restores the token-by-token path.  Returns the chunk size in effect through *effective: at most 16
 // when a matrix needs the warp-level kernel (int8 / int4 weights), 1 when the weight format or a
 // matrix shape is outside what the multi-column kernels cover.
 extern "C" int atlasx_model_set_prefill(atlasx_model* m, int chunk, int* effective) {
     AX_ARG(m && m->finalized, "model is not finalised");
-    AX_ARG(chunk >= 0 && chunk <= kPrefillMax, "chunk must be in 0..64");
+    AX_ARG(chunk >= 0 && chunk <= kPrefillMax, "chunk must be in 0..128");
     int eff = chunk < 2 ? 1 : chunk;
     if (eff > 1) { const int lim = prefill_limit(m); if (eff > lim) eff = lim; }
     if (eff > 1 && !m->pf_r) {

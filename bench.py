@@ -426,7 +426,7 @@ def main():
     ap.add_argument("--timeline", action="store_true",
                     help="record %%globaltimer stamps in every GEMV and attention launch of the captured step and print a "
                          "per-class summary on stderr; the stamps cost a little, so the JSON line is marked invalid")
-    ap.add_argument("--prefill", type=int, default=64, help="prompt tokens ingested per chunk before the timed region (1: token by token)")
+    ap.add_argument("--prefill", type=int, default=128, help="prompt tokens ingested per chunk before the timed region (1: token by token)")
     ap.add_argument("--weights", default="bf16", choices=["bf16", "int8", "int4"],
                     help="weight format held on the device (quantised from the same bf16 tensors); anything but bf16 marks the line invalid as the benchmark")
     ap.add_argument("--gemv-impl", type=int, default=0, help="0 automatic, 1 plain 128-bit loads, 2 bulk-copy pipeline")

@@ -299,7 +299,7 @@ double atlasx_model_step_bytes(const atlasx_model* m, int pos);
 int atlasx_model_kernel_launches_per_step(const atlasx_model* m);
 int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
 /* Prompt ingestion in chunks: atlasx_model_generate_greedy feeds the prompt `chunk` tokens at a
- * time (2..64; at most 16 with int8 / int4 weights) through the multi-column kernels, so the weights stream once per chunk instead of
+ * time (2..128 with bf16 weights, at most 64 with int8 and 16 with int4 weights) through the multi-column kernels, so the weights stream once per chunk instead of
  * once per token (the reference feeds one token per forward, crates/atlas-model/src/lib.rs:1611-1618).
  * 0 or 1 restores token-by-token ingestion (the default).  *effective receives the chunk in use:
  * 1 when a weight format or shape is outside what the multi-column kernel covers (f32 weights,

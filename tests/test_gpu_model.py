@@ -306,6 +306,35 @@ def test_chunked_prompt_ingestion_matches_token_by_token(ab, kv, fmt):
     assert np.max(np.abs(m.forward_one_gpu(int(got[-1])) - lo)) <= LOGIT_TOL
 
 
+@pytest.mark.parametrize("kv", ["f32", "bf16"])
+def test_chunked_prompt_ingestion_128_tokens(ab, kv):
+    """bf16 weights take 128 tokens per chunk (two attention launches of 64 tokens inside it): a 150-token prompt as
+    128 + 22 against token-by-token ingestion and against the CPU oracle; int8 weights are held to 64."""
+    cfg = dict(helpers.HD128, max_seq_len=192)
+    w = helpers.synth_weights(cfg, seed=31, norm_jitter=0.1)
+    kvd = ab.F32 if kv == "f32" else ab.BF16
+    prompt = orc.uniform_u32(150, 31, 1, cfg["vocab_size"])
+    plain = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=ab.BF16)
+    want = plain.generate(prompt, 8, 0.0)
+    m = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=ab.BF16)
+    assert m.set_prefill(128) == 128
+    got = m.generate(prompt, 8, 0.0)
+    o = helpers.oracle_model(cfg, _requantised(w, "bf16"), helpers.HD128_LAYERS, kv_round_bf16=(kv == "bf16"))
+    otoks, _, margins = o.generate_greedy(prompt, 8, want_logits=True)
+    if got != otoks.tolist():
+        i = next(j for j in range(8) if got[j] != otoks[j])
+        assert margins[i] <= 2 * LOGIT_TOL, (i, float(margins[i]))
+    o.reset()
+    for t in list(prompt) + got + [got[-1]]:
+        lo = o.forward_one(int(t))
+    assert np.max(np.abs(m.forward_one_gpu(int(got[-1])) - lo)) <= LOGIT_TOL
+    if kv == "f32":
+        assert got == want
+    m8 = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=ab.INT8)
+    assert m8.set_prefill(128) == 64
+    assert ab.Context.default().poll_device_error() == 0
+
+
 def test_chunked_prompt_ingestion_declines_unsupported_formats(ab, c1_weights):
     m = helpers.cuda_model(helpers.C1, c1_weights, kv_dtype=ab.F32)        # f32 weights
     assert m.set_prefill(16) == 1
