@@ -703,7 +703,7 @@ size_t ax_attn_mma_chunk_partial_floats(int n_tok, int n_heads, int n_splits) { 
 
 int ax_attn_mma_chunk_launch(atlasx_ctx* ctx, const AxAttnChunkArgs& a, bool pdl) {
     AX_ARG(ax_attn_mma_chunk_supported(128, a.n_heads, a.n_kv, ATLASX_BF16), "shape not covered by the chunk attention kernel");
-    AX_ARG(a.q && a.kc && a.vc && a.out && a.pos0 && a.partials && a.tickets && a.n_tok >= 1 && a.n_tok <= 64, "bad argument");
+    AX_ARG(a.q && a.kc && a.vc && a.out && a.pos0 && a.partials && a.tickets && a.n_tok >= 1 && a.n_tok <= 128, "bad argument");
     static bool attr_done[64] = {};
     if (!attr_done[ctx->device & 63]) {
         AX_CUDA(cudaFuncSetAttribute(ax_attn_mma_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kSmemBytes));

@@ -492,7 +492,7 @@ int run_step(atlasx_model* m, Profile* prof, bool advance, bool gather = true) {
 
 constexpr int kPrefillMax = 128;               // tokens per chunk with the tcgen05 kernel and bf16 weights; 64 with int8 weights;
 constexpr int kPrefillMaxMma = 16;             // 16 with the warp-level kernel
-constexpr int kAttnChunk = 64;                 // tokens per launch of the chunk attention
+constexpr int kAttnChunk = 128;                // tokens per launch of the chunk attention (one launch per chunk: 16520 tok/s against 16430 with two of 64)
 
 // ── prompt ingestion: row-wise helpers, one CTA per token ───────────────────────────
 // Every kernel of a chunk starts with griddepcontrol.wait, so each may be launched with programmatic stream

@@ -308,7 +308,7 @@ def test_chunked_prompt_ingestion_matches_token_by_token(ab, kv, fmt):
 
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
 def test_chunked_prompt_ingestion_128_tokens(ab, kv):
-    """bf16 weights take 128 tokens per chunk (two attention launches of 64 tokens inside it): a 150-token prompt as
+    """bf16 weights take 128 tokens per chunk: a 150-token prompt as
     128 + 22 against token-by-token ingestion and against the CPU oracle; int8 weights are held to 64."""
     cfg = dict(helpers.HD128, max_seq_len=192)
     w = helpers.synth_weights(cfg, seed=31, norm_jitter=0.1)
