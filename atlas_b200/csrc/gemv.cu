@@ -476,7 +476,7 @@ size_t ax_weight_bytes(const AxWeight& w) {
 int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, int epi, int n, float* y, bool pdl, const AxPeerOut* peer) {
     AX_ARG(w.data && y, "null pointer");
     AX_ARG(w.rows > 0 && w.cols > 0, "empty matrix");
-    AX_ARG(n >= 1 && n <= 64, "n must be in 1..64");
+    AX_ARG(n >= 1 && n <= 128, "n must be in 1..128");
     const int epc = w.dtype == ATLASX_F32 ? 4 : w.dtype == ATLASX_BF16 ? 8 : w.dtype == ATLASX_INT8 ? 16 : 32;
     const int ebits = w.dtype == ATLASX_F32 ? 32 : w.dtype == ATLASX_BF16 ? 16 : w.dtype == ATLASX_INT8 ? 8 : 4;
     const bool has_pro = pro.y || pro.wx || pro.embed || pro.resid_out;
@@ -489,7 +489,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
         if (ctx->tune.umma && ax_gemv_umma_supported(w, n, pro.base, y)) return ax_gemv_umma_launch(ctx, w, pro.base, n, y, false, pdl);
         if (ax_gemv_mma_supported(w, n, pro.base, y)) return ax_gemv_mma_launch(ctx, w, pro.base, n, y);
     }
-    AX_ARG(n <= 16, "more than 16 columns need bf16 weights with a column count that is a multiple of 64");
+    AX_ARG(n <= 16, "more than 16 columns need bf16 weights (up to 128) or int8 weights (up to 64) in the tensor-memory kernel's shapes");
     if (!vec_ok) {
         AX_ARG(!has_pro && epi == AX_EPI_PLAIN && pro.base, "fused prologue/epilogue need 16-byte aligned rows and n == 1");
         const int warps = 8;

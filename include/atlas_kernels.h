@@ -142,8 +142,8 @@ int atlasx_matrix_free(atlasx_matrix* m);
 int atlasx_matrix_info(const atlasx_matrix* m, int* rows, int* cols, int* dtype);   /* is_on_gpu / is_bf16 :349-362 */
 size_t atlasx_matrix_bytes(const atlasx_matrix* m);     /* weight bytes one product streams from HBM */
 /* GpuMatrix::sgemm_vec (:409-435): y[rows×n] = W·x[cols×n], x and y row-major in HBM, f32.
- * n == 1 is the decode GEMV; 2..16 (2..64 for bf16 weights whose column count is a multiple of 64) is the
- * skinny batched/verify case. */
+ * n == 1 is the decode GEMV; 2..16 (2..128 for bf16 weights with at least 64 columns, a multiple of 8; 2..64 for int8
+ * weights with at least 128 columns, a multiple of 16) is the skinny batched/verify case. */
 int atlasx_gemv(atlasx_ctx* ctx, const atlasx_matrix* m, const float* x_dev, int n, float* y_dev);
 /* GpuMatrix::sgemm (:371-400): same with host rhs/out (uploads x, downloads y) */
 int atlasx_matrix_sgemm(atlasx_ctx* ctx, const atlasx_matrix* m, const float* rhs_host, int k, int n, float* out_host);

@@ -166,7 +166,7 @@ def test_config3_lm_head_shape_bf16_multi_column(ab, n):
 def test_gemv_many_columns_tensor_memory_kernel(ab, fmt, n, shape):
     """Token batches of up to 64 columns run on the tcgen05 kernel (bf16 weights: tokens as hi|lo bf16 planes;
     int8 weights: raw weight bytes against three int8 digit planes of the tokens): one K block only, K split
-    over several CTAs with the ticketed merge, rows that do not fill the last 128-row tile, a K that ends inside
+    over several CTAs with the merge kernel behind it, rows that do not fill the last 128-row tile, a K that ends inside
     a block (zero-filled by the copy engine), column counts that are not multiples of 8.  Every output element
     against the oracle's f32 product of the stored weights; afterwards the bounded waits of the kernel must not
     have raised the device error word."""
@@ -178,6 +178,24 @@ def test_gemv_many_columns_tensor_memory_kernel(ab, fmt, n, shape):
     Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
     # hi + lo planes (bf16) and three base-254 digits (int8) keep f32 accuracy: far inside the 1e-3 parity bound
     assert rel_err(Y, orc.gemm(wo, X)) <= 2e-5
+    assert ab.Context.default().poll_device_error() == 0
+
+
+@pytest.mark.parametrize("n", [72, 100, 128])
+@pytest.mark.parametrize("shape", [(256, 512), (4096, 4096), (1000, 4096), (200, 11008), (300, 1376)], ids=lambda s: "%dx%d" % s)
+def test_gemv_up_to_128_columns_bf16(ab, n, shape):
+    """bf16 weights take up to 128 columns: hi and lo plane then fill the 256 columns of one tcgen05 MMA.  int8
+    weights (three planes) stop at 64."""
+    M, K = shape
+    w = orc.normal_f32(M * K, 53, M + K, 0.02).reshape(M, K)
+    X = orc.normal_f32(K * n, 53, n, 1.0).reshape(K, n)
+    gm, wo = make(ab, "bf16", w)
+    Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+    assert rel_err(Y, orc.gemm(wo, X)) <= 2e-5
+    if shape == (256, 512) and n == 72:
+        g8, _ = make(ab, "int8", w)
+        with pytest.raises(ab.AtlasError):
+            g8.sgemm_vec(ab.GpuVec.from_slice(X), n)
     assert ab.Context.default().poll_device_error() == 0
 
 
