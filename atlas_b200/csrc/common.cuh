@@ -81,6 +81,7 @@ struct atlasx_ctx {
     unsigned* attn_tickets = nullptr; size_t attn_tickets_cap = 0;   // uints, always zero between launches
     int* pos_dev = nullptr; size_t pos_cap = 0;
     void* split_scratch = nullptr; size_t split_scratch_cap = 0;   // bf16 hi/lo planes of the multi-column input
+    void* w_planes = nullptr; size_t w_planes_cap = 0;             // int4 weights of one matrix expanded to bf16 hi | lo planes (token batches)
     // argmax scratch
     float* amax_vals = nullptr; int* amax_idx = nullptr; unsigned* amax_ticket = nullptr; int* amax_out = nullptr;
     // device error word written by bounded waits

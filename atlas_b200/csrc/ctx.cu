@@ -90,7 +90,7 @@ extern "C" int atlasx_ctx_destroy(atlasx_ctx* c) {
     cudaStreamSynchronize(c->stream);
     atlasx_comm_destroy(c);
     ax_sample_free_scratch(c);
-    cudaFree(c->attn_partials); cudaFree(c->attn_tickets); cudaFree(c->pos_dev); cudaFree(c->split_scratch);
+    cudaFree(c->attn_partials); cudaFree(c->attn_tickets); cudaFree(c->pos_dev); cudaFree(c->split_scratch); cudaFree(c->w_planes);
     cudaFree(c->amax_vals); cudaFree(c->amax_idx); cudaFree(c->amax_ticket); cudaFree(c->amax_out);
     cudaFree(c->dev_error); cudaFreeHost(c->host_pin);
     cudaStreamDestroy(c->stream);

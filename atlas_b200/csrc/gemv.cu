@@ -488,6 +488,7 @@ int ax_gemv_launch(atlasx_ctx* ctx, const AxWeight& w, const AxPrologue& pro, in
     if (n > 1 && !has_pro && epi == AX_EPI_PLAIN && ctx->gemv_impl != 3) {   // gemv_impl 3 keeps the scalar kernel (A/B comparison)
         if (ctx->tune.umma && ax_gemv_umma_supported(w, n, pro.base, y)) return ax_gemv_umma_launch(ctx, w, pro.base, n, y, false, pdl);
         if (ax_gemv_mma_supported(w, n, pro.base, y)) return ax_gemv_mma_launch(ctx, w, pro.base, n, y);
+        if (ctx->tune.umma && ax_gemv_umma_int4_supported(w, n, pro.base, y)) return ax_gemv_umma_int4_launch(ctx, w, pro.base, n, y, false, pdl);
     }
     AX_ARG(n <= 16, "more than 16 columns need bf16 weights (up to 128) or int8 weights (up to 64) in the tensor-memory kernel's shapes");
     if (!vec_ok) {

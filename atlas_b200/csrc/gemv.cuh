@@ -120,6 +120,9 @@ struct AxUmmaParts {
 int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false, bool pdl = false,
                         float* ext_parts = nullptr, AxUmmaParts* pend = nullptr);
 size_t ax_gemv_umma_parts_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n);
+// int4 weights, up to 128 tokens: expanded to two bf16 planes in context scratch, then the bf16 product
+bool ax_gemv_umma_int4_supported(const AxWeight& w, int n, const float* x, const float* y);
+int ax_gemv_umma_int4_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major = false, bool pdl = false);
 // bf16 weights: address at which producer kernels may leave the hi|lo token plane themselves (then x = nullptr above)
 int ax_gemv_umma_plane(atlasx_ctx* ctx, const AxWeight& w, int n, uint16_t** plane, int* n8);
 int ax_gemv_init(atlasx_ctx* ctx);      // one-time function attributes

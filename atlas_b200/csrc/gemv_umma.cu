@@ -58,6 +58,8 @@ struct UmmaArgs {
     const float* wscale;          // int8: scale per row of W
     const float* xscale;          // int8: scale per token
     int KB, KS, T;                // K blocks, K splits, row tiles
+    int KBx;                      // K blocks of the token plane: block kb of W meets block kb mod KBx of the tokens (KBx = KB unless W is
+                                  // two bf16 planes side by side — int4 weights expanded to hi | lo)
     int stages, b_bytes;          // pipeline depth, bytes of one B stage (planes·nc rows × 128)
     int acc_cols, tmem_cols;      // columns of one accumulator (power of two ≥ 32 holding planes·nc) and of the allocation
     int persist;                  // 1: CTAs stay and take items from the counter; 0: one item per CTA
@@ -297,7 +299,7 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
                         mbar_expect_tx(bar, stage_bytes);
                         tma_load_2d(dst, &map_w, (kb0 + i) * a.kblk, tile * kTileM, bar);
                     }
-                    tma_load_2d(dst + kABytes, &map_x, (kb0 + i) * a.kblk, 0, bar);
+                    tma_load_2d(dst + kABytes, &map_x, ((kb0 + i) >= a.KBx ? (kb0 + i) - a.KBx : (kb0 + i)) * a.kblk, 0, bar);
                     s_issued = f + 1;
                 }
             }
@@ -417,6 +419,35 @@ __global__ void __launch_bounds__(kThreads) ax_gemv_umma_kernel(const __grid_con
     }
 }
 
+// int4 weights (crates/atlas-quant/src/lib.rs:111-168: two values per byte, even index in the high nibble, one scale per
+// block of the flat index) → two bf16 planes side by side, out[r][0..K) the hi parts and out[r][K..2K) the lo parts of
+// w = q · scale (dequant_nibble, :150-157): w = hi + lo to 2⁻¹⁷ relative.  A product over the 2K columns against the
+// tokens repeated (block kb of W meets block kb mod KBx of the token plane) is Σ w·x.  Thread = eight weights.
+__global__ void __launch_bounds__(256) ax_int4_planes_kernel(const uint32_t* __restrict__ q, const void* __restrict__ scales, int scales_f16,
+                                                             int block, int M, int K, uint16_t* __restrict__ out) {
+    const size_t idx = (size_t)blockIdx.x * 256 + threadIdx.x;
+    const int k8 = K / 8;
+    if (idx >= (size_t)M * k8) return;
+    const size_t r = idx / k8; const int wi = (int)(idx % k8);
+    const uint32_t word = __ldg(q + idx);
+    const size_t bi = (r * (size_t)K + (size_t)wi * 8) / (size_t)block;
+    const float sc = scales_f16 ? __half2float(reinterpret_cast<const __half*>(scales)[bi]) : reinterpret_cast<const float*>(scales)[bi];
+    uint32_t hi[4] = { 0u, 0u, 0u, 0u }, lo[4] = { 0u, 0u, 0u, 0u };
+#pragma unroll
+    for (int e = 0; e < 8; e++) {
+        const uint32_t byte = (word >> (8 * (e >> 1))) & 0xFFu;
+        const int nib = (e & 1) ? (int)(byte & 0xFu) : (int)(byte >> 4);
+        const float w = (float)(nib >= 8 ? nib - 16 : nib) * sc;
+        const uint16_t h = ax_f32_to_bf16_rne(w);
+        const uint16_t l = ax_f32_to_bf16_rne(w - ax_bf16_to_f32(h));
+        hi[e >> 1] |= (uint32_t)h << ((e & 1) * 16);
+        lo[e >> 1] |= (uint32_t)l << ((e & 1) * 16);
+    }
+    uint16_t* o = out + r * 2 * (size_t)K + (size_t)wi * 8;
+    *reinterpret_cast<uint4*>(o) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+    *reinterpret_cast<uint4*>(o + K) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+}
+
 // Partial tiles of a K-split product → Y: thread = four rows of one token of one row tile, splits added in order (the
 // result does not depend on timing).  The whole GPU takes part: the sums are a few MB that lie in L2.
 __global__ void __launch_bounds__(256) ax_umma_merge_kernel(const float* __restrict__ parts, float* __restrict__ Y, int M, int n, int KS, int T,
@@ -482,7 +513,9 @@ int make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols, u
 
 struct UmmaPlan { int nc, planes, kblk, T, KB, KS, stages, b_bytes, acc_cols, tmem_cols, persist, grid; size_t plane_bytes, xscale_bytes, parts_bytes, head_bytes, smem; };
 
-UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
+// cols: columns of W as the product walks them; x_cols: columns of the tokens (= cols, or cols / 2 for expanded int4 weights)
+UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8, int x_cols = 0) {
+    if (x_cols <= 0) x_cols = cols;
     UmmaPlan p;
     p.planes = i8 ? 3 : 2;
     p.nc = i8 ? (n + 15) / 16 * 16 : (n + 7) / 8 * 8;         // planes·nc must be a multiple of 16
@@ -535,7 +568,7 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8) {
         if (st > kMaxStages) st = kMaxStages;
         p.stages = st;
     }
-    p.plane_bytes = ((size_t)p.planes * p.nc * cols * (i8 ? 1 : 2) + 1023) / 1024 * 1024;
+    p.plane_bytes = ((size_t)p.planes * p.nc * x_cols * (i8 ? 1 : 2) + 1023) / 1024 * 1024;
     p.xscale_bytes = i8 ? 256 : 0;
     p.parts_bytes = p.KS > 1 ? (size_t)p.T * p.KS * n * kTileM * sizeof(float) : 0;
     p.head_bytes = kHeadBytes;                                           // the item counter
@@ -579,13 +612,15 @@ size_t ax_gemv_umma_parts_bytes(const atlasx_ctx* ctx, const AxWeight& w, int n)
     return make_plan(ctx, w.rows, w.cols, n, w.dtype == ATLASX_INT8).parts_bytes;
 }
 
-int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl,
-                        float* ext_parts, AxUmmaParts* pend) {
+namespace {
+// x_cols: columns of the tokens; w.cols = 2 · x_cols for int4 weights expanded into two planes side by side
+int umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl,
+                float* ext_parts, AxUmmaParts* pend, int x_cols) {
     const bool prepared = x == nullptr;
     if (prepared) x = y;                                                     // for the argument checks only
     AX_ARG(ax_gemv_umma_supported(w, n, x, y), "shape or format not covered by the tcgen05 multi-column kernel");
     const bool i8 = w.dtype == ATLASX_INT8;
-    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, i8);
+    const UmmaPlan p = make_plan(ctx, w.rows, w.cols, n, i8, x_cols);
     int rc = atlasx_ctx_ensure_split_scratch(ctx, p.plane_bytes + p.xscale_bytes + p.parts_bytes + p.head_bytes);
     if (rc) return rc;
     // scratch: [item counter, in an area of its own at the start][token planes][token scales][partial tiles]
@@ -597,7 +632,7 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
     CUtensorMap map_w, map_x;
     const uint32_t np = (uint32_t)(p.planes * p.nc);
     if ((rc = make_map(&map_w, w.data, (uint64_t)w.rows, (uint64_t)w.cols, kTileM, i8))) return rc;
-    if ((rc = make_map(&map_x, base, (uint64_t)np, (uint64_t)w.cols, np, i8))) return rc;
+    if ((rc = make_map(&map_x, base, (uint64_t)np, (uint64_t)x_cols, np, i8))) return rc;
 
     static bool attr_done[64] = {};
     const int dev = ctx->device & 63;
@@ -618,19 +653,19 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
         if (pdl) { cfg.attrs = attr; cfg.numAttrs = 1; }
         if (i8) {
             cfg.gridDim = dim3((unsigned)p.nc);
-            AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_digits_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
+            AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_digits_kernel, x, x_cols, n, p.nc, token_major ? 1 : 0,
                                        reinterpret_cast<int8_t*>(base), xscale, counter));
         } else {
-            const size_t work = (size_t)2 * p.nc * (w.cols / 8);
+            const size_t work = (size_t)2 * p.nc * (x_cols / 8);
             cfg.gridDim = dim3((unsigned)((work + 255) / 256));
-            AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, w.cols, n, p.nc, token_major ? 1 : 0,
+            AX_CUDA(cudaLaunchKernelEx(&cfg, ax_umma_split_kernel, x, x_cols, n, p.nc, token_major ? 1 : 0,
                                        reinterpret_cast<uint16_t*>(base), counter));
         }
     }
     UmmaArgs a;
     a.Y = y; a.M = w.rows; a.n = n; a.nc = p.nc; a.i8 = i8 ? 1 : 0; a.planes = p.planes; a.kblk = p.kblk;
     a.wscale = reinterpret_cast<const float*>(w.scales); a.xscale = xscale;
-    a.KB = p.KB; a.KS = p.KS; a.T = p.T;
+    a.KB = p.KB; a.KS = p.KS; a.T = p.T; a.KBx = (x_cols + p.kblk - 1) / p.kblk;
     a.stages = p.stages; a.b_bytes = p.b_bytes; a.acc_cols = p.acc_cols; a.tmem_cols = p.tmem_cols; a.persist = p.persist; a.counter = counter; a.token_major = token_major ? 1 : 0;
     a.parts = defer ? ext_parts : parts; a.err = ctx->dev_error;
     cudaLaunchConfig_t cfg = {};
@@ -644,4 +679,41 @@ int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int 
         AX_CUDA(cudaLaunchKernelEx(&mc, ax_umma_merge_kernel, (const float*)parts, y, w.rows, n, p.KS, p.T, token_major ? 1 : 0));
     }
     return ATLASX_OK;
+}
+}  // namespace
+
+int ax_gemv_umma_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl,
+                        float* ext_parts, AxUmmaParts* pend) {
+    return umma_launch(ctx, w, x, n, y, token_major, pdl, ext_parts, pend, w.cols);
+}
+
+// int4 weights, 17..128 tokens: the matrix is expanded into two bf16 planes side by side in context scratch (eight
+// bytes per weight written and read back — still several times faster than 16 tokens at a time on the warp-level
+// kernel, whose block scales stand between the MMAs of a row) and multiplied like a bf16 matrix of twice the columns.
+bool ax_gemv_umma_int4_supported(const AxWeight& w, int n, const float* x, const float* y) {
+    if (w.dtype != ATLASX_INT4 || n < 2 || n > kMaxTokens || !x || !y || !w.scales) return false;
+    if ((((uintptr_t)w.data | (uintptr_t)x) & 15) != 0) return false;
+    return w.block >= 8 && w.block % 8 == 0 && w.cols % w.block == 0 && w.cols % 64 == 0;     // whole K blocks: the token tile index wraps at K
+}
+
+int ax_gemv_umma_int4_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
+    AX_ARG(ax_gemv_umma_int4_supported(w, n, x, y), "shape or format not covered by the expanded int4 product");
+    const size_t need = (size_t)w.rows * 2 * (size_t)w.cols * sizeof(uint16_t);
+    if (need > ctx->w_planes_cap) {
+        cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;
+        cudaStreamIsCapturing(ctx->stream, &st);
+        if (st != cudaStreamCaptureStatusNone) return atlasx_fail(ATLASX_ERR_STATE, "the int4 plane scratch must be sized before stream capture");
+        AX_CUDA(cudaStreamSynchronize(ctx->stream));
+        cudaFree(ctx->w_planes); ctx->w_planes = nullptr; ctx->w_planes_cap = 0;
+        AX_CUDA(cudaMalloc(&ctx->w_planes, need));
+        ctx->w_planes_cap = need;
+    }
+    const size_t words = (size_t)w.rows * (w.cols / 8);
+    ax_int4_planes_kernel<<<(unsigned)((words + 255) / 256), 256, 0, ctx->stream>>>(
+        reinterpret_cast<const uint32_t*>(w.data), w.scales, w.scales_f16, w.block, w.rows, w.cols, reinterpret_cast<uint16_t*>(ctx->w_planes));
+    AX_CHECK_LAUNCH("ax_int4_planes_kernel");
+    AxWeight wp;
+    wp.data = ctx->w_planes; wp.rows = w.rows; wp.cols = 2 * w.cols; wp.dtype = ATLASX_BF16;
+    (void)pdl;                                                // the expansion kernel in front is an ordinary launch
+    return umma_launch(ctx, wp, x, n, y, token_major, false, nullptr, nullptr, w.cols);
 }

@@ -612,6 +612,7 @@ int prefill_limit(const atlasx_model* m) {
                 continue;
             }
             if (!ax_gemv_mma_supported(*w, 2, dummy, dummy)) return 1;
+            if (m->ctx->tune.umma && ax_gemv_umma_int4_supported(*w, limit, dummy, dummy)) continue;      // int4: expanded, then the bf16 product
             if (limit > kPrefillMaxMma) limit = kPrefillMaxMma;
         }
     }
@@ -625,7 +626,8 @@ int pf_product(atlasx_ctx* c, const AxWeight& w, const float* x, int n, float* y
     if (!ext_parts) pend = nullptr;
     if (!x) return ax_gemv_umma_launch(c, w, nullptr, n, y, true, pdl, ext_parts, pend);
     if (c->tune.umma && ax_gemv_umma_supported(w, n, x, y)) return ax_gemv_umma_launch(c, w, x, n, y, true, pdl, ext_parts, pend);
-    return ax_gemv_mma_launch(c, w, x, n, y, true);
+    if (ax_gemv_mma_supported(w, n, x, y)) return ax_gemv_mma_launch(c, w, x, n, y, true);
+    return ax_gemv_umma_int4_launch(c, w, x, n, y, true, pdl);
 }
 
 // Launch with programmatic stream serialization (the kernel waits for its predecessor itself).

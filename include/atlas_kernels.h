@@ -142,8 +142,9 @@ int atlasx_matrix_free(atlasx_matrix* m);
 int atlasx_matrix_info(const atlasx_matrix* m, int* rows, int* cols, int* dtype);   /* is_on_gpu / is_bf16 :349-362 */
 size_t atlasx_matrix_bytes(const atlasx_matrix* m);     /* weight bytes one product streams from HBM */
 /* GpuMatrix::sgemm_vec (:409-435): y[rows×n] = W·x[cols×n], x and y row-major in HBM, f32.
- * n == 1 is the decode GEMV; 2..16 (2..128 for bf16 weights with at least 64 columns, a multiple of 8; 2..64 for int8
- * weights with at least 128 columns, a multiple of 16) is the skinny batched/verify case. */
+ * n == 1 is the decode GEMV; 2..16 (2..128 for bf16 weights with at least 64 columns, a multiple of 8, and for int4
+ * weights whose column count is a multiple of 64 and of the block; 2..64 for int8 weights with at least 128 columns, a
+ * multiple of 16) is the skinny batched/verify case. */
 int atlasx_gemv(atlasx_ctx* ctx, const atlasx_matrix* m, const float* x_dev, int n, float* y_dev);
 /* GpuMatrix::sgemm (:371-400): same with host rhs/out (uploads x, downloads y) */
 int atlasx_matrix_sgemm(atlasx_ctx* ctx, const atlasx_matrix* m, const float* rhs_host, int k, int n, float* out_host);
@@ -299,7 +300,7 @@ double atlasx_model_step_bytes(const atlasx_model* m, int pos);
 int atlasx_model_kernel_launches_per_step(const atlasx_model* m);
 int atlasx_model_set_options(atlasx_model* m, int use_graph, int use_pdl);
 /* Prompt ingestion in chunks: atlasx_model_generate_greedy feeds the prompt `chunk` tokens at a
- * time (2..128 with bf16 weights, at most 64 with int8 and 16 with int4 weights) through the multi-column kernels, so the weights stream once per chunk instead of
+ * time (2..128 with bf16 and int4 weights, at most 64 with int8 weights) through the multi-column kernels, so the weights stream once per chunk instead of
  * once per token (the reference feeds one token per forward, crates/atlas-model/src/lib.rs:1611-1618).
  * 0 or 1 restores token-by-token ingestion (the default).  *effective receives the chunk in use:
  * 1 when a weight format or shape is outside what the multi-column kernel covers (f32 weights,

@@ -199,6 +199,21 @@ def test_gemv_up_to_128_columns_bf16(ab, n, shape):
     assert ab.Context.default().poll_device_error() == 0
 
 
+@pytest.mark.parametrize("n", [17, 40, 64, 128])
+@pytest.mark.parametrize("shape", [(256, 512), (4096, 4096), (1000, 4096), (200, 11008)], ids=lambda s: "%dx%d" % s)
+def test_gemv_many_columns_int4_expanded(ab, n, shape):
+    """More than 16 columns with int4 weights: the matrix is expanded on the device into bf16 hi | lo planes of
+    q · scale (w = hi + lo to 2⁻¹⁷) and multiplied by the tcgen05 kernel; against the oracle's dequantise-then-dot."""
+    M, K = shape
+    w = orc.normal_f32(M * K, 54, M + K, 0.02).reshape(M, K)
+    X = orc.normal_f32(K * n, 54, n, 1.0).reshape(K, n)
+    for fmt in ("int4", "int4_f16"):
+        gm, wo = make(ab, fmt, w)
+        Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
+        assert rel_err(Y, orc.gemm(wo, X)) <= 1e-4
+    assert ab.Context.default().poll_device_error() == 0
+
+
 def test_gemv_many_columns_propagates_nan_per_token(ab):
     """A NaN or inf in one token reaches every output of that token, and of that token only, on both
     tcgen05 paths."""

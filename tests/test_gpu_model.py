@@ -258,7 +258,7 @@ def test_head_dim_128_one_launch_attention_against_oracle(ab, kv, fmt):
 @pytest.mark.parametrize("kv", ["f32", "bf16"])
 @pytest.mark.parametrize("fmt", ["bf16", "int8", "int4"])
 def test_chunked_prompt_ingestion_matches_token_by_token(ab, kv, fmt):
-    """The prompt fed 16 (and 5; with bf16 and int8 weights also 32 and 64) tokens at a time through the multi-column
+    """The prompt fed 16 (and 5, 32, 64) tokens at a time through the multi-column
     kernels leaves the same caches and logits as the token-by-token path: same greedy continuation, same logits when the
     generation is continued by hand, for a prompt length that is no multiple of the chunk."""
     cfg = dict(helpers.HD128)
@@ -270,8 +270,8 @@ def test_chunked_prompt_ingestion_matches_token_by_token(ab, kv, fmt):
     want = plain.generate(prompt, 10, 0.0)
     want_next = plain.forward_one_gpu(int(want[-1]))
     tol = 2e-4 if kv == "f32" else 5e-3
-    big = 16 if fmt == "int4" else 64        # int4 matrices take the warp-level kernel: 16 tokens at most
-    for chunk in (16, 5) + ((32, 64) if fmt != "int4" else ()):
+    big = 64
+    for chunk in (16, 5, 32, 64):            # int4: the warp-level kernel up to 16 tokens, expanded to bf16 planes beyond
         m = helpers.cuda_model(cfg, w, helpers.HD128_LAYERS, kv_dtype=kvd, weight_format=code)
         assert m.set_prefill(chunk) == chunk
         got = m.generate(prompt, 10, 0.0)
