@@ -30,6 +30,8 @@
 //     weight bytes as A (128 int8 per K block) and the tokens as three int8 digit planes in base 254 with one
 //     scale per token (x ≈ s·(q1 + q2/254 + q3/254²), |error| ≤ 6e-8·max|x| of the token): the s32 sums in
 //     tensor memory are exact, the epilogue combines the planes and applies token and row scale.
+//   * int4 weights (more than 16 tokens) are first expanded into two bf16 planes side by side, [M][hi | lo] of q · scale,
+//     and multiplied as a bf16 matrix of 2K columns whose K block kb meets block kb mod (K / 64) of the token plane.
 //   * The tensor maps cover this GPU's own memory only and no copy is multicast.
 #include <cuda.h>
 
@@ -554,12 +556,12 @@ UmmaPlan make_plan(const atlasx_ctx* ctx, int rows, int cols, int n, bool i8, in
     if (st < 2) st = 2;
     p.stages = st;
     p.acc_cols = c;
-    // Persistent form: CTAs stay resident and take items from a counter, with two accumulators so that the epilogue of
-    // an item runs under the MMAs of the next.  Used when there are more items than CTA slots and either the items are
-    // long (at least 16 K blocks) or there are many per CTA (at least four): the lm_head-like matrices, where it
-    // measured 10–25 % faster; with a few short items per CTA the handshakes per item cost more than a fresh CTA
-    // (22016 × 4096 at 64 tokens, three items of 13 blocks per CTA: 83 → 96 µs).  Two CTAs per SM need their two
-    // allocations inside the 512 columns of tensor memory; the item ring needs items of at least four blocks.
+    // Persistent form (the rule is `resident` above): CTAs stay and take items from a counter, with two accumulators so
+    // that the epilogue of an item runs under the MMAs of the next.  Used when there are more items than CTA slots and
+    // either the items are long (at least 16 K blocks) or there are many per CTA (at least four): lm_head-like matrices
+    // and the wide layer matrices, where it measured 10–25 % faster; a few SHORT items per CTA cost more in handshakes
+    // than fresh CTAs do.  Two CTAs per SM need their two allocations inside the 512 columns of tensor memory (with
+    // 256-column accumulators one CTA per SM stays, with twice the stages); the item ring needs items of at least four blocks.
     p.persist = resident(p.KS) ? 1 : 0;
     p.tmem_cols = p.persist ? 2 * c : c;
     p.grid = p.persist ? per_sm * ctx->sm_count : p.T * p.KS;
