@@ -65,6 +65,7 @@ struct atlasx_ctx {
         int attn_mma = 1;              // ATLASX_ATTN_MMA=0: operator-form GQA attention on the scalar kernels instead of the tensor cores
         int umma = 1;                  // ATLASX_UMMA=0: token batches on the warp-level MMA kernel instead of tcgen05
         int umma_fused = 1;            // ATLASX_UMMA_FUSED=0: prompt chunks always split their tokens in a kernel of its own
+        int int4_fused = 1;            // ATLASX_INT4_FUSED=0: int4 token batches through bf16 planes in scratch instead of dequantising inside the product
         int umma_ks = 0;               // ATLASX_UMMA_KS=k: K splits of the tcgen05 product fixed instead of chosen by its cost model
         int umma_persist = 1;          // ATLASX_UMMA_PERSIST=0: one item per CTA instead of resident CTAs fed by a counter
         int attn_pack = 1;             // ATLASX_ATTN_PACK=0: ≤ 4 heads per KV head as columns with separate hi / lo MMAs

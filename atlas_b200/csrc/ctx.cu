@@ -64,6 +64,7 @@ extern "C" int atlasx_ctx_create(int device, atlasx_ctx** out) {
         env_int("ATLASX_UMMA", &c->tune.umma);
         env_int("ATLASX_UMMA_PERSIST", &c->tune.umma_persist);
         env_int("ATLASX_UMMA_KS", &c->tune.umma_ks);
+        env_int("ATLASX_INT4_FUSED", &c->tune.int4_fused);
         env_int("ATLASX_UMMA_FUSED", &c->tune.umma_fused);
         env_int("ATLASX_ATTN_PACK", &c->tune.attn_pack);
         env_int("ATLASX_ATTN_CFG", &c->tune.attn_cfg);

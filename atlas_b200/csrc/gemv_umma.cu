@@ -450,6 +450,200 @@ __global__ void __launch_bounds__(256) ax_int4_planes_kernel(const uint32_t* __r
     *reinterpret_cast<uint4*>(o + K) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
 }
 
+// ── int4 weights dequantised inside the product ─────────────────────────────────────────────────────────────────────
+// Same product for int4 weights (crates/atlas-quant/src/lib.rs:111-168) without a detour through HBM: the four warps that
+// read the accumulator at the end of an item spend its main loop as PRODUCERS of the A operand.  Thread r of them owns
+// row r of the 128-row tile: per K block it loads the 32 bytes of its row (64 weights) and the two block scales,
+// forms w = q · scale as dequant_nibble does (:150-157), splits w into bf16 hi + lo (w = hi + lo to 2⁻¹⁷ relative) and
+// stores the two 128-byte rows into the stage's hi and lo tiles in the 128-byte swizzle the MMA descriptors expect
+// (16-byte chunk c of row r at r·128 + ((c xor (r mod 8))·16)), then makes the stores visible to the tensor core
+// (fence.proxy.async) and arrives on the stage's barrier beside the token tile's bulk copy.  The MMA warp issues the
+// four K steps against the hi tile and the four against the lo tile into the same accumulator.  One CTA per SM, one item
+// per CTA; HBM sees half a byte per weight.
+struct Umma4Args {
+    float* Y;
+    int M, n, nc;
+    const uint8_t* Wq; int row_bytes;       // int4 bytes, K / 2 per row
+    const void* scales; int scales_f16, spr, block;   // scales per row = K / block, block a multiple of 32
+    int KB, KS, T, stages, b_bytes, acc_cols, token_major;
+    float* parts;
+    int* err;
+};
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo_elem, float hi_elem) {       // element with the lower index in the low half
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi_elem), "f"(lo_elem));      // round to nearest even, like ax_f32_to_bf16_rne
+    return r;
+}
+
+__global__ void __launch_bounds__(kThreads) ax_gemv_umma_int4_kernel(const __grid_constant__ CUtensorMap map_x, const Umma4Args a) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kMaxStages], empty_bar[kMaxStages], acc_full;
+    __shared__ uint32_t s_tmem;
+    __shared__ int s_abort, s_issued, s_go;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int ST = a.stages;
+    const int NP = 2 * a.nc;
+    const uint32_t stage_bytes = 2u * (uint32_t)kABytes + (uint32_t)a.b_bytes;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* const smem_gen = smem_raw + (smem0 - smem_u32(smem_raw));          // the same place as a generic pointer
+    volatile int* abort_flag = &s_abort;
+    const int item = (int)blockIdx.x;
+    const int tile = item / a.KS, ks = item - tile * a.KS;
+    const int kb0 = (int)((long long)a.KB * ks / a.KS);
+    const int nkb = (int)((long long)a.KB * (ks + 1) / a.KS) - kb0;
+
+    if (tid == 0) {
+        for (int s = 0; s < ST; s++) { mbar_init(smem_u32(&full_bar[s]), 1 + 128); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        mbar_init(smem_u32(&acc_full), 1);
+        s_abort = 0; s_issued = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" :: "r"(smem_u32(&s_tmem)), "r"((uint32_t)a.acc_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        if (lane == 0) {                                                     // token tiles
+            asm volatile("griddepcontrol.wait;" ::: "memory");
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % ST;
+                if (i >= ST && !mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((i / ST) - 1) & 1u, abort_flag, a.err, 711)) break;
+                const uint32_t bar = smem_u32(&full_bar[s]);
+                mbar_expect_tx(bar, (uint32_t)a.b_bytes);
+                tma_load_2d(smem0 + (uint32_t)s * stage_bytes + 2u * kABytes, &map_x, (kb0 + i) * 64, 0, bar);
+                s_issued = i + 1;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(kTileM >> 4) << 24);
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % ST;
+                if (!mbar_wait(smem_u32(&full_bar[s]), (uint32_t)(i / ST) & 1u, abort_flag, a.err, 712)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t sh = smem0 + (uint32_t)s * stage_bytes, sl = sh + kABytes, sb = sl + kABytes;
+#pragma unroll
+                for (int k = 0; k < kBlockBytes / 32; k++)
+                    umma_bf16(tmem, smem_desc_sw128(sh + k * 32), smem_desc_sw128(sb + k * 32), idesc, (uint32_t)((i | k) != 0));
+#pragma unroll
+                for (int k = 0; k < kBlockBytes / 32; k++)
+                    umma_bf16(tmem, smem_desc_sw128(sl + k * 32), smem_desc_sw128(sb + k * 32), idesc, 1u);
+                umma_commit(smem_u32(&empty_bar[s]));
+            }
+            umma_commit(smem_u32(&acc_full));                                // also on the way out of a failed wait
+        }
+    } else {
+        const int q = warp & 3;
+        const int r_in = q * 32 + lane;
+        const int row = tile * kTileM + r_in;
+        const bool live = row < a.M;
+        // ── producer of the A operand ──
+        const uint8_t* wrow = a.Wq + (size_t)(live ? row : 0) * a.row_bytes;
+        const size_t srow = (size_t)(live ? row : 0) * a.spr;
+        // the weights of three K blocks are on their way while one is dequantised
+        uint4 w0 = make_uint4(0u, 0u, 0u, 0u), w1 = w0, x0 = w0, x1 = w0, y0 = w0, y1 = w0;
+        if (live) {
+            w0 = ax_ldg_stream(wrow + (size_t)kb0 * 32); w1 = ax_ldg_stream(wrow + (size_t)kb0 * 32 + 16);
+            if (nkb > 1) { x0 = ax_ldg_stream(wrow + (size_t)(kb0 + 1) * 32); x1 = ax_ldg_stream(wrow + (size_t)(kb0 + 1) * 32 + 16); }
+            if (nkb > 2) { y0 = ax_ldg_stream(wrow + (size_t)(kb0 + 2) * 32); y1 = ax_ldg_stream(wrow + (size_t)(kb0 + 2) * 32 + 16); }
+        }
+        // the two block scales of a K block (its 64 weights lie in one or two blocks), fetched as far ahead as the weights
+        auto scales_of = [&](int kb) {
+            float2 r;
+            const size_t b0 = srow + (size_t)((kb * 64) / a.block), b1 = srow + (size_t)((kb * 64 + 32) / a.block);
+            if (a.scales_f16) { r.x = __half2float(reinterpret_cast<const __half*>(a.scales)[b0]); r.y = __half2float(reinterpret_cast<const __half*>(a.scales)[b1]); }
+            else { r.x = reinterpret_cast<const float*>(a.scales)[b0]; r.y = reinterpret_cast<const float*>(a.scales)[b1]; }
+            return r;
+        };
+        float2 sw = make_float2(0.f, 0.f), sx = sw, sy = sw;
+        if (live) { sw = scales_of(kb0); if (nkb > 1) sx = scales_of(kb0 + 1); if (nkb > 2) sy = scales_of(kb0 + 2); }
+        bool ok = true;
+        for (int i = 0; i < nkb; i++) {
+            const int s = i % ST, kb = kb0 + i;
+            uint4 n0 = make_uint4(0u, 0u, 0u, 0u), n1 = n0;
+            if (live && i + 3 < nkb) { n0 = ax_ldg_stream(wrow + (size_t)(kb + 3) * 32); n1 = ax_ldg_stream(wrow + (size_t)(kb + 3) * 32 + 16); }
+            const float sc[2] = { sw.x, sw.y };
+            float2 sn = make_float2(0.f, 0.f);
+            if (live && i + 3 < nkb) sn = scales_of(kb + 3);
+            if (i >= ST) {                                                   // one thread waits for the stage and tells the others
+                if (tid == 64) s_go = mbar_wait(smem_u32(&empty_bar[s]), (uint32_t)((i / ST) - 1) & 1u, abort_flag, a.err, 713) ? 1 : 0;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                const int go = s_go;
+                asm volatile("bar.sync 1, 128;" ::: "memory");
+                if (!go) { ok = false; break; }
+            }
+            uint8_t* hi_row = smem_gen + (size_t)s * stage_bytes + (size_t)r_in * 128;
+            uint8_t* lo_row = hi_row + kABytes;
+            const uint32_t words[8] = { w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w };
+#pragma unroll
+            for (int c = 0; c < 8; c++) {                                    // word c: elements 8c .. 8c+7, two per byte, even index in the high nibble
+                const float scale = sc[c >> 2];
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) {                                // signed bit-field extract: one instruction per nibble
+                    int nib;
+                    asm("bfe.s32 %0, %1, %2, 4;" : "=r"(nib) : "r"(words[c]), "r"(8 * (e >> 1) + ((e & 1) ? 0 : 4)));
+                    v[e] = (float)nib * scale;
+                }
+                uint32_t h[4], l[4];
+#pragma unroll
+                for (int p2 = 0; p2 < 4; p2++) {
+                    h[p2] = pack_bf16x2(v[2 * p2], v[2 * p2 + 1]);
+                    l[p2] = pack_bf16x2(v[2 * p2] - __uint_as_float(h[p2] << 16), v[2 * p2 + 1] - __uint_as_float(h[p2] & 0xFFFF0000u));
+                }
+                const int off = (c ^ (r_in & 7)) << 4;
+                *reinterpret_cast<uint4*>(hi_row + off) = make_uint4(h[0], h[1], h[2], h[3]);
+                *reinterpret_cast<uint4*>(lo_row + off) = make_uint4(l[0], l[1], l[2], l[3]);
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // generic-proxy stores → visible to the tensor core's reads
+            asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_u32(&full_bar[s])) : "memory");
+            w0 = x0; w1 = x1; x0 = y0; x1 = y1; y0 = n0; y1 = n1;
+            sw = sx; sx = sy; sy = sn;
+        }
+        // ── epilogue ──
+        if (tid == 64) s_go = (ok && mbar_wait(smem_u32(&acc_full), 0u, abort_flag, a.err, 714)) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_go) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t t_row = tmem + ((uint32_t)(q * 32) << 16);
+            float* part = a.parts + (size_t)item * a.n * kTileM;
+            for (int c = 0; c < a.nc && c < a.n; c += 8) {
+                float hi[8], lo[8];
+                tmem_ld8(t_row + (uint32_t)c, hi);
+                tmem_ld8(t_row + (uint32_t)(a.nc + c), lo);
+#pragma unroll
+                for (int e = 0; e < 8; e++) {
+                    const int j = c + e;
+                    if (j < a.n) {
+                        const float v = hi[e] + lo[e];
+                        if (a.KS > 1) part[(size_t)j * kTileM + r_in] = v;
+                        else if (live) a.Y[a.token_major ? (size_t)j * a.M + row : (size_t)row * a.n + j] = v;
+                    }
+                }
+            }
+        }
+    }
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (s_abort) {
+        if (tid == 32) { unsigned long long t0 = global_ns(); while (global_ns() - t0 < 2000000ull) { } }     // MMAs and copies issued before the failure: time to drain
+        __syncthreads();
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem), "r"((uint32_t)a.acc_cols) : "memory");
+    }
+}
+
 // Partial tiles of a K-split product → Y: thread = four rows of one token of one row tile, splits added in order (the
 // result does not depend on timing).  The whole GPU takes part: the sums are a few MB that lie in L2.
 __global__ void __launch_bounds__(256) ax_umma_merge_kernel(const float* __restrict__ parts, float* __restrict__ Y, int M, int n, int KS, int T,
@@ -698,8 +892,73 @@ bool ax_gemv_umma_int4_supported(const AxWeight& w, int n, const float* x, const
     return w.block >= 8 && w.block % 8 == 0 && w.cols % w.block == 0 && w.cols % 64 == 0;     // whole K blocks: the token tile index wraps at K
 }
 
+namespace {
+// int4 weights dequantised inside the product (ax_gemv_umma_int4_kernel): block scales over multiples of 32 elements
+int umma_int4_fused_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major) {
+    const int K = w.cols, nc = (n + 7) / 8 * 8, NP = 2 * nc;
+    const int b_bytes = NP * kBlockBytes;
+    const int stage = 2 * kABytes + b_bytes;
+    int st = (200 * 1024) / stage;
+    if (st > kMaxStages) st = kMaxStages;
+    if (st < 2) st = 2;
+    const int T = (w.rows + kTileM - 1) / kTileM, KB = K / 64;
+    // K splits as in make_plan, with one CTA per SM
+    int best = 1; double best_cost = 1e300;
+    for (int ks = 1; ks <= kMaxSplits && ks * 4 <= (KB > 4 ? KB : 4); ks++) {
+        const long long items = (long long)T * ks;
+        const long long waves = (items + ctx->sm_count - 1) / ctx->sm_count;
+        const double extra = ks > 1 ? 2.0 * n * kTileM * sizeof(float) * ks / ((double)KB * kABytes) : 0.0;
+        const double cost = (double)waves * ((double)KB / ks * (1.0 + extra) + 6.0);
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = ks; }
+    }
+    const int KS = best;
+    int c = 32; while (c < NP) c <<= 1;
+    const size_t plane_bytes = ((size_t)NP * K * 2 + 1023) / 1024 * 1024;
+    const size_t parts_bytes = KS > 1 ? (size_t)T * KS * n * kTileM * sizeof(float) : 0;
+    int rc = atlasx_ctx_ensure_split_scratch(ctx, kHeadBytes + plane_bytes + parts_bytes);
+    if (rc) return rc;
+    unsigned* counter = reinterpret_cast<unsigned*>(ctx->split_scratch);
+    uint8_t* base = reinterpret_cast<uint8_t*>(ctx->split_scratch) + kHeadBytes;
+    float* parts = reinterpret_cast<float*>(base + plane_bytes);
+    CUtensorMap map_x;
+    if ((rc = make_map(&map_x, base, (uint64_t)NP, (uint64_t)K, (uint32_t)NP, false))) return rc;
+    static bool attr_done[64] = {};
+    const int dev = ctx->device & 63;
+    if (!attr_done[dev]) {
+        AX_CUDA(cudaFuncSetAttribute(ax_gemv_umma_int4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024));
+        attr_done[dev] = true;
+    }
+    {
+        const size_t work = (size_t)2 * nc * (K / 8);
+        ax_umma_split_kernel<<<(unsigned)((work + 255) / 256), 256, 0, ctx->stream>>>(x, K, n, nc, token_major ? 1 : 0, reinterpret_cast<uint16_t*>(base), counter);
+        AX_CHECK_LAUNCH("ax_umma_split_kernel");
+    }
+    Umma4Args a;
+    a.Y = y; a.M = w.rows; a.n = n; a.nc = nc;
+    a.Wq = reinterpret_cast<const uint8_t*>(w.data); a.row_bytes = K / 2;
+    a.scales = w.scales; a.scales_f16 = w.scales_f16; a.spr = K / w.block; a.block = w.block;
+    a.KB = KB; a.KS = KS; a.T = T; a.stages = st; a.b_bytes = b_bytes; a.acc_cols = c; a.token_major = token_major ? 1 : 0;
+    a.parts = parts; a.err = ctx->dev_error;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(T * KS)); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = (size_t)st * stage + 1024; cfg.stream = ctx->stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;                                      // the weights are dequantised while the split kernel still runs
+    AX_CUDA(cudaLaunchKernelEx(&cfg, ax_gemv_umma_int4_kernel, map_x, a));
+    if (KS > 1) {
+        cudaLaunchConfig_t mc = {};
+        mc.gridDim = dim3((unsigned)(((size_t)T * n * (kTileM / 4) + 255) / 256)); mc.blockDim = dim3(256); mc.stream = ctx->stream;
+        mc.attrs = attr; mc.numAttrs = 1;
+        AX_CUDA(cudaLaunchKernelEx(&mc, ax_umma_merge_kernel, (const float*)parts, y, w.rows, n, KS, T, token_major ? 1 : 0));
+    }
+    return ATLASX_OK;
+}
+}  // namespace
+
 int ax_gemv_umma_int4_launch(atlasx_ctx* ctx, const AxWeight& w, const float* x, int n, float* y, bool token_major, bool pdl) {
     AX_ARG(ax_gemv_umma_int4_supported(w, n, x, y), "shape or format not covered by the expanded int4 product");
+    if (ctx->tune.int4_fused && w.block % 32 == 0) return umma_int4_fused_launch(ctx, w, x, n, y, token_major);
     const size_t need = (size_t)w.rows * 2 * (size_t)w.cols * sizeof(uint16_t);
     if (need > ctx->w_planes_cap) {
         cudaStreamCaptureStatus st = cudaStreamCaptureStatusNone;

@@ -44,8 +44,8 @@ def make(ab, fmt, w):
     if fmt == "int8":
         q, s = orc.int8_quantize(w)
         return ab.GpuMatrix.upload_int8(ab.Int8Tensor(q, s, M, K)), orc.int8_dequantize(q, s)
-    if fmt in ("int4", "int4_b64", "int4_f16"):
-        bs = 64 if fmt == "int4_b64" else 32
+    if fmt in ("int4", "int4_b64", "int4_f16", "int4_b16"):
+        bs = 64 if fmt == "int4_b64" else 16 if fmt == "int4_b16" else 32
         q, s = orc.int4_quantize(w, bs)
         f16 = fmt == "int4_f16"
         if f16:
@@ -202,12 +202,14 @@ def test_gemv_up_to_128_columns_bf16(ab, n, shape):
 @pytest.mark.parametrize("n", [17, 40, 64, 128])
 @pytest.mark.parametrize("shape", [(256, 512), (4096, 4096), (1000, 4096), (200, 11008)], ids=lambda s: "%dx%d" % s)
 def test_gemv_many_columns_int4_expanded(ab, n, shape):
-    """More than 16 columns with int4 weights: the matrix is expanded on the device into bf16 hi | lo planes of
-    q · scale (w = hi + lo to 2⁻¹⁷) and multiplied by the tcgen05 kernel; against the oracle's dequantise-then-dot."""
+    """More than 16 columns with int4 weights run on the tcgen05 kernel with w = q · scale as bf16 hi + lo parts
+    (w = hi + lo to 2⁻¹⁷): blocks of 32 and 64 (f32 and f16 scales) are dequantised inside the product kernel, by the
+    warps that read the accumulator afterwards; other block sizes (16 here) go through hi | lo planes expanded into
+    scratch.  Against the oracle's dequantise-then-dot."""
     M, K = shape
     w = orc.normal_f32(M * K, 54, M + K, 0.02).reshape(M, K)
     X = orc.normal_f32(K * n, 54, n, 1.0).reshape(K, n)
-    for fmt in ("int4", "int4_f16"):
+    for fmt in ("int4", "int4_f16", "int4_b64", "int4_b16"):
         gm, wo = make(ab, fmt, w)
         Y = gm.sgemm_vec(ab.GpuVec.from_slice(X), n).download().reshape(M, n)
         assert rel_err(Y, orc.gemm(wo, X)) <= 1e-4
