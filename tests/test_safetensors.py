@@ -96,6 +96,18 @@ def test_reader_rejects_damaged_files(tmp_path):
     _handwritten(p, {"w": {"dtype": "F32", "shape": [4], "data_offsets": [0, 64]}}, b"\0" * 16)
     with pytest.raises(ab.AtlasError, match="outside the file"):
         ab.SafetensorsFile.open(p)
+    _handwritten(p, {"w": {"dtype": "F32", "shape": [4], "data_offsets": [0.5, 16]}}, b"\0" * 16)
+    with pytest.raises(ab.AtlasError, match="not non-negative integers"):
+        ab.SafetensorsFile.open(p)
+    _handwritten(p, {"w": {"dtype": "F32", "shape": [4], "data_offsets": [-4, 16]}}, b"\0" * 16)
+    with pytest.raises(ab.AtlasError, match="not non-negative integers"):
+        ab.SafetensorsFile.open(p)
+    # a shape whose product wraps around 2^64 back to the element count must not pass for a match
+    # (3 · 0xAAAAAAAAAAAAAAAB ≡ 1 modulo 2^64, so the wrapped product of this shape equals the four stored elements)
+    _handwritten(p, {"w": {"dtype": "F32", "shape": [3, 0xAAAAAAAAAAAAAAAB, 4], "data_offsets": [0, 16]}}, b"\0" * 16)
+    f = ab.SafetensorsFile.open(p)
+    with pytest.raises(ab.AtlasError, match="shape and byte count disagree"):
+        f.get_f32("w")
     with pytest.raises(ab.AtlasError, match="cannot open"):
         ab.SafetensorsFile.open(str(tmp_path / "missing.safetensors"))
     open(p, "wb").write(struct.pack("<Q", 2) + b"{}")
