@@ -481,3 +481,15 @@ def test_greedy_branch_of_sample_token_equals_generate_greedy():
     b = m.generate_sampling([0, 1], 12, orc.sampling(1.0, top_k=20), seed=5)
     c = m.generate_sampling([0, 1], 12, orc.sampling(1.0, top_k=20), seed=6)
     assert np.array_equal(a, b) and not np.array_equal(a, c) and a.size == 12
+
+
+def test_bf16_hi_lo_split_keeps_17_bits():
+    """The tcgen05 products feed f32 values (tokens; dequantised int4 weights) to the tensor cores as two bf16 parts,
+    hi = rne(v) and lo = rne(v − hi).  The parts add up to v within 2⁻¹⁷ relative — the bound the kernels' comments and
+    the 2e-5 / 1e-4 tolerances of their GPU tests rest on."""
+    rng = np.random.default_rng(7)
+    v = (rng.standard_normal(400_000) * rng.choice([1e-3, 1.0, 37.5], 400_000)).astype(np.float32)
+    hi = orc.bf16_to_f32(orc.f32_to_bf16_rne(v)).astype(np.float32)
+    lo = orc.bf16_to_f32(orc.f32_to_bf16_rne((v - hi).astype(np.float32))).astype(np.float32)
+    err = np.abs(v.astype(np.float64) - (hi.astype(np.float64) + lo.astype(np.float64))) / np.abs(v)
+    assert err.max() <= 2.0 ** -16.9
