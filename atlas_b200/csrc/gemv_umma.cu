@@ -28,7 +28,7 @@
 //     and tensor memory is released before the CTA returns.
 //   * int8 weights (crates/atlas-quant/src/lib.rs:41-75: one f32 scale per row) run as kind::i8 with the raw
 //     weight bytes as A (128 int8 per K block) and the tokens as three int8 digit planes in base 254 with one
-//     scale per token (x ≈ s·(q1 + q2/254 + q3/254²), |error| ≤ 6e-8·max|x| of the token): the s32 sums in
+//     scale per token (x ≈ s·(q1 + q2/254 + q3/254²), |error| ≤ 1.2e-7·max|x| of the token): the s32 sums in
 //     tensor memory are exact, the epilogue combines the planes and applies token and row scale.
 //   * int4 weights (more than 16 tokens) are first expanded into two bf16 planes side by side, [M][hi | lo] of q · scale,
 //     and multiplied as a bf16 matrix of 2K columns whose K block kb meets block kb mod (K / 64) of the token plane.

@@ -493,3 +493,25 @@ def test_bf16_hi_lo_split_keeps_17_bits():
     lo = orc.bf16_to_f32(orc.f32_to_bf16_rne((v - hi).astype(np.float32))).astype(np.float32)
     err = np.abs(v.astype(np.float64) - (hi.astype(np.float64) + lo.astype(np.float64))) / np.abs(v)
     assert err.max() <= 2.0 ** -16.9
+
+
+def test_three_base_254_digits_keep_the_token_to_1e7_of_its_maximum():
+    """The int8 tcgen05 product sees a token as three int8 digit planes in base 254 with one scale per token:
+    x ≈ s · (q1 + q2/254 + q3/254²), s = max|x| / 127.  The same f32 arithmetic as the kernel, restated in numpy:
+    every digit fits an int8 and the reconstruction is within 1.2e-7 · max|x| of x (half a third digit, 6.1e-8 · max|x|,
+    plus the f32 rounding of x · 127 / max|x|, 6e-8 · |x|)."""
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal(11008).astype(np.float32)
+    x[3670] = np.float32(37.5)
+    mx = np.float32(np.max(np.abs(x)))
+    inv = np.float32(127.0) / mx
+    t = np.clip(x * inv, np.float32(-127.0), np.float32(127.0)).astype(np.float32)
+    q1 = np.rint(t).astype(np.float32)
+    rr = ((t - q1) * np.float32(254.0)).astype(np.float32)
+    q2 = np.rint(rr).astype(np.float32)
+    q3 = np.rint(((rr - q2) * np.float32(254.0)).astype(np.float32)).astype(np.float32)
+    for q in (q1, q2, q3):
+        assert np.all(np.abs(q) <= 127)
+    s = np.float64(mx) / 127.0
+    rec = s * (q1.astype(np.float64) + q2.astype(np.float64) / 254.0 + q3.astype(np.float64) / 254.0 ** 2)
+    assert np.max(np.abs(rec - x.astype(np.float64))) <= 1.2e-7 * float(mx)
