@@ -515,3 +515,19 @@ def test_three_base_254_digits_keep_the_token_to_1e7_of_its_maximum():
     s = np.float64(mx) / 127.0
     rec = s * (q1.astype(np.float64) + q2.astype(np.float64) / 254.0 + q3.astype(np.float64) / 254.0 ** 2)
     assert np.max(np.abs(rec - x.astype(np.float64))) <= 1.2e-7 * float(mx)
+
+
+def test_two_base_254_digits_per_group_of_32_keep_the_input_to_1_6e5_of_the_group_maximum():
+    """The single-column int8 / int4 GEMV sees its input through TWO int8 digits in base 254 with one scale per group
+    of 32 elements (x ≈ s · (q1 + q2/254), s = max|group| / 127): half a second digit is 1.55e-5 of the group's
+    maximum, which is what the 1e-4 linearity bound of the GPU tests allows for."""
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal(4096).astype(np.float32).reshape(-1, 32)
+    x[5, 7] = np.float32(37.5)
+    mx = np.max(np.abs(x), axis=1, keepdims=True).astype(np.float32)
+    t = np.clip(x * (np.float32(127.0) / mx), np.float32(-127.0), np.float32(127.0)).astype(np.float32)
+    q1 = np.rint(t).astype(np.float32)
+    q2 = np.rint(((t - q1) * np.float32(254.0)).astype(np.float32)).astype(np.float32)
+    assert np.all(np.abs(q1) <= 127) and np.all(np.abs(q2) <= 127)
+    rec = (mx.astype(np.float64) / 127.0) * (q1.astype(np.float64) + q2.astype(np.float64) / 254.0)
+    assert np.max(np.abs(rec - x.astype(np.float64)) / mx.astype(np.float64)) <= 1.6e-5
